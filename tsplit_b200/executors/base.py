@@ -1,0 +1,278 @@
+"""Baseline executors: ``Executor``, ``StreamExecutor``, ``MultiStreamExecutor``.
+
+Capability parity: ``gpu_ops/executor.py:21-158`` (allocate every node output
+once per feed shape and keep it), ``StreamExecutor.py:68-214`` (user-supplied
+stream) and ``MultiStreamExecutor.py:68-252`` (feeds copied on an H2D stream
+with one event per feed node).
+
+B200-first differences: feeds are staged through cached pinned buffers and one
+layout kernel instead of a fresh synchronous allocation+copy per run; the
+compute stream waits on events instead of the host; and the steady-state step
+can be captured once per feed shape into a CUDA graph and replayed
+(``use_graph=True``), which removes the per-node host work the reference pays on
+every iteration.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ndarray
+from ..graph import schedule_order
+from ..stream import create_stream_handle, Event
+from ..ops.misc import PlaceholderOp
+
+
+def _shape_of(v):
+    return tuple(v.shape)
+
+
+class FeedStager(object):
+    """Host -> device feed path: a pinned staging buffer and a device buffer per
+    fed node, reused across runs while the shape stays the same."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+        self.slots = {}
+
+    def put(self, node, value, stream):
+        if isinstance(value, ndarray.NDArray):
+            if value.ctx == self.ctx or value.ctx.device_type == self.ctx.device_type:
+                return value
+            value = value.asnumpy()
+        value = np.asarray(value)
+        if not ndarray.is_gpu_ctx(self.ctx) or self.ctx.device_type == 3:
+            return ndarray.array(value, self.ctx, use_pool=False)
+        shape = tuple(value.shape)
+        slot = self.slots.get(node)
+        if slot is None or slot[0] != shape:
+            n = int(np.prod(shape)) if shape else 1
+            pinned = torch.empty(max(n, 1), dtype=torch.float32, pin_memory=True)
+            dev = ndarray.empty(shape, self.ctx, use_pool=False)
+            raw = None
+            if len(shape) == 4:     # device array is channels-last: land row-major bytes first
+                raw = torch.empty(max(n, 1), dtype=torch.float32, device=self.ctx.torch_device)
+            slot = (shape, pinned, dev, raw)
+            self.slots[node] = slot
+        _, pinned, dev, raw = slot
+        n = int(np.prod(shape)) if shape else 1
+        pinned[:n].numpy()[...] = value.reshape(-1)
+        with torch.cuda.stream(stream.torch_stream):
+            if raw is None:
+                dev.t.view(-1)[:n].copy_(pinned[:n], non_blocking=True) if dev.t.is_contiguous() \
+                    else dev.t.copy_(pinned[:n].view(shape), non_blocking=True)
+            else:
+                raw[:n].copy_(pinned[:n], non_blocking=True)
+                from ..ops import _gpu as G
+                rm = []
+                acc = 1
+                for d in reversed(shape):
+                    rm.insert(0, acc)
+                    acc *= d
+                G.copy_raw(raw.data_ptr(), rm, dev.ptr, dev.strides, shape, stream)
+        return dev
+
+    def bytes_per_step(self, feed_dict):
+        return sum(int(np.prod(np.asarray(v).shape)) * 4 for v in feed_dict.values()
+                   if not isinstance(v, ndarray.NDArray))
+
+
+class Executor(object):
+    """Executor computes values for given set of nodes in a computation graph."""
+
+    def __init__(self, eval_node_list, ctx=None, stream=None, policy=None, use_graph=False):
+        self.eval_node_list = list(eval_node_list)
+        self.ctx = ctx
+        self.policy = policy
+        self.topo_order = schedule_order(self.eval_node_list)
+        self.use_numpy = ctx is None
+        self.on_device = ndarray.is_gpu_ctx(ctx) and ctx.device_type == 2
+        self.stream = stream
+        if self.stream is None and ctx is not None:
+            self.stream = create_stream_handle(ctx)
+        self.node_to_shape_map = None
+        self.node_to_arr_map = None
+        self.feed_shapes = None
+        self.stager = FeedStager(ctx) if ctx is not None else None
+        self.use_graph = bool(use_graph) and self.on_device
+        self._graph = None
+        self._graph_feed_arrs = None
+
+    # -- shapes ---------------------------------------------------------------
+    def infer_shape(self, feed_shapes):
+        self.node_to_shape_map = {}
+        for node in self.topo_order:
+            if node in feed_shapes:
+                shp = tuple(feed_shapes[node])
+            elif isinstance(node.op, PlaceholderOp):
+                shp = node.op.infer_shape(node, [])
+            else:
+                shp = node.op.infer_shape(node, [self.node_to_shape_map[i] for i in node.inputs])
+            if shp is not None:
+                shp = tuple(int(s) for s in shp)
+            self.node_to_shape_map[node] = shp
+            node.inferred_shape = shp
+
+    def memory_plan(self, feed_shapes):
+        """One array per computed node, kept until the feed shapes change."""
+        self.node_to_arr_map = {}
+        for node, shape in self.node_to_shape_map.items():
+            if node in feed_shapes or isinstance(node.op, PlaceholderOp) or shape is None:
+                continue
+            self.node_to_arr_map[node] = ndarray.empty(shape, ctx=self.ctx)
+
+    # -- feeds ---------------------------------------------------------------
+    def _ingest(self, feed_dict):
+        vals = {}
+        for node, value in feed_dict.items():
+            if self.use_numpy:
+                if isinstance(value, ndarray.NDArray):
+                    value = value.asnumpy()
+                assert isinstance(value, np.ndarray), "feed_dict value type not supported"
+                vals[node] = value
+            else:
+                assert isinstance(value, (np.ndarray, ndarray.NDArray)), "feed_dict value type not supported"
+                vals[node] = self.stager.put(node, value, self.stream)
+        return vals
+
+    def _placeholder_value(self, node):
+        v = node.tensor_value
+        assert v is not None, "placeholder %s values provided by feed_dict" % node.name
+        if self.use_numpy:
+            return v.asnumpy() if isinstance(v, ndarray.NDArray) else v
+        if isinstance(v, np.ndarray):
+            v = ndarray.array(v, self.ctx, use_pool=False)
+            node.tensor_value = v
+        return v
+
+    def _val(self, arr):
+        """What ops receive: NumPy views on host-backed contexts, NDArrays on CUDA."""
+        if self.use_numpy or self.on_device:
+            return arr
+        return arr.numpy_view() if isinstance(arr, ndarray.NDArray) else arr
+
+    # -- run ---------------------------------------------------------------------
+    def run(self, feed_dict, convert_to_numpy_ret_vals=False):
+        node_to_val = self._ingest(feed_dict)
+        feed_shapes = {n: _shape_of(v) for n, v in node_to_val.items()}
+        if feed_shapes != self.feed_shapes:
+            self.infer_shape(feed_shapes)
+            self.feed_shapes = feed_shapes
+            if not self.use_numpy:
+                self.memory_plan(feed_shapes)
+            self._graph = None
+
+        if self.use_graph:
+            self._run_graph(node_to_val)
+        else:
+            self._run_eager(node_to_val)
+
+        if self.stream is not None:
+            self.stream.sync()
+        outs = [node_to_val.get(n) for n in self.eval_node_list]
+        if convert_to_numpy_ret_vals and not self.use_numpy:
+            return [o.asnumpy() if isinstance(o, ndarray.NDArray) else o for o in outs]
+        return outs
+
+    def _run_eager(self, node_to_val):
+        host_like = not self.on_device
+        for node in self.topo_order:
+            if node in node_to_val:
+                continue
+            if isinstance(node.op, PlaceholderOp):
+                node_to_val[node] = self._placeholder_value(node)
+                continue
+            ins = [node_to_val[i] for i in node.inputs]
+            if self.use_numpy:
+                out = np.empty(self.node_to_shape_map[node], dtype=np.float32) \
+                    if self.node_to_shape_map[node] is not None else None
+                node.op.compute(node, ins, out, True, None)
+            elif host_like:
+                out = self.node_to_arr_map.get(node)
+                node.op.compute(node, [self._val(i) for i in ins],
+                                out.numpy_view() if out is not None else None, True, self.stream)
+            else:
+                out = self.node_to_arr_map.get(node)
+                node.op.compute(node, ins, out, False, self.stream)
+            node_to_val[node] = out
+        self._last_vals = node_to_val
+
+    # -- CUDA-graph replay ---------------------------------------------------------
+    def _run_graph(self, node_to_val):
+        """Capture the whole step once per feed shape; later runs only refresh the
+        feed buffers (their device addresses are stable) and replay."""
+        from ..runtime import cudagraph
+        if self._graph is None:
+            # one eager run first: lazily created side buffers and tensor maps
+            self._run_eager(dict(node_to_val))
+            self.stream.sync()
+            self._graph = cudagraph.capture(self.stream, lambda: self._run_eager(dict(node_to_val)))
+            self._graph_vals = self._last_vals
+        self._graph.launch(self.stream)
+        self._last_vals = self._graph_vals
+        node_to_val.update(self._graph_vals)
+
+
+class StreamExecutor(Executor):
+    """Same as :class:`Executor` with a caller-owned stream (``streams=`` may be a
+    single stream or a one-element list)."""
+
+    def __init__(self, eval_node_list, ctx=None, stream=None, streams=None, policy=None, use_graph=False):
+        if stream is None and streams is not None:
+            stream = streams[0] if isinstance(streams, (list, tuple)) else streams
+        Executor.__init__(self, eval_node_list, ctx=ctx, stream=stream, policy=policy, use_graph=use_graph)
+
+
+class MultiStreamExecutor(Executor):
+    """Three streams — H2D, compute, D2H.  Each feed is copied on the H2D stream
+    and followed by an event; the compute stream waits for a feed's event right
+    before the first node that consumes it, so later feeds overlap with earlier
+    compute."""
+
+    def __init__(self, eval_node_list, ctx=None, streams=None, policy=None):
+        Executor.__init__(self, eval_node_list, ctx=ctx, policy=policy)
+        if streams is None and ctx is not None:
+            streams = [create_stream_handle(ctx) for _ in range(3)]
+        self.streams = streams
+        if streams is not None:
+            self.h2d_stream, self.stream, self.d2h_stream = streams[0], streams[1], streams[2]
+        self.feed_events = {}
+
+    def _ingest(self, feed_dict):
+        if self.use_numpy:
+            return Executor._ingest(self, feed_dict)
+        vals = {}
+        for node, value in feed_dict.items():
+            vals[node] = self.stager.put(node, value, self.h2d_stream)
+            ev = self.feed_events.get(node)
+            if ev is None:
+                ev = self.feed_events[node] = Event(self.ctx)
+            ev.record(self.h2d_stream)
+        return vals
+
+    def _run_eager(self, node_to_val):
+        waited = set()
+        fed = set(self.feed_events) & set(node_to_val)
+        host_like = not self.on_device
+        for node in self.topo_order:
+            if node in node_to_val:
+                continue
+            if isinstance(node.op, PlaceholderOp):
+                node_to_val[node] = self._placeholder_value(node)
+                continue
+            for i in node.inputs:
+                if i in fed and i not in waited:
+                    self.stream.wait_event(self.feed_events[i])
+                    waited.add(i)
+            ins = [node_to_val[i] for i in node.inputs]
+            out = self.node_to_arr_map.get(node) if not self.use_numpy else \
+                np.empty(self.node_to_shape_map[node], dtype=np.float32)
+            if self.use_numpy:
+                node.op.compute(node, ins, out, True, None)
+            elif host_like:
+                node.op.compute(node, [self._val(i) for i in ins],
+                                out.numpy_view() if out is not None else None, True, self.stream)
+            else:
+                node.op.compute(node, ins, out, False, self.stream)
+            node_to_val[node] = out
+        self._last_vals = node_to_val

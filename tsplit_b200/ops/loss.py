@@ -1,0 +1,116 @@
+"""Softmax and softmax cross-entropy.
+
+Capability parity: ``gpu_ops/Softmax.py:6-60`` and
+``gpu_ops/SoftmaxCrossEntropy.py:39-118``.  The reference kernels run
+``<<<1,1024>>>`` with one thread per row and a serial mean
+(``src/ops/Softmax.cu:3-22``, ``SoftmaxCrossEntropy.cu:5-104``); here each row is
+reduced by one warp (or one CTA for wide rows) across all SMs and the mean is a
+deterministic two-stage reduction.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from ..graph import Op
+from . import _gpu as G
+
+
+def softmax_func(y):
+    b = y - np.max(y, axis=-1, keepdims=True)
+    e = np.exp(b)
+    return e / np.sum(e, axis=-1, keepdims=True)
+
+
+class SoftmaxOp(Op):
+    name = "Softmax"
+
+    def __call__(self, x):
+        return Op.__call__(self, x)
+
+    def np_compute(self, node, iv):
+        return softmax_func(iv[0]).astype(np.float32)
+
+    def gpu_compute(self, node, iv, out, stream):
+        G.softmax(iv[0], out, stream)
+
+    def gradient(self, node, g):
+        # dx = y * (g - sum(g * y, axis=-1, keepdims))  (the reference leaves this undefined)
+        from .elementwise import mul_op, add_op, opposite_op
+        from .shape import reduce_sum_op, broadcasttoTF_op
+        gy = mul_op(g, node)
+        s = reduce_sum_op(gy, [-1], keepdims=True)
+        return [mul_op(node, add_op(g, opposite_op(broadcasttoTF_op(s, g))))]
+
+    def infer_shape(self, node, s):
+        return tuple(s[0])
+
+    def flops(self, node, s, out):
+        return 5.0 * np.prod(out)
+
+
+class SoftmaxCrossEntropyOp(Op):
+    """``mean_rows(-sum(labels * log softmax(logits)))`` -> shape (1,)."""
+    name = "SoftmaxCrossEntropy"
+
+    def __call__(self, logits, labels):
+        return Op.__call__(self, logits, labels)
+
+    def np_compute(self, node, iv):
+        y, y_ = iv
+        b = y - np.max(y, axis=1, keepdims=True)
+        logsm = b - np.log(np.sum(np.exp(b), axis=1, keepdims=True))
+        return np.mean(-np.sum(y_ * logsm, axis=1), keepdims=True).astype(np.float32)
+
+    def gpu_compute(self, node, iv, out, stream):
+        G.softmax_ce(iv[0], iv[1], out, stream)
+
+    def gradient(self, node, g):
+        from .misc import zeroslike_op
+        return [softmaxcrossentropy_gradient_op(node.inputs[0], node.inputs[1], g),
+                zeroslike_op(node.inputs[1])]
+
+    def infer_shape(self, node, s):
+        assert tuple(s[0]) == tuple(s[1]), "logits %s and labels %s differ" % (s[0], s[1])
+        return (1,)
+
+    def flops(self, node, s, out):
+        return 6.0 * np.prod(s[0])
+
+
+class SoftmaxCrossEntropyGradientOp(Op):
+    """``(softmax(logits) - labels) * g / rows``."""
+    name = "SoftmaxCrossEntropyGradient"
+
+    def __call__(self, logits, labels, g):
+        return Op.__call__(self, logits, labels, g)
+
+    def np_compute(self, node, iv):
+        y, y_, g = iv
+        return ((softmax_func(y) - y_) * g.reshape(-1)[0] / y.shape[0]).astype(np.float32)
+
+    def gpu_compute(self, node, iv, out, stream):
+        G.softmax_ce_grad(iv[0], iv[1], iv[2], out, stream)
+
+    def gradient(self, node, g):
+        raise NotImplementedError
+
+    def infer_shape(self, node, s):
+        return tuple(s[0])
+
+    def flops(self, node, s, out):
+        return 6.0 * np.prod(out)
+
+
+_sm, _ce, _ceg = SoftmaxOp(), SoftmaxCrossEntropyOp(), SoftmaxCrossEntropyGradientOp()
+
+
+def softmax_op(node):
+    return _sm(node)
+
+
+def softmaxcrossentropy_op(node_A, node_B):
+    return _ce(node_A, node_B)
+
+
+def softmaxcrossentropy_gradient_op(node_A, node_B, node_C):
+    return _ceg(node_A, node_B, node_C)
