@@ -1,0 +1,409 @@
+// Element-wise, strided-copy and strided-reduce kernels (fp32).
+//
+// Flat variants move 16 bytes per thread per step with a grid sized to the SM
+// count (HBM-bound: one read + one write per element).  Strided variants take
+// the shape / stride tables as kernel parameters, so transpose, slice, concat,
+// pad, the broadcast family and layout changes (NCHW <-> channels-last) are all
+// one launch with no host-side table copies.
+//
+// Roles in the reference: src/ops/{Relu,AddConst,AddElewise,MultiplyConst,
+// MultiplyElewise,DivideConst,DivideElewise,Opposite,Sqrt,Tanh,Sigmoid,ArraySet,
+// Where,Transpose,Slice,Concat,Pad,Broadcast,BroadcastShape,ReduceSum,
+// ReduceSumAxisZero,Conv2dBroadcast,Conv2dReduceSum}.cu
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TSB_OK 0
+#define TSB_ERR_ARG 1
+#define TSB_ERR_LAUNCH 3
+
+namespace {
+
+enum { UN_COPY, UN_RELU, UN_SIGMOID, UN_TANH, UN_SQRT, UN_RSQRT, UN_NEG, UN_ADDC, UN_MULC, UN_CDIV, UN_FILL };
+enum { BIN_ADD, BIN_MUL, BIN_DIV, BIN_RELU_GRAD, BIN_SUB };
+
+constexpr int MAXD = 8;
+struct Dims {
+  long long shape[MAXD];
+  long long s0[MAXD];
+  long long s1[MAXD];
+  long long s2[MAXD];
+  int nd;
+};
+
+template <int OP>
+__device__ __forceinline__ float un(float x, float a) {
+  switch (OP) {
+    case UN_COPY: return x;
+    case UN_RELU: return fmaxf(x, 0.f);
+    case UN_SIGMOID: return 1.f / (1.f + __expf(-x));
+    case UN_TANH: return tanhf(x);
+    case UN_SQRT: return sqrtf(x);
+    case UN_RSQRT: return rsqrtf(x);
+    case UN_NEG: return -x;
+    case UN_ADDC: return x + a;
+    case UN_MULC: return x * a;
+    case UN_CDIV: return a / x;
+    default: return a;   // UN_FILL
+  }
+}
+template <int OP>
+__device__ __forceinline__ float bin(float a, float b) {
+  switch (OP) {
+    case BIN_ADD: return a + b;
+    case BIN_MUL: return a * b;
+    case BIN_DIV: return a / b;
+    case BIN_RELU_GRAD: return a > 0.f ? b : (a == 0.f ? 0.5f * b : 0.f);
+    default: return a - b;
+  }
+}
+
+template <int OP>
+__global__ void unary_flat(const float* __restrict__ x, float* __restrict__ y, long long n, float a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (vec) {
+    const long long n4 = n >> 2;
+    for (long long j = i; j < n4; j += stride) {
+      float4 v = OP == UN_FILL ? make_float4(0, 0, 0, 0) : reinterpret_cast<const float4*>(x)[j];
+      v.x = un<OP>(v.x, a); v.y = un<OP>(v.y, a); v.z = un<OP>(v.z, a); v.w = un<OP>(v.w, a);
+      reinterpret_cast<float4*>(y)[j] = v;
+    }
+    for (long long j = (n4 << 2) + i; j < n; j += stride) y[j] = un<OP>(OP == UN_FILL ? 0.f : x[j], a);
+  } else {
+    for (; i < n; i += stride) y[i] = un<OP>(OP == UN_FILL ? 0.f : x[i], a);
+  }
+}
+
+template <int OP>
+__global__ void binary_flat(const float* __restrict__ p, const float* __restrict__ q, float* __restrict__ y,
+                            long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(q) |
+                     reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (vec) {
+    const long long n4 = n >> 2;
+    for (long long j = i; j < n4; j += stride) {
+      const float4 a = reinterpret_cast<const float4*>(p)[j];
+      const float4 b = reinterpret_cast<const float4*>(q)[j];
+      float4 o;
+      o.x = bin<OP>(a.x, b.x); o.y = bin<OP>(a.y, b.y); o.z = bin<OP>(a.z, b.z); o.w = bin<OP>(a.w, b.w);
+      reinterpret_cast<float4*>(y)[j] = o;
+    }
+    for (long long j = (n4 << 2) + i; j < n; j += stride) y[j] = bin<OP>(p[j], q[j]);
+  } else {
+    for (; i < n; i += stride) y[i] = bin<OP>(p[i], q[i]);
+  }
+}
+
+__global__ void where_flat(const float* __restrict__ c, const float* __restrict__ a, const float* __restrict__ b,
+                           float* __restrict__ y, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = c[i] != 0.f ? a[i] : b[i];
+}
+
+// index decomposition: the LAST dim varies fastest across threads
+__device__ __forceinline__ void offsets2(const Dims& d, long long idx, long long& o0, long long& o1) {
+  o0 = 0; o1 = 0;
+#pragma unroll
+  for (int k = MAXD - 1; k >= 0; --k) {
+    if (k < d.nd) {
+      const long long c = idx % d.shape[k];
+      idx /= d.shape[k];
+      o0 += c * d.s0[k];
+      o1 += c * d.s1[k];
+    }
+  }
+}
+__device__ __forceinline__ void offsets3(const Dims& d, long long idx, long long& o0, long long& o1,
+                                         long long& o2) {
+  o0 = 0; o1 = 0; o2 = 0;
+#pragma unroll
+  for (int k = MAXD - 1; k >= 0; --k) {
+    if (k < d.nd) {
+      const long long c = idx % d.shape[k];
+      idx /= d.shape[k];
+      o0 += c * d.s0[k];
+      o1 += c * d.s1[k];
+      o2 += c * d.s2[k];
+    }
+  }
+}
+
+template <int OP>
+__global__ void unary_strided(const float* __restrict__ x, float* __restrict__ y, const Dims d, long long n,
+                              float a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+    long long ox, oy;
+    offsets2(d, i, ox, oy);
+    y[oy] = un<OP>(OP == UN_FILL ? 0.f : x[ox], a);
+  }
+}
+
+// 2-D tiled transpose-copy through shared memory for the common "two dims whose
+// fast axis differs between source and destination" case (NCHW <-> NHWC,
+// matrix transpose): both the read and the write are coalesced.
+__global__ void copy_tiled(const float* __restrict__ x, float* __restrict__ y, long long outer, long long R,
+                           long long Cc, long long xs_outer, long long xs_r, long long xs_c, long long ys_outer,
+                           long long ys_r, long long ys_c) {
+  // source is contiguous along c (xs_c == 1), destination along r (ys_r == 1)
+  __shared__ float tile[32][33];
+  const long long tiles_r = (R + 31) / 32, tiles_c = (Cc + 31) / 32;
+  const long long per_outer = tiles_r * tiles_c;
+  const long long total = outer * per_outer;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long o = t / per_outer;
+    const long long tr = (t % per_outer) / tiles_c, tc = t % tiles_c;
+    const long long r0 = tr * 32, c0 = tc * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+      const long long r = r0 + j, c = c0 + threadIdx.x;
+      if (r < R && c < Cc) tile[j][threadIdx.x] = x[o * xs_outer + r * xs_r + c * xs_c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+      const long long c = c0 + j, r = r0 + threadIdx.x;
+      if (r < R && c < Cc) y[o * ys_outer + r * ys_r + c * ys_c] = tile[threadIdx.x][j];
+    }
+    __syncthreads();
+  }
+}
+
+template <int OP>
+__global__ void binary_strided(const float* __restrict__ p, const float* __restrict__ q, float* __restrict__ y,
+                               const Dims d, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+    long long oa, ob, oy;
+    offsets3(d, i, oa, ob, oy);
+    y[oy] = bin<OP>(p[oa], q[ob]);
+  }
+}
+
+// y[keep] = sum_red x[keep, red].  One warp per output element when the reduced
+// extent is long, otherwise one thread.  Deterministic (fixed order + shuffles).
+struct RDims {
+  long long kshape[MAXD], kxs[MAXD], kys[MAXD];
+  long long rshape[MAXD], rxs[MAXD];
+  int nk, nr;
+};
+__global__ void reduce_sum_kernel(const float* __restrict__ x, float* __restrict__ y, const RDims d,
+                                  long long nkeep, long long nred) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long o = warp; o < nkeep; o += nwarps) {
+    long long idx = o, xo = 0, yo = 0;
+    for (int k = d.nk - 1; k >= 0; --k) {
+      const long long c = idx % d.kshape[k];
+      idx /= d.kshape[k];
+      xo += c * d.kxs[k];
+      yo += c * d.kys[k];
+    }
+    float acc = 0.f;
+    for (long long r = lane; r < nred; r += 32) {
+      long long ridx = r, ro = 0;
+      for (int k = d.nr - 1; k >= 0; --k) {
+        const long long c = ridx % d.rshape[k];
+        ridx /= d.rshape[k];
+        ro += c * d.rxs[k];
+      }
+      acc += x[xo + ro];
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) y[yo] = acc;
+  }
+}
+
+// Column sums of a row-major [rows, cols] view with cols contiguous (the
+// "reduce over leading dims" case: bias gradients, axis-0 sums): coalesced along
+// cols, two-stage and deterministic.
+__global__ void colsum_partial(const float* __restrict__ x, float* __restrict__ part, long long rows,
+                               long long cols, long long ld, int chunks) {
+  const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int ch = blockIdx.y;
+  if (c >= cols) return;
+  const long long per = (rows + chunks - 1) / chunks;
+  const long long r0 = ch * per, r1 = min(rows, r0 + per);
+  float acc = 0.f;
+  for (long long r = r0; r < r1; ++r) acc += x[r * ld + c];
+  part[(long long)ch * cols + c] = acc;
+}
+__global__ void colsum_final(const float* __restrict__ part, float* __restrict__ y, long long cols, int chunks,
+                             long long ys) {
+  const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.f;
+  for (int ch = 0; ch < chunks; ++ch) acc += part[(long long)ch * cols + c];
+  y[c * ys] = acc;
+}
+
+int grid_for(long long work_items, int threads) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  long long blocks = (work_items + threads - 1) / threads;
+  const long long cap = (long long)sms * 8;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+
+int done() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+float* g_colsum_scratch[64] = {nullptr};
+float* colsum_scratch() {   // 64 chunks x up to 64K columns
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!g_colsum_scratch[dev]) {
+    if (cudaMalloc(reinterpret_cast<void**>(&g_colsum_scratch[dev]), 64ll * 65536 * 4) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+  }
+  return g_colsum_scratch[dev];
+}
+
+}  // namespace
+
+#define UN_CASE(OPC) \
+  case OPC: unary_flat<OPC><<<grid, 256, 0, st>>>(x, y, n, alpha); break;
+#define UNS_CASE(OPC) \
+  case OPC: unary_strided<OPC><<<grid, 256, 0, st>>>(x, y, d, n, alpha); break;
+#define BIN_CASE(OPC) \
+  case OPC: binary_flat<OPC><<<grid, 256, 0, st>>>(a, b, y, n); break;
+#define BINS_CASE(OPC) \
+  case OPC: binary_strided<OPC><<<grid, 256, 0, st>>>(a, b, y, d, n); break;
+
+extern "C" {
+
+int tsb_ew_unary(int op, const float* x, float* y, long long n, float alpha, void* stream) {
+  if (n <= 0) return TSB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for((n + 3) / 4, 256);
+  switch (op) {
+    UN_CASE(UN_COPY) UN_CASE(UN_RELU) UN_CASE(UN_SIGMOID) UN_CASE(UN_TANH) UN_CASE(UN_SQRT) UN_CASE(UN_RSQRT)
+    UN_CASE(UN_NEG) UN_CASE(UN_ADDC) UN_CASE(UN_MULC) UN_CASE(UN_CDIV) UN_CASE(UN_FILL)
+    default: return TSB_ERR_ARG;
+  }
+  return done();
+}
+
+int tsb_ew_binary(int op, const float* a, const float* b, float* y, long long n, void* stream) {
+  if (n <= 0) return TSB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for((n + 3) / 4, 256);
+  switch (op) {
+    BIN_CASE(BIN_ADD) BIN_CASE(BIN_MUL) BIN_CASE(BIN_DIV) BIN_CASE(BIN_RELU_GRAD) BIN_CASE(BIN_SUB)
+    default: return TSB_ERR_ARG;
+  }
+  return done();
+}
+
+int tsb_where(const float* c, const float* a, const float* b, float* y, long long n, void* stream) {
+  if (n <= 0) return TSB_OK;
+  where_flat<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(c, a, b, y, n);
+  return done();
+}
+
+int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long* shape, const long long* xs,
+                      const long long* ys, float alpha, void* stream) {
+  if (nd < 1 || nd > MAXD) return TSB_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Dims d;
+  d.nd = nd;
+  long long n = 1;
+  for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = xs[i]; d.s1[i] = ys[i]; d.s2[i] = 0; n *= shape[i]; }
+  if (n <= 0) return TSB_OK;
+  // coalesced tiled path: copy where src is contiguous along the last dim and dst along another one
+  if (op == UN_COPY && nd >= 2 && nd <= 3 && xs[nd - 1] == 1 && ys[nd - 1] != 1) {
+    int rdim = -1;
+    for (int i = 0; i < nd - 1; ++i) if (ys[i] == 1) rdim = i;
+    if (rdim >= 0 && shape[rdim] >= 8 && shape[nd - 1] >= 8) {
+      long long outer = 1, xso = 0, yso = 0;
+      if (nd == 3) { const int od = rdim == 0 ? 1 : 0; outer = shape[od]; xso = xs[od]; yso = ys[od]; }
+      const long long tiles = outer * ((shape[rdim] + 31) / 32) * ((shape[nd - 1] + 31) / 32);
+      int grid = tiles > 148ll * 16 ? 148 * 16 : (int)tiles;
+      copy_tiled<<<grid, dim3(32, 8), 0, st>>>(x, y, outer, shape[rdim], shape[nd - 1], xso, xs[rdim], 1, yso, 1,
+                                               ys[nd - 1]);
+      return done();
+    }
+  }
+  if (op == UN_COPY && nd >= 2 && nd <= 3 && ys[nd - 1] == 1 && xs[nd - 1] != 1) {
+    int cdim = -1;   // the dim along which the source is contiguous
+    for (int i = 0; i < nd - 1; ++i) if (xs[i] == 1) cdim = i;
+    if (cdim >= 0 && shape[cdim] >= 8 && shape[nd - 1] >= 8) {
+      long long outer = 1, xso = 0, yso = 0;
+      if (nd == 3) { const int od = cdim == 0 ? 1 : 0; outer = shape[od]; xso = xs[od]; yso = ys[od]; }
+      // roles: r = last dim (dst-contiguous), c = cdim (src-contiguous)
+      const long long tiles = outer * ((shape[nd - 1] + 31) / 32) * ((shape[cdim] + 31) / 32);
+      int grid = tiles > 148ll * 16 ? 148 * 16 : (int)tiles;
+      copy_tiled<<<grid, dim3(32, 8), 0, st>>>(x, y, outer, shape[nd - 1], shape[cdim], xso, xs[nd - 1], 1, yso, 1,
+                                               ys[cdim]);
+      return done();
+    }
+  }
+  const int grid = grid_for(n, 256);
+  switch (op) {
+    UNS_CASE(UN_COPY) UNS_CASE(UN_RELU) UNS_CASE(UN_SIGMOID) UNS_CASE(UN_TANH) UNS_CASE(UN_SQRT)
+    UNS_CASE(UN_RSQRT) UNS_CASE(UN_NEG) UNS_CASE(UN_ADDC) UNS_CASE(UN_MULC) UNS_CASE(UN_CDIV) UNS_CASE(UN_FILL)
+    default: return TSB_ERR_ARG;
+  }
+  return done();
+}
+
+int tsb_strided_binary(int op, const float* a, const float* b, float* y, int nd, const long long* shape,
+                       const long long* as, const long long* bs, const long long* ys, void* stream) {
+  if (nd < 1 || nd > MAXD) return TSB_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Dims d;
+  d.nd = nd;
+  long long n = 1;
+  for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = as[i]; d.s1[i] = bs[i]; d.s2[i] = ys[i]; n *= shape[i]; }
+  if (n <= 0) return TSB_OK;
+  const int grid = grid_for(n, 256);
+  switch (op) {
+    BINS_CASE(BIN_ADD) BINS_CASE(BIN_MUL) BINS_CASE(BIN_DIV) BINS_CASE(BIN_RELU_GRAD) BINS_CASE(BIN_SUB)
+    default: return TSB_ERR_ARG;
+  }
+  return done();
+}
+
+int tsb_reduce_sum(const float* x, float* y, int nk, const long long* kshape, const long long* kxs,
+                   const long long* kys, int nr, const long long* rshape, const long long* rxs, void* stream) {
+  if (nk < 1 || nk > MAXD || nr < 1 || nr > MAXD) return TSB_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  RDims d;
+  d.nk = nk; d.nr = nr;
+  long long nkeep = 1, nred = 1;
+  for (int i = 0; i < nk; ++i) { d.kshape[i] = kshape[i]; d.kxs[i] = kxs[i]; d.kys[i] = kys[i]; nkeep *= kshape[i]; }
+  for (int i = 0; i < nr; ++i) { d.rshape[i] = rshape[i]; d.rxs[i] = rxs[i]; nred *= rshape[i]; }
+  if (nkeep <= 0) return TSB_OK;
+  // fast path: kept dims collapse to one contiguous column index and the reduced
+  // dims to one row index with a constant stride (e.g. [rows, cols] -> [cols])
+  if (nk == 1 && nr == 1 && kxs[0] == 1 && nkeep <= 65536 && nred >= 64) {
+    float* part = colsum_scratch();
+    if (part) {
+      int chunks = (int)(nred / 64 < 64 ? (nred / 64 < 1 ? 1 : nred / 64) : 64);
+      dim3 g1((unsigned)((nkeep + 127) / 128), chunks);
+      colsum_partial<<<g1, 128, 0, st>>>(x, part, nred, nkeep, rxs[0], chunks);
+      colsum_final<<<(unsigned)((nkeep + 127) / 128), 128, 0, st>>>(part, y, nkeep, chunks, kys[0]);
+      return done();
+    }
+  }
+  const int grid = grid_for(nkeep * 32, 256);
+  reduce_sum_kernel<<<grid, 256, 0, st>>>(x, y, d, nkeep, nred);
+  return done();
+}
+
+}  // extern "C"

@@ -1,0 +1,576 @@
+// TF32 GEMM on the 5th-generation tensor cores (sm_100a):
+//   C[M,N] (+)= op(A) * op(B), row-major fp32 operands, fp32 accumulate in TMEM.
+//
+// Structure (persistent, warp-specialised, one CTA per SM):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A and B into a
+//               128-byte-swizzled shared-memory ring (STAGES deep)
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma.kind::tf32
+//               (128 x BN x 8 per instruction) into one of two TMEM accumulators
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, store / accumulate
+//               to global while the MMA warp already works on the next tile
+// Transposed operands are handled by MN-major shared-memory descriptors, so no
+// operand is ever transposed in memory.  Optional split-K writes partial sums to
+// a workspace that a second, deterministic kernel reduces.
+//
+// Role in the reference: cublasSgemm / cublasSgemmStridedBatched
+// (src/ops/MatrixMult.cu:4-72, src/ops/BatchMatrixMult.cu:4-43).
+#include "tc_common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+
+using namespace tsb;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                 // 32 tf32 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;
+constexpr int A_STAGE_BYTES = BM * BK * 4;
+
+struct GemmParams {
+  float* c;
+  float* ws;          // split-K partials [splits][batch][M][N] (null when splits == 1)
+  int m, n, k;
+  int batch;
+  long long ldc, sc;  // C row stride / batch stride (elements)
+  int splits;
+  int accumulate;
+  int tiles_m, tiles_n;
+  int kblocks;        // ceil(K / BK)
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + C::STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* tfull = bars + 2 * C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.tiles_m * p.tiles_n;
+  const long long items = (long long)tiles * p.batch * p.splits;
+  const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int tile = (int)(item % tiles);
+        const long long rest = item / tiles;
+        const int b = (int)(rest % p.batch);
+        const int split = (int)(rest / p.batch);
+        const int m0 = (tile / p.tiles_n) * BM;
+        const int n0 = (tile % p.tiles_n) * BN;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kblocks, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x101)) { ok = false; break; }
+          mbar_expect_tx(&full[s], C::STAGE_BYTES);
+          uint8_t* sa = smem_a + s * A_STAGE_BYTES;
+          uint8_t* sb = smem_b + s * C::B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_3d(sa, &tmA, &full[s], k0, m0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 32; ++c) tma_load_3d(sa + c * (BK * 128), &tmA, &full[s], m0 + c * 32, k0, b);
+          }
+          if (!B_MN) {
+            tma_load_3d(sb, &tmB, &full[s], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) tma_load_3d(sb + c * (BK * 128), &tmB, &full[s], n0 + c * 32, k0, b);
+          }
+        }
+      }
+      if (!ok) {   // let copies that are still in flight land before the CTA goes away
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
+        const long long rest = item / tiles;
+        const int split = (int)(rest / p.batch);
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kblocks, kb0 + kb_per_split);
+        const int acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x102)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, p.status, 0x103)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
+          const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
+                                     : make_smem_desc(sa + k * (UMMA_K * 4), 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
+                                     : make_smem_desc(sb + k * (UMMA_K * 4), 16, 1024);
+            umma_tf32(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);     // frees the smem stage when these MMAs retire
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;              // TMEM lane quarter this warp may access
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
+      const int tile = (int)(item % tiles);
+      const long long rest = item / tiles;
+      const int b = (int)(rest % p.batch);
+      const int split = (int)(rest / p.batch);
+      const int m0 = (tile / p.tiles_n) * BM;
+      const int n0 = (tile % p.tiles_n) * BN;
+      const int acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      const int kb0 = split * kb_per_split;
+      const bool has_k = kb0 < p.kblocks;     // an empty K range contributes zeros
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x104)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      float* crow;
+      bool accumulate;
+      if (p.splits > 1) {
+        crow = p.ws + ((long long)(split * p.batch + b) * p.m + row) * p.n;
+        accumulate = false;
+      } else {
+        crow = p.c + (long long)b * p.sc + (long long)row * p.ldc;
+        accumulate = p.accumulate != 0;
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        if (has_k) {
+          tmem_ld_32x32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        const int col = n0 + c0;
+        if (row < p.m && col < p.n) {
+          float* dst = crow + col;
+          const bool vec_ok = (col + 32 <= p.n) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.n) dst[j] = accumulate ? dst[j] + v[j] : v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// Deterministic split-K reduction: c (+)= sum_s ws[s]
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, int splits,
+                                     long long per_split, int m, int n, long long ldc, long long sc,
+                                     int accumulate) {
+  const long long total = per_split;   // = batch * m * n
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[s * per_split + i];
+    const long long b = i / ((long long)m * n);
+    const long long r = (i / n) % m;
+    const long long col = i % n;
+    float* dst = c + b * sc + r * ldc + col;
+    *dst = accumulate ? *dst + acc : acc;
+  }
+}
+
+// Plain SIMT fallback for shapes the tensor-map rules exclude (leading dimension
+// not a multiple of 4 floats, unaligned base).  Tiny problems only.
+__global__ void gemm_simt_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                                 int m, int n, int k, long long lda, long long ldb, long long ldc, int ta, int tb,
+                                 long long sa, long long sb, long long sc, int accumulate) {
+  __shared__ float as[16][17], bs[16][17];
+  const int bz = blockIdx.z;
+  a += bz * sa; b += bz * sb; c += bz * sc;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int row = blockIdx.y * 16 + ty, col = blockIdx.x * 16 + tx;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < k; k0 += 16) {
+    const int ka = k0 + tx, kb = k0 + ty;
+    as[ty][tx] = (row < m && ka < k) ? (ta ? a[(long long)ka * lda + row] : a[(long long)row * lda + ka]) : 0.f;
+    bs[ty][tx] = (col < n && kb < k) ? (tb ? b[(long long)col * ldb + kb] : b[(long long)kb * ldb + col]) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) acc += as[ty][kk] * bs[kk][tx];
+    __syncthreads();
+  }
+  if (row < m && col < n) {
+    float* dst = c + (long long)row * ldc + col;
+    *dst = accumulate ? *dst + acc : acc;
+  }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------- host
+namespace tsb_host {
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_b,
+                  const uint32_t* box, bool atom32) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return TSB_ERR_TMAP;
+  // cache: identical descriptors are re-used across steps (addresses are stable under the pool)
+  struct Key {
+    const void* base; int rank; int atom32; uint64_t d[5], s[4]; uint32_t b[5];
+    bool operator==(const Key& o) const { return std::memcmp(this, &o, sizeof(Key)) == 0; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+      size_t h = 1469598103934665603ull;
+      for (size_t i = 0; i < sizeof(Key) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+      return h;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  Key key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base; key.rank = rank; key.atom32 = atom32 ? 1 : 0;
+  for (int i = 0; i < rank; ++i) { key.d[i] = dims[i]; key.b[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) key.s[i] = strides_b[i];
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return TSB_OK; }
+  }
+  cuuint64_t gd[5], gs[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_b[i];
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base), gd, gs, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return TSB_ERR_TMAP | ((int)r << 8);
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache[key] = *out;
+  }
+  return TSB_OK;
+}
+
+static int* g_status_host = nullptr;   // pinned, mapped: one word per device
+static int* g_status_dev[64] = {nullptr};
+
+int* status_word(cudaStream_t) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static std::mutex mu;
+  std::lock_guard<std::mutex> g(mu);
+  if (!g_status_host) {
+    if (cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), 64 * sizeof(int), cudaHostAllocMapped |
+                      cudaHostAllocPortable) != cudaSuccess)
+      return nullptr;
+    std::memset(g_status_host, 0, 64 * sizeof(int));
+  }
+  if (!g_status_dev[dev]) {
+    int* d = nullptr;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&d), g_status_host, 0) != cudaSuccess) return nullptr;
+    g_status_dev[dev] = d + dev;
+  }
+  return g_status_dev[dev];
+}
+
+int peek_status() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return g_status_host ? *(volatile int*)(g_status_host + dev) : 0;
+}
+
+int read_status(cudaStream_t stream) {
+  cudaStreamSynchronize(stream);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!g_status_host) return 0;
+  int v = *(volatile int*)(g_status_host + dev);
+  g_status_host[dev] = 0;
+  return v;
+}
+
+}  // namespace tsb_host
+
+namespace {
+
+// split-K workspace: grown on demand, per device, owned by the library
+struct Workspace {
+  float* ptr = nullptr;
+  size_t bytes = 0;
+};
+Workspace g_ws[64];
+
+float* get_workspace(size_t bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Workspace& w = g_ws[dev];
+  if (w.bytes < bytes) {
+    if (w.ptr) cudaFree(w.ptr);
+    w.ptr = nullptr; w.bytes = 0;
+    size_t want = bytes < (size_t(64) << 20) ? (size_t(64) << 20) : bytes;
+    if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    w.bytes = want;
+  }
+  return w.ptr;
+}
+
+int g_sm_count = 0;
+int sm_count() {
+  if (!g_sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  using C = Cfg<BN>;
+  auto kern = gemm_tf32_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
+    attr_set = true;
+  }
+  const long long items = (long long)p.tiles_m * p.tiles_n * p.batch * p.splits;
+  const int grid = (int)(items < sm_count() ? items : sm_count());
+  kern<<<grid, 192, C::SMEM_BYTES, st>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+template <int BN>
+int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                   cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_tc<BN, false, false>(ta, tb, p, st);
+  if (!a_mn && b_mn) return launch_tc<BN, false, true>(ta, tb, p, st);
+  if (a_mn && !b_mn) return launch_tc<BN, true, false>(ta, tb, p, st);
+  return launch_tc<BN, true, true>(ta, tb, p, st);
+}
+
+}  // namespace
+
+// Chooses the split-K factor: enough work items to fill the SMs when the tile
+// grid alone is small and K is long.
+static int choose_splits(long long tiles, int kblocks, int forced) {
+  if (forced > 0) return forced;
+  const int sms = sm_count();
+  if (tiles >= sms || kblocks < 16) return 1;
+  long long s = sms / tiles;
+  if (s > kblocks / 8) s = kblocks / 8;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : (int)s;
+}
+
+// Core entry shared by the allocating and the non-allocating front ends.
+//   ws / ws_bytes : split-K scratch supplied by the caller (may be null when splits resolves to 1)
+int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, int k, long long lda,
+                       long long ldb, long long ldc, int trans_a, int trans_b, int batch, long long sa,
+                       long long sb, long long sc, int accumulate, int forced_splits, float* ws,
+                       size_t ws_bytes, bool may_alloc, cudaStream_t st) {
+  if (m <= 0 || n <= 0 || k <= 0 || batch <= 0) return TSB_ERR_ARG;
+  const bool aligned = (lda % 4 == 0) && (ldb % 4 == 0) && (sa % 4 == 0) && (sb % 4 == 0) &&
+                       ((reinterpret_cast<uintptr_t>(a) & 15) == 0) && ((reinterpret_cast<uintptr_t>(b) & 15) == 0);
+  if (!aligned) {
+    dim3 blk(16, 16), grd((n + 15) / 16, (m + 15) / 16, batch);
+    gemm_simt_kernel<<<grd, blk, 0, st>>>(a, b, c, m, n, k, lda, ldb, ldc, trans_a, trans_b, sa, sb, sc,
+                                          accumulate);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+  }
+  const int bn = n > 128 ? 256 : (n > 64 ? 128 : 64);
+  GemmParams p;
+  p.c = c; p.m = m; p.n = n; p.k = k; p.batch = batch; p.ldc = ldc; p.sc = sc;
+  p.accumulate = accumulate;
+  p.tiles_m = (m + BM - 1) / BM;
+  p.tiles_n = (n + bn - 1) / bn;
+  p.kblocks = (k + BK - 1) / BK;
+  p.splits = choose_splits((long long)p.tiles_m * p.tiles_n * batch, p.kblocks, forced_splits);
+  if (p.splits > p.kblocks) p.splits = p.kblocks;
+  {   // no empty K ranges: re-derive the count from the per-split share
+    const int per = (p.kblocks + p.splits - 1) / p.splits;
+    p.splits = (p.kblocks + per - 1) / per;
+  }
+  p.ws = nullptr;
+  p.status = tsb_host::status_word(st);
+  if (!p.status) return TSB_ERR_LAUNCH;
+  if (p.splits > 1) {
+    const size_t need = (size_t)p.splits * batch * m * n * sizeof(float);
+    if (ws && ws_bytes >= need) {
+      p.ws = ws;
+    } else if (may_alloc) {
+      p.ws = get_workspace(need);
+      if (!p.ws) return TSB_ERR_OOM;
+    } else {
+      return TSB_ERR_SCRATCH;
+    }
+  }
+  // tensor maps (dims innermost first)
+  CUtensorMap ta, tb;
+  const uint64_t sab = (uint64_t)(batch > 1 ? sa : (long long)(trans_a ? k : m) * lda) * 4;
+  const uint64_t sbb = (uint64_t)(batch > 1 ? sb : (long long)(trans_b ? n : k) * ldb) * 4;
+  int rc;
+  if (!trans_a) {   // A[m][k], K contiguous -> K-major
+    uint64_t d[3] = {(uint64_t)k, (uint64_t)m, (uint64_t)batch}, s[2] = {(uint64_t)lda * 4, sab};
+    uint32_t bx[3] = {BK, BM, 1};
+    rc = tsb_host::make_tmap_f32(&ta, a, 3, d, s, bx);
+  } else {          // A stored [k][m], M contiguous -> MN-major
+    uint64_t d[3] = {(uint64_t)m, (uint64_t)k, (uint64_t)batch}, s[2] = {(uint64_t)lda * 4, sab};
+    uint32_t bx[3] = {32, BK, 1};
+    rc = tsb_host::make_tmap_f32(&ta, a, 3, d, s, bx, true);
+  }
+  if (rc) return rc;
+  if (trans_b) {    // B stored [n][k], K contiguous -> K-major
+    uint64_t d[3] = {(uint64_t)k, (uint64_t)n, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
+    uint32_t bx[3] = {BK, (uint32_t)bn, 1};
+    rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx);
+  } else {          // B[k][n], N contiguous -> MN-major
+    uint64_t d[3] = {(uint64_t)n, (uint64_t)k, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
+    uint32_t bx[3] = {32, BK, 1};
+    rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx, true);
+  }
+  if (rc) return rc;
+  const bool a_mn = trans_a != 0, b_mn = trans_b == 0;
+  if (bn == 256) rc = dispatch_major<256>(a_mn, b_mn, ta, tb, p, st);
+  else if (bn == 128) rc = dispatch_major<128>(a_mn, b_mn, ta, tb, p, st);
+  else rc = dispatch_major<64>(a_mn, b_mn, ta, tb, p, st);
+  if (rc) return rc;
+  if (p.splits > 1) {
+    const long long per_split = (long long)batch * m * n;
+    int blocks = (int)((per_split + 255) / 256);
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.ws, c, p.splits, per_split, m, n, ldc, sc, accumulate);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+  }
+  const int late = tsb_host::peek_status();
+  return late ? TSB_ERR_TIMEOUT | (late << 8) : TSB_OK;
+}
+
+extern "C" {
+
+int tsb_gemm_tf32(const float* a, const float* b, float* c, int m, int n, int k, long long lda, long long ldb,
+                  long long ldc, int trans_a, int trans_b, int batch, long long sa, long long sb, long long sc,
+                  int accumulate, void* stream) {
+  return tsb_gemm_tf32_impl(a, b, c, m, n, k, lda, ldb, ldc, trans_a, trans_b, batch, sa, sb, sc, accumulate, 0,
+                            nullptr, 0, true, static_cast<cudaStream_t>(stream));
+}
+
+// Same with an explicit split-K factor (tests, tuning).
+int tsb_gemm_tf32_splitk(const float* a, const float* b, float* c, int m, int n, int k, long long lda,
+                         long long ldb, long long ldc, int trans_a, int trans_b, int splits, void* stream) {
+  return tsb_gemm_tf32_impl(a, b, c, m, n, k, lda, ldb, ldc, trans_a, trans_b, 1, 0, 0, 0, 0, splits, nullptr, 0,
+                            true, static_cast<cudaStream_t>(stream));
+}
+
+// Synchronise the stream and return (then clear) the device-side wait status:
+// 0 = clean, otherwise the code of the wait that ran out.
+int tsb_device_status(void* stream) { return tsb_host::read_status(static_cast<cudaStream_t>(stream)); }
+
+}  // extern "C"
