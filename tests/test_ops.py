@@ -1,0 +1,217 @@
+"""Every graph op: the sm_100a kernel path against the NumPy oracle path, through
+the public Executor API (so layouts, strides and feed staging are covered too)."""
+import numpy as np
+import pytest
+
+from tsplit_b200 import ndarray, gpu_ops as ad
+from helpers import run_graph, assert_close
+
+
+
+@pytest.fixture(params=[pytest.param("cpu"), pytest.param("gpu", marks=pytest.mark.gpu)])
+def ctx(request):
+    return ndarray.cpu(0) if request.param == "cpu" else ndarray.gpu(0)
+
+R = np.random.RandomState(7)
+
+
+def f32(*shape, scale=1.0):
+    return (R.standard_normal(shape) * scale).astype(np.float32)
+
+
+def both(build, feeds, ctx, rtol=2e-3):
+    ref = run_graph(build, feeds, None)
+    got = run_graph(build, feeds, ctx)
+    for i, (g, r) in enumerate(zip(got, ref)):
+        if r is not None:
+            assert_close(g, r, rtol=rtol, what="output %d" % i)
+
+
+def unary_graph(fn):
+    def build():
+        x = ad.Variable("x")
+        return {"x": x}, [fn(x)]
+    return build
+
+
+@pytest.mark.parametrize("shape", [(5, 7), (2, 8, 6, 6), (1000,), (3, 4, 5)])
+def test_elementwise_unary(shape, ctx):
+    x = np.abs(f32(*shape)) + 0.5
+    for fn in (ad.relu_op, ad.sigmoid_op, ad.tanh_op, ad.sqrt_op, ad.rsqrt_op, ad.opposite_op,
+               lambda n: ad.addbyconst_op(n, 1.5), lambda n: ad.mul_byconst_op(n, -2.0),
+               lambda n: ad.div_const_op(3.0, n), ad.oneslike_op, ad.zeroslike_op):
+        both(unary_graph(fn), {"x": x - 0.7 if fn is ad.relu_op else x}, ctx)
+
+
+@pytest.mark.parametrize("shape", [(6, 10), (2, 4, 5, 5)])
+def test_elementwise_binary_and_where(shape, ctx):
+    a, b = f32(*shape), np.abs(f32(*shape)) + 0.5
+
+    def build():
+        x, y = ad.Variable("a"), ad.Variable("b")
+        c = ad.relu_op(x)
+        return {"a": x, "b": y}, [x + y, x * y, ad.div_op(x, y), ad.relu_gradient_op(x, y),
+                                  ad.where_op(c, x, y)]
+    both(build, {"a": a, "b": b}, ctx)
+
+
+def test_scalar_broadcast_add_mul(ctx):
+    def build():
+        x, s = ad.Variable("x"), ad.Variable("s")
+        return {"x": x, "s": s}, [ad.add_op(x, s), ad.mul_op(s, x)]
+    both(build, {"x": f32(4, 9), "s": np.array([2.5], np.float32)}, ctx)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_matmul_and_grads(ta, tb, ctx):
+    m, k, n = 96, 64, 80
+    a = f32(k, m) if ta else f32(m, k)
+    b = f32(n, k) if tb else f32(k, n)
+
+    def build():
+        A, B = ad.Variable("a"), ad.Variable("b")
+        C = ad.matmul_op(A, B, ta, tb)
+        loss = ad.reduce_sum_op(ad.mul_op(C, C), [0, 1])
+        ga, gb = ad.gradients(loss, [A, B])
+        return {"a": A, "b": B}, [C, ga, gb]
+    both(build, {"a": a, "b": b}, ctx, rtol=5e-3)
+
+
+def test_batch_matmul(ctx):
+    def build():
+        A, B = ad.Variable("a"), ad.Variable("b")
+        return {"a": A, "b": B}, [ad.batch_matmul_op(A, B), ad.batch_matmul_op(A, A, False, True)]
+    both(build, {"a": f32(2, 3, 64, 32), "b": f32(2, 3, 32, 48)}, ctx, rtol=5e-3)
+
+
+CONVS = [
+    # n, c, h, w, o, k, pad, stride
+    (2, 8, 12, 12, 16, 3, 1, 1),
+    (3, 3, 16, 16, 64, 3, 1, 1),       # RGB stem (padded-channel path)
+    (2, 64, 14, 14, 128, 3, 1, 1),
+    (2, 32, 9, 9, 64, 1, 0, 1),
+    (2, 16, 15, 15, 32, 3, 1, 2),
+    (1, 3, 32, 32, 64, 7, 3, 2),
+    (2, 72, 7, 7, 200, 3, 1, 1),       # ragged channel counts
+    (4, 256, 8, 8, 512, 3, 1, 1),      # wide tiles (BN = 256)
+]
+
+
+@pytest.mark.parametrize("n,c,h,w,o,k,pad,stride", CONVS)
+def test_conv2d_forward_and_gradients(n, c, h, w, o, k, pad, stride, ctx):
+    xv, wv = f32(n, c, h, w), f32(o, c, k, k, scale=0.2)
+
+    def build():
+        x, f = ad.Variable("x"), ad.Variable("w")
+        y = ad.conv2d_op(x, f, padding=pad, stride=stride)
+        loss = ad.reduce_sum_op(ad.mul_op(y, y), [0, 1, 2, 3])
+        gx, gf = ad.gradients(loss, [x, f])
+        return {"x": x, "w": f}, [y, gx, gf]
+    both(build, {"x": xv, "w": wv}, ctx, rtol=6e-3)
+
+
+def test_conv_asymmetric_kernel_and_padding(ctx):
+    def build():
+        x, f = ad.Variable("x"), ad.Variable("w")
+        y = ad.conv2d_op(x, f, padding=0, padding2=3, stride=1)
+        loss = ad.reduce_sum_op(y, [0, 1, 2, 3])
+        gx, gf = ad.gradients(loss, [x, f])
+        return {"x": x, "w": f}, [y, gx, gf]
+    both(build, {"x": f32(2, 16, 10, 10), "w": f32(24, 16, 1, 7, scale=0.2)}, ctx, rtol=6e-3)
+
+
+def test_conv_bias_helpers(ctx):
+    def build():
+        b, x = ad.Variable("b"), ad.Variable("x")
+        return {"b": b, "x": x}, [ad.conv2d_broadcastto_op(b, x), ad.conv2d_reducesum_op(x)]
+    both(build, {"b": f32(8), "x": f32(3, 8, 5, 5)}, ctx)
+
+
+@pytest.mark.parametrize("kind", ["max", "avg"])
+@pytest.mark.parametrize("k,pad,stride,hw", [(2, 0, 2, 8), (3, 1, 2, 9), (3, 1, 1, 6), (7, 0, 7, 7)])
+def test_pooling(kind, k, pad, stride, hw, ctx):
+    def build():
+        x = ad.Variable("x")
+        op = ad.max_pool2d_op if kind == "max" else ad.avg_pool2d_op
+        y = op(x, k, k, pad, stride)
+        loss = ad.reduce_sum_op(ad.mul_op(y, y), [0, 1, 2, 3])
+        gx, = ad.gradients(loss, [x])
+        return {"x": x}, [y, gx]
+    both(build, {"x": np.round(f32(2, 8, hw, hw) * 2) / 2}, ctx)    # ties on purpose
+
+
+def test_batch_norm_forward_backward(ctx):
+    def build():
+        x, s, b = ad.Variable("x"), ad.Variable("s"), ad.Variable("b")
+        y = ad.batch_normalization_op(x, s, b)
+        loss = ad.reduce_sum_op(ad.mul_op(y, y), [0, 1, 2, 3])
+        gx, gs, gb = ad.gradients(loss, [x, s, b])
+        return {"x": x, "s": s, "b": b}, [y, gx, gs, gb]
+    both(build, {"x": f32(4, 16, 6, 6) + 0.5, "s": f32(1, 16, 1, 1) + 1, "b": f32(1, 16, 1, 1)}, ctx, rtol=5e-3)
+
+
+def test_layer_norm(ctx):
+    def build():
+        x, s, b = ad.Variable("x"), ad.Variable("s"), ad.Variable("b")
+        y = ad.layer_normalization_op(x, s, b)
+        loss = ad.reduce_sum_op(ad.mul_op(y, y), [0, 1, 2])
+        gx, gs, gb = ad.gradients(loss, [x, s, b])
+        return {"x": x, "s": s, "b": b}, [y, gx, gs, gb]
+    both(build, {"x": f32(3, 5, 64), "s": f32(64) + 1, "b": f32(64)}, ctx, rtol=5e-3)
+
+
+def test_softmax_and_cross_entropy(ctx):
+    logits = f32(32, 1000)
+    labels = np.eye(1000, dtype=np.float32)[R.randint(0, 1000, 32)]
+
+    def build():
+        y, y_ = ad.Variable("y"), ad.Variable("y_")
+        loss = ad.softmaxcrossentropy_op(y, y_)
+        g, = ad.gradients(loss, [y])
+        return {"y": y, "y_": y_}, [ad.softmax_op(y), loss, g]
+    both(build, {"y": logits, "y_": labels}, ctx)
+
+
+def test_shape_family(ctx):
+    def build():
+        x, z = ad.Variable("x"), ad.Variable("z")
+        outs = [ad.array_reshape_op(x, (-1, 6 * 5 * 5)), ad.transpose_op(x, (0, 2, 3, 1)),
+                ad.transpose_op(z), ad.slice_op(x, (0, 1, 1, 0), (2, 3, -1, 4)),
+                ad.concat_op(x, x, axis=1), ad.pad_op(x, [(0, 0), (0, 0), (1, 2), (2, 1)]),
+                ad.reduce_sum_op(x, [0, 2, 3]), ad.reduce_sum_op(z, [1], keepdims=True),
+                ad.reducesumaxiszero_op(z), ad.broadcastto_op(z, ad.Variable("w", value=np.zeros((3, 7, 9), np.float32))),
+                ad.broadcast_shape_op(ad.reduce_sum_op(z, [1]), (7, 9), add_axes=[1])]
+        loss = ad.reduce_sum_op(ad.mul_op(outs[3], outs[3]), [0, 1, 2, 3]) + \
+            ad.reduce_sum_op(ad.pad_op(x, [(0, 0), (0, 0), (1, 1), (1, 1)]), [0, 1, 2, 3]) + \
+            ad.reduce_sum_op(ad.mul_op(outs[4], outs[4]), [0, 1, 2, 3]) + \
+            ad.reduce_sum_op(ad.mul_op(outs[0], outs[0]), [0, 1])
+        gx, = ad.gradients(loss, [x])
+        return {"x": x, "z": z}, outs + [gx]
+    both(build, {"x": f32(2, 6, 5, 5), "z": f32(7, 9)}, ctx)
+
+
+def test_embedding_onehot_dropout(ctx):
+    idx = R.randint(0, 50, (4, 6)).astype(np.float32)
+
+    def build():
+        t, i, x = ad.Variable("t"), ad.Variable("i"), ad.Variable("x")
+        e = ad.embedding_lookup_op(t, i)
+        loss = ad.reduce_sum_op(ad.mul_op(e, e), [0, 1, 2])
+        gt, = ad.gradients(loss, [t])
+        d = ad.dropout_op(x, 0.7, seed=1234)
+        gd, = ad.gradients(ad.reduce_sum_op(d, [0, 1]), [x])
+        return {"t": t, "i": i, "x": x}, [e, gt, ad.one_hot_op(i, 50), d, gd]
+    both(build, {"t": f32(50, 16), "i": idx, "x": f32(8, 32)}, ctx)
+
+
+def test_csrmm_and_csrmv(ctx):
+    import scipy.sparse
+    dense = f32(20, 8)
+    m = scipy.sparse.random(12, 20, density=0.3, random_state=3, dtype=np.float32).tocoo()
+    for ctx in (ctx,):
+        sp = ndarray.sparse_array(m.data, (m.row, m.col), (12, 20), ctx)
+        A, B = ad.Variable("A"), ad.Variable("B")
+        out = ad.csrmm_op(A, B)
+        ex = ad.Executor([out], ctx=ctx)
+        got = ex.run({A: sp, B: dense}, convert_to_numpy_ret_vals=True)[0]
+        assert_close(got, m.toarray() @ dense, rtol=1e-4)

@@ -1,0 +1,530 @@
+// Implicit-GEMM 2-D convolution on the 5th-generation tensor cores (sm_100a),
+// TF32 inputs / fp32 accumulate in TMEM, channels-last operands:
+//   mode 0  forward : y[n,oh,ow,o]  = sum_{kh,kw,c} x[n,oh*s-ph+kh,ow*s-pw+kw,c] * w[o,kh,kw,c]
+//   mode 1  dgrad   : dx[n,ih,iw,c] = sum_{kh,kw,o} dy[n,(ih+ph-kh)/s,(iw+pw-kw)/s,o] * w[o,kh,kw,c]
+//   mode 2  wgrad   : dw[o,kh,kw,c] = sum_{n,oh,ow} dy[n,oh,ow,o] * x[n,oh*s-ph+kh,ow*s-pw+kw,c]
+//
+// No im2col buffer exists anywhere.  The patch operand is gathered straight into
+// swizzled shared memory by four cp.async producer warps (zero-fill for padding
+// and tails); the dense operand (filters, or dy for wgrad) arrives by TMA; one
+// elected thread issues tcgen05.mma.kind::tf32 into double-buffered TMEM
+// accumulators; four epilogue warps drain TMEM to global while the next tile is
+// being multiplied.  wgrad splits its long reduction (all output pixels) across
+// CTAs and reduces the partial sums in a fixed order.
+//
+// Role in the reference: cudnnConvolutionForward / BackwardData / BackwardFilter
+// (src/ops/CudnnConv2d.cu:127-602).
+#include "tc_common.cuh"
+
+using namespace tsb;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;
+constexpr int UMMA_K = 8;
+constexpr int A_STAGE_BYTES = BM * BK * 4;
+constexpr int LAG = 2;                 // cp.async groups in flight per gather thread
+constexpr int NUM_THREADS = 320;       // warp0 TMA, warp1 MMA, warps2-5 epilogue, warps6-9 gather
+
+struct ConvParams {
+  const float* src;    // gathered tensor: x (fwd, wgrad) or dy (dgrad)
+  float* out;
+  float* ws;
+  int N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride;
+  int M;               // GEMM rows
+  int NC;              // GEMM columns of one column group
+  int K;               // fwd: KH*KW*C
+  int kblocks;         // k-blocks of one full reduction
+  int ocb;             // dgrad: ceil(O/32) k-blocks per filter tap
+  int tiles_m, tiles_n, taps;   // taps = KH*KW column groups (wgrad), else 1
+  int splits;
+  int accumulate;
+  long long ldc;
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+struct Item {
+  int m0, n0, tap, split, kb0, kb1;
+};
+
+__device__ __forceinline__ Item decode_item(const ConvParams& p, long long item, int BN_) {
+  Item it;
+  const int tiles = p.tiles_m * p.tiles_n * p.taps;
+  const int tile = (int)(item % tiles);
+  it.split = (int)(item / tiles);
+  const int per_m = p.tiles_n * p.taps;
+  it.m0 = (tile / per_m) * BM;
+  const int r = tile % per_m;
+  it.tap = r / p.tiles_n;
+  it.n0 = (r % p.tiles_n) * BN_;
+  const int per = (p.kblocks + p.splits - 1) / p.splits;
+  it.kb0 = it.split * per;
+  it.kb1 = min(p.kblocks, it.kb0 + per);
+  return it;
+}
+
+template <int MODE, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + C::STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* tfull = bars + 2 * C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1 + 4);      // TMA expect_tx arrive + one arrive per gather warp
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const long long items = (long long)p.tiles_m * p.tiles_n * p.taps * p.splits;
+  // which shared-memory operand the TMA fills / the gather warps fill
+  constexpr bool TMA_IS_A = (MODE == 2);
+  constexpr int TMA_BYTES = TMA_IS_A ? A_STAGE_BYTES : C::B_STAGE_BYTES;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const Item w = decode_item(p, item, BN);
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x201)) { ok = false; break; }
+          mbar_expect_tx(&full[s], TMA_BYTES);
+          if (MODE == 0) {          // filters [O][K], K-major
+            tma_load_2d(smem_b + s * C::B_STAGE_BYTES, &tm, &full[s], kb * BK, w.n0);
+          } else if (MODE == 1) {   // filters viewed (C, tap, O): MN-major chunks of 32 channels
+            const int tap = kb / p.ocb, o0 = (kb % p.ocb) * BK;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_3d(smem_b + s * C::B_STAGE_BYTES + c * (BK * 128), &tm, &full[s], w.n0 + c * 32, tap, o0);
+          } else {                  // dy [pixels][O]: MN-major chunks of 32 output channels
+#pragma unroll
+            for (int c = 0; c < BM / 32; ++c)
+              tma_load_2d(smem_a + s * A_STAGE_BYTES + c * (BK * 128), &tm, &full[s], w.m0 + c * 32, kb * BK);
+          }
+        }
+      }
+      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr int A_MN = (MODE == 2) ? 1 : 0;
+      constexpr int B_MN = (MODE == 0) ? 0 : 1;
+      constexpr uint32_t idesc = make_idesc_tf32(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
+        const Item w = decode_item(p, item, BN);
+        const int acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x202)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, p.status, 0x203)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
+          const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
+                                     : make_smem_desc(sa + k * (UMMA_K * 4), 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
+                                     : make_smem_desc(sb + k * (UMMA_K * 4), 16, 1024);
+            umma_tf32(d_tmem, da, db, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
+      const Item w = decode_item(p, item, BN);
+      const int acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      const bool has_k = w.kb0 < w.kb1;
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x204)) { ok = false; break; }
+      tc_fence_after();
+      const int row = w.m0 + q * 32 + lane;
+      const long long coloff = (MODE == 2) ? (long long)w.tap * p.C : 0;
+      float* crow;
+      bool accumulate;
+      if (p.splits > 1) {
+        crow = p.ws + ((long long)w.split * p.M + row) * p.ldc + coloff;
+        accumulate = false;
+      } else {
+        crow = p.out + (long long)row * p.ldc + coloff;
+        accumulate = p.accumulate != 0;
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        if (has_k) {
+          tmem_ld_32x32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        const int col = w.n0 + c0;
+        if (row < p.M && col < p.NC) {
+          float* dst = crow + col;
+          const bool vec_ok = (col + 32 <= p.NC) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.NC) dst[j] = accumulate ? dst[j] + v[j] : v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  } else {
+    // ---------------------------------------------------------------- gather producers (warps 6..9)
+    const int t = threadIdx.x - 6 * 32;       // 0..127
+    uint32_t it = 0;                          // k-blocks issued by this thread
+    uint32_t arrived = 0;                     // k-blocks whose data this warp has published
+    bool ok = true;
+    auto publish = [&](uint32_t upto) {       // arrive for k-blocks [arrived, upto)
+      for (; arrived < upto; ++arrived) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[arrived % C::STAGES]);
+      }
+    };
+    for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const Item w = decode_item(p, item, BN);
+      if (MODE == 0 || MODE == 1) {
+        // A tile: 128 rows (pixels) x 32 k, K-major, 128B swizzle.  Thread owns 16B chunk j of rows rg+16i.
+        const int j = t & 7, rg = t >> 3;
+        const int PH = (MODE == 0) ? p.OH : p.H, PW = (MODE == 0) ? p.OW : p.W;   // pixel grid of the rows
+        const int SH = (MODE == 0) ? p.H : p.OH, SW = (MODE == 0) ? p.W : p.OW;   // grid of the gathered tensor
+        const int SC = (MODE == 0) ? p.C : p.O;                                   // its channel count
+        long long base[8];
+        int a0[8], b0[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int pix = w.m0 + rg + 16 * i;
+          if (pix < p.M) {
+            const int n = pix / (PH * PW);
+            const int rem = pix - n * (PH * PW);
+            const int y = rem / PW, x = rem - y * PW;
+            base[i] = (long long)n * SH * SW * SC;
+            if (MODE == 0) { a0[i] = y * p.stride - p.ph; b0[i] = x * p.stride - p.pw; }
+            else           { a0[i] = y + p.ph;            b0[i] = x + p.pw; }
+          } else {
+            base[i] = 0; a0[i] = -(1 << 28); b0[i] = -(1 << 28);
+          }
+        }
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x205)) { ok = false; break; }
+          int kh, kw, ch;
+          bool kvalid;
+          if (MODE == 0) {
+            const int k = kb * BK + j * 4;
+            kvalid = k < p.K;
+            const int tap = k / p.C;
+            ch = k - tap * p.C;
+            kh = tap / p.KW; kw = tap - kh * p.KW;
+          } else {
+            const int tap = kb / p.ocb;
+            ch = (kb - tap * p.ocb) * BK + j * 4;
+            kvalid = ch < p.O;
+            kh = tap / p.KW; kw = tap - kh * p.KW;
+          }
+          const uint32_t sdst = smem_u32(smem_a + s * A_STAGE_BYTES);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = rg + 16 * i;
+            int yy, xx;
+            bool v = kvalid;
+            if (MODE == 0) {
+              yy = a0[i] + kh; xx = b0[i] + kw;
+            } else {
+              const int ty = a0[i] - kh, tx = b0[i] - kw;
+              if (p.stride == 1) { yy = ty; xx = tx; }
+              else {
+                yy = ty / p.stride; xx = tx / p.stride;
+                v = v && ty >= 0 && tx >= 0 && (yy * p.stride == ty) && (xx * p.stride == tx);
+              }
+            }
+            v = v && (unsigned)yy < (unsigned)SH && (unsigned)xx < (unsigned)SW;
+            const float* src = v ? p.src + base[i] + ((long long)yy * SW + xx) * SC + ch : p.src;
+            cp_async16(sdst + r * 128 + ((j ^ (r & 7)) << 4), src, v);
+          }
+          cp_async_commit();
+          if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
+        }
+      } else {
+        // wgrad B tile: 32 rows (pixels = k) x BN channels, MN-major, 128B swizzle with 32B atoms.
+        constexpr int PPR = BN / 4;            // 16-byte pieces per pixel row
+        constexpr int RPP = 128 / PPR;         // pixel rows covered by one pass of the 128 threads
+        constexpr int PASSES = BK / RPP;
+        const int pc = t % PPR, kr0 = t / PPR;
+        const int ch = w.n0 + pc * 4;
+        const bool cvalid = ch < p.C;
+        const int kh = w.tap / p.KW, kw = w.tap - kh * p.KW;
+        const int chunk = pc >> 3, u = pc & 7;
+        const int mpix = p.N * p.OH * p.OW;
+        // pixel state of row kr0 at the first k-block
+        int pix = w.kb0 * BK + kr0;
+        int n = pix / (p.OH * p.OW);
+        int rem = pix - n * (p.OH * p.OW);
+        int oy = rem / p.OW, ox = rem - oy * p.OW;
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x206)) { ok = false; break; }
+          const uint32_t sdst = smem_u32(smem_b + s * C::B_STAGE_BYTES) + chunk * (BK * 128);
+          int pn = n, py = oy, px = ox, ppix = pix;
+#pragma unroll
+          for (int ps = 0; ps < PASSES; ++ps) {
+            const int kr = kr0 + ps * RPP;
+            const int yy = py * p.stride - p.ph + kh, xx = px * p.stride - p.pw + kw;
+            const bool v = cvalid && ppix < mpix && (unsigned)yy < (unsigned)p.H &&
+                           (unsigned)xx < (unsigned)p.W;
+            const float* src = v ? p.src + (((long long)pn * p.H + yy) * p.W + xx) * p.C + ch : p.src;
+            const uint32_t piece = (uint32_t)((((u >> 1) ^ (kr & 3)) << 1) | (u & 1));
+            cp_async16(sdst + kr * 128 + (piece << 4), src, v);
+            // advance the pixel by RPP
+            ppix += RPP; px += RPP;
+            while (px >= p.OW) { px -= p.OW; ++py; }
+            while (py >= p.OH) { py -= p.OH; ++pn; }
+          }
+          cp_async_commit();
+          if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
+          // advance the base pixel by one k-block
+          pix += BK; ox += BK;
+          while (ox >= p.OW) { ox -= p.OW; ++oy; }
+          while (oy >= p.OH) { oy -= p.OH; ++n; }
+        }
+      }
+    }
+    cp_async_wait<0>();
+    if (ok) publish(it);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+__global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restrict__ out, int splits,
+                                   long long per_split, int accumulate) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_split;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[s * per_split + i];
+    out[i] = accumulate ? out[i] + acc : acc;
+  }
+}
+
+struct Workspace {
+  float* ptr = nullptr;
+  size_t bytes = 0;
+};
+Workspace g_ws[64];
+float* get_ws(size_t bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Workspace& w = g_ws[dev];
+  if (w.bytes < bytes) {
+    if (w.ptr) cudaFree(w.ptr);
+    w.ptr = nullptr; w.bytes = 0;
+    size_t want = bytes < (size_t(128) << 20) ? (size_t(128) << 20) : bytes;
+    if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    w.bytes = want;
+  }
+  return w.ptr;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int MODE, int BN>
+int launch(const CUtensorMap& tm, const ConvParams& p, cudaStream_t st) {
+  using C = Cfg<BN>;
+  auto kern = conv_tf32_kernel<MODE, BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
+    attr_set = true;
+  }
+  const long long items = (long long)p.tiles_m * p.tiles_n * p.taps * p.splits;
+  const int grid = (int)(items < sm_count() ? items : sm_count());
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tm, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+template <int MODE>
+int launch_bn(int bn, const CUtensorMap& tm, const ConvParams& p, cudaStream_t st) {
+  if (bn == 256) return launch<MODE, 256>(tm, p, st);
+  if (bn == 128) return launch<MODE, 128>(tm, p, st);
+  return launch<MODE, 64>(tm, p, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+// kind 0: y = conv(x, w);  1: x(dx) = dgrad(y(dy), w);  2: w(dw) = wgrad(x, y(dy)).
+// x[N,H,W,C], w[O,KH,KW,C], y[N,OH,OW,O] dense channels-last fp32; C % 4 == 0 and O % 4 == 0.
+int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int W, int O, int KH, int KW, int OH,
+               int OW, int ph, int pw, int stride, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kind < 0 || kind > 2 || N <= 0 || stride <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (O % 4)) return TSB_ERR_UNSUPPORTED;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
+    return TSB_ERR_UNSUPPORTED;
+  if ((long long)N * OH * OW >= (1ll << 31) || (long long)N * H * W >= (1ll << 31)) return TSB_ERR_UNSUPPORTED;
+  ConvParams p;
+  p.N = N; p.C = C; p.H = H; p.W = W; p.O = O; p.KH = KH; p.KW = KW; p.OH = OH; p.OW = OW;
+  p.ph = ph; p.pw = pw; p.stride = stride;
+  p.ws = nullptr; p.accumulate = 0; p.splits = 1; p.taps = 1; p.K = KH * KW * C; p.ocb = (O + 31) / 32;
+  p.status = tsb_host::status_word(st);
+  if (!p.status) return TSB_ERR_LAUNCH;
+  CUtensorMap tm;
+  int rc, bn;
+  if (kind == 0) {
+    p.src = x; p.out = y; p.M = N * OH * OW; p.NC = O; p.ldc = O;
+    p.kblocks = (p.K + BK - 1) / BK;
+    bn = O > 128 ? 256 : (O > 64 ? 128 : 64);
+    uint64_t d[2] = {(uint64_t)p.K, (uint64_t)O}, s[1] = {(uint64_t)p.K * 4};
+    uint32_t bx[2] = {BK, (uint32_t)bn};
+    rc = tsb_host::make_tmap_f32(&tm, w, 2, d, s, bx, false);
+  } else if (kind == 1) {
+    p.src = y; p.out = x; p.M = N * H * W; p.NC = C; p.ldc = C;
+    p.kblocks = KH * KW * p.ocb;
+    bn = C > 128 ? 256 : (C > 64 ? 128 : 64);
+    uint64_t d[3] = {(uint64_t)C, (uint64_t)KH * KW, (uint64_t)O};
+    uint64_t s[2] = {(uint64_t)C * 4, (uint64_t)KH * KW * C * 4};
+    uint32_t bx[3] = {32, 1, BK};
+    rc = tsb_host::make_tmap_f32(&tm, w, 3, d, s, bx, true);
+  } else {
+    const long long mpix = (long long)N * OH * OW;
+    p.src = x; p.out = w; p.M = O; p.NC = C; p.ldc = (long long)KH * KW * C;
+    p.taps = KH * KW;
+    p.kblocks = (int)((mpix + BK - 1) / BK);
+    bn = C > 128 ? 256 : (C > 64 ? 128 : 64);
+    uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
+    uint32_t bx[2] = {32, BK};
+    rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
+  }
+  if (rc) return rc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.NC + bn - 1) / bn;
+  if (kind == 2) {
+    const long long tiles = (long long)p.tiles_m * p.tiles_n * p.taps;
+    int splits = (int)((2ll * sm_count() + tiles - 1) / tiles);
+    if (splits > p.kblocks / 4) splits = p.kblocks / 4;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    const int per = (p.kblocks + splits - 1) / splits;
+    p.splits = (p.kblocks + per - 1) / per;
+    if (p.splits > 1) {
+      const size_t need = (size_t)p.splits * O * KH * KW * C * sizeof(float);
+      p.ws = get_ws(need);
+      if (!p.ws) return TSB_ERR_OOM;
+    }
+  }
+  if (kind == 0) rc = launch_bn<0>(bn, tm, p, st);
+  else if (kind == 1) rc = launch_bn<1>(bn, tm, p, st);
+  else rc = launch_bn<2>(bn, tm, p, st);
+  if (rc) return rc;
+  if (p.splits > 1) {
+    const long long per_split = (long long)O * KH * KW * C;
+    int blocks = (int)((per_split + 255) / 256);
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    conv_splitk_reduce<<<blocks, 256, 0, st>>>(p.ws, p.out, p.splits, per_split, 0);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+  }
+  const int late = tsb_host::peek_status();
+  return late ? TSB_ERR_TIMEOUT | (late << 8) : TSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,253 @@
+// One-hot, embedding lookup (+ scatter-add gradient), counter-based dropout,
+// CSR sparse x dense products, and the multi-tensor optimizer step.
+//
+// Roles in the reference: src/ops/OneHot.cu, EmbeddingLookup.cu (which ignores
+// the ids; this one honours them), CudnnDropout.cu, CuSparseCsrmv.cu /
+// CuSparseCsrmm.cu (legacy cuSPARSE) and Optimizers.cu:3-149 (one launch per
+// parameter tensor there, one launch per 64 tensors here).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TSB_OK 0
+#define TSB_ERR_ARG 1
+#define TSB_ERR_LAUNCH 3
+
+namespace {
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+int ew_grid(long long work) {
+  long long blocks = (work + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+int done() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+__global__ void one_hot_kernel(const float* __restrict__ idx, float* __restrict__ y, long long n, long long k) {
+  const long long total = n * k;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / k, c = i - r * k;
+    y[i] = ((long long)idx[r] == c) ? 1.f : 0.f;
+  }
+}
+
+__global__ void embedding_kernel(const float* __restrict__ table, const float* __restrict__ idx,
+                                 float* __restrict__ y, long long n, long long vocab, long long dim) {
+  const long long total = n * dim;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / dim, c = i - r * dim;
+    long long id = (long long)idx[r];
+    y[i] = (id >= 0 && id < vocab) ? table[id * dim + c] : 0.f;
+  }
+}
+
+__global__ void embedding_grad_kernel(const float* __restrict__ g, const float* __restrict__ idx,
+                                      float* __restrict__ dtable, long long n, long long vocab, long long dim) {
+  const long long total = n * dim;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / dim, c = i - r * dim;
+    long long id = (long long)idx[r];
+    if (id >= 0 && id < vocab) atomicAdd(dtable + id * dim + c, g[i]);
+  }
+}
+
+// splitmix64 of (seed, element index): the keep decision is a pure function of both
+__device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long i) {
+  unsigned long long x = i + seed * 0x9E3779B97F4A7C15ull;
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27; x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return (float)(x >> 40) * (1.0f / 16777216.0f);
+}
+
+__global__ void dropout_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float keep,
+                               unsigned long long seed) {
+  const float inv = 1.f / keep;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    y[i] = uniform01(seed, (unsigned long long)i) < keep ? x[i] * inv : 0.f;
+}
+
+// out[r, :] = sum_j vals[j] * dense[col[j], :]   (one warp per sparse row)
+__global__ void csrmm_kernel(const float* __restrict__ vals, const float* __restrict__ rowptr,
+                             const float* __restrict__ colidx, long long nrow, const float* __restrict__ dense,
+                             float* __restrict__ out, long long ncols) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (row >= nrow) return;
+  const long long b = (long long)rowptr[row], e = (long long)rowptr[row + 1];
+  for (long long c = lane; c < ncols; c += 32) {
+    float acc = 0.f;
+    for (long long j = b; j < e; ++j) acc += vals[j] * dense[(long long)colidx[j] * ncols + c];
+    out[row * ncols + c] = acc;
+  }
+}
+// out[col[j], :] += vals[j] * dense[r, :]   (transposed sparse operand; out pre-zeroed)
+__global__ void csrmm_t_kernel(const float* __restrict__ vals, const float* __restrict__ rowptr,
+                               const float* __restrict__ colidx, long long nrow, const float* __restrict__ dense,
+                               float* __restrict__ out, long long ncols) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (row >= nrow) return;
+  const long long b = (long long)rowptr[row], e = (long long)rowptr[row + 1];
+  for (long long j = b; j < e; ++j) {
+    const float v = vals[j];
+    const long long oc = (long long)colidx[j];
+    for (long long c = lane; c < ncols; c += 32) atomicAdd(out + oc * ncols + c, v * dense[row * ncols + c]);
+  }
+}
+__global__ void zero_kernel(float* __restrict__ y, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    y[i] = 0.f;
+}
+
+// ------------------------------------------------------------------ optimizers
+constexpr int MAX_TENSORS = 64;
+struct OptArgs {
+  float* p[MAX_TENSORS];
+  const float* g[MAX_TENSORS];
+  float* s1[MAX_TENSORS];
+  float* s2[MAX_TENSORS];
+  long long n[MAX_TENSORS];
+  float h[8];
+  int count;
+};
+
+template <int KIND>
+__device__ __forceinline__ void opt_one(float& p, float g, float& s1, float& s2, const float* h) {
+  if (KIND == 0) {                // sgd: h = {lr}
+    p -= h[0] * g;
+  } else if (KIND == 1) {         // momentum: h = {lr, momentum}
+    s1 = h[1] * s1 - h[0] * g;
+    p += s1;
+  } else if (KIND == 2) {         // nesterov
+    const float lr_g = -h[0] * g;
+    s1 = h[1] * (s1 + lr_g);
+    p += s1 + lr_g;
+  } else if (KIND == 3) {         // adagrad: h = {lr, eps}
+    s1 += g * g;
+    p -= h[0] * g / (sqrtf(s1) + h[1]);
+  } else {                        // adam: h = {lr, b1, b2, b1^t, b2^t, eps}
+    s1 = h[1] * s1 + (1.f - h[1]) * g;
+    s2 = h[2] * s2 + (1.f - h[2]) * g * g;
+    const float mc = s1 / (1.f - h[3]);
+    const float vc = s2 / (1.f - h[4]);
+    p -= h[0] * mc / (sqrtf(vc) + h[5]);
+  }
+}
+
+template <int KIND>
+__global__ void opt_kernel(const OptArgs a) {
+  const int t = blockIdx.y;
+  if (t >= a.count) return;
+  float* p = a.p[t];
+  const float* g = a.g[t];
+  float* s1 = a.s1[t];
+  float* s2 = a.s2[t];
+  const long long n = a.n[t];
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float pv = p[i], v1 = (KIND >= 1) ? s1[i] : 0.f, v2 = (KIND == 4) ? s2[i] : 0.f;
+    opt_one<KIND>(pv, g[i], v1, v2, a.h);
+    p[i] = pv;
+    if (KIND >= 1) s1[i] = v1;
+    if (KIND == 4) s2[i] = v2;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tsb_one_hot(const float* idx, float* y, long long n, long long k, void* stream) {
+  if (n <= 0 || k <= 0) return TSB_ERR_ARG;
+  one_hot_kernel<<<ew_grid(n * k), 256, 0, static_cast<cudaStream_t>(stream)>>>(idx, y, n, k);
+  return done();
+}
+
+int tsb_embedding(const float* table, const float* idx, float* y, long long n, long long vocab, long long dim,
+                  void* stream) {
+  if (n <= 0) return TSB_OK;
+  embedding_kernel<<<ew_grid(n * dim), 256, 0, static_cast<cudaStream_t>(stream)>>>(table, idx, y, n, vocab, dim);
+  return done();
+}
+
+int tsb_embedding_grad(const float* g, const float* idx, float* dtable, long long n, long long vocab,
+                       long long dim, void* stream) {
+  if (n <= 0) return TSB_OK;
+  embedding_grad_kernel<<<ew_grid(n * dim), 256, 0, static_cast<cudaStream_t>(stream)>>>(g, idx, dtable, n, vocab,
+                                                                                         dim);
+  return done();
+}
+
+int tsb_dropout(const float* x, float* y, long long n, float keep, unsigned long long seed, void* stream) {
+  if (n <= 0) return TSB_OK;
+  if (!(keep > 0.f)) return TSB_ERR_ARG;
+  dropout_kernel<<<ew_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n, keep, seed);
+  return done();
+}
+
+int tsb_csrmm(const float* vals, const float* rowptr, const float* colidx, long long nrow, long long ncol,
+              const float* dense, float* out, int trans_a, long long ncols_dense, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (nrow <= 0 || ncols_dense <= 0) return TSB_ERR_ARG;
+  const long long threads = nrow * 32;
+  if (!trans_a) {
+    csrmm_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(vals, rowptr, colidx, nrow, dense, out,
+                                                                     ncols_dense);
+  } else {
+    zero_kernel<<<ew_grid(ncol * ncols_dense), 256, 0, st>>>(out, ncol * ncols_dense);
+    csrmm_t_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(vals, rowptr, colidx, nrow, dense, out,
+                                                                       ncols_dense);
+  }
+  return done();
+}
+
+int tsb_optimizer_step(int kind, int count, float** params, const float** grads, float** slot1, float** slot2,
+                       const long long* sizes, const float* hyper, void* stream) {
+  if (count <= 0 || count > MAX_TENSORS || kind < 0 || kind > 4) return TSB_ERR_ARG;
+  OptArgs a;
+  a.count = count;
+  long long biggest = 0;
+  for (int i = 0; i < count; ++i) {
+    a.p[i] = params[i]; a.g[i] = grads[i];
+    a.s1[i] = slot1 ? slot1[i] : nullptr;
+    a.s2[i] = slot2 ? slot2[i] : nullptr;
+    a.n[i] = sizes[i];
+    if (sizes[i] > biggest) biggest = sizes[i];
+    if (kind >= 1 && !a.s1[i]) return TSB_ERR_ARG;
+    if (kind == 4 && !a.s2[i]) return TSB_ERR_ARG;
+  }
+  for (int i = 0; i < 8; ++i) a.h[i] = hyper[i];
+  long long bx = (biggest + 255) / 256;
+  if (bx > 2 * sm_count()) bx = 2 * sm_count();
+  if (bx < 1) bx = 1;
+  dim3 grid((unsigned)bx, count);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (kind) {
+    case 0: opt_kernel<0><<<grid, 256, 0, st>>>(a); break;
+    case 1: opt_kernel<1><<<grid, 256, 0, st>>>(a); break;
+    case 2: opt_kernel<2><<<grid, 256, 0, st>>>(a); break;
+    case 3: opt_kernel<3><<<grid, 256, 0, st>>>(a); break;
+    default: opt_kernel<4><<<grid, 256, 0, st>>>(a); break;
+  }
+  return done();
+}
+
+}  // extern "C"

@@ -1,0 +1,335 @@
+// Batch normalisation (training mode, channels-last [rows, C] view with a row
+// stride) and layer normalisation, fp32.
+//
+// Batch norm forward = column statistics (two-stage, fixed order, combined in
+// double) + one fused normalise/scale/shift(/ReLU) pass; backward = one column
+// reduction (sum dy, sum dy*xhat) + one fused dx pass.  All passes read/write
+// 16 bytes per thread and are HBM-bound by construction: x is read twice and y
+// written once in forward; dy and x are read twice and dx written once in
+// backward.  The statistics / apply stages are also exported separately so a
+// micro-tensor executor can accumulate statistics over batch pieces.
+//
+// Role in the reference: cudnnBatchNormalizationForwardTraining / Backward
+// (src/ops/CudnnBn.cu:12-382).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TSB_OK 0
+#define TSB_ERR_ARG 1
+#define TSB_ERR_UNSUPPORTED 2
+#define TSB_ERR_LAUNCH 3
+#define TSB_ERR_OOM 5
+
+namespace {
+
+constexpr int MAX_CHUNKS = 128;
+constexpr long long SCRATCH_FLOATS = 2ll * MAX_CHUNKS * 8192;   // two partial planes, up to 8192 channels
+
+float* g_scratch[64] = {nullptr};
+float* scratch() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!g_scratch[dev]) {
+    if (cudaMalloc(reinterpret_cast<void**>(&g_scratch[dev]), SCRATCH_FLOATS * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+  }
+  return g_scratch[dev];
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+int done() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+// Column partial sums over a chunk of rows.  Block = 32 (float4 columns) x 8 (row lanes).
+// MODE 0: p0 = sum x, p1 = sum x^2.   MODE 1: p0 = sum dy, p1 = sum dy * (x - mean) * invstd.
+template <int MODE>
+__global__ void col_partial(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mean,
+                            const float* __restrict__ invstd, float* __restrict__ part, long long rows, int C,
+                            long long lda, long long ldb, int chunks) {
+  __shared__ float4 s0[8][32], s1[8][32];
+  const int c4 = blockIdx.x * 32 + threadIdx.x;   // float4 column
+  const int c = c4 * 4;
+  const int ch = blockIdx.y;
+  const long long per = (rows + chunks - 1) / chunks;
+  const long long r0 = ch * per, r1 = min(rows, r0 + per);
+  float4 acc0 = make_float4(0, 0, 0, 0), acc1 = make_float4(0, 0, 0, 0);
+  if (c < C) {
+    float4 mu = make_float4(0, 0, 0, 0), is = make_float4(1, 1, 1, 1);
+    if (MODE == 1) {
+      mu = *reinterpret_cast<const float4*>(mean + c);
+      is = *reinterpret_cast<const float4*>(invstd + c);
+    }
+    for (long long r = r0 + threadIdx.y; r < r1; r += 8) {
+      const float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
+      if (MODE == 0) {
+        acc0.x += v.x; acc0.y += v.y; acc0.z += v.z; acc0.w += v.w;
+        acc1.x += v.x * v.x; acc1.y += v.y * v.y; acc1.z += v.z * v.z; acc1.w += v.w * v.w;
+      } else {
+        const float4 x = *reinterpret_cast<const float4*>(b + r * ldb + c);
+        acc0.x += v.x; acc0.y += v.y; acc0.z += v.z; acc0.w += v.w;
+        acc1.x += v.x * (x.x - mu.x) * is.x; acc1.y += v.y * (x.y - mu.y) * is.y;
+        acc1.z += v.z * (x.z - mu.z) * is.z; acc1.w += v.w * (x.w - mu.w) * is.w;
+      }
+    }
+  }
+  s0[threadIdx.y][threadIdx.x] = acc0;
+  s1[threadIdx.y][threadIdx.x] = acc1;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float4 t0 = s0[0][threadIdx.x], t1 = s1[0][threadIdx.x];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) {
+      const float4 u0 = s0[j][threadIdx.x], u1 = s1[j][threadIdx.x];
+      t0.x += u0.x; t0.y += u0.y; t0.z += u0.z; t0.w += u0.w;
+      t1.x += u1.x; t1.y += u1.y; t1.z += u1.z; t1.w += u1.w;
+    }
+    float* p0 = part + (long long)ch * C + c;
+    float* p1 = part + (long long)MAX_CHUNKS * 8192 + (long long)ch * C + c;   // second plane
+    *reinterpret_cast<float4*>(p0) = t0;
+    *reinterpret_cast<float4*>(p1) = t1;
+  }
+}
+
+// Forward finalise: mean / invstd from the partial sums (+ running statistics).
+// accumulate != 0 adds the partials into sum/sumsq planes instead (micro-batches).
+__global__ void bn_finalize_fwd(const float* __restrict__ part, int chunks, int C, double count, float eps,
+                                float momentum, float* __restrict__ mean, float* __restrict__ invstd,
+                                float* __restrict__ run_mean, float* __restrict__ run_var) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, ss = 0.0;
+  for (int ch = 0; ch < chunks; ++ch) {
+    s += part[(long long)ch * C + c];
+    ss += part[(long long)MAX_CHUNKS * 8192 + (long long)ch * C + c];
+  }
+  const double m = s / count;
+  double var = ss / count - m * m;
+  if (var < 0.0) var = 0.0;
+  mean[c] = (float)m;
+  invstd[c] = (float)(1.0 / sqrt(var + (double)eps));
+  if (run_mean) {
+    run_mean[c] = momentum * run_mean[c] + (1.f - momentum) * (float)m;
+    run_var[c] = momentum * run_var[c] + (1.f - momentum) * (float)var;
+  }
+}
+
+__global__ void bn_finalize_bwd(const float* __restrict__ part, int chunks, int C, float* __restrict__ dscale,
+                                float* __restrict__ dbias) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, ss = 0.0;
+  for (int ch = 0; ch < chunks; ++ch) {
+    s += part[(long long)ch * C + c];
+    ss += part[(long long)MAX_CHUNKS * 8192 + (long long)ch * C + c];
+  }
+  dbias[c] = (float)s;
+  dscale[c] = (float)ss;
+}
+
+__global__ void bn_apply_fwd(const float* __restrict__ x, const float* __restrict__ scale,
+                             const float* __restrict__ bias, const float* __restrict__ mean,
+                             const float* __restrict__ invstd, float* __restrict__ y, long long rows, int C,
+                             long long ldx, long long ldy, int relu) {
+  const int C4 = C >> 2;
+  const long long total = rows * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / C4;
+    const int c = (int)(i - r * C4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
+    const float4 mu = *reinterpret_cast<const float4*>(mean + c);
+    const float4 is = *reinterpret_cast<const float4*>(invstd + c);
+    const float4 g = *reinterpret_cast<const float4*>(scale + c);
+    const float4 b = *reinterpret_cast<const float4*>(bias + c);
+    float4 o;
+    o.x = (v.x - mu.x) * is.x * g.x + b.x; o.y = (v.y - mu.y) * is.y * g.y + b.y;
+    o.z = (v.z - mu.z) * is.z * g.z + b.z; o.w = (v.w - mu.w) * is.w * g.w + b.w;
+    if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+    *reinterpret_cast<float4*>(y + r * ldy + c) = o;
+  }
+}
+
+__global__ void bn_apply_bwd(const float* __restrict__ dy, const float* __restrict__ x,
+                             const float* __restrict__ scale, const float* __restrict__ mean,
+                             const float* __restrict__ invstd, const float* __restrict__ dscale,
+                             const float* __restrict__ dbias, float* __restrict__ dx, long long rows, int C,
+                             long long lddy, long long ldx, long long lddx, float inv_count) {
+  const int C4 = C >> 2;
+  const long long total = rows * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / C4;
+    const int c = (int)(i - r * C4) * 4;
+    const float4 g = *reinterpret_cast<const float4*>(dy + r * lddy + c);
+    const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
+    const float4 mu = *reinterpret_cast<const float4*>(mean + c);
+    const float4 is = *reinterpret_cast<const float4*>(invstd + c);
+    const float4 sc = *reinterpret_cast<const float4*>(scale + c);
+    const float4 ds = *reinterpret_cast<const float4*>(dscale + c);
+    const float4 db = *reinterpret_cast<const float4*>(dbias + c);
+    float4 o;
+    o.x = sc.x * is.x * (g.x - db.x * inv_count - (v.x - mu.x) * is.x * ds.x * inv_count);
+    o.y = sc.y * is.y * (g.y - db.y * inv_count - (v.y - mu.y) * is.y * ds.y * inv_count);
+    o.z = sc.z * is.z * (g.z - db.z * inv_count - (v.z - mu.z) * is.z * ds.z * inv_count);
+    o.w = sc.w * is.w * (g.w - db.w * inv_count - (v.w - mu.w) * is.w * ds.w * inv_count);
+    *reinterpret_cast<float4*>(dx + r * lddx + c) = o;
+  }
+}
+
+int pick_chunks(long long rows, int C) {
+  const int col_blocks = (C / 4 + 31) / 32;
+  long long want = (4ll * sm_count() + col_blocks - 1) / col_blocks;
+  if (want > MAX_CHUNKS) want = MAX_CHUNKS;
+  if (want > (rows + 63) / 64) want = (rows + 63) / 64;
+  return want < 1 ? 1 : (int)want;
+}
+
+int ew_grid(long long work) {
+  long long blocks = (work + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+
+// ------------------------------------------------------------------ layer norm (one warp per row)
+__global__ void ln_fwd(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ bias,
+                       float* __restrict__ y, float* __restrict__ mean, float* __restrict__ invstd, long long rows,
+                       int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const float* xr = x + row * D;
+  float s = 0.f, ss = 0.f;
+  for (int i = lane; i < D; i += 32) { const float v = xr[i]; s += v; ss += v * v; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { s += __shfl_xor_sync(0xffffffffu, s, o); ss += __shfl_xor_sync(0xffffffffu, ss, o); }
+  const float m = s / D;
+  const float var = fmaxf(ss / D - m * m, 0.f);
+  const float is = rsqrtf(var + eps);
+  if (lane == 0) { mean[row] = m; invstd[row] = is; }
+  float* yr = y + row * D;
+  for (int i = lane; i < D; i += 32) yr[i] = (xr[i] - m) * is * scale[i] + bias[i];
+}
+
+__global__ void ln_bwd_dx(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ scale,
+                          const float* __restrict__ mean, const float* __restrict__ invstd, float* __restrict__ dx,
+                          long long rows, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const float m = mean[row], is = invstd[row];
+  const float* xr = x + row * D;
+  const float* gr = dy + row * D;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float gs = gr[i] * scale[i];
+    s1 += gs;
+    s2 += gs * (xr[i] - m) * is;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
+  s1 /= D; s2 /= D;
+  float* dr = dx + row * D;
+  for (int i = lane; i < D; i += 32) dr[i] = is * (gr[i] * scale[i] - s1 - (xr[i] - m) * is * s2);
+}
+
+// column sums for dscale / dbias of layer norm: partials over row chunks
+__global__ void ln_bwd_params_partial(const float* __restrict__ dy, const float* __restrict__ x,
+                                      const float* __restrict__ mean, const float* __restrict__ invstd,
+                                      float* __restrict__ part, long long rows, int D, int chunks) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int ch = blockIdx.y;
+  if (c >= D) return;
+  const long long per = (rows + chunks - 1) / chunks;
+  const long long r0 = ch * per, r1 = min(rows, r0 + per);
+  float a = 0.f, b = 0.f;
+  for (long long r = r0; r < r1; ++r) {
+    const float g = dy[r * D + c];
+    a += g;
+    b += g * (x[r * D + c] - mean[r]) * invstd[r];
+  }
+  part[(long long)ch * D + c] = a;
+  part[(long long)MAX_CHUNKS * 8192 + (long long)ch * D + c] = b;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tsb_bn_forward(const float* x, const float* scale, const float* bias, float* y, float* save_mean,
+                   float* save_invstd, float* run_mean, float* run_var, long long rows, long long C,
+                   long long ldx, long long ldy, float momentum, float eps, int relu, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (ldy % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
+  float* part = scratch();
+  if (!part) return TSB_ERR_OOM;
+  const int chunks = pick_chunks(rows, (int)C);
+  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
+  col_partial<0><<<grid, blk, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, chunks);
+  bn_finalize_fwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, (double)rows, eps, momentum,
+                                                               save_mean, save_invstd, run_mean, run_var);
+  bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
+                                                        ldx, ldy, relu);
+  return done();
+}
+
+int tsb_bn_backward(const float* dy, const float* x, const float* scale, const float* save_mean,
+                    const float* save_invstd, float* dx, float* dscale, float* dbias, long long rows, long long C,
+                    long long ldx, long long lddy, long long lddx, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
+  float* part = scratch();
+  if (!part) return TSB_ERR_OOM;
+  const int chunks = pick_chunks(rows, (int)C);
+  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
+  col_partial<1><<<grid, blk, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, chunks);
+  bn_finalize_bwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, dscale, dbias);
+  bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
+                                                        rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows);
+  return done();
+}
+
+int tsb_layer_norm(const float* x, const float* scale, const float* bias, float* y, float* mean, float* invstd,
+                   long long rows, long long D, float eps, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || D <= 0) return TSB_ERR_ARG;
+  const long long threads = rows * 32;
+  ln_fwd<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(x, scale, bias, y, mean, invstd, rows, (int)D, eps);
+  return done();
+}
+
+int tsb_layer_norm_grad(const float* dy, const float* x, const float* scale, const float* mean,
+                        const float* invstd, float* dx, float* dscale, float* dbias, long long rows, long long D,
+                        void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || D <= 0) return TSB_ERR_ARG;
+  if (D > 8192) return TSB_ERR_UNSUPPORTED;
+  float* part = scratch();
+  if (!part) return TSB_ERR_OOM;
+  const long long threads = rows * 32;
+  ln_bwd_dx<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(dy, x, scale, mean, invstd, dx, rows, (int)D);
+  int chunks = (int)((rows + 31) / 32);
+  if (chunks > MAX_CHUNKS) chunks = MAX_CHUNKS;
+  dim3 grid((unsigned)((D + 127) / 128), chunks);
+  ln_bwd_params_partial<<<grid, 128, 0, st>>>(dy, x, mean, invstd, part, rows, (int)D, chunks);
+  bn_finalize_bwd<<<(unsigned)((D + 127) / 128), 128, 0, st>>>(part, chunks, (int)D, dscale, dbias);
+  return done();
+}
+
+}  // extern "C"

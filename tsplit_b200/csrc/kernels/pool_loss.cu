@@ -1,0 +1,302 @@
+// Pooling (channels-last), softmax, softmax cross-entropy (+ gradient).
+//
+// Pooling: one thread per (pixel, 4-channel vector), 16-byte accesses.  The max
+// gradient is a gather over the windows containing an input pixel and gives the
+// gradient to the FIRST maximum of each window (row-major), so it is
+// deterministic, needs no atomics and no zero-fill pass.
+// Softmax family: one CTA per row with warp-shuffle reductions; the mean of the
+// row losses is a fixed-order second stage.
+//
+// Roles in the reference: cudnnPoolingForward/Backward (src/ops/CudnnMaxPool.cu,
+// CudnnAvgPool.cu) and the <<<1,1024>>> kernels of src/ops/Softmax.cu:3-22 and
+// src/ops/SoftmaxCrossEntropy.cu:5-104.
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#define TSB_OK 0
+#define TSB_ERR_ARG 1
+#define TSB_ERR_UNSUPPORTED 2
+#define TSB_ERR_LAUNCH 3
+#define TSB_ERR_OOM 5
+
+namespace {
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+int ew_grid(long long work) {
+  long long blocks = (work + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+int done() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+struct PoolP {
+  int n, c, h, w, oh, ow, kh, kw, pad, stride;
+  long long xsn, xsh, xsw, ysn, ysh, ysw;
+};
+
+template <int KIND>
+__global__ void pool_fwd(const float* __restrict__ x, float* __restrict__ y, const PoolP p) {
+  const int C4 = p.c >> 2;
+  const long long total = (long long)p.n * p.oh * p.ow * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C4) * 4;
+    long long r = i / C4;
+    const int ox = (int)(r % p.ow); r /= p.ow;
+    const int oy = (int)(r % p.oh);
+    const int n = (int)(r / p.oh);
+    float4 acc = KIND == 0 ? make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX) : make_float4(0, 0, 0, 0);
+    for (int a = 0; a < p.kh; ++a) {
+      const int iy = oy * p.stride - p.pad + a;
+      if ((unsigned)iy >= (unsigned)p.h) continue;
+      for (int b = 0; b < p.kw; ++b) {
+        const int ix = ox * p.stride - p.pad + b;
+        if ((unsigned)ix >= (unsigned)p.w) continue;
+        const float4 v = *reinterpret_cast<const float4*>(x + n * p.xsn + iy * p.xsh + ix * p.xsw + c);
+        if (KIND == 0) {
+          acc.x = fmaxf(acc.x, v.x); acc.y = fmaxf(acc.y, v.y); acc.z = fmaxf(acc.z, v.z); acc.w = fmaxf(acc.w, v.w);
+        } else {
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      }
+    }
+    if (KIND == 1) {
+      const float s = 1.f / (float)(p.kh * p.kw);
+      acc.x *= s; acc.y *= s; acc.z *= s; acc.w *= s;
+    }
+    *reinterpret_cast<float4*>(y + n * p.ysn + oy * p.ysh + ox * p.ysw + c) = acc;
+  }
+}
+
+__device__ __forceinline__ int ceil_div_pos(int a, int b) { return a <= 0 ? 0 : (a + b - 1) / b; }
+
+template <int KIND>
+__global__ void pool_bwd(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ dy,
+                         float* __restrict__ dx, const PoolP p) {
+  const int C4 = p.c >> 2;
+  const long long total = (long long)p.n * p.h * p.w * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C4) * 4;
+    long long r = i / C4;
+    const int ix = (int)(r % p.w); r /= p.w;
+    const int iy = (int)(r % p.h);
+    const int n = (int)(r / p.h);
+    // output windows that contain (iy, ix)
+    const int oy0 = ceil_div_pos(iy + p.pad - p.kh + 1, p.stride), oy1 = min(p.oh - 1, (iy + p.pad) / p.stride);
+    const int ox0 = ceil_div_pos(ix + p.pad - p.kw + 1, p.stride), ox1 = min(p.ow - 1, (ix + p.pad) / p.stride);
+    float4 acc = make_float4(0, 0, 0, 0);
+    float4 me = make_float4(0, 0, 0, 0);
+    if (KIND == 0) me = *reinterpret_cast<const float4*>(x + n * p.xsn + iy * p.xsh + ix * p.xsw + c);
+    for (int oy = oy0; oy <= oy1; ++oy) {
+      for (int ox = ox0; ox <= ox1; ++ox) {
+        const float4 g = *reinterpret_cast<const float4*>(dy + n * p.ysn + oy * p.ysh + ox * p.ysw + c);
+        if (KIND == 1) {
+          acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+          continue;
+        }
+        const float4 m = *reinterpret_cast<const float4*>(y + n * p.ysn + oy * p.ysh + ox * p.ysw + c);
+        // am I the first maximum of this window?  (scan the elements that precede me)
+        bool fx = me.x == m.x, fy = me.y == m.y, fz = me.z == m.z, fw = me.w == m.w;
+        if (fx | fy | fz | fw) {
+          const int my_a = iy - (oy * p.stride - p.pad), my_b = ix - (ox * p.stride - p.pad);
+          for (int a = 0; a <= my_a; ++a) {
+            const int yy = oy * p.stride - p.pad + a;
+            if ((unsigned)yy >= (unsigned)p.h) continue;
+            const int bend = (a == my_a) ? my_b : p.kw;
+            for (int b = 0; b < bend; ++b) {
+              const int xx = ox * p.stride - p.pad + b;
+              if ((unsigned)xx >= (unsigned)p.w) continue;
+              const float4 v = *reinterpret_cast<const float4*>(x + n * p.xsn + yy * p.xsh + xx * p.xsw + c);
+              fx = fx && v.x != m.x; fy = fy && v.y != m.y; fz = fz && v.z != m.z; fw = fw && v.w != m.w;
+            }
+          }
+          if (fx) acc.x += g.x;
+          if (fy) acc.y += g.y;
+          if (fz) acc.z += g.z;
+          if (fw) acc.w += g.w;
+        }
+      }
+    }
+    if (KIND == 1) {
+      const float s = 1.f / (float)(p.kh * p.kw);
+      acc.x *= s; acc.y *= s; acc.z *= s; acc.w *= s;
+    }
+    *reinterpret_cast<float4*>(dx + n * p.xsn + iy * p.xsh + ix * p.xsw + c) = acc;
+  }
+}
+
+// ------------------------------------------------------------------ softmax family
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float r = sh[0];
+  for (int i = 1; i < (blockDim.x >> 5); ++i) r = fmaxf(r, sh[i]);
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float r = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) r += sh[i];
+  __syncthreads();
+  return r;
+}
+
+__global__ void softmax_rows(const float* __restrict__ x, float* __restrict__ y, long long rows, long long cols) {
+  __shared__ float sh[8];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    float m = -FLT_MAX;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, xr[i]);
+    m = block_max(m, sh);
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) s += __expf(xr[i] - m);
+    s = block_sum(s, sh);
+    const float inv = 1.f / s;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) y[row * cols + i] = __expf(xr[i] - m) * inv;
+  }
+}
+
+__global__ void ce_rows(const float* __restrict__ x, const float* __restrict__ lab, float* __restrict__ row_loss,
+                        long long rows, long long cols) {
+  __shared__ float sh[8];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    const float* lr = lab + row * cols;
+    float m = -FLT_MAX;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, xr[i]);
+    m = block_max(m, sh);
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) s += expf(xr[i] - m);
+    s = block_sum(s, sh);
+    const float lse = m + logf(s);
+    float l = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) l -= lr[i] * (xr[i] - lse);
+    l = block_sum(l, sh);
+    if (threadIdx.x == 0) row_loss[row] = l;
+  }
+}
+
+__global__ void mean_rows(const float* __restrict__ row_loss, float* __restrict__ out, long long rows) {
+  __shared__ float sh[32];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < rows; i += blockDim.x) s += row_loss[i];
+  s = block_sum(s, sh);
+  if (threadIdx.x == 0) out[0] = s / (float)rows;
+}
+
+__global__ void ce_grad_rows(const float* __restrict__ x, const float* __restrict__ lab, const float* __restrict__ g,
+                             float* __restrict__ dx, long long rows, long long cols) {
+  __shared__ float sh[8];
+  const float scale = g[0] / (float)rows;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    float m = -FLT_MAX;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, xr[i]);
+    m = block_max(m, sh);
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) s += expf(xr[i] - m);
+    s = block_sum(s, sh);
+    const float inv = 1.f / s;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x)
+      dx[row * cols + i] = (expf(xr[i] - m) * inv - lab[row * cols + i]) * scale;
+  }
+}
+
+float* g_rows[64] = {nullptr};
+long long g_rows_cap[64] = {0};
+float* row_scratch(long long rows) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (g_rows_cap[dev] < rows) {
+    if (g_rows[dev]) cudaFree(g_rows[dev]);
+    long long want = rows < 65536 ? 65536 : rows;
+    if (cudaMalloc(reinterpret_cast<void**>(&g_rows[dev]), want * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      g_rows[dev] = nullptr; g_rows_cap[dev] = 0;
+      return nullptr;
+    }
+    g_rows_cap[dev] = want;
+  }
+  return g_rows[dev];
+}
+
+}  // namespace
+
+extern "C" {
+
+int tsb_pool_fwd(int kind, const float* x, float* y, int n, int c, int h, int w, int oh, int ow, int kh, int kw,
+                 int pad, int stride, long long xsn, long long xsh, long long xsw, long long ysn, long long ysh,
+                 long long ysw, void* stream) {
+  if ((c % 4) || (xsw % 4) || (ysw % 4)) return TSB_ERR_UNSUPPORTED;
+  PoolP p{n, c, h, w, oh, ow, kh, kw, pad, stride, xsn, xsh, xsw, ysn, ysh, ysw};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = ew_grid((long long)n * oh * ow * (c / 4));
+  if (kind == 0) pool_fwd<0><<<grid, 256, 0, st>>>(x, y, p);
+  else pool_fwd<1><<<grid, 256, 0, st>>>(x, y, p);
+  return done();
+}
+
+int tsb_pool_bwd(int kind, const float* x, const float* y, const float* dy, float* dx, int n, int c, int h, int w,
+                 int oh, int ow, int kh, int kw, int pad, int stride, long long xsn, long long xsh, long long xsw,
+                 long long ysn, long long ysh, long long ysw, void* stream) {
+  if ((c % 4) || (xsw % 4) || (ysw % 4)) return TSB_ERR_UNSUPPORTED;
+  if (kind == 0 && (!x || !y)) return TSB_ERR_ARG;
+  PoolP p{n, c, h, w, oh, ow, kh, kw, pad, stride, xsn, xsh, xsw, ysn, ysh, ysw};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = ew_grid((long long)n * h * w * (c / 4));
+  if (kind == 0) pool_bwd<0><<<grid, 256, 0, st>>>(x, y, dy, dx, p);
+  else pool_bwd<1><<<grid, 256, 0, st>>>(x, y, dy, dx, p);
+  return done();
+}
+
+int tsb_softmax(const float* x, float* y, long long rows, long long cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
+  const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  softmax_rows<<<grid, cols >= 1024 ? 256 : 128, 0, static_cast<cudaStream_t>(stream)>>>(x, y, rows, cols);
+  return done();
+}
+
+int tsb_softmax_ce(const float* x, const float* labels, float* loss, long long rows, long long cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
+  float* rl = row_scratch(rows);
+  if (!rl) return TSB_ERR_OOM;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  ce_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(x, labels, rl, rows, cols);
+  mean_rows<<<1, 1024, 0, st>>>(rl, loss, rows);
+  return done();
+}
+
+int tsb_softmax_ce_grad(const float* x, const float* labels, const float* g, float* dx, long long rows,
+                        long long cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
+  const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  ce_grad_rows<<<grid, cols >= 1024 ? 256 : 128, 0, static_cast<cudaStream_t>(stream)>>>(x, labels, g, dx, rows,
+                                                                                         cols);
+  return done();
+}
+
+}  // extern "C"

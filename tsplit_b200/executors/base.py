@@ -35,7 +35,7 @@ class FeedStager(object):
         self.ctx = ctx
         self.slots = {}
 
-    def put(self, node, value, stream):
+    def put(self, node, value, stream, channels_last=None):
         if isinstance(value, ndarray.NDArray):
             if value.ctx == self.ctx or value.ctx.device_type == self.ctx.device_type:
                 return value
@@ -45,12 +45,13 @@ class FeedStager(object):
             return ndarray.array(value, self.ctx, use_pool=False)
         shape = tuple(value.shape)
         slot = self.slots.get(node)
-        if slot is None or slot[0] != shape:
+        if slot is None or slot[0] != shape or slot[2].is_channels_last() != bool(
+                len(shape) == 4 and (channels_last is None or channels_last)):
             n = int(np.prod(shape)) if shape else 1
             pinned = torch.empty(max(n, 1), dtype=torch.float32, pin_memory=True)
-            dev = ndarray.empty(shape, self.ctx, use_pool=False)
+            dev = ndarray.empty(shape, self.ctx, use_pool=False, channels_last=channels_last)
             raw = None
-            if len(shape) == 4:     # device array is channels-last: land row-major bytes first
+            if dev.is_channels_last() and not dev.t.is_contiguous():   # land row-major bytes first
                 raw = torch.empty(max(n, 1), dtype=torch.float32, device=self.ctx.torch_device)
             slot = (shape, pinned, dev, raw)
             self.slots[node] = slot
@@ -112,6 +113,8 @@ class Executor(object):
                 shp = tuple(int(s) for s in shp)
             self.node_to_shape_map[node] = shp
             node.inferred_shape = shp
+        from .. import layout
+        self.node_layout = layout.resolve(self.topo_order, self.node_to_shape_map)
 
     def memory_plan(self, feed_shapes):
         """One array per computed node, kept until the feed shapes change."""
@@ -119,21 +122,34 @@ class Executor(object):
         for node, shape in self.node_to_shape_map.items():
             if node in feed_shapes or isinstance(node.op, PlaceholderOp) or shape is None:
                 continue
-            self.node_to_arr_map[node] = ndarray.empty(shape, ctx=self.ctx)
+            self.node_to_arr_map[node] = ndarray.empty(shape, ctx=self.ctx,
+                                                       channels_last=self.node_layout.get(node))
 
     # -- feeds ---------------------------------------------------------------
     def _ingest(self, feed_dict):
         vals = {}
         for node, value in feed_dict.items():
-            if self.use_numpy:
+            if isinstance(value, ndarray.ND_Sparse_Array):
+                vals[node] = value
+            elif self.use_numpy:
                 if isinstance(value, ndarray.NDArray):
                     value = value.asnumpy()
                 assert isinstance(value, np.ndarray), "feed_dict value type not supported"
                 vals[node] = value
             else:
                 assert isinstance(value, (np.ndarray, ndarray.NDArray)), "feed_dict value type not supported"
-                vals[node] = self.stager.put(node, value, self.stream)
+                vals[node] = self.stager.put(node, value, self.stream, self._feed_layout(node, value))
         return vals
+
+    def _feed_layout(self, node, value):
+        """Channels-last only for 4-D feeds consumed by an image operator."""
+        if len(getattr(value, "shape", ())) != 4:
+            return False
+        cache = self.__dict__.setdefault("_feed_layout_cache", {})
+        if node not in cache:
+            from .. import layout
+            cache[node] = any(node in u.inputs and u.op.name in layout.IMAGE_OPS for u in self.topo_order)
+        return cache[node]
 
     def _placeholder_value(self, node):
         v = node.tensor_value
@@ -141,7 +157,7 @@ class Executor(object):
         if self.use_numpy:
             return v.asnumpy() if isinstance(v, ndarray.NDArray) else v
         if isinstance(v, np.ndarray):
-            v = ndarray.array(v, self.ctx, use_pool=False)
+            v = ndarray.array(v, self.ctx, use_pool=False, channels_last=self._feed_layout(node, v))
             node.tensor_value = v
         return v
 
@@ -243,7 +259,7 @@ class MultiStreamExecutor(Executor):
             return Executor._ingest(self, feed_dict)
         vals = {}
         for node, value in feed_dict.items():
-            vals[node] = self.stager.put(node, value, self.h2d_stream)
+            vals[node] = self.stager.put(node, value, self.h2d_stream, self._feed_layout(node, value))
             ev = self.feed_events.get(node)
             if ev is None:
                 ev = self.feed_events[node] = Event(self.ctx)

@@ -314,13 +314,13 @@ class _stream_scope(object):
             self.ctxmgr.__exit__(*a)
 
 
-def empty(shape, ctx=cpu(0), pinned=False, use_pool=True):
+def empty(shape, ctx=cpu(0), pinned=False, use_pool=True, channels_last=None):
     """Uninitialised fp32 array on ``ctx``; goes through the context's pool when
     one is installed and raises :class:`OutOfHBMBudget` when it does not fit."""
     shape = tuple(int(s) for s in shape)
     n = _numel(shape)
     pool = _POOLS.get(ctx) if use_pool else None
-    cl = is_cuda_ctx(ctx)
+    cl = is_cuda_ctx(ctx) if channels_last is None else (bool(channels_last) and is_cuda_ctx(ctx))
     if pool is not None:
         blk, flat = pool.alloc(n * 4)
         return NDArray(_make_view(flat[:n], shape, cl), ctx, block=blk, pool=pool)
@@ -332,10 +332,11 @@ def empty(shape, ctx=cpu(0), pinned=False, use_pool=True):
     return NDArray(_make_view(flat[:n], shape, cl), ctx)
 
 
-def array(arr, ctx=cpu(0), use_pool=True):
-    """Create an array from a NumPy source (converted to fp32)."""
+def array(arr, ctx=cpu(0), use_pool=True, channels_last=None):
+    """Create an array from a NumPy source (converted to fp32).  4-D arrays on a
+    CUDA context are stored channels-last unless ``channels_last=False``."""
     arr = np.asarray(arr, dtype=np.float32)
-    ret = empty(arr.shape, ctx, use_pool=use_pool)
+    ret = empty(arr.shape, ctx, use_pool=use_pool, channels_last=channels_last)
     ret._sync_copyfrom(arr)
     return ret
 

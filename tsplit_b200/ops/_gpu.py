@@ -296,12 +296,67 @@ def conv2d(kind, x, w, y, ph, pw, stride, stream):
     n, c, h, wd = x.shape
     o, _, kh, kw = w.shape
     _, _, oh, ow = y.shape
+    # inputs that arrive row-major (e.g. straight out of a transpose) are re-laid-out once
+    if kind != 1 and not x.is_channels_last():
+        x = _as_channels_last(x, "cl_x", stream)
+    if kind != 2 and not w.is_channels_last():
+        w = _as_channels_last(w, "cl_w", stream)
+    if kind != 0 and not y.is_channels_last():
+        y = _as_channels_last(y, "cl_y", stream)
     assert x.is_channels_last() and w.is_channels_last() and y.is_channels_last(), \
         "conv kernels need dense channels-last operands"
+    if c % 4:
+        return _conv2d_padded_channels(kind, x, w, y, ph, pw, stride, stream)
     rc = lib().tsb_conv2d(c_int(kind), _p(x), _p(w), _p(y), c_int(n), c_int(c), c_int(h), c_int(wd),
                           c_int(o), c_int(kh), c_int(kw), c_int(oh), c_int(ow), c_int(ph), c_int(pw),
                           c_int(stride), _s(stream))
     _check(rc, "conv2d kind %d" % kind)
+
+
+_PAD_CACHE = {}
+
+
+def _as_channels_last(arr, tag, stream):
+    from .. import ndarray
+    key = (tag, arr.shape, arr.ctx.device_id)
+    buf = _PAD_CACHE.get(key)
+    if buf is None:
+        buf = _PAD_CACHE[key] = ndarray.empty(arr.shape, arr.ctx, use_pool=False, channels_last=True)
+    copy(arr, buf, stream)
+    return buf
+
+
+def _padded(arr, c4, tag):
+    """Cached channels-last scratch with the channel count rounded up to a
+    multiple of 4 (the gather moves 16-byte pieces).  The padding lanes are
+    zeroed once at creation; every use rewrites only the real channels."""
+    from .. import ndarray
+    shape = (arr.shape[0], c4, arr.shape[2], arr.shape[3])
+    key = (tag, shape, arr.ctx.device_id)
+    buf = _PAD_CACHE.get(key)
+    if buf is None:
+        buf = ndarray.empty(shape, arr.ctx, use_pool=False)
+        buf.t.zero_()
+        _PAD_CACHE[key] = buf
+    return buf
+
+
+def _conv2d_padded_channels(kind, x, w, y, ph, pw, stride, stream):
+    """Input-channel count not a multiple of 4 (the RGB stem): run the kernel on
+    zero-padded copies of x and w; only the real channels are copied back."""
+    c = x.shape[1]
+    c4 = (c + 3) // 4 * 4
+    x4, w4 = _padded(x, c4, "x"), _padded(w, c4, "w")
+    xs, ws = x4.strides, w4.strides
+    if kind in (0, 2):
+        copy_raw(x.ptr, x.strides, x4.ptr, xs, x.shape, stream)
+    if kind in (0, 1):
+        copy_raw(w.ptr, w.strides, w4.ptr, ws, w.shape, stream)
+    conv2d(kind, x4, w4, y, ph, pw, stride, stream)
+    if kind == 1:
+        copy_raw(x4.ptr, xs, x.ptr, x.strides, x.shape, stream)
+    elif kind == 2:
+        copy_raw(w4.ptr, ws, w.ptr, w.strides, w.shape, stream)
 
 
 def csrmm(vals, rowptr, colidx, nrow, ncol, dense, out, trans_a, ncols_dense, stream):

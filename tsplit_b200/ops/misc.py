@@ -190,8 +190,8 @@ def philox_like_mask(shape, keep_prob, seed):
     ``csrc/kernels/misc.cu``)."""
     n = int(np.prod(shape))
     i = np.arange(n, dtype=np.uint64)
-    x = (i + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15)) & np.uint64(0xFFFFFFFFFFFFFFFF)
     with np.errstate(over="ignore"):
+        x = i + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15)
         x ^= x >> np.uint64(30)
         x *= np.uint64(0xBF58476D1CE4E5B9)
         x ^= x >> np.uint64(27)
@@ -206,9 +206,9 @@ class DropoutOp(Op):
     (node seed, element index), so forward, recompute and backward agree."""
     name = "Dropout"
 
-    def __call__(self, x, keep_prob):
+    def __call__(self, x, keep_prob, seed=None):
         node = Op.__call__(self, x, keep_prob=float(keep_prob))
-        node.attrs["seed"] = 0x5EED0000 + node.id
+        node.attrs["seed"] = (0x5EED0000 + node.id) if seed is None else int(seed)
         return node
 
     def np_compute(self, node, iv):
@@ -246,8 +246,8 @@ class DropoutGradientOp(Op):
 _drop, _dropg = DropoutOp(), DropoutGradientOp()
 
 
-def dropout_op(node_in, keep_prob):
-    return _drop(node_in, keep_prob)
+def dropout_op(node_in, keep_prob, seed=None):
+    return _drop(node_in, keep_prob, seed)
 
 
 def dropout_gradient_op(node_in, keep_prob, forward_node):
