@@ -1,0 +1,447 @@
+"""Plan-driven memory-saving execution engine.
+
+One engine runs every memory policy of the reference — vDNN
+(``gpu_ops/vdnnExecutor.py:21-340``), SuperNeurons
+(``superNeuronsExecutor.py:23-616``), Chen-style recompute
+(``recomputeExecutor.py:21-384``), Capuchin (``capuchinExecutor.py:67-364``)
+and the TSplit micro-tensor plan.  A policy only *classifies* forward tensors
+(keep / swap / drop) and places prefetch triggers; the engine owns liveness,
+allocation under the HBM budget, the three streams and the event discipline:
+
+* compute, H2D and D2H streams; a consumer waits on the producer's or the
+  swap-in's event, never on the host (the reference synchronises both streams
+  after every node, ``vdnnExecutor.py:273-274``);
+* device memory read by an in-flight D2H copy is released only when that copy's
+  event has completed (event-deferred free), so blocks can be re-used without a
+  stream sync;
+* running out of budget raises ``OutOfHBMBudget`` instead of asserting.
+
+It runs unchanged on the simulated device (host storage, NumPy kernels), which
+is how the policies are tested without a GPU.
+"""
+from __future__ import annotations
+
+import time
+from collections import OrderedDict
+
+import numpy as np
+
+from .. import ndarray
+from ..ndarray import OutOfHBMBudget
+from ..stream import create_stream_handle, Event
+from ..ops.misc import PlaceholderOp
+from .base import Executor
+
+KEEP, SWAP, DROP = 0, 1, 2
+
+
+def nbytes(shape):
+    n = 4
+    for s in shape:
+        n *= int(s)
+    return n
+
+
+class MemoryExecutor(Executor):
+    """Base of all memory-saving executors."""
+
+    policy_name = "keep"
+    lazy_evict = False           # swap-class tensors stay resident until memory is needed (LRU)
+    recompute_mode = "speed"     # "speed": keep rematerialised intermediates; "memory": free them at once
+
+    def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None, trace=None):
+        Executor.__init__(self, eval_node_list, ctx=ctx, policy=policy)
+        assert ctx is not None and ndarray.is_gpu_ctx(ctx), "memory executors need a (simulated) GPU context"
+        if streams is None:
+            streams = [self.stream, create_stream_handle(ctx), create_stream_handle(ctx)]
+        self.streams = streams
+        self.stream, self.h2d_stream, self.d2h_stream = streams[0], streams[1], streams[2]
+        self.budget_bytes = budget_bytes
+        self.trace = trace
+        self.index = {n: i for i, n in enumerate(self.topo_order)}
+        self.stats = {}
+        self._planned_for = None
+
+    # ------------------------------------------------------------------ analysis
+    def analyze(self):
+        """Liveness facts per tensor, in schedule positions."""
+        order = self.topo_order
+        self.users = {n: [] for n in order}
+        for n in order:
+            for i in set(n.inputs):
+                self.users[i].append(n)
+        self.is_fwd = {n: n.phase == "forward" for n in order}
+        first_bwd = next((self.index[n] for n in order if n.phase != "forward"), len(order))
+        self.first_bwd_index = first_bwd
+        self.last_use, self.last_fwd_use, self.first_bwd_use = {}, {}, {}
+        evals = set(self.eval_node_list)
+        for n in order:
+            idx = [self.index[u] for u in self.users[n]]
+            self.last_use[n] = max(idx) if idx else self.index[n]
+            f = [j for j in idx if j < first_bwd]
+            b = [j for j in idx if j >= first_bwd]
+            self.last_fwd_use[n] = max(f) if f else self.index[n]
+            self.first_bwd_use[n] = min(b) if b else None
+            if n in evals:
+                self.last_use[n] = len(order)          # never released
+        self.managed = [n for n in order if self._manageable(n, evals)]
+
+    def _manageable(self, n, evals):
+        """Forward activations that are needed again in backward."""
+        return (self.is_fwd[n] and not isinstance(n.op, PlaceholderOp) and n not in self.feed_shapes
+                and self.first_bwd_use.get(n) is not None and n not in evals
+                and self.node_to_shape_map[n] is not None)
+
+    def classify(self):
+        """Policy hook: fill ``self.cls`` (node -> KEEP/SWAP/DROP) and
+        ``self.prefetch_at`` (schedule index -> tensors to swap in early)."""
+        self.cls = {}
+        self.prefetch_at = {}
+
+    def _extend_sources(self):
+        """A dropped tensor is rebuilt from its inputs, so those must stay
+        recoverable until the dropped tensor's last use."""
+        for n in reversed(self.topo_order):
+            if self.cls.get(n, KEEP) == DROP:
+                for u in n.inputs:
+                    if self.last_use[u] < self.last_use[n]:
+                        self.last_use[u] = self.last_use[n]
+
+    def plan(self):
+        self.analyze()
+        self.classify()
+        self._extend_sources()
+        self.release_at = {}
+        for n in self.topo_order:
+            self.release_at.setdefault(self.last_use[n], []).append(n)
+        self.fwd_release_at = {}
+        for n, c in self.cls.items():
+            if c != KEEP:
+                self.fwd_release_at.setdefault(self.last_fwd_use[n], []).append(n)
+
+    # ------------------------------------------------------------------ memory state
+    def _reset_state(self):
+        self.arr = {}                 # node -> device NDArray (resident)
+        self.host = {}                # node -> pinned host NDArray holding a valid copy
+        self.pending = []             # (event, NDArray) device arrays waiting for their D2H copy
+        self.swapin_event = {}        # node -> event of an in-flight H2D copy
+        self.lru = OrderedDict()      # lazy-evict cache: node -> True (MRU last)
+        self.locked = set()
+        self.stats = dict(swap_out_bytes=0, swap_in_bytes=0, recomputed_nodes=0, evictions=0,
+                          peak_bytes=0, prefetch_hits=0, on_demand_swapins=0)
+
+    def _reap(self, block=False):
+        """Release device arrays whose D2H copy has completed."""
+        keep = []
+        for ev, a in self.pending:
+            if block:
+                ev.sync()
+            if block or ev.query():
+                a._release()
+            else:
+                keep.append((ev, a))
+        self.pending = keep
+
+    def _evict_one(self):
+        """LRU eviction for lazy-evict policies: drop the least recently used
+        unlocked cache entry whose host copy is complete."""
+        for n in list(self.lru.keys()):
+            if n in self.locked or n not in self.arr:
+                continue
+            a = self.arr[n]
+            a.gpu2cpu_event.sync()
+            del self.arr[n]
+            del self.lru[n]
+            a._release()
+            self.stats["evictions"] += 1
+            return True
+        return False
+
+    def _alloc(self, node):
+        shape = self.node_to_shape_map[node]
+        cl = self.node_layout.get(node)
+        self._reap(False)
+        while True:
+            try:
+                a = ndarray.empty(shape, self.ctx, channels_last=cl)
+                break
+            except OutOfHBMBudget:
+                if self.pending:
+                    self._reap(True)
+                    continue
+                if self._evict_one():
+                    continue
+                if self._emergency_free(node):
+                    continue
+                raise
+        pool = ndarray.get_pool(self.ctx)
+        if pool is not None:
+            used = pool.stats()["used"]
+            if used > self.stats["peak_bytes"]:
+                self.stats["peak_bytes"] = used
+        return a
+
+    def _emergency_free(self, node):
+        return False
+
+    def _host_buffer(self, node):
+        h = self.host_bufs.get(node)
+        if h is None:
+            h = self.host_bufs[node] = ndarray.empty(self.node_to_shape_map[node], ndarray.cpu(0),
+                                                     pinned=self.on_device)
+        return h
+
+    def _raw_copy(self, dst, src, stream):
+        """Byte copy of a dense array between device and pinned host (same element order)."""
+        if self.on_device:
+            import torch
+            with torch.cuda.stream(stream.torch_stream):
+                # both sides are dense with the same logical shape; physical order may differ
+                # (channels-last on device, row-major on host), so copy through flat storage views
+                flat_dev = src.t if src.is_cuda else dst.t
+                n = flat_dev.numel()
+                dev_flat = flat_dev.as_strided((n,), (1,))
+                host = dst.t if src.is_cuda else src.t
+                host_flat = host.reshape(-1)
+                if src.is_cuda:
+                    host_flat.copy_(dev_flat, non_blocking=True)
+                else:
+                    dev_flat.copy_(host_flat, non_blocking=True)
+        else:
+            dst.t.reshape(-1)[...] = src.t.reshape(-1)
+
+    def _swap_out(self, node):
+        a = self.arr[node]
+        h = self._host_buffer(node)
+        ev = Event(self.ctx)
+        ev.record(self.stream)                       # data is complete at this point of compute
+        self.d2h_stream.wait_event(ev)
+        self._raw_copy(h, a, self.d2h_stream)
+        a.gpu2cpu_event.record(self.d2h_stream)
+        self.host[node] = h
+        self.stats["swap_out_bytes"] += a.nbytes
+        self._log("swap_out", node)
+
+    def _swap_in(self, node, prefetch=False):
+        if node in self.arr or node in self.swapin_event:
+            return
+        a = self._alloc(node)
+        h = self.host[node]
+        ev = Event(self.ctx)
+        ev.record(self.stream)                       # the block's previous owner is done here
+        self.h2d_stream.wait_event(ev)
+        self._raw_copy(a, h, self.h2d_stream)
+        a.cpu2gpu_event.record(self.h2d_stream)
+        self.arr[node] = a
+        self.swapin_event[node] = a.cpu2gpu_event
+        self.stats["swap_in_bytes"] += a.nbytes
+        self.stats["prefetch_hits" if prefetch else "on_demand_swapins"] += 1
+        self._log("swap_in", node)
+
+    def _release(self, node, final=False):
+        a = self.arr.pop(node, None)
+        self.lru.pop(node, None)
+        self.swapin_event.pop(node, None)
+        if a is None:
+            return
+        if node in self.host and a.gpu2cpu_event.recorded and not a.gpu2cpu_event.query():
+            self.pending.append((a.gpu2cpu_event, a))     # D2H still reading it
+        else:
+            a._release()
+        if final:
+            self.host.pop(node, None)
+
+    # ------------------------------------------------------------------ execution helpers
+    def _value(self, node):
+        return self.arr[node]
+
+    def _launch(self, node, out):
+        ins = [self.arr[i] for i in node.inputs]
+        for i in node.inputs:
+            ev = self.swapin_event.pop(i, None)
+            if ev is not None:
+                self.stream.wait_event(ev)
+        t0 = time.perf_counter() if self.trace is not None else 0
+        if self.on_device:
+            node.op.compute(node, ins, out, False, self.stream)
+        else:
+            node.op.compute(node, [a.numpy_view() if isinstance(a, ndarray.NDArray) else a for a in ins],
+                            out.numpy_view() if out is not None else None, True, self.stream)
+        if self.trace is not None:
+            self.trace.append(("op", node.desc, node.op.name, t0, time.perf_counter()))
+
+    def _log(self, kind, node):
+        if self.trace is not None:
+            self.trace.append((kind, node.desc, node.op.name, time.perf_counter(), time.perf_counter()))
+
+    def _ensure(self, node, temps):
+        """Make ``node`` resident: cache hit, swap-in, or recompute from its inputs."""
+        if node in self.arr:
+            if node in self.lru:
+                self.lru.move_to_end(node)
+            return
+        if node in self.host:
+            self._swap_in(node)
+            return
+        assert node.inputs, "tensor %s was released and cannot be rebuilt" % node.desc
+        for i in node.inputs:
+            self._ensure(i, temps)
+            self.locked.add(i)
+        out = self._alloc(node)
+        self.arr[node] = out
+        self._launch(node, out)
+        for i in node.inputs:
+            self.locked.discard(i)
+        self.stats["recomputed_nodes"] += 1
+        temps.append(node)
+        self._log("recompute", node)
+
+    # ------------------------------------------------------------------ run
+    def memory_plan(self, feed_shapes):
+        self.node_to_arr_map = {}
+        self.host_bufs = {}
+        self.plan()
+
+    def run(self, feed_dict, convert_to_numpy_ret_vals=False):
+        node_to_val = self._ingest(feed_dict)
+        feed_shapes = {n: tuple(v.shape) for n, v in node_to_val.items()}
+        if feed_shapes != self.feed_shapes:
+            self.feed_shapes = feed_shapes
+            self.infer_shape(feed_shapes)
+            self.memory_plan(feed_shapes)
+        self._reset_state()
+        for n, v in node_to_val.items():
+            self.arr[n] = v
+        self._execute()
+        self.stream.sync()
+        self._reap(True)
+        outs = [self.arr.get(n) for n in self.eval_node_list]
+        if convert_to_numpy_ret_vals:
+            outs = [o.asnumpy() if isinstance(o, ndarray.NDArray) else o for o in outs]
+        # drop everything that is not a result, a feed or a parameter
+        for n in list(self.arr.keys()):
+            if n not in self.eval_node_list and not isinstance(n.op, PlaceholderOp) and n not in node_to_val:
+                self._release(n, final=True)
+        self._reap(True)
+        return outs
+
+    def _execute(self):
+        order = self.topo_order
+        for idx, node in enumerate(order):
+            if node in self.arr:
+                continue
+            if isinstance(node.op, PlaceholderOp):
+                self.arr[node] = self._placeholder_value(node)
+                continue
+            for t in self.prefetch_at.get(idx, ()):
+                if t in self.host and t not in self.arr:
+                    try:
+                        self._swap_in(t, prefetch=True)
+                    except OutOfHBMBudget:
+                        pass                       # no room yet: it will be fetched on demand
+            temps = []
+            for i in node.inputs:
+                self._ensure(i, temps)
+                self.locked.add(i)
+            shape = self.node_to_shape_map[node]
+            out = self._alloc(node) if shape is not None else None
+            if out is not None:
+                self.arr[node] = out
+            self._launch(node, out)
+            for i in node.inputs:
+                self.locked.discard(i)
+            self._after_node(idx, node, temps)
+
+    def _after_node(self, idx, node, temps):
+        # forward: offload / drop policy-managed tensors at their last forward use
+        for t in self.fwd_release_at.get(idx, ()):
+            if t not in self.arr:
+                continue
+            c = self.cls[t]
+            if c == SWAP:
+                if t not in self.host:
+                    self._swap_out(t)
+                if self.lazy_evict:
+                    self.lru[t] = True
+                    self.lru.move_to_end(t)
+                else:
+                    self._release(t)
+            elif c == DROP:
+                self._release(t)
+        # rematerialised intermediates
+        for t in temps:
+            if t in self.arr and t not in node.inputs:
+                if self.recompute_mode == "memory" or self.last_use[t] <= idx:
+                    self._release(t)
+        if self.recompute_mode == "memory" and idx >= self.first_bwd_index:
+            for t in node.inputs:
+                if self.cls.get(t, KEEP) == DROP and self.last_use[t] > idx and t in self.arr:
+                    self._release(t)
+        # final releases
+        for t in self.release_at.get(idx, ()):
+            if t in self.arr and not isinstance(t.op, PlaceholderOp) and t not in self.feed_shapes:
+                self._release(t, final=True)
+        if node not in self.users or (not self.users[node] and node not in self.eval_node_list):
+            if node in self.arr:
+                self._release(node, final=True)
+
+    # ------------------------------------------------------------------ cost model
+    TF32_FLOP_PER_MS = 3.0e11       # sustained tensor-core rate assumed by the static model
+    HBM_BYTES_PER_MS = 5.0e9
+    LAUNCH_MS = 0.004
+
+    def profile_ops(self):
+        """Per-node time in ms.  Static roofline estimate (the reference's
+        ``Op.profile(is_static=True)`` role, ``gpu_ops/Conv2d.py:80-90``); a
+        measured table can be supplied through ``self.measured_op_ms``."""
+        measured = getattr(self, "measured_op_ms", None)
+        est = {}
+        for n in self.topo_order:
+            if isinstance(n.op, PlaceholderOp) or n in self.feed_shapes:
+                continue
+            if measured and n in measured:
+                est[n] = measured[n]
+                continue
+            out = self.node_to_shape_map.get(n)
+            ins = [self.node_to_shape_map.get(i) for i in n.inputs]
+            try:
+                fl = float(n.op.flops(n, ins, out))
+            except Exception:
+                fl = 0.0
+            by = sum(nbytes(s) for s in ins if s is not None) + (nbytes(out) if out is not None else 0)
+            est[n] = max(fl / self.TF32_FLOP_PER_MS, by / self.HBM_BYTES_PER_MS) + self.LAUNCH_MS
+        return est
+
+    def measure_ops(self, feed_dict, repeats=2):
+        """Event-timed per-node device time (ms) from a keep-everything run; the
+        role of the reference's ``Op.profile(is_static=False)``."""
+        assert self.on_device, "measured profiling needs a CUDA context"
+        import torch
+        base = Executor(self.eval_node_list, ctx=self.ctx)
+        base.run(feed_dict)
+        vals = dict(base._last_vals)
+        table = {}
+        for n in base.topo_order:
+            if isinstance(n.op, PlaceholderOp) or n in feed_dict or n.op.name == "Optimizer":
+                continue
+            ins = [vals[i] for i in n.inputs]
+            out = base.node_to_arr_map.get(n)
+            best = None
+            for _ in range(repeats):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(base.stream.torch_stream)
+                n.op.compute(n, ins, out, False, base.stream)
+                b.record(base.stream.torch_stream)
+                b.synchronize()
+                ms = a.elapsed_time(b)
+                best = ms if best is None else min(best, ms)
+            table[n] = best
+        self.measured_op_ms = table
+        return table
+
+    def tensor_bytes(self, node):
+        shp = self.node_to_shape_map.get(node)
+        return nbytes(shp) if shp is not None else 0
+
+    def show_tensor_in_gpu(self):
+        return [(n.desc, self.tensor_bytes(n)) for n in self.arr]

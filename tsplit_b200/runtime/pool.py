@@ -1,0 +1,107 @@
+"""Capped activation pool: one arena tensor + the native offset allocator.
+
+``MemoryPool(ctx, capacity_bytes)`` reserves the whole budget up front (device
+memory on a CUDA context, host memory on the simulated device) and serves
+``ndarray.empty`` through ``ndarray.set_pool(ctx, pool)``.  Running out raises
+:class:`tsplit_b200.ndarray.OutOfHBMBudget`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int64, c_void_p
+
+import torch
+
+from .. import _base
+from .. import ndarray
+
+_ALIGN = 256
+
+
+def _lib():
+    lib = _base.runtime()
+    if not getattr(lib, "_pool_typed", False):
+        lib.tsb_pool_create.restype = c_void_p
+        lib.tsb_pool_create.argtypes = [c_int64, c_int64]
+        lib.tsb_pool_destroy.argtypes = [c_void_p]
+        lib.tsb_pool_alloc.argtypes = [c_void_p, c_int64, ctypes.POINTER(c_int64)]
+        lib.tsb_pool_free.argtypes = [c_void_p, c_int64]
+        lib.tsb_pool_try.argtypes = [c_void_p, c_int64]
+        lib.tsb_pool_stats.argtypes = [c_void_p, ctypes.POINTER(c_int64)]
+        lib.tsb_pool_reset_peak.argtypes = [c_void_p]
+        lib.tsb_pool_block_size.restype = c_int64
+        lib.tsb_pool_block_size.argtypes = [c_void_p, c_int64]
+        lib._pool_typed = True
+    return lib
+
+
+class MemoryPool(object):
+    def __init__(self, ctx, capacity_bytes):
+        self.ctx = ctx
+        self.capacity = int(capacity_bytes) // _ALIGN * _ALIGN
+        n_floats = self.capacity // 4
+        dev = ctx.torch_device if ctx.device_type == 2 else torch.device("cpu")
+        self.arena = torch.empty(n_floats, dtype=torch.float32, device=dev)
+        self.lib = _lib()
+        self.handle = self.lib.tsb_pool_create(self.capacity, _ALIGN)
+        assert self.handle, "pool creation failed"
+
+    def __del__(self):
+        try:
+            if self.handle:
+                self.lib.tsb_pool_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+    # -- allocator interface used by ndarray.empty --------------------------------
+    def alloc(self, nbytes):
+        off = c_int64()
+        rc = self.lib.tsb_pool_alloc(self.handle, int(nbytes), ctypes.byref(off))
+        if rc == 5:
+            st = self.stats()
+            raise ndarray.OutOfHBMBudget(
+                "GPU available memory is not enough! need %.1f MB, free %.1f MB (largest block %.1f MB) "
+                "of a %.1f MB budget" % (nbytes / 2**20, st["free"] / 2**20, st["largest_free"] / 2**20,
+                                         st["capacity"] / 2**20))
+        assert rc == 0, "pool alloc error %d" % rc
+        o = off.value // 4
+        n = max((int(nbytes) + 3) // 4, 1)
+        return off.value, self.arena[o:o + n]
+
+    def free(self, block):
+        if self.handle:
+            rc = self.lib.tsb_pool_free(self.handle, int(block))
+            assert rc == 0, "pool free of unknown block %r" % (block,)
+
+    def try_alloc(self, nbytes):
+        return bool(self.lib.tsb_pool_try(self.handle, int(nbytes)))
+
+    def stats(self):
+        out = (c_int64 * 7)()
+        self.lib.tsb_pool_stats(self.handle, out)
+        keys = ("capacity", "used", "free", "largest_free", "peak", "allocs", "fails")
+        return dict(zip(keys, [int(v) for v in out]))
+
+    def reset_peak(self):
+        self.lib.tsb_pool_reset_peak(self.handle)
+
+    def address_of(self, block):
+        return self.arena.data_ptr() + int(block)
+
+
+class use_pool(object):
+    """``with use_pool(ctx, capacity_bytes) as pool:`` — install a capped pool for
+    the duration of the block."""
+
+    def __init__(self, ctx, capacity_bytes):
+        self.ctx = ctx
+        self.pool = MemoryPool(ctx, capacity_bytes)
+
+    def __enter__(self):
+        self.prev = ndarray.get_pool(self.ctx)
+        ndarray.set_pool(self.ctx, self.pool)
+        return self.pool
+
+    def __exit__(self, *a):
+        ndarray.set_pool(self.ctx, self.prev)
