@@ -104,3 +104,77 @@ def test_optimizer_inside_memory_executor_trains():
     x, y = m.synthetic_batch(8, seed=1)
     losses = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0][0]) for _ in range(6)]
     assert losses[-1] < losses[0]
+
+
+def test_tsplit_plan_fits_budget_and_matches_base():
+    batch = 8
+    ref = reference_run(small_cnn, batch, steps=1)
+    peak_keep = base_peak_bytes(small_cnn, batch)
+    ctx = ndarray.simgpu(0)
+    m = small_cnn()
+    grads = ad.gradients(m.loss, m.variables)
+    x, y = m.synthetic_batch(batch, seed=1)
+    cap = int(peak_keep * 0.7)
+    with use_pool(ctx, cap) as pool:
+        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, host_link_gbs=0.05, max_split=4)
+        outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
+        plan = ex.plan_result
+        assert plan.fits and plan.predicted_peak_bytes <= cap
+        assert pool.stats()["peak"] <= cap
+        c = plan.counts()
+        assert c["swap"] + c["recompute"] > 0
+    for i, (o, r) in enumerate(zip(outs, ref)):
+        assert_close(o, r, rtol=1e-4, what="tsplit output %d" % i)
+
+
+def test_tsplit_micro_tensors_are_streamed():
+    batch = 8
+    ctx = ndarray.simgpu(0)
+    m = small_cnn()
+    grads = ad.gradients(m.loss, m.variables)
+    x, y = m.synthetic_batch(batch, seed=1)
+    peak_keep = base_peak_bytes(small_cnn, batch)
+    ref = reference_run(small_cnn, batch, steps=1)
+    with use_pool(ctx, int(peak_keep * 0.7)):
+        # a slow link makes every swapped tensor worth splitting
+        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, host_link_gbs=0.001, max_split=4)
+        ex.TF32_FLOP_PER_MS = 1e13      # make recompute look expensive so the plan prefers swapping
+        ex.HBM_BYTES_PER_MS = 1e3
+        outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
+    assert ex.stats["swap_out_bytes"] > 0
+    if ex.plan_result.counts()["split_tensors"]:
+        assert ex.stats["micro_transfers"] > 0
+    for i, (o, r) in enumerate(zip(outs, ref)):
+        assert_close(o, r, rtol=1e-4, what="tsplit output %d" % i)
+
+
+def test_simulator_and_planner_entry_points():
+    ctx = ndarray.simgpu(0)
+    m = small_cnn()
+    grads = ad.gradients(m.loss, m.variables)
+    x, y = m.synthetic_batch(8, seed=1)
+    peak_keep = base_peak_bytes(small_cnn, 8)
+    plan = ad.microopPlanner([m.loss] + grads, ctx=ctx, budget_bytes=int(peak_keep * 0.65)).run({m.X: x, m.y_: y})
+    assert plan.fits
+    sim = ad.microopOptimizer([m.loss] + grads, ctx=ctx, budget_bytes=int(peak_keep * 0.65)).run({m.X: x, m.y_: y})
+    assert sim["fits"] and sim["predicted_peak_bytes"] <= int(peak_keep * 0.65) and sim["predicted_ms"] > 0
+    loose = ad.microopOptimizer([m.loss] + grads, ctx=ctx, budget_bytes=1 << 40).run({m.X: x, m.y_: y})
+    assert loose["plan"].counts()["swap"] == 0 and loose["plan"].counts()["recompute"] == 0
+    assert loose["predicted_ms"] <= sim["predicted_ms"] + 1e-9
+
+
+def test_max_batch_search_finds_the_boundary():
+    ctx = ndarray.simgpu(0)
+    peak8 = base_peak_bytes(small_cnn, 8)
+
+    def build():
+        m = small_cnn()
+        build.m = m
+        return ad.MemoryExecutor([m.loss] + ad.gradients(m.loss, m.variables), ctx=ctx)
+
+    def feeds(b):
+        x, y = build.m.synthetic_batch(b, seed=1)
+        return {build.m.X: x, build.m.y_: y}
+    with use_pool(ctx, peak8 + 4096):
+        best = ad.max_batch_search(build, feeds, lo=1, hi=32)
+    assert 8 <= best < 16

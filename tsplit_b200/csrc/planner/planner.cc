@@ -1,0 +1,310 @@
+// TSplit planner core: timeline simulation of a training step under an HBM
+// budget and a greedy search over per-tensor decisions.
+//
+// The reference ships only the hooks of its planner (per-op Profiler{time,
+// input, output, workspace} structs, src/common/profiler.h:13-22, and swap-cost
+// constants, python/athena/profiler.py:8-14); the planner modules themselves
+// (microopPlanner / microopOptimizer) are absent.  This is a fresh design:
+//
+//   simulate():  walks the schedule with three clocks (compute, H2D, D2H).  Swap
+//     class tensors are copied out after their last forward use and freed when
+//     the copy ends; they come back at their prefetch trigger (or on demand,
+//     stalling compute).  Drop class tensors are freed at once and rebuilt from
+//     their inputs when needed (cost = producer time, recursively).  A tensor
+//     moved as k micro-tensors exposes only 1/k of its transfer on the critical
+//     path (the consumer starts on the first piece).  Tracks peak bytes and
+//     reports the first position where the budget is exceeded.
+//
+//   plan():  while the simulated peak exceeds the budget, look at the peak
+//     position, score every idle candidate there by memory saved per millisecond
+//     of added step time (swap vs. recompute vs. finer micro-tensor split) and
+//     apply the best; then place prefetch triggers by walking back from each
+//     first backward use until the transfer is hidden.
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <limits>
+#include <vector>
+
+namespace {
+
+enum { KEEP = 0, SWAP = 1, DROP = 2 };
+
+struct Graph {
+  int n;
+  const int64_t* out_bytes;
+  const double* time_ms;
+  const int* phase;
+  const int* managed;
+  const int* recomputable;
+  const int* splittable;
+  const int64_t* ws_bytes;
+  const int* in_ptr;
+  const int* in_idx;
+  const int* pinned;
+  int64_t budget;
+  double bw;   // bytes per ms, per direction
+  std::vector<int> last_use, last_fwd_use, first_bwd_use;
+  int first_bwd;
+};
+
+struct Result {
+  double time_ms = 0;
+  int64_t peak = 0;
+  int peak_pos = -1;
+  int first_over = -1;
+  double stall_ms = 0;
+  std::vector<int64_t> mem_at;
+};
+
+void liveness(Graph& g) {
+  g.last_use.assign(g.n, -1);
+  g.last_fwd_use.assign(g.n, -1);
+  g.first_bwd_use.assign(g.n, -1);
+  g.first_bwd = g.n;
+  for (int i = 0; i < g.n; ++i)
+    if (g.phase[i] != 0) { g.first_bwd = i; break; }
+  for (int i = 0; i < g.n; ++i) {
+    g.last_use[i] = std::max(g.last_use[i], i);
+    g.last_fwd_use[i] = std::max(g.last_fwd_use[i], i < g.first_bwd ? i : -1);
+    for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) {
+      const int u = g.in_idx[e];
+      g.last_use[u] = std::max(g.last_use[u], i);
+      if (i < g.first_bwd) g.last_fwd_use[u] = std::max(g.last_fwd_use[u], i);
+      else if (g.first_bwd_use[u] < 0) g.first_bwd_use[u] = i;
+    }
+  }
+  for (int i = 0; i < g.n; ++i)
+    if (g.pinned[i]) g.last_use[i] = g.n;
+}
+
+// dropped tensors are rebuilt from their inputs: keep those recoverable long enough
+void extend_sources(const Graph& g, const std::vector<int>& cls, std::vector<int>& last_use) {
+  last_use = g.last_use;
+  for (int i = g.n - 1; i >= 0; --i)
+    if (cls[i] == DROP)
+      for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) {
+        const int u = g.in_idx[e];
+        if (last_use[u] < last_use[i]) last_use[u] = last_use[i];
+      }
+}
+
+Result simulate(const Graph& g, const std::vector<int>& cls, const std::vector<int>& split,
+                const std::vector<int>& prefetch_at) {
+  Result r;
+  r.mem_at.assign(g.n, 0);
+  std::vector<int> last_use;
+  extend_sources(g, cls, last_use);
+  std::vector<char> resident(g.n, 0), on_host(g.n, 0);
+  std::vector<double> arrival(g.n, 0.0);
+  std::vector<std::vector<int>> fetch_at(g.n + 1), release_at(g.n + 1), fwd_release_at(g.n + 1);
+  for (int t = 0; t < g.n; ++t) {
+    if (cls[t] == SWAP && prefetch_at[t] >= 0 && prefetch_at[t] < g.n) fetch_at[prefetch_at[t]].push_back(t);
+    if (last_use[t] < g.n) release_at[last_use[t]].push_back(t);
+    if (cls[t] != KEEP && g.last_fwd_use[t] >= 0) fwd_release_at[g.last_fwd_use[t]].push_back(t);
+  }
+  struct Pending { double when; int64_t bytes; };
+  std::vector<Pending> pending;      // device bytes waiting for their D2H copy
+  double tc = 0, th2d = 0, td2h = 0;
+  int64_t mem = 0;
+  auto reap = [&](double now) {
+    for (size_t k = 0; k < pending.size();) {
+      if (pending[k].when <= now) { mem -= pending[k].bytes; pending[k] = pending.back(); pending.pop_back(); }
+      else ++k;
+    }
+  };
+  auto make_room = [&](int64_t need) {
+    reap(tc);
+    while (mem + need > g.budget && !pending.empty()) {      // wait for the earliest copy-out to finish
+      size_t best = 0;
+      for (size_t k = 1; k < pending.size(); ++k) if (pending[k].when < pending[best].when) best = k;
+      if (pending[best].when > tc) { r.stall_ms += pending[best].when - tc; tc = pending[best].when; }
+      reap(tc);
+    }
+  };
+  auto exposed = [&](int t) { return (double)g.out_bytes[t] / g.bw; };
+  // recursive rebuild cost / residency
+  std::vector<int> stack;
+  auto ensure = [&](int t, auto&& self) -> void {
+    if (resident[t]) { if (arrival[t] > tc) { r.stall_ms += arrival[t] - tc; tc = arrival[t]; } return; }
+    if (on_host[t]) {                                         // on-demand swap-in
+      make_room(g.out_bytes[t]);
+      const double start = std::max(th2d, tc);
+      const double full = exposed(t);
+      th2d = start + full;
+      const double first_piece = start + full / std::max(1, split[t]);
+      mem += g.out_bytes[t];
+      resident[t] = 1;
+      arrival[t] = th2d;
+      if (first_piece > tc) { r.stall_ms += first_piece - tc; tc = first_piece; }
+      return;
+    }
+    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) self(g.in_idx[e], self);
+    make_room(g.out_bytes[t] + g.ws_bytes[t]);
+    mem += g.out_bytes[t];
+    resident[t] = 1;
+    arrival[t] = 0;
+    tc += g.time_ms[t];
+    stack.push_back(t);
+  };
+  for (int i = 0; i < g.n; ++i) {
+    for (int t : fetch_at[i]) {
+      if (resident[t] || !on_host[t]) continue;
+      reap(tc);
+      // leave head-room for what the schedule allocates before the tensor is used
+      int64_t reserve = 0;
+      for (int j = i; j <= g.first_bwd_use[t] && j < g.n; ++j)
+        reserve = std::max(reserve, g.out_bytes[j] + g.ws_bytes[j]);
+      if (mem + g.out_bytes[t] + 2 * reserve > g.budget) continue;   // no room yet: fetched on demand later
+      const double start = std::max(th2d, tc);
+      th2d = start + exposed(t);
+      mem += g.out_bytes[t];
+      resident[t] = 1;
+      arrival[t] = start + exposed(t) / std::max(1, split[t]);   // consumer can start on the first piece
+    }
+    stack.clear();
+    for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) ensure(g.in_idx[e], ensure);
+    make_room(g.out_bytes[i] + g.ws_bytes[i]);
+    mem += g.out_bytes[i];
+    resident[i] = 1;
+    const int64_t with_ws = mem + g.ws_bytes[i];
+    r.mem_at[i] = with_ws;
+    if (with_ws > r.peak) { r.peak = with_ws; r.peak_pos = i; }
+    if (with_ws > g.budget && r.first_over < 0) r.first_over = i;
+    tc += g.time_ms[i] * (1.0 + 0.01 * (std::max(1, split[i]) - 1));
+    for (int t : fwd_release_at[i]) {
+      if (!resident[t]) continue;
+      if (cls[t] == SWAP) {
+        const double start = std::max(td2h, tc - g.time_ms[i] * (1.0 - 1.0 / std::max(1, split[t])));
+        td2h = start + exposed(t);
+        on_host[t] = 1;
+        resident[t] = 0;
+        pending.push_back({td2h, g.out_bytes[t]});
+      } else {
+        resident[t] = 0;
+        mem -= g.out_bytes[t];
+      }
+    }
+    for (int t : stack) {      // rebuilt intermediates that nobody needs later
+      bool is_input = false;
+      for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) is_input |= (g.in_idx[e] == t);
+      if (!is_input && resident[t] && last_use[t] <= i) { resident[t] = 0; mem -= g.out_bytes[t]; }
+    }
+    for (int t : release_at[i])
+      if (resident[t]) { resident[t] = 0; mem -= g.out_bytes[t]; on_host[t] = 0; }
+  }
+  r.time_ms = std::max(tc, std::max(th2d, td2h));
+  return r;
+}
+
+void place_prefetch(const Graph& g, const std::vector<int>& cls, std::vector<int>& prefetch_at) {
+  // cumulative compute time per position
+  std::vector<double> t0(g.n + 1, 0.0);
+  for (int i = 0; i < g.n; ++i) t0[i + 1] = t0[i] + g.time_ms[i];
+  // process in order of first backward use so transfers queue up realistically
+  std::vector<int> order;
+  for (int t = 0; t < g.n; ++t) if (cls[t] == SWAP && g.first_bwd_use[t] >= 0) order.push_back(t);
+  std::sort(order.begin(), order.end(), [&](int a, int b) { return g.first_bwd_use[a] < g.first_bwd_use[b]; });
+  double link_free = 0.0;
+  for (int t : order) {
+    const double need = (double)g.out_bytes[t] / g.bw;
+    const int use = g.first_bwd_use[t];
+    int trig = use;
+    while (trig > g.first_bwd && t0[use] - t0[trig] < need * 1.25) --trig;
+    const double start = std::max(link_free, t0[trig]);
+    link_free = start + need;
+    prefetch_at[t] = trig;
+  }
+}
+
+double rebuild_ms(const Graph& g, const std::vector<int>& cls, int t, int depth = 0) {
+  // producer time plus the time of dropped inputs that would have to be rebuilt first
+  double ms = g.time_ms[t];
+  if (depth > 64) return ms;
+  for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) {
+    const int u = g.in_idx[e];
+    if (cls[u] == DROP) ms += rebuild_ms(g, cls, u, depth + 1);
+  }
+  return ms;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Simulate a given plan.  out[0] = step ms, out[1] = peak bytes, out[2] = first position over budget (-1 = fits),
+// out[3] = stall ms, out[4] = peak position.  mem_at (may be null) receives bytes in use at every position.
+int tsb_plan_simulate(int n, const int64_t* out_bytes, const double* time_ms, const int* phase, const int* managed,
+                      const int* recomputable, const int* splittable, const int64_t* ws_bytes, const int* in_ptr,
+                      const int* in_idx, const int* pinned, int64_t budget, double bw_bytes_per_ms, const int* cls,
+                      const int* split, const int* prefetch_at, double* out, int64_t* mem_at) {
+  if (n <= 0 || !out) return 1;
+  Graph g{n, out_bytes, time_ms, phase, managed, recomputable, splittable, ws_bytes, in_ptr, in_idx, pinned, budget,
+          bw_bytes_per_ms, {}, {}, {}, 0};
+  liveness(g);
+  std::vector<int> c(cls, cls + n), s(split, split + n), p(prefetch_at, prefetch_at + n);
+  Result r = simulate(g, c, s, p);
+  out[0] = r.time_ms; out[1] = (double)r.peak; out[2] = r.first_over; out[3] = r.stall_ms; out[4] = r.peak_pos;
+  if (mem_at) std::memcpy(mem_at, r.mem_at.data(), sizeof(int64_t) * n);
+  return 0;
+}
+
+// Search a plan under `budget`.  Writes cls / split / prefetch_at (length n) and the same `out` summary as
+// tsb_plan_simulate for the chosen plan.  Returns 0 when the plan fits, 5 when no plan was found.
+int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, const int* phase, const int* managed,
+                    const int* recomputable, const int* splittable, const int64_t* ws_bytes, const int* in_ptr,
+                    const int* in_idx, const int* pinned, int64_t budget, double bw_bytes_per_ms, int max_split,
+                    int* cls_out, int* split_out, int* prefetch_out, double* out) {
+  if (n <= 0 || !out) return 1;
+  Graph g{n, out_bytes, time_ms, phase, managed, recomputable, splittable, ws_bytes, in_ptr, in_idx, pinned, budget,
+          bw_bytes_per_ms, {}, {}, {}, 0};
+  liveness(g);
+  std::vector<int> cls(n, KEEP), split(n, 1), prefetch(n, -1);
+  Result r = simulate(g, cls, split, prefetch);
+  int guard = 0;
+  while (r.first_over >= 0 && guard++ < 4 * n) {
+    const int pos = r.peak_pos >= 0 ? r.first_over : r.first_over;
+    // candidates: managed KEEP tensors that are alive but idle at `pos`
+    int best = -1, best_cls = KEEP;
+    double best_score = -1.0;
+    for (int t = 0; t < n; ++t) {
+      if (!g.managed[t] || cls[t] != KEEP || out_bytes[t] <= 0) continue;
+      if (!(t < pos && g.last_fwd_use[t] < pos && g.first_bwd_use[t] > pos)) continue;   // idle across pos
+      // swap: exposed cost = what the idle window cannot hide (split later shrinks it further)
+      double idle = 0.0;
+      for (int i = g.last_fwd_use[t] + 1; i < g.first_bwd_use[t]; ++i) idle += time_ms[i];
+      const double xfer = 2.0 * (double)out_bytes[t] / g.bw;
+      const double swap_cost = std::max(0.0, xfer - idle) + 0.02 * xfer;     // link is shared: small tax
+      double rec_cost = std::numeric_limits<double>::infinity();
+      if (g.recomputable[t]) {
+        int uses_bwd = 0;
+        for (int i = g.first_bwd; i < n; ++i)
+          for (int e = in_ptr[i]; e < in_ptr[i + 1]; ++e) uses_bwd += (in_idx[e] == t);
+        rec_cost = rebuild_ms(g, cls, t) * std::max(1, std::min(uses_bwd, 2));
+      }
+      const double cost = std::min(swap_cost, rec_cost);
+      const double score = (double)out_bytes[t] / (cost + 1e-3);
+      if (score > best_score) { best_score = score; best = t; best_cls = rec_cost < swap_cost ? DROP : SWAP; }
+    }
+    if (best < 0) break;      // the peak is this op's own working set: nothing idle left to evict
+    cls[best] = best_cls;
+    if (best_cls == SWAP) {
+      // micro-tensor split: pipeline the transfer when it would otherwise be exposed
+      const double xfer = (double)out_bytes[best] / g.bw;
+      int k = 1;
+      while (k < max_split && xfer / k > 0.25 && g.splittable[best]) k *= 2;
+      split[best] = k;
+    }
+    place_prefetch(g, cls, prefetch);
+    r = simulate(g, cls, split, prefetch);
+  }
+  place_prefetch(g, cls, prefetch);
+  r = simulate(g, cls, split, prefetch);
+  std::memcpy(cls_out, cls.data(), sizeof(int) * n);
+  std::memcpy(split_out, split.data(), sizeof(int) * n);
+  std::memcpy(prefetch_out, prefetch.data(), sizeof(int) * n);
+  out[0] = r.time_ms; out[1] = (double)r.peak; out[2] = r.first_over; out[3] = r.stall_ms; out[4] = r.peak_pos;
+  return r.first_over < 0 ? 0 : 5;
+}
+
+}  // extern "C"

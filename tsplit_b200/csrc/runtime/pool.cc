@@ -73,6 +73,36 @@ int tsb_pool_alloc(void* h, int64_t bytes, int64_t* offset) {
   return 0;
 }
 
+// Same, but carves the block from the TOP of the highest free range that fits.
+// Long-lived tensors (results, parameter gradients) go there so they do not
+// fragment the low end where short-lived activations churn.
+int tsb_pool_alloc_high(void* h, int64_t bytes, int64_t* offset) {
+  Pool* p = static_cast<Pool*>(h);
+  if (!p || bytes < 0 || !offset) return 1;
+  const int64_t need = round_up(bytes > 0 ? bytes : 1, p->align);
+  std::lock_guard<std::mutex> g(p->mu);
+  for (auto it = p->blocks.rbegin(); it != p->blocks.rend(); ++it) {
+    if (!it->second.second || it->second.first < need) continue;
+    const int64_t off = it->first, size = it->second.first;
+    p->free_by_size.erase({size, off});
+    if (size > need) {
+      p->blocks[off] = {size - need, true};
+      p->free_by_size.insert({size - need, off});
+      p->blocks[off + size - need] = {need, false};
+      *offset = off + size - need;
+    } else {
+      p->blocks[off].second = false;
+      *offset = off;
+    }
+    p->used += need;
+    if (p->used > p->peak) p->peak = p->used;
+    ++p->n_alloc;
+    return 0;
+  }
+  ++p->n_fail;
+  return 5;
+}
+
 int tsb_pool_free(void* h, int64_t offset) {
   Pool* p = static_cast<Pool*>(h);
   if (!p) return 1;

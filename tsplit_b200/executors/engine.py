@@ -85,6 +85,7 @@ class MemoryExecutor(Executor):
             if n in evals:
                 self.last_use[n] = len(order)          # never released
         self.managed = [n for n in order if self._manageable(n, evals)]
+        self._managed_set = set(self.managed)
 
     def _manageable(self, n, evals):
         """Forward activations that are needed again in backward."""
@@ -163,7 +164,8 @@ class MemoryExecutor(Executor):
         self._reap(False)
         while True:
             try:
-                a = ndarray.empty(shape, self.ctx, channels_last=cl)
+                a = ndarray.empty(shape, self.ctx, channels_last=cl,
+                                  long_lived=self.last_use.get(node, 0) >= len(self.topo_order))
                 break
             except OutOfHBMBudget:
                 if self.pending:
@@ -181,8 +183,34 @@ class MemoryExecutor(Executor):
                 self.stats["peak_bytes"] = used
         return a
 
+    spill_on_pressure = False     # planned executors spill an idle activation instead of failing
+
     def _emergency_free(self, node):
-        return False
+        """Last resort when the plan fits in bytes but not in contiguous blocks
+        (fragmentation) or a prefetch arrived early: spill the resident managed
+        activation whose next use is farthest away.  It comes back on demand."""
+        if not self.spill_on_pressure or getattr(self, "_no_spill", False):
+            return False
+        cur = self._cursor
+        best, best_next = None, -1
+        for t in self.arr:
+            if t in self.locked or t not in self._managed_set or t in self.swapin_event:
+                continue
+            nxt = min((self.index[u] for u in self.users[t] if self.index[u] >= cur), default=None)
+            if nxt is None or nxt == cur:
+                continue
+            if nxt > best_next:
+                best, best_next = t, nxt
+        if best is None:
+            return False
+        if best not in self.host:
+            self._swap_out(best)
+        a = self.arr[best]
+        a.gpu2cpu_event.sync()
+        self._release(best)
+        self._reap(True)
+        self.stats["evictions"] += 1
+        return True
 
     def _host_buffer(self, node):
         h = self.host_bufs.get(node)
@@ -327,18 +355,23 @@ class MemoryExecutor(Executor):
 
     def _execute(self):
         order = self.topo_order
+        self._cursor = 0
         for idx, node in enumerate(order):
+            self._cursor = idx
             if node in self.arr:
                 continue
             if isinstance(node.op, PlaceholderOp):
                 self.arr[node] = self._placeholder_value(node)
                 continue
             for t in self.prefetch_at.get(idx, ()):
-                if t in self.host and t not in self.arr:
+                if t in self.host and t not in self.arr and self._room_for_prefetch(t, idx):
+                    self._no_spill = True
                     try:
                         self._swap_in(t, prefetch=True)
                     except OutOfHBMBudget:
                         pass                       # no room yet: it will be fetched on demand
+                    finally:
+                        self._no_spill = False
             temps = []
             for i in node.inputs:
                 self._ensure(i, temps)
@@ -351,6 +384,16 @@ class MemoryExecutor(Executor):
             for i in node.inputs:
                 self.locked.discard(i)
             self._after_node(idx, node, temps)
+
+    def _room_for_prefetch(self, t, idx):
+        """Prefetch only when the pool keeps head-room for what the schedule
+        allocates before ``t`` is used (twice the largest output on the way)."""
+        pool = ndarray.get_pool(self.ctx)
+        if pool is None:
+            return True
+        use = self.first_bwd_use.get(t) or idx
+        reserve = max((self.tensor_bytes(n) for n in self.topo_order[idx:use + 1]), default=0)
+        return pool.stats()["free"] >= self.tensor_bytes(t) + 2 * reserve
 
     def _after_node(self, idx, node, temps):
         # forward: offload / drop policy-managed tensors at their last forward use

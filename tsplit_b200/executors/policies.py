@@ -108,6 +108,7 @@ class capuchinExecutor(MemoryExecutor):
     enough (by measured time) to arrive before the first backward use."""
     policy_name = "capuchin"
     lazy_evict = True
+    spill_on_pressure = True
 
     def __init__(self, *a, host_link_gbs=50.0, **kw):
         MemoryExecutor.__init__(self, *a, **kw)

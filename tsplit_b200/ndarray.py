@@ -314,7 +314,7 @@ class _stream_scope(object):
             self.ctxmgr.__exit__(*a)
 
 
-def empty(shape, ctx=cpu(0), pinned=False, use_pool=True, channels_last=None):
+def empty(shape, ctx=cpu(0), pinned=False, use_pool=True, channels_last=None, long_lived=False):
     """Uninitialised fp32 array on ``ctx``; goes through the context's pool when
     one is installed and raises :class:`OutOfHBMBudget` when it does not fit."""
     shape = tuple(int(s) for s in shape)
@@ -322,7 +322,7 @@ def empty(shape, ctx=cpu(0), pinned=False, use_pool=True, channels_last=None):
     pool = _POOLS.get(ctx) if use_pool else None
     cl = is_cuda_ctx(ctx) if channels_last is None else (bool(channels_last) and is_cuda_ctx(ctx))
     if pool is not None:
-        blk, flat = pool.alloc(n * 4)
+        blk, flat = pool.alloc(n * 4, long_lived) if long_lived else pool.alloc(n * 4)
         return NDArray(_make_view(flat[:n], shape, cl), ctx, block=blk, pool=pool)
     if ctx.device_type == 2:
         flat = torch.empty(max(n, 1), dtype=torch.float32, device=ctx.torch_device)

@@ -186,9 +186,8 @@ class Conv2dGradFilterOp(Op):
         return 2.0 * s[1][0] * s[1][2] * s[1][3] * out[0] * out[1] * out[2] * out[3]
 
     def workspace_bytes(self, node, s, out):
-        # split-K partial sums (bounded by the kernel's split heuristic)
-        n = out[0] * out[1] * out[2] * out[3]
-        return 4 * n * 8
+        # split-K partial sums live in a library-owned buffer outside the activation pool
+        return 0
 
 
 class Conv2dBroadcastToOp(Op):

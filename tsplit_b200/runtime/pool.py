@@ -25,6 +25,7 @@ def _lib():
         lib.tsb_pool_create.argtypes = [c_int64, c_int64]
         lib.tsb_pool_destroy.argtypes = [c_void_p]
         lib.tsb_pool_alloc.argtypes = [c_void_p, c_int64, ctypes.POINTER(c_int64)]
+        lib.tsb_pool_alloc_high.argtypes = [c_void_p, c_int64, ctypes.POINTER(c_int64)]
         lib.tsb_pool_free.argtypes = [c_void_p, c_int64]
         lib.tsb_pool_try.argtypes = [c_void_p, c_int64]
         lib.tsb_pool_stats.argtypes = [c_void_p, ctypes.POINTER(c_int64)]
@@ -55,9 +56,10 @@ class MemoryPool(object):
             pass
 
     # -- allocator interface used by ndarray.empty --------------------------------
-    def alloc(self, nbytes):
+    def alloc(self, nbytes, long_lived=False):
         off = c_int64()
-        rc = self.lib.tsb_pool_alloc(self.handle, int(nbytes), ctypes.byref(off))
+        fn = self.lib.tsb_pool_alloc_high if long_lived else self.lib.tsb_pool_alloc
+        rc = fn(self.handle, int(nbytes), ctypes.byref(off))
         if rc == 5:
             st = self.stats()
             raise ndarray.OutOfHBMBudget(
