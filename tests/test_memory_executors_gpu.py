@@ -1,0 +1,74 @@
+"""Memory policies on a real GPU: pinned-host swaps on the copy streams,
+event-ordered reuse of pool blocks, recompute and micro-tensor transfers must
+reproduce the keep-everything executor."""
+import numpy as np
+import pytest
+
+from tsplit_b200 import ndarray, gpu_ops as ad, optimizer
+from tsplit_b200.models import vgg, resnet
+from tsplit_b200.runtime.pool import use_pool
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def net():
+    return vgg(16, num_classes=32, image=64, width_div=4, fc_width=256, seed=5)
+
+
+def run(cls, policy, cap, batch=16, steps=2, **kw):
+    ctx = ndarray.gpu(0)
+    m = net()
+    grads = ad.gradients(m.loss, m.variables)
+    x, y = m.synthetic_batch(batch, seed=2)
+    with use_pool(ctx, cap) as pool:
+        ex = cls([m.loss] + grads, ctx=ctx, policy=policy, **kw)
+        for _ in range(steps):
+            pool.reset_peak()
+            outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
+        return outs, pool.stats()["peak"], ex
+
+
+@pytest.fixture(scope="module")
+def keep_all():
+    outs, peak, _ = run(ad.MemoryExecutor, None, 4 << 30)
+    return outs, peak
+
+
+@pytest.mark.parametrize("cls,policy", [(ad.vdnnExecutor, "all"), (ad.vdnnExecutor, "conv"),
+                                        (ad.recomputeExecutor, "speed"), (ad.recomputeExecutor, "memory"),
+                                        (ad.superNeuronsExecutor, None)])
+def test_policy_on_gpu_matches_keep_all(cls, policy, keep_all):
+    ref, peak_keep = keep_all
+    outs, peak, ex = run(cls, policy, 4 << 30)
+    for i, (o, r) in enumerate(zip(outs, ref)):
+        assert_close(o, r, rtol=2e-3, what="%s/%s output %d" % (cls.__name__, policy, i))
+    assert peak < peak_keep
+    assert ex.stats["swap_out_bytes"] > 0 or ex.stats["recomputed_nodes"] > 0
+
+
+def test_tsplit_and_capuchin_under_a_tight_cap(keep_all):
+    ref, peak_keep = keep_all
+    cap = int(peak_keep * 0.7)
+    with pytest.raises(ndarray.OutOfHBMBudget):
+        run(ad.MemoryExecutor, None, cap, steps=1)
+    for cls, kw in ((ad.microopExecutor, dict(host_link_gbs=20.0, max_split=4)), (ad.capuchinExecutor, {})):
+        outs, peak, ex = run(cls, None, cap, steps=3, **kw)
+        assert peak <= cap
+        for i, (o, r) in enumerate(zip(outs, ref)):
+            assert_close(o, r, rtol=2e-3, what="%s output %d" % (cls.__name__, i))
+
+
+def test_training_with_graph_replay_matches_eager():
+    ctx = ndarray.gpu(0)
+    losses = {}
+    for use_graph in (False, True):
+        m = net()
+        opt = optimizer.MomentumOptimizer(0.01, 0.9, ctx=ctx)
+        train = opt.minimize(m.loss)
+        ex = ad.Executor([m.loss, train], ctx=ctx, use_graph=use_graph)
+        x, y = m.synthetic_batch(16, seed=2)
+        xd, yd = ndarray.array(x, ctx), ndarray.array(y, ctx)
+        losses[use_graph] = [float(ex.run({m.X: xd, m.y_: yd})[0].asnumpy()[0]) for _ in range(5)]
+    assert_close(np.array(losses[True]), np.array(losses[False]), rtol=5e-3)
+    assert losses[False][-1] < losses[False][0]

@@ -57,12 +57,20 @@ def runtime():
     return lib
 
 
+def _counted(name):
+    key = "counted:" + name
+    if key not in _cache:
+        from .utils.launch_counter import CountingLib
+        _cache[key] = CountingLib(_load(name))
+    return _cache[key]
+
+
 def kernels():
-    return _load("libtsplit_kernels.so")
+    return _counted("libtsplit_kernels.so")
 
 
 def comm():
-    return _load("libtsplit_comm.so")
+    return _counted("libtsplit_comm.so")
 
 
 def have(name):

@@ -177,6 +177,7 @@ class Executor(object):
             if not self.use_numpy:
                 self.memory_plan(feed_shapes)
             self._graph = None
+            self._graph_warm = False
 
         if self.use_graph:
             self._run_graph(node_to_val)
@@ -218,9 +219,13 @@ class Executor(object):
         """Capture the whole step once per feed shape; later runs only refresh the
         feed buffers (their device addresses are stable) and replay."""
         from ..runtime import cudagraph
+        if self._graph is None and not getattr(self, "_graph_warm", False):
+            # first step with these shapes runs eagerly: it creates the lazily allocated side
+            # buffers, tensor maps and workspaces that a capture must not allocate
+            self._run_eager(node_to_val)
+            self._graph_warm = True
+            return
         if self._graph is None:
-            # one eager run first: lazily created side buffers and tensor maps
-            self._run_eager(dict(node_to_val))
             self.stream.sync()
             self._graph = cudagraph.capture(self.stream, lambda: self._run_eager(dict(node_to_val)))
             self._graph_vals = self._last_vals

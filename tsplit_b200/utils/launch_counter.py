@@ -1,0 +1,46 @@
+"""Counts kernel launches issued through the native kernel libraries.
+
+Every call of a ``tsb_*`` entry point goes through a thin proxy that adds the
+number of kernels that entry launches (a lower bound: conditional extra kernels
+such as a split-K reduction are not counted)."""
+from __future__ import annotations
+
+_count = [0]
+
+#: kernels launched per entry point (entries not listed launch one)
+KERNELS_PER_ENTRY = {
+    "tsb_bn_forward": 3, "tsb_bn_backward": 3, "tsb_softmax_ce": 2, "tsb_layer_norm_grad": 3,
+    "tsb_graph_begin": 0, "tsb_graph_end": 0, "tsb_graph_destroy": 0, "tsb_device_status": 0,
+    "tsb_mem_info": 0,
+}
+
+
+def reset():
+    _count[0] = 0
+
+
+def count():
+    return _count[0]
+
+
+class CountingLib(object):
+    """Proxy around a ``ctypes.CDLL`` that counts launches per call."""
+
+    def __init__(self, lib):
+        object.__setattr__(self, "_lib", lib)
+        object.__setattr__(self, "_wrapped", {})
+
+    def __getattr__(self, name):
+        w = self._wrapped.get(name)
+        if w is not None:
+            return w
+        fn = getattr(self._lib, name)
+        k = KERNELS_PER_ENTRY.get(name, 1)
+        if not name.startswith("tsb_") or k == 0:
+            return fn
+
+        def call(*a, _fn=fn, _k=k):
+            _count[0] += _k
+            return _fn(*a)
+        self._wrapped[name] = call
+        return call
