@@ -269,7 +269,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
         const int PH = (MODE == 0) ? p.OH : p.H, PW = (MODE == 0) ? p.OW : p.W;   // pixel grid of the rows
         const int SH = (MODE == 0) ? p.H : p.OH, SW = (MODE == 0) ? p.W : p.OW;   // grid of the gathered tensor
         const int SC = (MODE == 0) ? p.C : p.O;                                   // its channel count
-        long long base[8];
+        const float* rowptr[8];        // origin of the row's patch (may point outside; never read when invalid)
         int a0[8], b0[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -278,11 +278,14 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
             const int n = pix / (PH * PW);
             const int rem = pix - n * (PH * PW);
             const int y = rem / PW, x = rem - y * PW;
-            base[i] = (long long)n * SH * SW * SC;
             if (MODE == 0) { a0[i] = y * p.stride - p.ph; b0[i] = x * p.stride - p.pw; }
             else           { a0[i] = y + p.ph;            b0[i] = x + p.pw; }
+            if (MODE == 0 || p.stride == 1)
+              rowptr[i] = p.src + (((long long)n * SH + a0[i]) * SW + b0[i]) * SC;
+            else
+              rowptr[i] = p.src + (long long)n * SH * SW * SC;
           } else {
-            base[i] = 0; a0[i] = -(1 << 28); b0[i] = -(1 << 28);
+            rowptr[i] = p.src; a0[i] = -(1 << 28); b0[i] = -(1 << 28);
           }
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
@@ -303,68 +306,81 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
             kvalid = ch < p.O;
             kh = tap / p.KW; kw = tap - kh * p.KW;
           }
+          // element offset of this k-chunk relative to the row origin
+          const int delta = (MODE == 0) ? (kh * SW + kw) * SC + ch : -((kh * SW + kw) * SC) + ch;
           const uint32_t sdst = smem_u32(smem_a + s * A_STAGE_BYTES);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int r = rg + 16 * i;
-            int yy, xx;
             bool v = kvalid;
+            const float* src;
             if (MODE == 0) {
-              yy = a0[i] + kh; xx = b0[i] + kw;
+              v = v && (unsigned)(a0[i] + kh) < (unsigned)SH && (unsigned)(b0[i] + kw) < (unsigned)SW;
+              src = rowptr[i] + delta;
+            } else if (p.stride == 1) {
+              v = v && (unsigned)(a0[i] - kh) < (unsigned)SH && (unsigned)(b0[i] - kw) < (unsigned)SW;
+              src = rowptr[i] + delta;
             } else {
               const int ty = a0[i] - kh, tx = b0[i] - kw;
-              if (p.stride == 1) { yy = ty; xx = tx; }
-              else {
-                yy = ty / p.stride; xx = tx / p.stride;
-                v = v && ty >= 0 && tx >= 0 && (yy * p.stride == ty) && (xx * p.stride == tx);
-              }
+              const int yy = ty / p.stride, xx = tx / p.stride;
+              v = v && ty >= 0 && tx >= 0 && (yy * p.stride == ty) && (xx * p.stride == tx) &&
+                  yy < SH && xx < SW;
+              src = rowptr[i] + ((long long)yy * SW + xx) * SC + ch;
             }
-            v = v && (unsigned)yy < (unsigned)SH && (unsigned)xx < (unsigned)SW;
-            const float* src = v ? p.src + base[i] + ((long long)yy * SW + xx) * SC + ch : p.src;
-            cp_async16(sdst + r * 128 + ((j ^ (r & 7)) << 4), src, v);
+            cp_async16(sdst + r * 128 + ((j ^ (r & 7)) << 4), v ? src : p.src, v);
           }
           cp_async_commit();
           if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
         }
       } else {
-        // wgrad B tile: 32 rows (pixels = k) x BN channels, MN-major, 128B swizzle with 32B atoms.
-        constexpr int PPR = BN / 4;            // 16-byte pieces per pixel row
-        constexpr int RPP = 128 / PPR;         // pixel rows covered by one pass of the 128 threads
-        constexpr int PASSES = BK / RPP;
-        const int pc = t % PPR, kr0 = t / PPR;
-        const int ch = w.n0 + pc * 4;
-        const bool cvalid = ch < p.C;
-        const int kh = w.tap / p.KW, kw = w.tap - kh * p.KW;
-        const int chunk = pc >> 3, u = pc & 7;
+        // wgrad B tile: 32 rows (pixels = k) x BN columns, MN-major, 128B swizzle with 32B atoms.
+        // Columns are the flattened (tap, channel) index, so one tile spans several filter taps and
+        // the dy tile is shared between them.  Thread owns pixel row t/4 and every 4th 16-byte piece.
+        constexpr int PPT = BN / 16;           // pieces per thread
+        const int kr = t >> 2, sub = t & 3;
         const int mpix = p.N * p.OH * p.OW;
-        // pixel state of row kr0 at the first k-block
-        int pix = w.kb0 * BK + kr0;
+        int poff[PPT];                         // element offset of the piece relative to the row's origin
+        int ptap[PPT];                         // (kh << 16) | kw, or -1 when the column is out of range
+#pragma unroll
+        for (int i = 0; i < PPT; ++i) {
+          const int col = w.n0 + (i * 4 + sub) * 4;
+          if (col < p.NC) {
+            const int tap = col / p.C, ch = col - tap * p.C;
+            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            ptap[i] = (kh << 16) | kw;
+            poff[i] = (kh * p.W + kw) * p.C + ch;
+          } else {
+            ptap[i] = -1; poff[i] = 0;
+          }
+        }
+        // pixel state of this thread's row at the first k-block
+        int pix = w.kb0 * BK + kr;
         int n = pix / (p.OH * p.OW);
         int rem = pix - n * (p.OH * p.OW);
         int oy = rem / p.OW, ox = rem - oy * p.OW;
+        const uint32_t rowsw = (uint32_t)(kr & 3);
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x206)) { ok = false; break; }
-          const uint32_t sdst = smem_u32(smem_b + s * C::B_STAGE_BYTES) + chunk * (BK * 128);
-          int pn = n, py = oy, px = ox, ppix = pix;
+          const uint32_t sdst = smem_u32(smem_b + s * C::B_STAGE_BYTES) + kr * 128;
+          const int y0 = oy * p.stride - p.ph, x0 = ox * p.stride - p.pw;
+          const bool pvalid = pix < mpix;
+          const float* rowptr = p.src + (((long long)n * p.H + y0) * p.W + x0) * p.C;
 #pragma unroll
-          for (int ps = 0; ps < PASSES; ++ps) {
-            const int kr = kr0 + ps * RPP;
-            const int yy = py * p.stride - p.ph + kh, xx = px * p.stride - p.pw + kw;
-            const bool v = cvalid && ppix < mpix && (unsigned)yy < (unsigned)p.H &&
-                           (unsigned)xx < (unsigned)p.W;
-            const float* src = v ? p.src + (((long long)pn * p.H + yy) * p.W + xx) * p.C + ch : p.src;
-            const uint32_t piece = (uint32_t)((((u >> 1) ^ (kr & 3)) << 1) | (u & 1));
-            cp_async16(sdst + kr * 128 + (piece << 4), src, v);
-            // advance the pixel by RPP
-            ppix += RPP; px += RPP;
-            while (px >= p.OW) { px -= p.OW; ++py; }
-            while (py >= p.OH) { py -= p.OH; ++pn; }
+          for (int i = 0; i < PPT; ++i) {
+            const int pc = i * 4 + sub;
+            const int kh = ptap[i] >> 16, kw = ptap[i] & 0xffff;
+            const bool v = pvalid && ptap[i] >= 0 && (unsigned)(y0 + kh) < (unsigned)p.H &&
+                           (unsigned)(x0 + kw) < (unsigned)p.W;
+            const float* src = v ? rowptr + poff[i] : p.src;
+            const uint32_t u = (uint32_t)(pc & 7);
+            const uint32_t piece = (((u >> 1) ^ rowsw) << 1) | (u & 1);
+            cp_async16(sdst + (pc >> 3) * (BK * 128) + (piece << 4), src, v);
           }
           cp_async_commit();
           if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
-          // advance the base pixel by one k-block
+          // advance the pixel by one k-block
           pix += BK; ox += BK;
           while (ox >= p.OW) { ox -= p.OW; ++oy; }
           while (oy >= p.OH) { oy -= p.OH; ++n; }
@@ -486,10 +502,10 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     rc = tsb_host::make_tmap_f32(&tm, w, 3, d, s, bx, true);
   } else {
     const long long mpix = (long long)N * OH * OW;
-    p.src = x; p.out = w; p.M = O; p.NC = C; p.ldc = (long long)KH * KW * C;
-    p.taps = KH * KW;
+    p.src = x; p.out = w; p.M = O; p.NC = KH * KW * C; p.ldc = (long long)KH * KW * C;
+    p.taps = 1;
     p.kblocks = (int)((mpix + BK - 1) / BK);
-    bn = C > 128 ? 256 : (C > 64 ? 128 : 64);
+    bn = p.NC > 128 ? 256 : (p.NC > 64 ? 128 : 64);
     uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
     uint32_t bx[2] = {32, BK};
     rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
