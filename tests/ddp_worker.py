@@ -1,0 +1,56 @@
+"""Worker for the 2-GPU data-parallel test (launched by torchrun): trains a small
+CNN for a few steps with the fused all-reduce + optimizer kernel and with the
+NCCL all-reduce + local update baseline from identical initial weights and data;
+parameters must agree."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from tsplit_b200 import ndarray, gpu_ops as ad, optimizer      # noqa: E402
+from tsplit_b200.models import vgg                              # noqa: E402
+from tsplit_b200.parallel import ddp                            # noqa: E402
+
+
+def train(mode, rank, ctx, steps=4):
+    m = vgg(16, num_classes=16, image=32, width_div=8, fc_width=64, seed=11)
+    opt = optimizer.MomentumOptimizer(0.05, 0.9, ctx=ctx)
+    train_op = opt.minimize(m.loss)
+    comm = ddp.attach(opt, dist, mode=mode)
+    ex = ad.Executor([m.loss, train_op], ctx=ctx)
+    x, y = m.synthetic_batch(8, seed=100 + rank)
+    losses = []
+    for _ in range(steps):
+        losses.append(float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0][0]))
+    if hasattr(comm, "check"):
+        comm.check(ex.stream)
+    torch.cuda.synchronize()
+    return losses, [p.asnumpy() for p in opt.params]
+
+
+def main():
+    rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = ndarray.gpu(local)
+    l_ref, p_ref = train("nccl", rank, ctx)
+    l_fused, p_fused = train("fused", rank, ctx)
+    for a, b in zip(p_fused, p_ref):
+        np.testing.assert_allclose(a, b, rtol=5e-3, atol=5e-4)
+    # every rank must hold identical parameters after the fused update
+    flat = torch.cat([torch.from_numpy(p).reshape(-1) for p in p_fused]).cuda()
+    other = flat.clone()
+    dist.broadcast(other, src=0)
+    assert torch.equal(flat, other), "ranks diverged"
+    dist.barrier()
+    if rank == 0:
+        print("losses nccl", l_ref, "fused", l_fused)
+        print("DDP_OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,76 @@
+"""Fused all-reduce + optimizer: bucket layout on CPU, all-ranks-on-one-GPU
+emulation of the reduce/update/broadcast math, and a real 2-GPU run against
+NCCL all-reduce + a local update."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tsplit_b200.parallel.fused_allreduce import bucket_layout
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_bucket_layout_pads_every_tensor_to_four_floats():
+    offs, total = bucket_layout([5, 8, 1, 1024])
+    assert offs == [0, 8, 16, 20] and total == 20 + 1024
+    assert all(o % 4 == 0 for o in offs)
+
+
+def _np_update(kind, p, g, s1, s2, h):
+    if kind == 0:
+        return p - h[0] * g, s1, s2
+    if kind == 1:
+        s1 = h[1] * s1 - h[0] * g
+        return p + s1, s1, s2
+    if kind == 2:
+        lr_g = -h[0] * g
+        s1 = h[1] * (s1 + lr_g)
+        return p + s1 + lr_g, s1, s2
+    if kind == 3:
+        s1 = s1 + g * g
+        return p - h[0] * g / (np.sqrt(s1) + h[1]), s1, s2
+    s1 = h[1] * s1 + (1 - h[1]) * g
+    s2 = h[2] * s2 + (1 - h[2]) * g * g
+    return p - h[0] * (s1 / (1 - h[3])) / (np.sqrt(s2 / (1 - h[4])) + h[5]), s1, s2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,hyper", [(0, [0.1]), (1, [0.1, 0.9]), (2, [0.1, 0.9]), (3, [0.1, 1e-7]),
+                                        (4, [0.01, 0.9, 0.999, 0.9, 0.999, 1e-7])])
+@pytest.mark.parametrize("world,n", [(2, 4096), (8, 1000004), (3, 52)])
+def test_all_ranks_emulated_on_one_gpu(kind, hyper, world, n):
+    from tsplit_b200.parallel.fused_allreduce import emulate
+    g = torch.Generator(device="cuda").manual_seed(kind * 10 + world)
+    grads = [torch.randn(n, device="cuda", generator=g) for _ in range(world)]
+    p0 = torch.randn(n, device="cuda", generator=g)
+    params = [p0.clone() for _ in range(world)]
+    s1 = torch.rand(n, device="cuda", generator=g)
+    s2 = torch.rand(n, device="cuda", generator=g)
+    s1_0, s2_0 = s1.clone(), s2.clone()
+    emulate(kind, grads, params, s1, s2, hyper)
+    torch.cuda.synchronize()
+    gm = sum(x.double() for x in grads).cpu().numpy() / world
+    ref_p, ref_s1, ref_s2 = _np_update(kind, p0.double().cpu().numpy(), gm, s1_0.double().cpu().numpy(),
+                                       s2_0.double().cpu().numpy(), hyper)
+    for r in range(world):
+        np.testing.assert_allclose(params[r].cpu().numpy(), ref_p, rtol=2e-5, atol=2e-6)
+    if kind >= 1:
+        np.testing.assert_allclose(s1.cpu().numpy(), ref_s1, rtol=2e-5, atol=2e-6)
+    if kind == 4:
+        np.testing.assert_allclose(s2.cpu().numpy(), ref_s2, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.gpu
+def test_two_gpu_training_matches_nccl_baseline():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSPLIT_NVLS="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29613", os.path.join(HERE, "ddp_worker.py")]
+    res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-4000:]
+    assert "DDP_OK" in res.stdout, res.stdout[-4000:]
