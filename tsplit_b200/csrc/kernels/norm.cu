@@ -14,11 +14,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "norm_static.h"
+
 #define TSB_OK 0
 #define TSB_ERR_ARG 1
 #define TSB_ERR_UNSUPPORTED 2
 #define TSB_ERR_LAUNCH 3
 #define TSB_ERR_OOM 5
+#define TSB_ERR_SCRATCH 7
 
 namespace {
 
@@ -190,6 +193,27 @@ __global__ void bn_apply_bwd(const float* __restrict__ dy, const float* __restri
   }
 }
 
+// ---- statistics scratch that lives in the library image (see norm_static.h) ----------------
+// Two planes of MAX_CHUNKS x 8192 floats (8 MiB), resident on every GPU that loads the library
+// until the process exits.  Host code must not hand this name to a kernel: here it is only a
+// host-side stand-in, so the device address is looked up once per device.
+static __device__ __align__(256) float g_static_stats_scratch[SCRATCH_FLOATS];
+float* g_static_scratch_addr[64] = {nullptr};
+
+// Device address of the static scratch on the CURRENT device (looked up on first use).
+int static_scratch(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TSB_ERR_ARG;
+  if (!g_static_scratch_addr[dev]) {
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_stats_scratch);
+    if (e != cudaSuccess || !ptr) return TSB_ERR_LAUNCH | ((int)e << 8);
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return TSB_OK;
+}
+
 int pick_chunks(long long rows, int C) {
   const int col_blocks = (C / 4 + 31) / 32;
   long long want = (4ll * sm_count() + col_blocks - 1) / col_blocks;
@@ -280,6 +304,29 @@ int tsb_bn_forward(const float* x, const float* scale, const float* bias, float*
   if (!part) return TSB_ERR_OOM;
   const int chunks = pick_chunks(rows, (int)C);
   dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
+  col_partial<0><<<grid, blk, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, chunks);
+  bn_finalize_fwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, (double)rows, eps, momentum,
+                                                               save_mean, save_invstd, run_mean, run_var);
+  bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
+                                                        ldx, ldy, relu);
+  return done();
+}
+
+// Batch-norm forward that allocates nothing (declared and documented in norm_static.h).
+int tsb_bn_forward_static(const float* x, const float* scale, const float* bias, float* y, float* save_mean,
+                          float* save_invstd, float* run_mean, float* run_var, long long rows, long long C,
+                          long long ldx, long long ldy, float momentum, float eps, int relu, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0) return TSB_ERR_ARG;
+  if (C > TSB_BN_STATIC_MAX_CHANNELS) return TSB_ERR_SCRATCH;      // partial planes would not fit
+  if ((C % 4) || (ldx % 4) || (ldy % 4)) return TSB_ERR_UNSUPPORTED;
+  float* part = nullptr;
+  const int rc = static_scratch(&part);
+  if (rc) return rc;
+  const int chunks = pick_chunks(rows, (int)C);
+  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
+  // every partial word that the finalise step reads is written by the statistics step of the
+  // same call, so nothing in the shared array has to be cleared between calls
   col_partial<0><<<grid, blk, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, chunks);
   bn_finalize_fwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, (double)rows, eps, momentum,
                                                                save_mean, save_invstd, run_mean, run_var);
