@@ -25,7 +25,7 @@ OBJ = os.path.join(os.path.dirname(HERE), "build", "obj")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-fopenmp"]
 
 
 def _nvcc():
@@ -74,7 +74,8 @@ def build_all(verbose=False, cuda=True):
     host_src = sorted(glob.glob(os.path.join(CSRC, "runtime", "*.cc")) +
                       glob.glob(os.path.join(CSRC, "planner", "*.cc")) +
                       glob.glob(os.path.join(CSRC, "comm", "*.cc")))
-    built.append(_compile_group("tsplit_runtime", host_src, headers, "g++", CXX_FLAGS, ["-pthread"], verbose))
+    built.append(_compile_group("tsplit_runtime", host_src, headers, "g++", CXX_FLAGS, ["-pthread", "-fopenmp"],
+                                verbose))
     if cuda:
         inc = ["-I", os.path.join(CSRC, "kernels")]
         ksrc = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))

@@ -1,0 +1,188 @@
+// Host (CPU) operator library: OpenMP kernels for the operators a CPU-only run
+// spends its time in.  Capability parity with the reference's oneDNN / OpenMP
+// backend (src/dnnl_ops/*.cpp: matmul, element-wise, conv, pooling, batch-norm,
+// softmax cross-entropy, optimizers); plain C++ here, since oneDNN is not part of
+// this build.  Row-major fp32 throughout.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+extern "C" {
+
+// C[m,n] = op(A) * op(B); lda/ldb are the row strides of the STORED matrices.
+int tsb_cpu_matmul(const float* a, const float* b, float* c, int m, int n, int k, int trans_a, int trans_b) {
+  const int lda = trans_a ? m : k, ldb = trans_b ? k : n;
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < m; ++i) {
+    float* crow = c + (int64_t)i * n;
+    std::fill(crow, crow + n, 0.f);
+    for (int p = 0; p < k; ++p) {
+      const float av = trans_a ? a[(int64_t)p * lda + i] : a[(int64_t)i * lda + p];
+      if (!trans_b) {
+        const float* brow = b + (int64_t)p * ldb;
+        for (int j = 0; j < n; ++j) crow[j] += av * brow[j];
+      } else {
+        for (int j = 0; j < n; ++j) crow[j] += av * b[(int64_t)j * ldb + p];
+      }
+    }
+  }
+  return 0;
+}
+
+// op: 0 add, 1 mul, 2 div, 3 relu_grad(x, g)
+int tsb_cpu_binary(int op, const float* a, const float* b, float* y, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    switch (op) {
+      case 0: y[i] = a[i] + b[i]; break;
+      case 1: y[i] = a[i] * b[i]; break;
+      case 2: y[i] = a[i] / b[i]; break;
+      default: y[i] = a[i] > 0.f ? b[i] : (a[i] == 0.f ? 0.5f * b[i] : 0.f);
+    }
+  }
+  return 0;
+}
+
+// op: 1 relu, 2 sigmoid, 3 tanh, 4 sqrt, 5 rsqrt, 6 neg, 7 add const, 8 mul const, 9 const / x
+int tsb_cpu_unary(int op, const float* x, float* y, int64_t n, float alpha) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const float v = x[i];
+    switch (op) {
+      case 1: y[i] = v > 0.f ? v : 0.f; break;
+      case 2: y[i] = 1.f / (1.f + std::exp(-v)); break;
+      case 3: y[i] = std::tanh(v); break;
+      case 4: y[i] = std::sqrt(v); break;
+      case 5: y[i] = 1.f / std::sqrt(v); break;
+      case 6: y[i] = -v; break;
+      case 7: y[i] = v + alpha; break;
+      case 8: y[i] = v * alpha; break;
+      case 9: y[i] = alpha / v; break;
+      default: y[i] = v;
+    }
+  }
+  return 0;
+}
+
+// NCHW x OIHW cross-correlation.
+int tsb_cpu_conv2d(const float* x, const float* w, float* y, int N, int C, int H, int W, int O, int KH, int KW, int ph,
+                   int pw, int stride) {
+  const int OH = (H + 2 * ph - KH) / stride + 1, OW = (W + 2 * pw - KW) / stride + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int o = 0; o < O; ++o) {
+      float* yo = y + ((int64_t)n * O + o) * OH * OW;
+      std::fill(yo, yo + (int64_t)OH * OW, 0.f);
+      for (int c = 0; c < C; ++c) {
+        const float* xc = x + ((int64_t)n * C + c) * H * W;
+        const float* wc = w + ((int64_t)o * C + c) * KH * KW;
+        for (int kh = 0; kh < KH; ++kh)
+          for (int kw = 0; kw < KW; ++kw) {
+            const float wv = wc[kh * KW + kw];
+            for (int oh = 0; oh < OH; ++oh) {
+              const int ih = oh * stride - ph + kh;
+              if (ih < 0 || ih >= H) continue;
+              for (int ow = 0; ow < OW; ++ow) {
+                const int iw = ow * stride - pw + kw;
+                if (iw < 0 || iw >= W) continue;
+                yo[oh * OW + ow] += wv * xc[ih * W + iw];
+              }
+            }
+          }
+      }
+    }
+  return 0;
+}
+
+// kind 0 max, 1 average (count includes padding); NCHW.
+int tsb_cpu_pool2d(int kind, const float* x, float* y, int N, int C, int H, int W, int KH, int KW, int pad, int stride) {
+  const int OH = (H + 2 * pad - KH) / stride + 1, OW = (W + 2 * pad - KW) / stride + 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t nc = 0; nc < (int64_t)N * C; ++nc) {
+    const float* xc = x + nc * H * W;
+    float* yc = y + nc * OH * OW;
+    for (int oh = 0; oh < OH; ++oh)
+      for (int ow = 0; ow < OW; ++ow) {
+        float acc = kind == 0 ? -INFINITY : 0.f;
+        for (int kh = 0; kh < KH; ++kh)
+          for (int kw = 0; kw < KW; ++kw) {
+            const int ih = oh * stride - pad + kh, iw = ow * stride - pad + kw;
+            if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+            const float v = xc[ih * W + iw];
+            acc = kind == 0 ? std::max(acc, v) : acc + v;
+          }
+        yc[oh * OW + ow] = kind == 0 ? acc : acc / (float)(KH * KW);
+      }
+  }
+  return 0;
+}
+
+// Spatial batch-norm forward, NCHW; writes mean / invstd [C].
+int tsb_cpu_batchnorm(const float* x, const float* scale, const float* bias, float* y, float* mean, float* invstd, int N,
+                      int C, int HW, float eps) {
+#pragma omp parallel for schedule(static)
+  for (int c = 0; c < C; ++c) {
+    double s = 0, ss = 0;
+    for (int n = 0; n < N; ++n) {
+      const float* p = x + ((int64_t)n * C + c) * HW;
+      for (int i = 0; i < HW; ++i) { s += p[i]; ss += (double)p[i] * p[i]; }
+    }
+    const double cnt = (double)N * HW, m = s / cnt;
+    const double var = std::max(0.0, ss / cnt - m * m);
+    const float is = (float)(1.0 / std::sqrt(var + eps));
+    mean[c] = (float)m; invstd[c] = is;
+    for (int n = 0; n < N; ++n) {
+      const float* p = x + ((int64_t)n * C + c) * HW;
+      float* q = y + ((int64_t)n * C + c) * HW;
+      for (int i = 0; i < HW; ++i) q[i] = (p[i] - (float)m) * is * scale[c] + bias[c];
+    }
+  }
+  return 0;
+}
+
+// loss[0] = mean over rows of -sum(labels * log_softmax(logits)); dx optional = (softmax - labels) / rows.
+int tsb_cpu_softmax_ce(const float* logits, const float* labels, float* loss, float* dx, int64_t rows, int64_t cols) {
+  double total = 0;
+#pragma omp parallel for reduction(+ : total) schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* xr = logits + r * cols;
+    const float* lr = labels + r * cols;
+    float m = xr[0];
+    for (int64_t i = 1; i < cols; ++i) m = std::max(m, xr[i]);
+    double s = 0;
+    for (int64_t i = 0; i < cols; ++i) s += std::exp((double)xr[i] - m);
+    const double lse = m + std::log(s);
+    double l = 0;
+    for (int64_t i = 0; i < cols; ++i) {
+      l -= lr[i] * (xr[i] - lse);
+      if (dx) dx[r * cols + i] = (float)((std::exp(xr[i] - lse) - lr[i]) / (double)rows);
+    }
+    total += l;
+  }
+  loss[0] = (float)(total / (double)rows);
+  return 0;
+}
+
+// kind: 0 sgd, 1 momentum, 2 nesterov, 3 adagrad, 4 adam; hyper as in the GPU kernel.
+int tsb_cpu_optimizer(int kind, float* p, const float* g, float* s1, float* s2, int64_t n, const float* h) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const float gi = g[i];
+    switch (kind) {
+      case 0: p[i] -= h[0] * gi; break;
+      case 1: s1[i] = h[1] * s1[i] - h[0] * gi; p[i] += s1[i]; break;
+      case 2: { const float lr_g = -h[0] * gi; s1[i] = h[1] * (s1[i] + lr_g); p[i] += s1[i] + lr_g; break; }
+      case 3: s1[i] += gi * gi; p[i] -= h[0] * gi / (std::sqrt(s1[i]) + h[1]); break;
+      default: {
+        s1[i] = h[1] * s1[i] + (1.f - h[1]) * gi;
+        s2[i] = h[2] * s2[i] + (1.f - h[2]) * gi * gi;
+        p[i] -= h[0] * (s1[i] / (1.f - h[3])) / (std::sqrt(s2[i] / (1.f - h[4])) + h[5]);
+      }
+    }
+  }
+  return 0;
+}
+
+}  // extern "C"

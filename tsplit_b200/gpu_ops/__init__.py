@@ -23,3 +23,5 @@ from ..ops.misc import (Variable, placeholder_op, oneslike_op, zeroslike_op, one
                         embedding_lookup_op, embedding_lookup_gradient_op, dropout_op, dropout_gradient_op,
                         swap_out_op, swap_in_op, split_op)
 from ..executors import *          # noqa: F401,F403
+from ..parallel.graph_hooks import (distributed_gradients, ps_gradients, distributed_communicate_op,   # noqa: E402
+                                    ps_communicate_op)
