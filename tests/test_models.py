@@ -1,0 +1,72 @@
+"""Every model family builds, differentiates and trains (loss goes down) on the
+NumPy path at a reduced size; the GPU variants check one step against NumPy."""
+import numpy as np
+import pytest
+
+from tsplit_b200 import ndarray, gpu_ops as ad, optimizer
+from tsplit_b200.models import mlp, vgg, resnet, inception_v4, transformer, lstm
+from helpers import assert_close
+
+
+def _train(loss, feed, ctx, steps, lr=0.01, opt_cls=optimizer.SGDOptimizer):
+    opt = opt_cls(lr, ctx=ctx) if ctx is not None else opt_cls(lr)
+    train = opt.minimize(loss)
+    ex = ad.Executor([loss, train], ctx=ctx)
+    return [float(np.asarray(ex.run(feed, convert_to_numpy_ret_vals=True)[0]).reshape(-1)[0]) for _ in range(steps)]
+
+
+def test_mlp_baseline_config_trains_on_cpu():
+    m = mlp()                                   # 784-256-256-10, no bias
+    x, y = m.synthetic_batch(128)
+    losses = _train(m.loss, {m.X: x, m.y_: y}, None, 12, lr=0.1)
+    assert losses[-1] < losses[0] * 0.5
+
+
+@pytest.mark.parametrize("build", [
+    lambda: vgg(16, num_classes=10, image=32, width_div=16, fc_width=32),
+    lambda: resnet(26, num_classes=10, image=32, width_div=16),
+    lambda: inception_v4(num_classes=10, image=75, width_div=16),
+    lambda: lstm(steps=6, features=8, hidden=16, num_classes=5),
+], ids=["vgg16", "resnet", "inception_v4", "lstm"])
+def test_image_and_sequence_models_train_on_cpu(build):
+    m = build()
+    x, y = m.synthetic_batch(4)
+    losses = _train(m.loss, {m.X: x, m.y_: y}, None, 5, lr=0.02)
+    assert np.all(np.isfinite(losses)) and losses[-1] < losses[0]
+
+
+def test_transformer_trains_on_cpu():
+    t = transformer(vocab_size=50, d_model=16, num_heads=2, d_ff=32, num_blocks=1, maxlen1=6, maxlen2=6,
+                    batch_size=3)
+    losses = _train(t.loss, t.synthetic_batch(), None, 6, lr=0.01, opt_cls=optimizer.AdamOptimizer)
+    assert np.all(np.isfinite(losses)) and losses[-1] < losses[0]
+
+
+def _one_step_grads(build_loss_vars_feed, ctx):
+    loss, variables, feed = build_loss_vars_feed()
+    grads = ad.gradients(loss, variables)
+    ex = ad.Executor([loss] + grads, ctx=ctx)
+    return [np.asarray(o) for o in ex.run(feed, convert_to_numpy_ret_vals=True)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["resnet", "inception_v4", "transformer", "lstm"])
+def test_models_one_step_gpu_matches_numpy(name):
+    def build():
+        if name == "transformer":
+            t = transformer(vocab_size=64, d_model=32, num_heads=4, d_ff=64, num_blocks=1, maxlen1=8, maxlen2=8,
+                            batch_size=4, seed=7)
+            return t.loss, t.variables, t.synthetic_batch()
+        m = {"resnet": lambda: resnet(26, num_classes=16, image=32, width_div=8, seed=7),
+             "inception_v4": lambda: inception_v4(num_classes=16, image=75, width_div=8, seed=7),
+             "lstm": lambda: lstm(steps=6, features=8, hidden=16, num_classes=8, seed=7)}[name]()
+        x, y = m.synthetic_batch(4, seed=3)
+        return m.loss, m.variables, {m.X: x, m.y_: y}
+    ref = _one_step_grads(build, None)
+    got = _one_step_grads(build, ndarray.gpu(0))
+    assert_close(got[0], ref[0], rtol=5e-3, what="loss")
+    worst = 0.0
+    for g, r in zip(got[1:], ref[1:]):
+        scale = max(np.abs(r).max(), 1e-3)
+        worst = max(worst, np.abs(g - r).max() / scale)
+    assert worst < 5e-2, "largest relative gradient error %.3e" % worst

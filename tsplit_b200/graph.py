@@ -93,10 +93,8 @@ class Op(object):
         node.op = self
         node.inputs = list(inputs)
         node.attrs = attrs
-        if inputs:
-            node.name = "%s(%s)" % (self.name, ",".join(i.name for i in inputs))
-        else:
-            node.name = self.name
+        # names stay O(1): nesting the input names doubles their length at every join of a DAG
+        node.name = self.name
         node.desc = "%s_%d" % (self.name, node.id)
         return node
 

@@ -3,3 +3,6 @@ Inception-v4, Transformer encoder-decoder, LSTM."""
 from .mlp import mlp
 from .vgg import vgg
 from .resnet import resnet
+from .inception import inception_v4
+from .transformer import transformer, TransformerConfig, TransformerModel
+from .lstm import lstm
