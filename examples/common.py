@@ -1,0 +1,97 @@
+"""Shared driver of the example scripts: policy name -> executor, timed runs with
+CUDA events, and the batch-size sweep that stops at the first OutOfHBMBudget
+(the reference's sweep loops until its executor asserts,
+``examples/imagenet_vgg.py:159-178``)."""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import numpy as np                                            # noqa: E402
+
+from tsplit_b200 import ndarray, gpu_ops as ad                # noqa: E402
+from tsplit_b200.runtime.pool import MemoryPool               # noqa: E402
+
+POLICIES = ["None", "base", "vdnnconv", "vdnnall", "superneurons", "recompute_memory", "recompute_speed",
+            "capuchin", "simulator", "profiler", "planner", "tsplit"]
+
+
+def make_executor(policy, nodes, ctx):
+    if policy in ("None", "base"):
+        return ad.Executor(nodes, ctx=ctx)
+    if policy == "vdnnconv":
+        return ad.vdnnExecutor(nodes, ctx=ctx, policy="conv")
+    if policy == "vdnnall":
+        return ad.vdnnExecutor(nodes, ctx=ctx, policy="all")
+    if policy == "superneurons":
+        return ad.superNeuronsExecutor(nodes, ctx=ctx)
+    if policy == "recompute_memory":
+        return ad.recomputeExecutor(nodes, ctx=ctx, policy="memory")
+    if policy == "recompute_speed":
+        return ad.recomputeExecutor(nodes, ctx=ctx, policy="speed")
+    if policy == "capuchin":
+        return ad.capuchinExecutor(nodes, ctx=ctx)
+    if policy == "simulator":
+        return ad.microopOptimizer(nodes, ctx=ctx)
+    if policy == "profiler":
+        return ad.profileExecutor(nodes, ctx=ctx)
+    if policy == "planner":
+        return ad.microopPlanner(nodes, ctx=ctx)
+    if policy == "tsplit":
+        return ad.microopExecutor(nodes, ctx=ctx)
+    raise NotImplementedError(policy)
+
+
+def default_ctx():
+    import torch
+    return ndarray.gpu(0) if torch.cuda.is_available() else ndarray.simgpu(0)
+
+
+def timed_run(executor, feed, iters=3):
+    """One warm-up run, then ``iters`` timed runs; seconds per iteration."""
+    out = executor.run(feed)
+    if not isinstance(out, list):
+        return out
+    t0 = time.time()
+    for _ in range(iters):
+        executor.run(feed)
+    return (time.time() - t0) / iters
+
+
+def sweep(run_at_batch, batches, out_path=None):
+    """Call ``run_at_batch(b)`` for growing b until the budget is exceeded."""
+    results = []
+    for b in batches:
+        try:
+            t = run_at_batch(b)
+        except ndarray.OutOfHBMBudget as e:
+            print("Batch size: %d does not fit: %s" % (b, e))
+            break
+        print("Batch size: {} , time: {} s".format(b, t))
+        results.append((b, t))
+        if out_path:
+            with open(out_path, "a") as f:
+                f.write("Batch size: {} , time: {} s\n".format(b, t))
+    return results
+
+
+def parse(description, extra=None):
+    p = argparse.ArgumentParser(description=description)
+    p.add_argument("-l", "--layer", type=int, default=0)
+    p.add_argument("-p", "--policy", default="None", choices=POLICIES)
+    p.add_argument("-b", "--batch", type=int, default=0, help="single batch size (0 = sweep)")
+    p.add_argument("--cap-gib", type=float, default=16.0, help="HBM budget of the activation pool")
+    p.add_argument("--out", default=None, help="append results to this file")
+    if extra:
+        extra(p)
+    return p.parse_args()
+
+
+def with_pool(ctx, cap_gib):
+    pool = MemoryPool(ctx, int(cap_gib * 2**30))
+    ndarray.set_pool(ctx, pool)
+    return pool

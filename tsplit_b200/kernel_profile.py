@@ -1,0 +1,88 @@
+"""Per-operator time sweeps over batch, channel and spatial size (the role of the
+reference's ``kernel_profile/{conv2d,matmul,bn,maxpool,relu}.py``): each point is
+measured with CUDA events after a warm-up, reported as ms and achieved TFLOP/s or
+GB/s.
+
+    python -m tsplit_b200.kernel_profile conv2d --sweep batch
+"""
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+
+
+def _time(fn, iters=5):
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def sweep(op, axis, points=None):
+    from . import ndarray
+    from .ops import _gpu as G
+    from .stream import current_stream
+    ctx = ndarray.gpu(0)
+    st = current_stream(ctx)
+    base = dict(batch=32, channel=128, hw=56)
+    points = points or {"batch": [1, 8, 32, 64, 128, 256], "channel": [16, 64, 128, 256, 512, 1024],
+                        "hw": [8, 14, 28, 56, 112, 224]}[axis]
+    rows = []
+    for v in points:
+        cfg = dict(base)
+        cfg[axis] = v
+        n, c, hw = cfg["batch"], cfg["channel"], cfg["hw"]
+        if op == "matmul":
+            a, b, out = (ndarray.empty(s, ctx) for s in ((n * 64, c * 8), (c * 8, c * 8), (n * 64, c * 8)))
+            for t in (a, b):
+                t.t.normal_()
+            ms = _time(lambda: G.gemm(a, b, out, False, False, st, m=n * 64, n=c * 8, k=c * 8, lda=c * 8,
+                                      ldb=c * 8, ldc=c * 8))
+            rows.append((v, ms, 2.0 * n * 64 * (c * 8) ** 2 / ms / 1e9, "TFLOP/s"))
+            continue
+        x = ndarray.empty((n, c, hw, hw), ctx)
+        x.t.normal_()
+        y = ndarray.empty((n, c, hw, hw), ctx)
+        if op == "conv2d":
+            w = ndarray.empty((c, c, 3, 3), ctx)
+            w.t.normal_()
+            ms = _time(lambda: G.conv2d(0, x, w, y, 1, 1, 1, st))
+            rows.append((v, ms, 2.0 * n * hw * hw * c * c * 9 / ms / 1e9, "TFLOP/s"))
+        elif op == "relu":
+            ms = _time(lambda: G.unary(G.UN_RELU, x, y, st))
+            rows.append((v, ms, 2.0 * x.nbytes / ms / 1e6, "GB/s"))
+        elif op == "bn":
+            s, b = ndarray.empty((1, c, 1, 1), ctx), ndarray.empty((1, c, 1, 1), ctx)
+            s.t.fill_(1.0)
+            b.t.zero_()
+            stats = [ndarray.empty((c,), ctx) for _ in range(4)]
+            ms = _time(lambda: G.bn_forward(x, s, b, y, stats[0], stats[1], stats[2], stats[3], 0.99, 0.01,
+                                            False, st))
+            rows.append((v, ms, 3.0 * x.nbytes / ms / 1e6, "GB/s"))
+        elif op == "maxpool":
+            yo = ndarray.empty((n, c, hw // 2, hw // 2), ctx)
+            ms = _time(lambda: G.pool(0, x, yo, 2, 2, 0, 2, st))
+            rows.append((v, ms, 1.25 * x.nbytes / ms / 1e6, "GB/s"))
+        else:
+            raise ValueError(op)
+    return rows
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu"])
+    p.add_argument("--sweep", default="batch", choices=["batch", "channel", "hw"])
+    a = p.parse_args()
+    for v, ms, rate, unit in sweep(a.op, a.sweep):
+        print("%s=%-6d %9.4f ms  %9.1f %s" % (a.sweep, v, ms, rate, unit))
+
+
+if __name__ == "__main__":
+    main()
