@@ -215,3 +215,19 @@ def test_csrmm_and_csrmv(ctx):
         ex = ad.Executor([out], ctx=ctx)
         got = ex.run({A: sp, B: dense}, convert_to_numpy_ret_vals=True)[0]
         assert_close(got, m.toarray() @ dense, rtol=1e-4)
+
+
+def test_fused_batch_norm_relu_forward_backward(ctx):
+    def build(fused):
+        def b():
+            x, s, bb = ad.Variable("x"), ad.Variable("s"), ad.Variable("b")
+            y = ad.batch_normalization_relu_op(x, s, bb) if fused else ad.relu_op(ad.batch_normalization_op(x, s, bb))
+            loss = ad.reduce_sum_op(ad.mul_op(y, y), [0, 1, 2, 3])
+            gx, gs, gb = ad.gradients(loss, [x, s, bb])
+            return {"x": x, "s": s, "b": bb}, [y, gx, gs, gb]
+        return b
+    feeds = {"x": f32(4, 16, 6, 6) + 0.2, "s": f32(1, 16, 1, 1) + 1, "b": f32(1, 16, 1, 1)}
+    ref = run_graph(build(False), feeds, None)
+    got = run_graph(build(True), feeds, ctx)
+    for i, (g, r) in enumerate(zip(got, ref)):
+        assert_close(g, r, rtol=5e-3, what="output %d" % i)

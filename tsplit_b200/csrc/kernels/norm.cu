@@ -59,10 +59,12 @@ int done() {
 
 // Column partial sums over a chunk of rows.  Block = 32 (float4 columns) x 8 (row lanes).
 // MODE 0: p0 = sum x, p1 = sum x^2.   MODE 1: p0 = sum dy, p1 = sum dy * (x - mean) * invstd.
+// `mask` (MODE 1 only, may be null): output of a fused ReLU; dy counts only where mask > 0.
 template <int MODE>
 __global__ void col_partial(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mean,
                             const float* __restrict__ invstd, float* __restrict__ part, long long rows, int C,
-                            long long lda, long long ldb, int chunks) {
+                            long long lda, long long ldb, int chunks, const float* __restrict__ mask = nullptr,
+                            long long ldm = 0) {
   __shared__ float4 s0[8][32], s1[8][32];
   const int c4 = blockIdx.x * 32 + threadIdx.x;   // float4 column
   const int c = c4 * 4;
@@ -77,7 +79,12 @@ __global__ void col_partial(const float* __restrict__ a, const float* __restrict
       is = *reinterpret_cast<const float4*>(invstd + c);
     }
     for (long long r = r0 + threadIdx.y; r < r1; r += 8) {
-      const float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
+      float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
+      if (MODE == 1 && mask) {
+        const float4 m = *reinterpret_cast<const float4*>(mask + r * ldm + c);
+        v.x = m.x > 0.f ? v.x : 0.f; v.y = m.y > 0.f ? v.y : 0.f;
+        v.z = m.z > 0.f ? v.z : 0.f; v.w = m.w > 0.f ? v.w : 0.f;
+      }
       if (MODE == 0) {
         acc0.x += v.x; acc0.y += v.y; acc0.z += v.z; acc0.w += v.w;
         acc1.x += v.x * v.x; acc1.y += v.y * v.y; acc1.z += v.z * v.z; acc1.w += v.w * v.w;
@@ -170,14 +177,20 @@ __global__ void bn_apply_bwd(const float* __restrict__ dy, const float* __restri
                              const float* __restrict__ scale, const float* __restrict__ mean,
                              const float* __restrict__ invstd, const float* __restrict__ dscale,
                              const float* __restrict__ dbias, float* __restrict__ dx, long long rows, int C,
-                             long long lddy, long long ldx, long long lddx, float inv_count) {
+                             long long lddy, long long ldx, long long lddx, float inv_count,
+                             const float* __restrict__ mask = nullptr, long long ldm = 0) {
   const int C4 = C >> 2;
   const long long total = rows * C4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / C4;
     const int c = (int)(i - r * C4) * 4;
-    const float4 g = *reinterpret_cast<const float4*>(dy + r * lddy + c);
+    float4 g = *reinterpret_cast<const float4*>(dy + r * lddy + c);
+    if (mask) {
+      const float4 m = *reinterpret_cast<const float4*>(mask + r * ldm + c);
+      g.x = m.x > 0.f ? g.x : 0.f; g.y = m.y > 0.f ? g.y : 0.f;
+      g.z = m.z > 0.f ? g.z : 0.f; g.w = m.w > 0.f ? g.w : 0.f;
+    }
     const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
     const float4 mu = *reinterpret_cast<const float4*>(mean + c);
     const float4 is = *reinterpret_cast<const float4*>(invstd + c);
@@ -349,6 +362,27 @@ int tsb_bn_backward(const float* dy, const float* x, const float* scale, const f
   bn_finalize_bwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
                                                         rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows);
+  return done();
+}
+
+// Backward of the fused batch-norm + ReLU: `y` is the fused forward output; the incoming
+// gradient is masked by y > 0 on the fly in both passes, so no separate ReLU-gradient pass
+// (and no gradient tensor for the batch-norm output) exists.
+int tsb_bn_relu_backward(const float* dy, const float* x, const float* y, const float* scale,
+                         const float* save_mean, const float* save_invstd, float* dx, float* dscale, float* dbias,
+                         long long rows, long long C, long long ldx, long long lddy, long long ldy, long long lddx,
+                         void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4) || (ldy % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
+  float* part = scratch();
+  if (!part) return TSB_ERR_OOM;
+  const int chunks = pick_chunks(rows, (int)C);
+  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
+  col_partial<1><<<grid, blk, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, chunks, y, ldy);
+  bn_finalize_bwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, dscale, dbias);
+  bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
+                                                        rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows, y, ldy);
   return done();
 }
 

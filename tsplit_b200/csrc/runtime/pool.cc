@@ -134,6 +134,43 @@ int tsb_pool_free(void* h, int64_t offset) {
   return 0;
 }
 
+// Pack every used block towards offset 0 (order preserved) so that the free space becomes one
+// range.  Writes up to `max_moves` relocations (old offset, new offset, size), lowest first, and
+// returns their number; the caller moves the bytes in that order (each move goes downwards).
+int tsb_pool_compact(void* h, int64_t* old_off, int64_t* new_off, int64_t* sizes, int max_moves) {
+  Pool* p = static_cast<Pool*>(h);
+  if (!p) return 0;
+  std::lock_guard<std::mutex> g(p->mu);
+  std::map<int64_t, std::pair<int64_t, bool>> packed;
+  int64_t cursor = 0;
+  int n = 0;
+  for (auto& kv : p->blocks) {
+    if (kv.second.second) continue;
+    if (kv.first != cursor) {
+      if (n >= max_moves) {          // table too small: keep the remaining blocks where they are
+        cursor = kv.first;
+      } else {
+        old_off[n] = kv.first; new_off[n] = cursor; sizes[n] = kv.second.first;
+        ++n;
+      }
+    }
+    packed[cursor] = {kv.second.first, false};
+    cursor += kv.second.first;
+  }
+  p->free_by_size.clear();
+  // rebuild the free ranges between / after the packed blocks
+  std::map<int64_t, std::pair<int64_t, bool>> rebuilt;
+  int64_t pos = 0;
+  for (auto& kv : packed) {
+    if (kv.first > pos) { rebuilt[pos] = {kv.first - pos, true}; p->free_by_size.insert({kv.first - pos, pos}); }
+    rebuilt[kv.first] = kv.second;
+    pos = kv.first + kv.second.first;
+  }
+  if (pos < p->capacity) { rebuilt[pos] = {p->capacity - pos, true}; p->free_by_size.insert({p->capacity - pos, pos}); }
+  p->blocks.swap(rebuilt);
+  return n;
+}
+
 // 1 when a block of `bytes` could be allocated right now
 int tsb_pool_try(void* h, int64_t bytes) {
   Pool* p = static_cast<Pool*>(h);

@@ -175,6 +175,8 @@ class MemoryExecutor(Executor):
                     continue
                 if self._emergency_free(node):
                     continue
+                if self._compact(nbytes(shape)):
+                    continue
                 raise
         pool = ndarray.get_pool(self.ctx)
         if pool is not None:
@@ -182,6 +184,27 @@ class MemoryExecutor(Executor):
             if used > self.stats["peak_bytes"]:
                 self.stats["peak_bytes"] = used
         return a
+
+    def _compact(self, need):
+        """Defragment the pool when the bytes exist but no single hole is large
+        enough: drain the streams, pack live blocks, re-bind the arrays."""
+        pool = ndarray.get_pool(self.ctx)
+        if pool is None or getattr(self, "_no_spill", False):
+            return False
+        st = pool.stats()
+        if st["free"] < need + 256 or st["largest_free"] >= need:
+            return False
+        for s in self.streams:
+            s.sync()
+        self._reap(True)
+        moves = pool.compact()
+        if not moves:
+            return False
+        for a in self.arr.values():
+            if isinstance(a, ndarray.NDArray) and a._pool is pool and a._block in moves:
+                a._rebind(moves[a._block])
+        self.stats["compactions"] = self.stats.get("compactions", 0) + 1
+        return True
 
     spill_on_pressure = False     # planned executors spill an idle activation instead of failing
 

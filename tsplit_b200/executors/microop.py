@@ -35,7 +35,7 @@ from .engine import MemoryExecutor, KEEP, SWAP, DROP
 BATCH_SEPARABLE = {"Conv2d", "Conv2dGradData", "Relu", "ReluGradient", "Add", "Mul", "MaxPool2d", "AvgPool2d",
                    "MaxPool2dGradient", "AvgPool2dGradient", "Dropout", "DropoutGradient", "AddConst", "MulConst"}
 #: ops that are cheap enough to rebuild instead of moving their output over the host link
-RECOMPUTABLE = {"Relu", "BatchNorm", "MaxPool2d", "AvgPool2d", "Add", "Mul", "AddConst", "MulConst", "Reshape",
+RECOMPUTABLE = {"Relu", "BatchNorm", "BatchNormRelu", "MaxPool2d", "AvgPool2d", "Add", "Mul", "AddConst", "MulConst", "Reshape",
                 "Transpose", "Dropout", "Concat", "Slice", "Pad", "Sigmoid", "Tanh", "BroadcastTo",
                 "BroadcastShape", "BroadcastToTF", "Conv2dBroadcastTo", "LayerNorm", "Softmax", "Opposite"}
 

@@ -13,7 +13,8 @@ from ..ops.conv import (conv2d_op, conv2d_gradient_of_data_op, conv2d_gradient_o
 from ..ops.pool import max_pool2d_op, max_pool2d_gradient_op, avg_pool2d_op, avg_pool2d_gradient_op
 from ..ops.norm import (batch_normalization_op, batch_normalization_gradient_op,
                         batch_normalization_gradient_of_data_op, batch_normalization_gradient_of_scale_op,
-                        batch_normalization_gradient_of_bias_op, layer_normalization_op)
+                        batch_normalization_gradient_of_bias_op, layer_normalization_op,
+                        batch_normalization_relu_op)
 from ..ops.shape import (array_reshape_op, array_reshape_gradient_op, transpose_op, slice_op,
                          slice_gradient_op, concat_op, concat_gradient_op, pad_op, pad_gradient_op,
                          broadcastto_op, broadcast_shape_op, broadcasttoTF_op, reduce_sum_op,

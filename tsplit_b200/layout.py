@@ -11,7 +11,7 @@ from __future__ import annotations
 IMAGE_OPS = {
     "Conv2d", "Conv2dGradData", "Conv2dGradFilter", "Conv2dBroadcastTo", "MaxPool2d", "AvgPool2d",
     "MaxPool2dGradient", "AvgPool2dGradient", "BatchNorm", "BatchNormGradient", "BatchNormGradData",
-    "BatchNormGradScale", "BatchNormGradBias",
+    "BatchNormGradScale", "BatchNormGradBias", "BatchNormRelu", "BatchNormReluGradient",
 }
 FOLLOW_OPS = {
     "Add", "Mul", "Div", "ReluGradient", "AddConst", "MulConst", "DivConst", "Opposite", "Sqrt", "Rsqrt",

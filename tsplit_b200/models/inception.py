@@ -23,7 +23,7 @@ class _Net(object):
         s = self.p.get(name + "_bn_scale", (1, cout, 1, 1), const=1.0)
         b = self.p.get(name + "_bn_bias", (1, cout, 1, 1), const=0.0)
         x = ad.conv2d_op(x, w, padding=ph, padding2=pw, stride=stride)
-        return ad.relu_op(ad.batch_normalization_op(x, s, b))
+        return ad.batch_normalization_relu_op(x, s, b)
 
 
 def _cat(parts):

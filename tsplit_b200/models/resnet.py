@@ -13,8 +13,7 @@ def conv_bn(p, x, cin, cout, k, stride, pad, name, relu=True):
     scale = p.get(name + "_bn_scale", (1, cout, 1, 1), const=1.0)
     bias = p.get(name + "_bn_bias", (1, cout, 1, 1), const=0.0)
     x = ad.conv2d_op(x, w, padding=pad, stride=stride)
-    x = ad.batch_normalization_op(x, scale, bias)
-    return ad.relu_op(x) if relu else x
+    return ad.batch_normalization_relu_op(x, scale, bias) if relu else ad.batch_normalization_op(x, scale, bias)
 
 
 def bottleneck(p, x, cin, mid, stride, name):

@@ -14,8 +14,7 @@ def conv_bn_relu(p, x, cin, cout, name):
     scale = p.get(name + "_bn_scale", (1, cout, 1, 1), const=1.0)
     bias = p.get(name + "_bn_bias", (1, cout, 1, 1), const=0.0)
     x = ad.conv2d_op(x, w, padding=1, stride=1)
-    x = ad.batch_normalization_op(x, scale, bias)
-    return ad.relu_op(x)
+    return ad.batch_normalization_relu_op(x, scale, bias)
 
 
 def vgg(num_layers=16, num_classes=1000, image=224, width_div=1, fc_width=4096, seed=123):

@@ -194,6 +194,14 @@ class NDArray(object):
         self._block = None
         self.t = None
 
+    def _rebind(self, new_block):
+        """Point this array at its block's new place after the pool was compacted."""
+        shape, strides = tuple(self.t.shape), tuple(self.t.stride())
+        n = self.t.numel()
+        o = int(new_block) // 4
+        self.t = self._pool.arena[o:o + max(n, 1)].as_strided(shape, strides)
+        self._block = int(new_block)
+
     # -- swap state --------------------------------------------------------
     def is_swapout_ok(self):
         return self.gpu2cpu_event.query()

@@ -96,6 +96,67 @@ class BatchNormOp(Op):
         return 8.0 * np.prod(out)
 
 
+class BatchNormReluOp(BatchNormOp):
+    """``relu(batch_norm(x))`` in one pass over the data (the normalise / scale /
+    shift kernel applies the ReLU before it stores), with a backward that masks
+    the incoming gradient by ``y > 0`` on the fly.  Compared with the two-node
+    form this removes one activation tensor and three memory passes per layer."""
+    name = "BatchNormRelu"
+
+    def np_compute(self, node, iv):
+        return np.maximum(BatchNormOp.np_compute(self, node, iv), 0)
+
+    def gpu_compute(self, node, iv, out, stream):
+        x, scale, bias = iv
+        st = node.state
+        c = x.shape[1]
+        if "mean" not in st or st["mean"].shape != (c,):
+            st["mean"], st["invstd"] = _small((c,), x.ctx), _small((c,), x.ctx)
+            st["run_mean"], st["run_var"] = _small((c,), x.ctx, 0.0), _small((c,), x.ctx, 1.0)
+        G.bn_forward(x, scale, bias, out, st["mean"], st["invstd"], st["run_mean"], st["run_var"],
+                     node.attrs["momentum"], node.attrs["eps"], True, stream)
+
+    def gradient(self, node, g):
+        x, scale, bias = node.inputs
+        bg = _bnrg(g, x, scale, node, eps=node.attrs["eps"], fwd=node)
+        return [bg, batch_normalization_gradient_of_scale_op(bg, scale),
+                batch_normalization_gradient_of_bias_op(bg, bias)]
+
+
+class BatchNormReluGradientOp(Op):
+    name = "BatchNormReluGradient"
+
+    def __call__(self, g, x, scale, y, eps=0.01, fwd=None):
+        node = Op.__call__(self, g, x, scale, y, eps=eps, fwd=fwd)
+        node.state = {}
+        return node
+
+    def np_compute(self, node, iv):
+        g, x, scale, y = iv
+        fwd = node.attrs["fwd"]
+        mean, invstd = fwd.state["np_mean"], fwd.state["np_invstd"]
+        dx, ds, db = np_bn_backward(g * (y > 0), x, scale, mean, invstd)
+        node.state["np_dscale"], node.state["np_dbias"] = ds.reshape(scale.shape), db.reshape(scale.shape)
+        return dx
+
+    def gpu_compute(self, node, iv, out, stream):
+        g, x, scale, y = iv
+        fwd, st = node.attrs["fwd"], node.state
+        if "dscale" not in st or st["dscale"].shape != tuple(scale.shape):
+            st["dscale"], st["dbias"] = _small(scale.shape, x.ctx), _small(scale.shape, x.ctx)
+        G.bn_relu_backward(g, x, y, scale, fwd.state["mean"], fwd.state["invstd"], out, st["dscale"],
+                           st["dbias"], stream)
+
+    def gradient(self, node, g):
+        raise NotImplementedError
+
+    def infer_shape(self, node, s):
+        return tuple(s[1])
+
+    def flops(self, node, s, out):
+        return 13.0 * np.prod(out)
+
+
 class BatchNormGradientOp(Op):
     """Computes dx (its output) and keeps dscale / dbias in side buffers that the
     ``..._of_scale`` / ``..._of_bias`` nodes hand out."""
@@ -258,6 +319,7 @@ class LayerNormGradientOp(Op):
         return tuple(s[1])
 
 
+_bnr, _bnrg = BatchNormReluOp(), BatchNormReluGradientOp()
 _bn, _bng, _bngd, _bngs, _bngb = (BatchNormOp(), BatchNormGradientOp(), BatchNormGradDataOp(),
                                   BatchNormGradScaleOp(), BatchNormGradBiasOp())
 _ln, _lng, _lng_data, _lng_scale, _lng_bias = (LayerNormOp(), LayerNormGradientOp(), BatchNormGradDataOp(),
@@ -266,6 +328,11 @@ _ln, _lng, _lng_data, _lng_scale, _lng_bias = (LayerNormOp(), LayerNormGradientO
 
 def batch_normalization_op(node_in, bn_scale, bn_bias, momentum=0.99, eps=0.01):
     return _bn(node_in, bn_scale, bn_bias, momentum, eps)
+
+
+def batch_normalization_relu_op(node_in, bn_scale, bn_bias, momentum=0.99, eps=0.01):
+    """Fused ``relu(batch_normalization(x))`` (extension: no counterpart op in the reference)."""
+    return _bnr(node_in, bn_scale, bn_bias, momentum, eps)
 
 
 def batch_normalization_gradient_op(out_gradient, in_node, bn_scale, eps, fwd=None):

@@ -27,6 +27,7 @@ def _lib():
         lib.tsb_pool_alloc.argtypes = [c_void_p, c_int64, ctypes.POINTER(c_int64)]
         lib.tsb_pool_alloc_high.argtypes = [c_void_p, c_int64, ctypes.POINTER(c_int64)]
         lib.tsb_pool_free.argtypes = [c_void_p, c_int64]
+        lib.tsb_pool_compact.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_int]
         lib.tsb_pool_try.argtypes = [c_void_p, c_int64]
         lib.tsb_pool_stats.argtypes = [c_void_p, ctypes.POINTER(c_int64)]
         lib.tsb_pool_reset_peak.argtypes = [c_void_p]
@@ -57,8 +58,12 @@ class MemoryPool(object):
 
     # -- allocator interface used by ndarray.empty --------------------------------
     def alloc(self, nbytes, long_lived=False):
+        """Long-lived blocks and small blocks (< 1/256 of the pool) are carved from the
+        top, large short-lived activations from the bottom, so the small ones do not
+        pin holes between the large ones."""
         off = c_int64()
-        fn = self.lib.tsb_pool_alloc_high if long_lived else self.lib.tsb_pool_alloc
+        high = long_lived or nbytes * 256 < self.capacity
+        fn = self.lib.tsb_pool_alloc_high if high else self.lib.tsb_pool_alloc
         rc = fn(self.handle, int(nbytes), ctypes.byref(off))
         if rc == 5:
             st = self.stats()
@@ -75,6 +80,24 @@ class MemoryPool(object):
         if self.handle:
             rc = self.lib.tsb_pool_free(self.handle, int(block))
             assert rc == 0, "pool free of unknown block %r" % (block,)
+
+    def compact(self, max_moves=65536):
+        """Defragment: pack all live blocks to the bottom and move their bytes.
+        Returns {old_block: new_block}; holders of views into the arena must re-bind
+        (``NDArray._rebind``).  The caller guarantees that no kernel or copy is in flight."""
+        old = (c_int64 * max_moves)()
+        new = (c_int64 * max_moves)()
+        size = (c_int64 * max_moves)()
+        n = self.lib.tsb_pool_compact(self.handle, old, new, size, max_moves)
+        moves = {}
+        for i in range(n):
+            o, d, b = old[i] // 4, new[i] // 4, size[i] // 4
+            if d + b <= o:
+                self.arena[d:d + b].copy_(self.arena[o:o + b])
+            else:                                   # overlapping ranges: go through a temporary
+                self.arena[d:d + b].copy_(self.arena[o:o + b].clone())
+            moves[int(old[i])] = int(new[i])
+        return moves
 
     def try_alloc(self, nbytes):
         return bool(self.lib.tsb_pool_try(self.handle, int(nbytes)))
