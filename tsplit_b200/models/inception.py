@@ -110,7 +110,7 @@ def inception_v4(num_classes=1000, image=299, width_div=1, seed=123, dropout_kee
     hw = (hw - 3) // 2 + 1; hw = (hw - 3) // 2 + 1
     x = ad.avg_pool2d_op(x, hw, hw, 0, hw)
     x = ad.array_reshape_op(x, (-1, ch))
-    x = ad.dropout_op(x, dropout_keep)
+    x = ad.dropout_op(x, dropout_keep, seed=seed + 17)
     w = p.he("incep_fc_weight", (ch, num_classes), ch)
     y = ad.matmul_op(x, w)
     loss = ad.softmaxcrossentropy_op(y, y_)
