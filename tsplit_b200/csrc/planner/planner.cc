@@ -262,6 +262,7 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
   std::vector<int> cls(n, KEEP), split(n, 1), prefetch(n, -1);
   Result r = simulate(g, cls, split, prefetch);
   int guard = 0;
+  double link_ms = 0.0;     // host-link time already committed to earlier swap decisions
   while (r.first_over >= 0 && guard++ < 4 * n) {
     const int pos = r.peak_pos >= 0 ? r.first_over : r.first_over;
     // candidates: managed KEEP tensors that are alive but idle at `pos`
@@ -274,7 +275,8 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
       double idle = 0.0;
       for (int i = g.last_fwd_use[t] + 1; i < g.first_bwd_use[t]; ++i) idle += time_ms[i];
       const double xfer = 2.0 * (double)out_bytes[t] / g.bw;
-      const double swap_cost = std::max(0.0, xfer - idle) + 0.02 * xfer;     // link is shared: small tax
+      // the link is shared: what earlier decisions already occupy cannot hide this transfer
+      const double swap_cost = std::max(0.0, link_ms + xfer - idle) + 0.05 * xfer;
       double rec_cost = std::numeric_limits<double>::infinity();
       if (g.recomputable[t]) {
         int uses_bwd = 0;
@@ -289,6 +291,7 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
     if (best < 0) break;      // the peak is this op's own working set: nothing idle left to evict
     cls[best] = best_cls;
     if (best_cls == SWAP) {
+      link_ms += 2.0 * (double)out_bytes[best] / g.bw;
       // micro-tensor split: pipeline the transfer when it would otherwise be exposed
       const double xfer = (double)out_bytes[best] / g.bw;
       int k = 1;

@@ -127,6 +127,7 @@ class MemoryExecutor(Executor):
         self.pending = []             # (event, NDArray) device arrays waiting for their D2H copy
         self.swapin_event = {}        # node -> event of an in-flight H2D copy
         self.lru = OrderedDict()      # lazy-evict cache: node -> True (MRU last)
+        self._prefetch_queue = []
         self.locked = set()
         self.stats = dict(swap_out_bytes=0, swap_in_bytes=0, recomputed_nodes=0, evictions=0,
                           peak_bytes=0, prefetch_hits=0, on_demand_swapins=0)
@@ -386,15 +387,25 @@ class MemoryExecutor(Executor):
             if isinstance(node.op, PlaceholderOp):
                 self.arr[node] = self._placeholder_value(node)
                 continue
-            for t in self.prefetch_at.get(idx, ()):
-                if t in self.host and t not in self.arr and self._room_for_prefetch(t, idx):
+            # prefetches that found no room stay queued and are retried before every later node
+            self._prefetch_queue.extend(self.prefetch_at.get(idx, ()))
+            if self._prefetch_queue:
+                self._reap(False)
+                waiting = []
+                for t in self._prefetch_queue:
+                    if t not in self.host or t in self.arr:
+                        continue
+                    if waiting or not self._room_for_prefetch(t, idx):
+                        waiting.append(t)          # keep the order: earlier uses first
+                        continue
                     self._no_spill = True
                     try:
                         self._swap_in(t, prefetch=True)
                     except OutOfHBMBudget:
-                        pass                       # no room yet: it will be fetched on demand
+                        waiting.append(t)
                     finally:
                         self._no_spill = False
+                self._prefetch_queue = waiting
             temps = []
             for i in node.inputs:
                 self._ensure(i, temps)
@@ -410,13 +421,15 @@ class MemoryExecutor(Executor):
 
     def _room_for_prefetch(self, t, idx):
         """Prefetch only when the pool keeps head-room for what the schedule
-        allocates before ``t`` is used (twice the largest output on the way)."""
+        allocates before ``t`` is used (the largest output on the way)."""
         pool = ndarray.get_pool(self.ctx)
         if pool is None:
             return True
         use = self.first_bwd_use.get(t) or idx
         reserve = max((self.tensor_bytes(n) for n in self.topo_order[idx:use + 1]), default=0)
-        return pool.stats()["free"] >= self.tensor_bytes(t) + 2 * reserve
+        st = pool.stats()
+        need = self.tensor_bytes(t)
+        return st["largest_free"] >= need and st["free"] >= need + reserve
 
     def _after_node(self, idx, node, temps):
         # forward: offload / drop policy-managed tensors at their last forward use
