@@ -52,6 +52,8 @@ def parse_args():
     p.add_argument("--max-batch", type=int, default=256, help="upper bound of the max-batch search")
     p.add_argument("--host-link-gbs", type=float, default=45.0)
     p.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    p.add_argument("--plan-frac", type=float, default=0.9,
+                   help="fraction of the cap the planner may fill (the rest absorbs fragmentation)")
     return p.parse_args()
 
 
@@ -125,7 +127,8 @@ def make_executor(args, model, train_op, ctx):
     if pol == "base":
         return ad.MemoryExecutor(nodes, ctx=ctx)
     if pol == "tsplit":
-        return ad.microopExecutor(nodes, ctx=ctx, host_link_gbs=args.host_link_gbs)
+        return ad.microopExecutor(nodes, ctx=ctx, host_link_gbs=args.host_link_gbs,
+                                  budget_bytes=int(args.cap_gib * 2**30 * args.plan_frac))
     if pol in ("vdnnall", "vdnnconv"):
         return ad.vdnnExecutor(nodes, ctx=ctx, policy=pol[4:])
     if pol.startswith("recompute"):
@@ -144,7 +147,7 @@ def find_max_batch(args, model, train_op, ctx, cap_bytes):
         return args.max_batch
 
     def fits(b):
-        sim = ad.microopOptimizer(nodes, ctx=ctx, budget_bytes=int(cap_bytes * 0.9),
+        sim = ad.microopOptimizer(nodes, ctx=ctx, budget_bytes=int(cap_bytes * args.plan_frac),
                                   host_link_gbs=args.host_link_gbs)
         x = np.empty((b,) + model.input_shape, dtype=np.float32)
         y = np.empty((b, model.num_classes), dtype=np.float32)

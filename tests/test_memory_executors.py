@@ -11,7 +11,7 @@ from helpers import assert_close
 
 
 def small_cnn():
-    return vgg(16, num_classes=10, image=32, width_div=8, fc_width=64, seed=3)
+    return vgg(16, num_classes=10, image=64, width_div=8, fc_width=64, seed=3)
 
 
 def reference_run(model_fn, batch, steps=2):

@@ -197,7 +197,10 @@ Result simulate(const Graph& g, const std::vector<int>& cls, const std::vector<i
   return r;
 }
 
-void place_prefetch(const Graph& g, const std::vector<int>& cls, std::vector<int>& prefetch_at) {
+// min_trigger[t] (when >= 0): a tensor swapped to relieve a backward position must not be fetched
+// back before that position has passed.
+void place_prefetch(const Graph& g, const std::vector<int>& cls, std::vector<int>& prefetch_at,
+                    const std::vector<int>& min_trigger) {
   // cumulative compute time per position
   std::vector<double> t0(g.n + 1, 0.0);
   for (int i = 0; i < g.n; ++i) t0[i + 1] = t0[i] + g.time_ms[i];
@@ -211,6 +214,7 @@ void place_prefetch(const Graph& g, const std::vector<int>& cls, std::vector<int
     const int use = g.first_bwd_use[t];
     int trig = use;
     while (trig > g.first_bwd && t0[use] - t0[trig] < need * 1.25) --trig;
+    if (min_trigger[t] >= 0 && trig < min_trigger[t]) trig = std::min(min_trigger[t], use);
     const double start = std::max(link_free, t0[trig]);
     link_free = start + need;
     prefetch_at[t] = trig;
@@ -263,45 +267,64 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
   Result r = simulate(g, cls, split, prefetch);
   int guard = 0;
   double link_ms = 0.0;     // host-link time already committed to earlier swap decisions
+  std::vector<char> tried_drop(n, 0);
+  std::vector<int> min_trigger(n, -1);
   while (r.first_over >= 0 && guard++ < 4 * n) {
     const int pos = r.peak_pos >= 0 ? r.first_over : r.first_over;
-    // candidates: managed KEEP tensors that are alive but idle at `pos`
-    int best = -1, best_cls = KEEP;
-    double best_score = -1.0;
+    // candidates: managed KEEP tensors that are alive but idle at `pos`, scored by bytes saved per
+    // millisecond of added step time for their cheaper option
+    struct Cand { double score; int t; int cls; };
+    std::vector<Cand> cands;
     for (int t = 0; t < n; ++t) {
       if (!g.managed[t] || cls[t] != KEEP || out_bytes[t] <= 0) continue;
       if (!(t < pos && g.last_fwd_use[t] < pos && g.first_bwd_use[t] > pos)) continue;   // idle across pos
-      // swap: exposed cost = what the idle window cannot hide (split later shrinks it further)
       double idle = 0.0;
       for (int i = g.last_fwd_use[t] + 1; i < g.first_bwd_use[t]; ++i) idle += time_ms[i];
       const double xfer = 2.0 * (double)out_bytes[t] / g.bw;
       // the link is shared: what earlier decisions already occupy cannot hide this transfer
       const double swap_cost = std::max(0.0, link_ms + xfer - idle) + 0.05 * xfer;
-      double rec_cost = std::numeric_limits<double>::infinity();
-      if (g.recomputable[t]) {
+      cands.push_back({(double)out_bytes[t] / (swap_cost + 1e-3), t, SWAP});
+      if (g.recomputable[t] && !tried_drop[t]) {
         int uses_bwd = 0;
         for (int i = g.first_bwd; i < n; ++i)
           for (int e = in_ptr[i]; e < in_ptr[i + 1]; ++e) uses_bwd += (in_idx[e] == t);
-        rec_cost = rebuild_ms(g, cls, t) * std::max(1, std::min(uses_bwd, 2));
+        const double rec_cost = rebuild_ms(g, cls, t) * std::max(1, std::min(uses_bwd, 2));
+        cands.push_back({(double)out_bytes[t] / (rec_cost + 1e-3), t, DROP});
       }
-      const double cost = std::min(swap_cost, rec_cost);
-      const double score = (double)out_bytes[t] / (cost + 1e-3);
-      if (score > best_score) { best_score = score; best = t; best_cls = rec_cost < swap_cost ? DROP : SWAP; }
     }
-    if (best < 0) break;      // the peak is this op's own working set: nothing idle left to evict
-    cls[best] = best_cls;
-    if (best_cls == SWAP) {
-      link_ms += 2.0 * (double)out_bytes[best] / g.bw;
-      // micro-tensor split: pipeline the transfer when it would otherwise be exposed
-      const double xfer = (double)out_bytes[best] / g.bw;
+    std::sort(cands.begin(), cands.end(), [](const Cand& a, const Cand& b) { return a.score > b.score; });
+    bool accepted = false;
+    for (size_t ci = 0; ci < cands.size() && ci < 24 && !accepted; ++ci) {
+      const int t = cands[ci].t;
+      if (cls[t] != KEEP) continue;
+      cls[t] = cands[ci].cls;
       int k = 1;
-      while (k < max_split && xfer / k > 0.25 && g.splittable[best]) k *= 2;
-      split[best] = k;
+      if (cands[ci].cls == SWAP) {
+        // micro-tensor split: pipeline the transfer when it would otherwise be exposed
+        const double xfer1 = (double)out_bytes[t] / g.bw;
+        while (k < max_split && xfer1 / k > 0.25 && g.splittable[t]) k *= 2;
+      }
+      split[t] = k;
+      const int saved_trigger = min_trigger[t];
+      if (cands[ci].cls == SWAP && pos >= g.first_bwd) min_trigger[t] = pos + 1;
+      place_prefetch(g, cls, prefetch, min_trigger);
+      Result trial = simulate(g, cls, split, prefetch);
+      // keep the decision only when it relieves the position that was over budget
+      const bool better = trial.first_over < 0 || trial.first_over > pos || trial.mem_at[pos] < r.mem_at[pos];
+      if (better) {
+        if (cands[ci].cls == SWAP) link_ms += 2.0 * (double)out_bytes[t] / g.bw;
+        r = trial;
+        accepted = true;
+      } else {
+        if (cands[ci].cls == DROP) tried_drop[t] = 1;   // rebuilding it only moves the bytes to its inputs
+        cls[t] = KEEP;
+        split[t] = 1;
+        min_trigger[t] = saved_trigger;
+      }
     }
-    place_prefetch(g, cls, prefetch);
-    r = simulate(g, cls, split, prefetch);
+    if (!accepted) break;      // the peak is the op's own working set: nothing idle left to evict
   }
-  place_prefetch(g, cls, prefetch);
+  place_prefetch(g, cls, prefetch, min_trigger);
   r = simulate(g, cls, split, prefetch);
   std::memcpy(cls_out, cls.data(), sizeof(int) * n);
   std::memcpy(split_out, split.data(), sizeof(int) * n);

@@ -75,6 +75,9 @@ class microopExecutor(MemoryExecutor):
         self.max_split = int(max_split)
         self.plan_result = None
         self.split = {}
+        #: every forward op may be rebuilt (the planner prices it by the op's time); False restricts
+        #: recomputation to the cheap, memory-bound operators
+        self.recompute_any = True
 
     # ------------------------------------------------------------------ planning
     def _budget(self):
@@ -97,7 +100,7 @@ class microopExecutor(MemoryExecutor):
             time_ms.append(float(ms.get(n, 0.0)))
             phase.append(0 if self.is_fwd[n] else 1)
             mg.append(1 if n in managed else 0)
-            rc.append(1 if n.op.name in RECOMPUTABLE else 0)
+            rc.append(1 if (n.op.name in RECOMPUTABLE or self.recompute_any) else 0)
             batch_like = self.node_to_shape_map[n] is not None and len(self.node_to_shape_map[n]) >= 1
             sp.append(1 if batch_like else 0)
             try:

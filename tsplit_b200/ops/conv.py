@@ -95,8 +95,12 @@ class Conv2dOp(Op):
         return (n, o, oh, ow)
 
     def flops(self, node, s, out):
+        """Effective work for the cost model: thin reductions (few input channels)
+        run below the tensor-core rate, so they are charged proportionally more."""
         o, c, kh, kw = s[1]
-        return 2.0 * out[0] * out[2] * out[3] * o * c * kh * kw
+        k = c * kh * kw
+        eff = min(1.0, (k / 1536.0) ** 0.5) * min(1.0, (o / 256.0) ** 0.5)
+        return 2.0 * out[0] * out[2] * out[3] * o * c * kh * kw / max(eff, 0.05)
 
     def workspace_bytes(self, node, s, out):
         return 0

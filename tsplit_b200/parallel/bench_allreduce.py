@@ -1,0 +1,120 @@
+"""Bandwidth of the fused all-reduce + momentum-SGD + parameter-broadcast kernel
+against its NVLink roofline, and against the NCCL all-reduce + separate update it
+replaces.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
+        --master-port 29555 -m tsplit_b200.parallel.bench_allreduce --mb 100 400
+
+For a bucket of S bytes on N GPUs the fused kernel moves S*(N-1)/N bytes in
+(gradient shards read from peers) and S*(N-1)/N bytes out (new parameters stored
+to peers) per GPU; both directions run concurrently, so the link-time floor is
+S*(N-1)/N divided by the per-direction peer bandwidth (770 GB/s measured copy,
+900 GB/s nominal).  Timed on the device with CUDA events, max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import ndarray
+from ..graph import Node
+from ..stream import current_stream
+from .fused_allreduce import FusedCommunicator
+
+LINK_GBS_MEASURED = 770.0
+
+
+class _Opt(object):
+    """The three things the communicator needs from an optimizer."""
+    kind, initial_accumulator_value = 1, 0.0
+
+    def __init__(self, n, ctx):
+        node = Node()
+        node.tensor_value = ndarray.empty((n,), ctx, use_pool=False)
+        node.tensor_value.t.normal_()
+        self.tensors = [node]
+
+    @property
+    def params(self):
+        return [n.tensor_value for n in self.tensors]
+
+    def hyper(self):
+        return [0.01, 0.9]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mb", type=float, nargs="+", default=[100.0, 553.0])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--nvls", type=int, default=0, help="1 = multimem.ld_reduce / multimem.st through NVSwitch")
+    args = ap.parse_args()
+    rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world = dist.get_world_size()
+    ctx = ndarray.gpu(local)
+    st = current_stream(ctx)
+    for mb in args.mb:
+        n = int(mb * 2**20 / 4) // (4 * world) * (4 * world)
+        opt = _Opt(n, ctx)
+        comm = FusedCommunicator(opt, dist, use_multimem=bool(args.nvls))
+        grad = ndarray.empty((n,), ctx, use_pool=False)
+        grad.t.normal_()
+        # the kernel proper (gradients already in the bucket): time launches back to back
+        comm.grad_bucket.copy_(grad.t)
+
+        def fused_once():
+            comm.epoch += 1
+            from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
+            hv = (c_float * 8)(0.01, 0.9, 0, 0, 0, 0, 0, 0)
+            rc = comm.lib.tsb_fused_allreduce_update(
+                c_int(1), c_int(comm.rank), c_int(comm.world), comm.grad_ptrs, comm.param_ptrs, comm.flag_ptrs,
+                c_void_p(comm.grad_mc), c_void_p(comm.param_mc), c_void_p(comm.slot1.data_ptr()),
+                c_void_p(comm.slot2.data_ptr()), c_longlong(comm.n), hv, c_uint(comm.epoch), c_void_p(st.handle))
+            assert rc == 0, rc
+
+        vel = torch.zeros(n, device="cuda")
+        par = torch.randn(n, device="cuda")
+
+        def nccl_once():
+            dist.all_reduce(grad.t)
+            grad.t.mul_(1.0 / world)
+            vel.mul_(0.9).add_(grad.t, alpha=-0.01)
+            par.add_(vel)
+
+        results = {}
+        for name, fn in (("fused", fused_once), ("nccl+update", nccl_once)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1) / args.iters], device="cuda")
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            results[name] = float(ms.item())
+        comm.check(st)
+        if rank == 0:
+            s_bytes = n * 4
+            floor_ms = s_bytes * (world - 1) / world / (LINK_GBS_MEASURED * 1e6)
+            bus = 2.0 * s_bytes * (world - 1) / world / (results["fused"] * 1e6)
+            print(json.dumps({"bucket_mb": round(s_bytes / 2**20, 1), "world": world, "nvls": args.nvls,
+                              "fused_ms": round(results["fused"], 4), "nccl_plus_update_ms":
+                              round(results["nccl+update"], 4), "link_floor_ms": round(floor_ms, 4),
+                              "fraction_of_link_roofline_of_measured": round(floor_ms / results["fused"], 3),
+                              "bus_gbs": round(bus, 1)}))
+        del comm, opt
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
