@@ -310,7 +310,9 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
       place_prefetch(g, cls, prefetch, min_trigger);
       Result trial = simulate(g, cls, split, prefetch);
       // keep the decision only when it relieves the position that was over budget
-      const bool better = trial.first_over < 0 || trial.first_over > pos || trial.mem_at[pos] < r.mem_at[pos];
+      // ... and does not raise the peak somewhere else (a long rebuild chain in backward can)
+      const bool better = trial.first_over < 0 ||
+                          ((trial.first_over > pos || trial.mem_at[pos] < r.mem_at[pos]) && trial.peak <= r.peak);
       if (better) {
         if (cands[ci].cls == SWAP) link_ms += 2.0 * (double)out_bytes[t] / g.bw;
         r = trial;

@@ -429,7 +429,16 @@ class MemoryExecutor(Executor):
         reserve = max((self.tensor_bytes(n) for n in self.topo_order[idx:use + 1]), default=0)
         st = pool.stats()
         need = self.tensor_bytes(t)
-        return st["largest_free"] >= need and st["free"] >= need + reserve
+        if st["largest_free"] < need:
+            return False
+        plan_budget = self.planning_budget()
+        if plan_budget is not None:          # same rule as the planner's simulator
+            return st["used"] + need + 2 * reserve <= plan_budget
+        return st["free"] >= need + reserve
+
+    def planning_budget(self):
+        """Bytes the plan was made for (None: no plan-level budget)."""
+        return None
 
     def _after_node(self, idx, node, temps):
         # forward: offload / drop policy-managed tensors at their last forward use

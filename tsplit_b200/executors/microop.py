@@ -86,6 +86,9 @@ class microopExecutor(MemoryExecutor):
         pool = ndarray.get_pool(self.ctx)
         return int(pool.capacity * 0.9) if pool is not None else 1 << 62
 
+    def planning_budget(self):
+        return self._budget()
+
     def _graph_arrays(self):
         order = self.topo_order
         idx = self.index
