@@ -24,7 +24,7 @@ constexpr int BM = 128;
 constexpr int BK = 32;
 constexpr int UMMA_K = 8;
 constexpr int A_STAGE_BYTES = BM * BK * 4;
-constexpr int LAG = 2;                 // cp.async groups in flight per gather thread
+constexpr int LAG = 2;                 // cp.async groups in flight per gather thread (measured: 3 starves the MMA of ready stages)
 constexpr int NUM_THREADS = 320;       // warp0 TMA, warp1 MMA, warps2-5 epilogue, warps6-9 gather
 
 struct ConvParams {
@@ -514,11 +514,21 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.NC + bn - 1) / bn;
   if (kind == 2) {
+    // split the pixel reduction so that the work items fill whole waves of CTAs
     const long long tiles = (long long)p.tiles_m * p.tiles_n * p.taps;
-    int splits = (int)((2ll * sm_count() + tiles - 1) / tiles);
-    if (splits > p.kblocks / 4) splits = p.kblocks / 4;
-    if (splits > 64) splits = 64;
-    if (splits < 1) splits = 1;
+    const int sms = sm_count();
+    int splits = 1;
+    double best_eff = 0.0;
+    for (int waves = 1; waves <= 4; ++waves) {
+      int s = (int)((long long)waves * sms / tiles);
+      if (s < 1) s = 1;
+      if (s > p.kblocks / 4) s = p.kblocks / 4 > 0 ? p.kblocks / 4 : 1;
+      if (s > 64) s = 64;
+      const long long items = tiles * s;
+      const double eff = (double)items / (double)(((items + sms - 1) / sms) * sms);
+      // prefer more waves only when they are clearly better balanced (each split costs a partial-sum pass)
+      if (eff > best_eff + 0.04) { best_eff = eff; splits = s; }
+    }
     const int per = (p.kblocks + splits - 1) / splits;
     p.splits = (p.kblocks + per - 1) / per;
     if (p.splits > 1) {

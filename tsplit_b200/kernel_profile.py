@@ -75,11 +75,66 @@ def sweep(op, axis, points=None):
     return rows
 
 
+def single(op, batch, channel, hw, iters):
+    """One configuration, ``iters`` launches after one warm-up: the small case a
+    profiler capture is taken on.  Prints ms and the achieved rate."""
+    import torch
+    from . import ndarray
+    from .ops import _gpu as G
+    from .stream import current_stream
+    ctx = ndarray.gpu(0)
+    st = current_stream(ctx)
+    n, c = batch, channel
+    if op == "matmul":
+        m = batch * 64
+        a, b, out = (ndarray.empty(s, ctx) for s in ((m, c * 8), (c * 8, c * 8), (m, c * 8)))
+        a.t.normal_(), b.t.normal_()
+        fn = lambda: G.gemm(a, b, out, False, False, st, m=m, n=c * 8, k=c * 8, lda=c * 8, ldb=c * 8, ldc=c * 8)
+        work, unit = 2.0 * m * (c * 8) ** 2 / 1e9, "TFLOP/s"
+    else:
+        x = ndarray.empty((n, c, hw, hw), ctx)
+        y = ndarray.empty((n, c, hw, hw), ctx)
+        x.t.normal_(), y.t.normal_()
+        if op.startswith("conv"):
+            w = ndarray.empty((c, c, 3, 3), ctx)
+            w.t.normal_()
+            kind = {"conv_fwd": 0, "conv_dgrad": 1, "conv_wgrad": 2}[op]
+            fn = lambda: G.conv2d(kind, x, w, y, 1, 1, 1, st)
+            work, unit = 2.0 * n * hw * hw * c * c * 9 / 1e9, "TFLOP/s"
+        else:
+            s_, b_ = ndarray.empty((1, c, 1, 1), ctx), ndarray.empty((1, c, 1, 1), ctx)
+            s_.t.fill_(1.0), b_.t.zero_()
+            stats = [ndarray.empty((c,), ctx) for _ in range(4)]
+            G.bn_forward(x, s_, b_, y, stats[0], stats[1], stats[2], stats[3], 0.99, 0.01, True, st)
+            if op == "bn":
+                fn = lambda: G.bn_forward(x, s_, b_, y, stats[0], stats[1], stats[2], stats[3], 0.99, 0.01, True, st)
+                work, unit = 3.0 * x.nbytes / 1e6, "GB/s"
+            else:   # bnrelu_bwd
+                dx = ndarray.empty((n, c, hw, hw), ctx)
+                ds, db = ndarray.empty((1, c, 1, 1), ctx), ndarray.empty((1, c, 1, 1), ctx)
+                g = ndarray.empty((n, c, hw, hw), ctx)
+                g.t.normal_()
+                fn = lambda: G.bn_relu_backward(g, x, y, s_, stats[0], stats[1], dx, ds, db, stream=st)
+                work, unit = 7.0 * x.nbytes / 1e6, "GB/s"
+    ms = _time(fn, iters)
+    print("%s batch=%d channel=%d hw=%d: %.4f ms, %.1f %s" % (op, batch, channel, hw, ms, work / ms, unit))
+    return ms
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu"])
+    p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu", "conv_fwd", "conv_dgrad",
+                                  "conv_wgrad", "bnrelu_bwd"])
     p.add_argument("--sweep", default="batch", choices=["batch", "channel", "hw"])
+    p.add_argument("--single", action="store_true", help="one configuration (for profiler captures)")
+    p.add_argument("--batch", type=int, default=32)
+    p.add_argument("--channel", type=int, default=256)
+    p.add_argument("--hw", type=int, default=56)
+    p.add_argument("--iters", type=int, default=3)
     a = p.parse_args()
+    if a.single or a.op in ("conv_fwd", "conv_dgrad", "conv_wgrad", "bnrelu_bwd"):
+        single(a.op if a.op != "conv2d" else "conv_fwd", a.batch, a.channel, a.hw, a.iters)
+        return
     for v, ms, rate, unit in sweep(a.op, a.sweep):
         print("%s=%-6d %9.4f ms  %9.1f %s" % (a.sweep, v, ms, rate, unit))
 
