@@ -5,7 +5,7 @@
 //   mode 2  wgrad   : dw[o,kh,kw,c] = sum_{n,oh,ow} dy[n,oh,ow,o] * x[n,oh*s-ph+kh,ow*s-pw+kw,c]
 //
 // No im2col buffer exists anywhere.  The patch operand is gathered straight into
-// swizzled shared memory by four cp.async producer warps (zero-fill for padding
+// swizzled shared memory by eight cp.async producer warps (zero-fill for padding
 // and tails); the dense operand (filters, or dy for wgrad) arrives by TMA; one
 // elected thread issues tcgen05.mma.kind::tf32 into double-buffered TMEM
 // accumulators; four epilogue warps drain TMEM to global while the next tile is
@@ -25,7 +25,9 @@ constexpr int BK = 32;
 constexpr int UMMA_K = 8;
 constexpr int A_STAGE_BYTES = BM * BK * 4;
 constexpr int LAG = 2;                 // cp.async groups in flight per gather thread (measured: 3 starves the MMA of ready stages)
-constexpr int NUM_THREADS = 320;       // warp0 TMA, warp1 MMA, warps2-5 epilogue, warps6-9 gather
+constexpr int GATHER_WARPS = 8;        // two per scheduler, so one warp's address arithmetic hides the other's
+constexpr int GATHER_THREADS = GATHER_WARPS * 32;
+constexpr int NUM_THREADS = 6 * 32 + GATHER_THREADS;   // warp0 TMA, warp1 MMA, warps2-5 epilogue, then gather
 
 struct ConvParams {
   const float* src;    // gathered tensor: x (fwd, wgrad) or dy (dgrad)
@@ -103,7 +105,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&full[s], 1 + 4);      // TMA expect_tx arrive + one arrive per gather warp
+      mbar_init(&full[s], 1 + GATHER_WARPS);   // TMA expect_tx arrive + one arrive per gather warp
       mbar_init(&empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -249,8 +251,13 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
   } else {
-    // ---------------------------------------------------------------- gather producers (warps 6..9)
-    const int t = threadIdx.x - 6 * 32;       // 0..127
+    // ---------------------------------------------------------------- gather producers (warps 6..)
+    // The loop over k-blocks is kept short on purpose: with few warps per scheduler the chain of
+    // dependent address instructions, not the memory system, bounds the rate of k-blocks.  So
+    // everything that depends only on the tile (row origins, which filter taps fall inside the
+    // image, shared-memory offsets) is computed once per tile, and the (tap, channel) position
+    // advances incrementally instead of being divided out of k.
+    const int t = threadIdx.x - 6 * 32;       // 0..GATHER_THREADS-1
     uint32_t it = 0;                          // k-blocks issued by this thread
     uint32_t arrived = 0;                     // k-blocks whose data this warp has published
     bool ok = true;
@@ -261,19 +268,26 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
         if (lane == 0) mbar_arrive(&full[arrived % C::STAGES]);
       }
     };
+    const int ntaps = p.KH * p.KW;
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const Item w = decode_item(p, item, BN);
       if (MODE == 0 || MODE == 1) {
-        // A tile: 128 rows (pixels) x 32 k, K-major, 128B swizzle.  Thread owns 16B chunk j of rows rg+16i.
+        // A tile: 128 rows (pixels) x 32 k, K-major, 128B swizzle.  Thread owns 16B chunk j of rows rg+32i.
+        constexpr int RPT = BM / (GATHER_THREADS / 8);   // rows per thread
+        constexpr int RSTEP = GATHER_THREADS / 8;
         const int j = t & 7, rg = t >> 3;
+        const uint32_t soff = (uint32_t)(rg * 128 + ((j ^ (rg & 7)) << 4));   // (rg + RSTEP*i) & 7 == rg & 7
         const int PH = (MODE == 0) ? p.OH : p.H, PW = (MODE == 0) ? p.OW : p.W;   // pixel grid of the rows
         const int SH = (MODE == 0) ? p.H : p.OH, SW = (MODE == 0) ? p.W : p.OW;   // grid of the gathered tensor
         const int SC = (MODE == 0) ? p.C : p.O;                                   // its channel count
-        const float* rowptr[8];        // origin of the row's patch (may point outside; never read when invalid)
-        int a0[8], b0[8];
+        const bool masked = ntaps <= 64 && (MODE == 0 || p.stride == 1);
+        const float* rowptr[RPT];      // origin of the row's patch (may point outside; never read when invalid)
+        int a0[RPT], b0[RPT];
+        unsigned long long vmask[RPT]; // bit tap = that filter tap reads inside the image for this row
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int pix = w.m0 + rg + 16 * i;
+        for (int i = 0; i < RPT; ++i) {
+          const int pix = w.m0 + rg + RSTEP * i;
+          vmask[i] = 0;
           if (pix < p.M) {
             const int n = pix / (PH * PW);
             const int rem = pix - n * (PH * PW);
@@ -284,70 +298,102 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
               rowptr[i] = p.src + (((long long)n * SH + a0[i]) * SW + b0[i]) * SC;
             else
               rowptr[i] = p.src + (long long)n * SH * SW * SC;
+            if (masked) {
+              unsigned long long colm = 0;
+              for (int kw = 0; kw < p.KW; ++kw) {
+                const int xx = (MODE == 0) ? b0[i] + kw : b0[i] - kw;
+                if ((unsigned)xx < (unsigned)SW) colm |= 1ull << kw;
+              }
+              for (int kh = 0; kh < p.KH; ++kh) {
+                const int yy = (MODE == 0) ? a0[i] + kh : a0[i] - kh;
+                if ((unsigned)yy < (unsigned)SH) vmask[i] |= colm << (kh * p.KW);
+              }
+            }
           } else {
             rowptr[i] = p.src; a0[i] = -(1 << 28); b0[i] = -(1 << 28);
           }
         }
+        // (tap, channel) position of this thread's chunk at the first k-block
+        int tap, kh, kw, ch, ob = 0;
+        if (MODE == 0) {
+          const int k = w.kb0 * BK + j * 4;
+          tap = k / p.C; ch = k - tap * p.C;
+        } else {
+          tap = w.kb0 / p.ocb; ob = w.kb0 - tap * p.ocb;
+          ch = ob * BK + j * 4;
+        }
+        kh = tap / p.KW; kw = tap - kh * p.KW;
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x205)) { ok = false; break; }
-          int kh, kw, ch;
-          bool kvalid;
-          if (MODE == 0) {
-            const int k = kb * BK + j * 4;
-            kvalid = k < p.K;
-            const int tap = k / p.C;
-            ch = k - tap * p.C;
-            kh = tap / p.KW; kw = tap - kh * p.KW;
-          } else {
-            const int tap = kb / p.ocb;
-            ch = (kb - tap * p.ocb) * BK + j * 4;
-            kvalid = ch < p.O;
-            kh = tap / p.KW; kw = tap - kh * p.KW;
-          }
+          const bool kvalid = (MODE == 0) ? (tap < ntaps) : (ch < p.O);
           // element offset of this k-chunk relative to the row origin
           const int delta = (MODE == 0) ? (kh * SW + kw) * SC + ch : -((kh * SW + kw) * SC) + ch;
-          const uint32_t sdst = smem_u32(smem_a + s * A_STAGE_BYTES);
+          const uint32_t sdst = smem_u32(smem_a + s * A_STAGE_BYTES) + soff;
+          if (masked) {
+            const int sh = tap & 63;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = rg + 16 * i;
-            bool v = kvalid;
-            const float* src;
-            if (MODE == 0) {
-              v = v && (unsigned)(a0[i] + kh) < (unsigned)SH && (unsigned)(b0[i] + kw) < (unsigned)SW;
-              src = rowptr[i] + delta;
-            } else if (p.stride == 1) {
-              v = v && (unsigned)(a0[i] - kh) < (unsigned)SH && (unsigned)(b0[i] - kw) < (unsigned)SW;
-              src = rowptr[i] + delta;
-            } else {
-              const int ty = a0[i] - kh, tx = b0[i] - kw;
-              const int yy = ty / p.stride, xx = tx / p.stride;
-              v = v && ty >= 0 && tx >= 0 && (yy * p.stride == ty) && (xx * p.stride == tx) &&
-                  yy < SH && xx < SW;
-              src = rowptr[i] + ((long long)yy * SW + xx) * SC + ch;
+            for (int i = 0; i < RPT; ++i) {
+              const bool v = kvalid && ((vmask[i] >> sh) & 1ull);
+              cp_async16(sdst + i * (RSTEP * 128), v ? rowptr[i] + delta : p.src, v);
             }
-            cp_async16(sdst + r * 128 + ((j ^ (r & 7)) << 4), v ? src : p.src, v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) {
+              bool v = kvalid;
+              const float* src;
+              if (MODE == 0) {
+                v = v && (unsigned)(a0[i] + kh) < (unsigned)SH && (unsigned)(b0[i] + kw) < (unsigned)SW;
+                src = rowptr[i] + delta;
+              } else if (p.stride == 1) {
+                v = v && (unsigned)(a0[i] - kh) < (unsigned)SH && (unsigned)(b0[i] - kw) < (unsigned)SW;
+                src = rowptr[i] + delta;
+              } else {
+                const int ty = a0[i] - kh, tx = b0[i] - kw;
+                const int yy = ty / p.stride, xx = tx / p.stride;
+                v = v && ty >= 0 && tx >= 0 && (yy * p.stride == ty) && (xx * p.stride == tx) &&
+                    yy < SH && xx < SW;
+                src = rowptr[i] + ((long long)yy * SW + xx) * SC + ch;
+              }
+              cp_async16(sdst + i * (RSTEP * 128), v ? src : p.src, v);
+            }
           }
           cp_async_commit();
           if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
+          // advance to the next k-block
+          if (MODE == 0) {
+            ch += BK;
+            while (ch >= p.C) {
+              ch -= p.C; ++tap;
+              if (++kw == p.KW) { kw = 0; ++kh; }
+            }
+          } else {
+            ch += BK;
+            if (++ob == p.ocb) {
+              ob = 0; ch = j * 4; ++tap;
+              if (++kw == p.KW) { kw = 0; ++kh; }
+            }
+          }
         }
       } else {
         // wgrad B tile: 32 rows (pixels = k) x BN columns, MN-major, 128B swizzle with 32B atoms.
         // Columns are the flattened (tap, channel) index, so one tile spans several filter taps and
-        // the dy tile is shared between them.  Thread owns pixel row t/4 and every 4th 16-byte piece.
-        constexpr int PPT = BN / 16;           // pieces per thread
-        const int kr = t >> 2, sub = t & 3;
+        // the dy tile is shared between them.  Thread owns pixel row t/8 and 16-byte piece t%8 of
+        // every 32-column chunk, so its swizzled position inside a chunk is a per-thread constant.
+        constexpr int PPT = BN / 32;           // pieces per thread = 32-column chunks of the tile
+        const int kr = t >> 3, sub = t & 7;
         const int mpix = p.N * p.OH * p.OW;
+        const bool masked = ntaps <= 64;
         int poff[PPT];                         // element offset of the piece relative to the row's origin
-        int ptap[PPT];                         // (kh << 16) | kw, or -1 when the column is out of range
+        int ptap[PPT];                         // filter tap of the piece, or -1 when the column is out of range
 #pragma unroll
         for (int i = 0; i < PPT; ++i) {
-          const int col = w.n0 + (i * 4 + sub) * 4;
+          const int col = w.n0 + i * 32 + sub * 4;
           if (col < p.NC) {
             const int tap = col / p.C, ch = col - tap * p.C;
             const int kh = tap / p.KW, kw = tap - kh * p.KW;
-            ptap[i] = (kh << 16) | kw;
+            ptap[i] = tap;
             poff[i] = (kh * p.W + kw) * p.C + ch;
           } else {
             ptap[i] = -1; poff[i] = 0;
@@ -358,25 +404,38 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
         int n = pix / (p.OH * p.OW);
         int rem = pix - n * (p.OH * p.OW);
         int oy = rem / p.OW, ox = rem - oy * p.OW;
-        const uint32_t rowsw = (uint32_t)(kr & 3);
+        const uint32_t piece = ((((uint32_t)sub >> 1) ^ (uint32_t)(kr & 3)) << 1) | ((uint32_t)sub & 1);
+        const uint32_t soff = (uint32_t)(kr * 128) + (piece << 4);
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x206)) { ok = false; break; }
-          const uint32_t sdst = smem_u32(smem_b + s * C::B_STAGE_BYTES) + kr * 128;
+          const uint32_t sdst = smem_u32(smem_b + s * C::B_STAGE_BYTES) + soff;
           const int y0 = oy * p.stride - p.ph, x0 = ox * p.stride - p.pw;
           const bool pvalid = pix < mpix;
           const float* rowptr = p.src + (((long long)n * p.H + y0) * p.W + x0) * p.C;
+          if (masked) {
+            unsigned long long tapmask = 0;    // bit tap = that tap of this pixel reads inside the image
+            if (pvalid) {
+              unsigned long long colm = 0;
+              for (int kw = 0; kw < p.KW; ++kw)
+                if ((unsigned)(x0 + kw) < (unsigned)p.W) colm |= 1ull << kw;
+              for (int kh = 0; kh < p.KH; ++kh)
+                if ((unsigned)(y0 + kh) < (unsigned)p.H) tapmask |= colm << (kh * p.KW);
+            }
 #pragma unroll
-          for (int i = 0; i < PPT; ++i) {
-            const int pc = i * 4 + sub;
-            const int kh = ptap[i] >> 16, kw = ptap[i] & 0xffff;
-            const bool v = pvalid && ptap[i] >= 0 && (unsigned)(y0 + kh) < (unsigned)p.H &&
-                           (unsigned)(x0 + kw) < (unsigned)p.W;
-            const float* src = v ? rowptr + poff[i] : p.src;
-            const uint32_t u = (uint32_t)(pc & 7);
-            const uint32_t piece = (((u >> 1) ^ rowsw) << 1) | (u & 1);
-            cp_async16(sdst + (pc >> 3) * (BK * 128) + (piece << 4), src, v);
+            for (int i = 0; i < PPT; ++i) {
+              const bool v = ptap[i] >= 0 && ((tapmask >> (ptap[i] & 63)) & 1ull);
+              cp_async16(sdst + i * (BK * 128), v ? rowptr + poff[i] : p.src, v);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < PPT; ++i) {
+              const int kh = ptap[i] / p.KW, kw = ptap[i] - kh * p.KW;
+              const bool v = pvalid && ptap[i] >= 0 && (unsigned)(y0 + kh) < (unsigned)p.H &&
+                             (unsigned)(x0 + kw) < (unsigned)p.W;
+              cp_async16(sdst + i * (BK * 128), v ? rowptr + poff[i] : p.src, v);
+            }
           }
           cp_async_commit();
           if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
