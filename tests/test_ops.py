@@ -94,6 +94,12 @@ CONVS = [
     (1, 3, 32, 32, 64, 7, 3, 2),
     (2, 72, 7, 7, 200, 3, 1, 1),       # ragged channel counts
     (4, 256, 8, 8, 512, 3, 1, 1),      # wide tiles (BN = 256)
+    # channel counts that are multiples of 32 take the TMA im2col path on the GPU
+    (2, 32, 13, 11, 96, 3, 1, 2),      # strided, non-square image
+    (2, 64, 10, 10, 32, 5, 2, 1),      # 5x5 window
+    (1, 32, 40, 40, 32, 3, 0, 1),      # no padding, several tiles of pixels
+    (3, 96, 6, 6, 160, 3, 1, 1),       # pixel tiles that span images
+    (5, 128, 7, 9, 64, 3, 1, 1),
 ]
 
 

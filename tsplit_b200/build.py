@@ -25,6 +25,8 @@ OBJ = os.path.join(os.path.dirname(HERE), "build", "obj")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
+# extra nvcc flags for developer builds, e.g. TSB_NVCC_EXTRA="-DTSB_CONV_PROF" (role-time counters)
+NVCC_FLAGS += os.environ.get("TSB_NVCC_EXTRA", "").split()
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-fopenmp"]
 
 

@@ -14,6 +14,11 @@
 //
 // Role in the reference: cudnnConvolutionForward / BackwardData / BackwardFilter
 // (src/ops/CudnnConv2d.cu:127-602).
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "tc_common.cuh"
 
 using namespace tsb;
@@ -24,7 +29,6 @@ constexpr int BM = 128;
 constexpr int BK = 32;
 constexpr int UMMA_K = 8;
 constexpr int A_STAGE_BYTES = BM * BK * 4;
-constexpr int LAG = 2;                 // cp.async groups in flight per gather thread (measured: 3 starves the MMA of ready stages)
 constexpr int GATHER_WARPS = 8;        // two per scheduler, so one warp's address arithmetic hides the other's
 constexpr int GATHER_THREADS = GATHER_WARPS * 32;
 constexpr int NUM_THREADS = 6 * 32 + GATHER_THREADS;   // warp0 TMA, warp1 MMA, warps2-5 epilogue, then gather
@@ -44,6 +48,7 @@ struct ConvParams {
   int accumulate;
   long long ldc;
   int* status;
+  unsigned long long* prof;   // role-time counters (only written when built with -DTSB_CONV_PROF)
 };
 
 template <int BN>
@@ -59,11 +64,30 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   const int sz = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// Arrival on `bar` that the hardware performs once every cp.async issued so far by this thread has
+// written shared memory.  `.noinc`: the barrier's expected count already includes this arrival.
+// The tensor core may read the stage as soon as the barrier's phase completes; no proxy fence
+// stands between the copies and the MMA (same protocol as CUTLASS's sm100 cp.async mainloop,
+// cutlass/gemm/collective/sm100_mma_cpasync_warpspecialized.hpp).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Developer diagnostic: with -DTSB_CONV_PROF each role adds the cycles it spent waiting / working to
+// sixteen global counters, and the host prints them per CTA after every launch (which it then
+// synchronises).  Off by default: the macros expand to nothing.
+#ifdef TSB_CONV_PROF
+#define PROF_DECL(n) long long prof_##n = 0
+#define PROF_BEGIN(n) const long long prof_t_##n = clock64()
+#define PROF_END(n) prof_##n += clock64() - prof_t_##n
+#define PROF_FLUSH(idx, n) atomicAdd(&p.prof[idx], (unsigned long long)prof_##n)
+#else
+#define PROF_DECL(n)
+#define PROF_BEGIN(n)
+#define PROF_END(n)
+#define PROF_FLUSH(idx, n)
+#endif
 
 struct Item {
   int m0, n0, tap, split, kb0, kb1;
@@ -85,9 +109,12 @@ __device__ __forceinline__ Item decode_item(const ConvParams& p, long long item,
   return it;
 }
 
-template <int MODE, int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
+// IM2COL: the patch operand also arrives by TMA (im2col-mode tensor map `tmi`), so the CTA has no
+// gather warps at all; needs the gathered tensor's channel count to be a multiple of 32 and is not
+// used for strided dgrad.  Otherwise the eight cp.async warps below gather it.
+template <int MODE, int BN, bool IM2COL>
+__global__ void __launch_bounds__(IM2COL ? 192 : NUM_THREADS, 1)
+conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi, const ConvParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -105,7 +132,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&full[s], 1 + GATHER_WARPS);   // TMA expect_tx arrive + one arrive per gather warp
+      mbar_init(&full[s], IM2COL ? 1 : 1 + GATHER_THREADS);   // TMA expect_tx arrive (+ one arrive per gather thread)
       mbar_init(&empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -114,6 +141,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
     }
     fence_barrier_init();
     tma_prefetch_desc(&tm);
+    if (IM2COL) tma_prefetch_desc(&tmi);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -131,15 +159,108 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (IM2COL && MODE == 0) {
+      // forward with both operands by TMA: one im2col box (128 pixels x 32 channels of one filter
+      // tap) and one weight box per k-block; k runs over (tap, 32-channel block)
+      if (lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        PROF_DECL(tw); PROF_DECL(tt);
+        PROF_BEGIN(tt);
+        const int cpb = p.C >> 5;
+        for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+          const Item w = decode_item(p, item, BN);
+          const int n = w.m0 / (p.OH * p.OW);
+          const int rem = w.m0 - n * (p.OH * p.OW);
+          const int oy = rem / p.OW, ox = rem - oy * p.OW;
+          const int bw = ox * p.stride - p.pw, bh = oy * p.stride - p.ph;   // base position of the first pixel
+          int tap = w.kb0 / cpb, cb = w.kb0 - tap * cpb;
+          int kh = tap / p.KW, kw = tap - kh * p.KW;
+          for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+            const int s = it % C::STAGES;
+            const uint32_t ph = (it / C::STAGES) & 1;
+            PROF_BEGIN(tw);
+            if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x201)) { ok = false; break; }
+            PROF_END(tw);
+            mbar_expect_tx(&full[s], C::STAGE_BYTES);
+            tma_load_im2col_4d(smem_a + s * A_STAGE_BYTES, &tmi, &full[s], cb * 32, bw, bh, n, (uint16_t)kw,
+                               (uint16_t)kh);
+            tma_load_2d(smem_b + s * C::B_STAGE_BYTES, &tm, &full[s], kb * BK, w.n0);
+            if (++cb == cpb) {
+              cb = 0;
+              if (++kw == p.KW) { kw = 0; ++kh; }
+            }
+          }
+        }
+        PROF_END(tt);
+        PROF_FLUSH(4, tw); PROF_FLUSH(5, tt);
+        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    } else if (IM2COL && MODE == 2) {
+      // wgrad with both operands by TMA, one box per lane so that the issue cost of the twelve
+      // boxes of a k-block overlaps: lanes 0-3 fetch the dy tile (four chunks of 32 output
+      // channels), lane 4+i fetches chunk i of the patch tile = 32 pixels x 32 channels of the
+      // filter tap that the chunk's columns belong to.
+      constexpr int NCH = BN / 32;
+      const int ci = lane - 4;
       uint32_t it = 0;
       bool ok = true;
+      PROF_DECL(tw); PROF_DECL(tt);
+      PROF_BEGIN(tt);
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const Item w = decode_item(p, item, BN);
+        int c0 = 0, kh = 0, kw = 0;
+        bool cvalid = false;
+        if (ci >= 0 && ci < NCH) {
+          const int col = w.n0 + ci * 32;
+          cvalid = col < p.NC;
+          const int tap = col / p.C;
+          c0 = col - tap * p.C;
+          kh = tap / p.KW; kw = tap - kh * p.KW;
+        }
+        int nv = (p.NC - w.n0 + 31) / 32;
+        if (nv > NCH) nv = NCH;
+        const uint32_t tx = A_STAGE_BYTES + nv * (BK * 128);
+        // position of the first pixel of the first k-block
+        const int pix0 = w.kb0 * BK;
+        int n = pix0 / (p.OH * p.OW);
+        const int rem = pix0 - n * (p.OH * p.OW);
+        int oy = rem / p.OW, ox = rem - oy * p.OW;
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          PROF_BEGIN(tw);
+          const bool got = mbar_wait(&empty[s], ph ^ 1, p.status, 0x201);
+          PROF_END(tw);
+          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+          if (lane == 0) mbar_expect_tx(&full[s], tx);
+          __syncwarp();
+          if (lane < 4)
+            tma_load_2d(smem_a + s * A_STAGE_BYTES + lane * (BK * 128), &tm, &full[s], w.m0 + lane * 32, kb * BK);
+          else if (cvalid)
+            tma_load_im2col_4d(smem_b + s * C::B_STAGE_BYTES + ci * (BK * 128), &tmi, &full[s], c0,
+                               ox * p.stride - p.pw, oy * p.stride - p.ph, n, (uint16_t)kw, (uint16_t)kh);
+          ox += BK;
+          while (ox >= p.OW) { ox -= p.OW; ++oy; }
+          while (oy >= p.OH) { oy -= p.OH; ++n; }
+        }
+      }
+      PROF_END(tt);
+      if (lane == 0) { PROF_FLUSH(4, tw); PROF_FLUSH(5, tt); }
+      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    } else if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      PROF_DECL(tw); PROF_DECL(tt);
+      PROF_BEGIN(tt);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const Item w = decode_item(p, item, BN);
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
+          PROF_BEGIN(tw);
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x201)) { ok = false; break; }
+          PROF_END(tw);
           mbar_expect_tx(&full[s], TMA_BYTES);
           if (MODE == 0) {          // filters [O][K], K-major
             tma_load_2d(smem_b + s * C::B_STAGE_BYTES, &tm, &full[s], kb * BK, w.n0);
@@ -155,6 +276,8 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
           }
         }
       }
+      PROF_END(tt);
+      PROF_FLUSH(4, tw); PROF_FLUSH(5, tt);
       if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
   } else if (warp == 1) {
@@ -163,46 +286,63 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
       constexpr int A_MN = (MODE == 2) ? 1 : 0;
       constexpr int B_MN = (MODE == 0) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc_tf32(BM, BN, A_MN, B_MN);
+      // shared-memory descriptors: MN-major operands use the 32-byte-atom 128B swizzle (chunks of 32
+      // columns BK*128 bytes apart, 1024 bytes per K step), K-major ones the plain 128B swizzle
+      constexpr uint32_t A_HI = A_MN ? smem_desc_hi(512, LAYOUT_SW128_BASE32B) : smem_desc_hi(1024);
+      constexpr uint32_t B_HI = B_MN ? smem_desc_hi(512, LAYOUT_SW128_BASE32B) : smem_desc_hi(1024);
+      constexpr uint32_t A_KSTEP = (A_MN ? 1024 : UMMA_K * 4) >> 4, B_KSTEP = (B_MN ? 1024 : UMMA_K * 4) >> 4;
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), A_MN ? BK * 128 : 16);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), B_MN ? BK * 128 : 16);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
+      PROF_DECL(mf); PROF_DECL(me); PROF_DECL(mi); PROF_DECL(mt);
+      PROF_BEGIN(mt);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
         const Item w = decode_item(p, item, BN);
         const int acc = acc_it & 1;
         const uint32_t acc_ph = (acc_it >> 1) & 1;
+        PROF_BEGIN(me);
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x202)) { ok = false; break; }
+        PROF_END(me);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
+          PROF_BEGIN(mf);
           if (!mbar_wait(&full[s], ph, p.status, 0x203)) { ok = false; break; }
+          PROF_END(mf);
+          PROF_BEGIN(mi);
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
-          const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
+          const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (C::B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? make_smem_desc(sa + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
-                                     : make_smem_desc(sa + k * (UMMA_K * 4), 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc(sb + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
-                                     : make_smem_desc(sb + k * (UMMA_K * 4), 16, 1024);
-            umma_tf32(d_tmem, da, db, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_tf32(d_tmem, smem_desc_join(A_HI, a_lo + k * A_KSTEP), smem_desc_join(B_HI, b_lo + k * B_KSTEP),
+                      idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
+          PROF_END(mi);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
+      PROF_END(mt);
+      PROF_FLUSH(0, mf); PROF_FLUSH(1, me); PROF_FLUSH(2, mi); PROF_FLUSH(3, mt);
     }
   } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;
     uint32_t acc_it = 0;
     bool ok = true;
+    PROF_DECL(ew); PROF_DECL(et);
+    PROF_BEGIN(et);
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
       const Item w = decode_item(p, item, BN);
       const int acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
       const bool has_k = w.kb0 < w.kb1;
+      PROF_BEGIN(ew);
       if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x204)) { ok = false; break; }
+      PROF_END(ew);
       tc_fence_after();
       const int row = w.m0 + q * 32 + lane;
       const long long coloff = (MODE == 2) ? (long long)w.tap * p.C : 0;
@@ -250,7 +390,9 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
-  } else {
+    PROF_END(et);
+    if (warp == 2 && lane == 0) { PROF_FLUSH(11, ew); PROF_FLUSH(12, et); }
+  } else if (!IM2COL) {
     // ---------------------------------------------------------------- gather producers (warps 6..)
     // The loop over k-blocks is kept short on purpose: with few warps per scheduler the chain of
     // dependent address instructions, not the memory system, bounds the rate of k-blocks.  So
@@ -259,15 +401,9 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
     // advances incrementally instead of being divided out of k.
     const int t = threadIdx.x - 6 * 32;       // 0..GATHER_THREADS-1
     uint32_t it = 0;                          // k-blocks issued by this thread
-    uint32_t arrived = 0;                     // k-blocks whose data this warp has published
     bool ok = true;
-    auto publish = [&](uint32_t upto) {       // arrive for k-blocks [arrived, upto)
-      for (; arrived < upto; ++arrived) {
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[arrived % C::STAGES]);
-      }
-    };
+    PROF_DECL(ge); PROF_DECL(gt);
+    PROF_BEGIN(gt);
     const int ntaps = p.KH * p.KW;
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const Item w = decode_item(p, item, BN);
@@ -326,7 +462,9 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
+          PROF_BEGIN(ge);
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x205)) { ok = false; break; }
+          PROF_END(ge);
           const bool kvalid = (MODE == 0) ? (tap < ntaps) : (ch < p.O);
           // element offset of this k-chunk relative to the row origin
           const int delta = (MODE == 0) ? (kh * SW + kw) * SC + ch : -((kh * SW + kw) * SC) + ch;
@@ -359,8 +497,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
               cp_async16(sdst + i * (RSTEP * 128), v ? src : p.src, v);
             }
           }
-          cp_async_commit();
-          if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
+          cp_async_arrive(&full[s]);     // this thread's arrival fires when its copies above have landed
           // advance to the next k-block
           if (MODE == 0) {
             ch += BK;
@@ -409,7 +546,9 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
+          PROF_BEGIN(ge);
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x206)) { ok = false; break; }
+          PROF_END(ge);
           const uint32_t sdst = smem_u32(smem_b + s * C::B_STAGE_BYTES) + soff;
           const int y0 = oy * p.stride - p.ph, x0 = ox * p.stride - p.pw;
           const bool pvalid = pix < mpix;
@@ -437,8 +576,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
               cp_async16(sdst + i * (BK * 128), v ? rowptr + poff[i] : p.src, v);
             }
           }
-          cp_async_commit();
-          if (it + 1 > LAG + arrived) { cp_async_wait<LAG>(); publish(it + 1 - LAG); }
+          cp_async_arrive(&full[s]);     // this thread's arrival fires when its copies above have landed
           // advance the pixel by one k-block
           pix += BK; ox += BK;
           while (ox >= p.OW) { ox -= p.OW; ++oy; }
@@ -446,8 +584,9 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const ConvParams p) {
         }
       }
     }
-    cp_async_wait<0>();
-    if (ok) publish(it);
+    cp_async_wait_all();                     // nothing of this thread is in flight when the CTA exits
+    PROF_END(gt);
+    if (warp == 6 && lane == 0) { PROF_FLUSH(6, ge); PROF_FLUSH(9, gt); }
   }
 
   tc_fence_before();
@@ -468,19 +607,43 @@ __global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restri
   }
 }
 
+// Filters for stride-1 dgrad run through the forward kernel: out[c][KH-1-kh][KW-1-kw][o] = w[o][kh][kw][c].
+// One 32x32 tile of the (o, c) plane of one tap per block, transposed through shared memory.
+__global__ void flip_transpose_filters(const float* __restrict__ w, float* __restrict__ out, int O, int C, int KH,
+                                       int KW) {
+  __shared__ float tile[32][33];
+  const int tap = blockIdx.z, kh = tap / KW, kw = tap - kh * KW;
+  const int ftap = (KH - 1 - kh) * KW + (KW - 1 - kw);
+  const int taps = KH * KW;
+  const int c0 = blockIdx.x * 32, o0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int o = o0 + r, c = c0 + threadIdx.x;
+    tile[r][threadIdx.x] = (o < O && c < C) ? w[((long long)o * taps + tap) * C + c] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r, o = o0 + threadIdx.x;
+    if (c < C && o < O) out[((long long)c * taps + ftap) * O + o] = tile[threadIdx.x][r];
+  }
+}
+
+// Library-owned scratch (split-K partial sums, transposed filters), one buffer per (stream, slot)
+// so that convolutions running concurrently on different streams never share one.  Grows on demand.
 struct Workspace {
   float* ptr = nullptr;
   size_t bytes = 0;
 };
-Workspace g_ws[64];
-float* get_ws(size_t bytes) {
+float* get_ws(cudaStream_t st, int slot, size_t bytes, size_t floor_bytes) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, cudaStream_t, int>, Workspace> table;
   int dev = 0;
   cudaGetDevice(&dev);
-  Workspace& w = g_ws[dev];
+  std::lock_guard<std::mutex> g(mu);
+  Workspace& w = table[std::make_tuple(dev, st, slot)];
   if (w.bytes < bytes) {
     if (w.ptr) cudaFree(w.ptr);
     w.ptr = nullptr; w.bytes = 0;
-    size_t want = bytes < (size_t(128) << 20) ? (size_t(128) << 20) : bytes;
+    const size_t want = bytes < floor_bytes ? floor_bytes : bytes;
     if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     w.bytes = want;
   }
@@ -498,10 +661,11 @@ int sm_count() {
   return n;
 }
 
-template <int MODE, int BN>
-int launch(const CUtensorMap& tm, const ConvParams& p, cudaStream_t st) {
+template <int MODE, int BN, bool IM2COL>
+int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
   using C = Cfg<BN>;
-  auto kern = conv_tf32_kernel<MODE, BN>;
+  auto kern = conv_tf32_kernel<MODE, BN, IM2COL>;
+  constexpr int threads = IM2COL ? 192 : NUM_THREADS;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
@@ -510,16 +674,84 @@ int launch(const CUtensorMap& tm, const ConvParams& p, cudaStream_t st) {
   }
   const long long items = (long long)p.tiles_m * p.tiles_n * p.taps * p.splits;
   const int grid = (int)(items < sm_count() ? items : sm_count());
-  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tm, p);
+#ifdef TSB_CONV_PROF
+  static unsigned long long* prof = nullptr;
+  if (!prof) cudaMalloc(reinterpret_cast<void**>(&prof), 16 * sizeof(unsigned long long));
+  cudaMemsetAsync(prof, 0, 16 * sizeof(unsigned long long), st);
+  ConvParams pp = p;
+  pp.prof = prof;
+  kern<<<grid, threads, C::SMEM_BYTES, st>>>(tm, tmi, pp);
+  unsigned long long h[16];
+  cudaMemcpyAsync(h, prof, sizeof(h), cudaMemcpyDeviceToHost, st);
+  cudaStreamSynchronize(st);
+  const double kbs = (double)items / grid * ((p.kblocks + p.splits - 1) / p.splits);   // k-blocks per CTA
+  fprintf(stderr,
+          "[conv prof] mode %d bn %d im2col %d grid %d kblocks/cta %.0f | cycles per k-block: mma total %.0f (wait "
+          "full %.0f, wait tmem %.0f, issue %.0f) | tma total %.0f (wait empty %.0f) | gather total %.0f (wait empty "
+          "%.0f) | epilogue total %.0f (wait tmem-full %.0f)\n",
+          MODE, BN, (int)IM2COL, grid, kbs, h[3] / kbs / grid, h[0] / kbs / grid, h[1] / kbs / grid,
+          h[2] / kbs / grid, h[5] / kbs / grid, h[4] / kbs / grid, h[9] / kbs / grid, h[6] / kbs / grid,
+          h[12] / kbs / grid, h[11] / kbs / grid);
+#else
+  kern<<<grid, threads, C::SMEM_BYTES, st>>>(tm, tmi, p);
+#endif
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
-template <int MODE>
-int launch_bn(int bn, const CUtensorMap& tm, const ConvParams& p, cudaStream_t st) {
-  if (bn == 256) return launch<MODE, 256>(tm, p, st);
-  if (bn == 128) return launch<MODE, 128>(tm, p, st);
-  return launch<MODE, 64>(tm, p, st);
+template <int MODE, bool IM2COL>
+int launch_bn(int bn, const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
+  if (bn == 256) return launch<MODE, 256, IM2COL>(tm, tmi, p, st);
+  if (bn == 128) return launch<MODE, 128, IM2COL>(tm, tmi, p, st);
+  return launch<MODE, 64, IM2COL>(tm, tmi, p, st);
+}
+
+ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH, int OW, int ph, int pw,
+                       int stride) {
+  ConvParams p;
+  p.N = N; p.C = C; p.H = H; p.W = W; p.O = O; p.KH = KH; p.KW = KW; p.OH = OH; p.OW = OW;
+  p.ph = ph; p.pw = pw; p.stride = stride;
+  p.src = nullptr; p.out = nullptr; p.ws = nullptr; p.accumulate = 0; p.splits = 1; p.taps = 1;
+  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr;
+  p.M = 0; p.NC = 0; p.kblocks = 0; p.tiles_m = 0; p.tiles_n = 0; p.ldc = 0;
+  return p;
+}
+
+// im2col-mode map of the activation `a`[N,H,W,C] for a KHxKW window with this padding and stride.
+// Returns TSB_ERR_UNSUPPORTED when the shape is outside what the TMA path handles (the caller
+// then gathers with cp.async instead).
+int im2col_map(CUtensorMap* out, const float* a, int N, int C, int H, int W, int KH, int KW, int OH, int OW, int ph,
+               int pw, int stride, int pixels, bool atom32) {
+  if (C % 32) return TSB_ERR_UNSUPPORTED;
+  if (KH > 255 || KW > 255) return TSB_ERR_UNSUPPORTED;
+  if (H + 2 * ph < KH || W + 2 * pw < KW) return TSB_ERR_UNSUPPORTED;
+  if ((H + 2 * ph - KH) / stride + 1 != OH || (W + 2 * pw - KW) / stride + 1 != OW) return TSB_ERR_UNSUPPORTED;
+  const int lower[2] = {-pw, -ph};
+  const int upper[2] = {pw - (KW - 1), ph - (KH - 1)};
+  return tsb_host::make_tmap_im2col_f32(out, a, C, W, H, N, lower, upper, 32, pixels, stride, stride, atom32);
+}
+
+// out[N,OH,OW,O] = conv(src[N,H,W,C], wts[O,KH,KW,C]).  Serves forward, and stride-1 dgrad with
+// flipped and transposed filters.
+int run_forward(const float* src, const float* wts, float* out, int N, int C, int H, int W, int O, int KH, int KW,
+                int OH, int OW, int ph, int pw, int stride, cudaStream_t st) {
+  ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
+  p.status = tsb_host::status_word(st);
+  if (!p.status) return TSB_ERR_LAUNCH;
+  p.src = src; p.out = out; p.M = N * OH * OW; p.NC = O; p.ldc = O;
+  p.kblocks = (p.K + BK - 1) / BK;
+  const int bn = O > 128 ? 256 : (O > 64 ? 128 : 64);
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.NC + bn - 1) / bn;
+  CUtensorMap tm, tmi;
+  uint64_t d[2] = {(uint64_t)p.K, (uint64_t)O}, s[1] = {(uint64_t)p.K * 4};
+  uint32_t bx[2] = {BK, (uint32_t)bn};
+  int rc = tsb_host::make_tmap_f32(&tm, wts, 2, d, s, bx, false);
+  if (rc) return rc;
+  rc = im2col_map(&tmi, src, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BM, false);
+  if (rc == TSB_OK) return launch_bn<0, true>(bn, tm, tmi, p, st);
+  if (rc != TSB_ERR_UNSUPPORTED) return rc;
+  return launch_bn<0, false>(bn, tm, tm, p, st);
 }
 
 }  // namespace
@@ -536,78 +768,86 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
   if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
     return TSB_ERR_UNSUPPORTED;
   if ((long long)N * OH * OW >= (1ll << 31) || (long long)N * H * W >= (1ll << 31)) return TSB_ERR_UNSUPPORTED;
-  ConvParams p;
-  p.N = N; p.C = C; p.H = H; p.W = W; p.O = O; p.KH = KH; p.KW = KW; p.OH = OH; p.OW = OW;
-  p.ph = ph; p.pw = pw; p.stride = stride;
-  p.ws = nullptr; p.accumulate = 0; p.splits = 1; p.taps = 1; p.K = KH * KW * C; p.ocb = (O + 31) / 32;
-  p.status = tsb_host::status_word(st);
-  if (!p.status) return TSB_ERR_LAUNCH;
-  CUtensorMap tm;
-  int rc, bn;
+  int rc;
   if (kind == 0) {
-    p.src = x; p.out = y; p.M = N * OH * OW; p.NC = O; p.ldc = O;
-    p.kblocks = (p.K + BK - 1) / BK;
-    bn = O > 128 ? 256 : (O > 64 ? 128 : 64);
-    uint64_t d[2] = {(uint64_t)p.K, (uint64_t)O}, s[1] = {(uint64_t)p.K * 4};
-    uint32_t bx[2] = {BK, (uint32_t)bn};
-    rc = tsb_host::make_tmap_f32(&tm, w, 2, d, s, bx, false);
+    rc = run_forward(x, w, y, N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride, st);
+  } else if (kind == 1 && stride == 1 && (O % 32) == 0 && ph <= KH - 1 && pw <= KW - 1) {
+    // stride-1 dgrad = forward convolution of dy with the flipped, transposed filters
+    const size_t wbytes = (size_t)C * KH * KW * O * sizeof(float);
+    float* wt = get_ws(st, 1, wbytes, size_t(16) << 20);
+    if (!wt) return TSB_ERR_OOM;
+    dim3 grid((C + 31) / 32, (O + 31) / 32, KH * KW);
+    flip_transpose_filters<<<grid, dim3(32, 8), 0, st>>>(w, wt, O, C, KH, KW);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+    rc = run_forward(y, wt, x, N, O, OH, OW, C, KH, KW, H, W, KH - 1 - ph, KW - 1 - pw, 1, st);
   } else if (kind == 1) {
+    ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
+    p.status = tsb_host::status_word(st);
+    if (!p.status) return TSB_ERR_LAUNCH;
     p.src = y; p.out = x; p.M = N * H * W; p.NC = C; p.ldc = C;
     p.kblocks = KH * KW * p.ocb;
-    bn = C > 128 ? 256 : (C > 64 ? 128 : 64);
+    const int bn = C > 128 ? 256 : (C > 64 ? 128 : 64);
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.NC + bn - 1) / bn;
+    CUtensorMap tm;
     uint64_t d[3] = {(uint64_t)C, (uint64_t)KH * KW, (uint64_t)O};
     uint64_t s[2] = {(uint64_t)C * 4, (uint64_t)KH * KW * C * 4};
     uint32_t bx[3] = {32, 1, BK};
     rc = tsb_host::make_tmap_f32(&tm, w, 3, d, s, bx, true);
+    if (rc) return rc;
+    rc = launch_bn<1, false>(bn, tm, tm, p, st);
   } else {
+    ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
+    p.status = tsb_host::status_word(st);
+    if (!p.status) return TSB_ERR_LAUNCH;
     const long long mpix = (long long)N * OH * OW;
     p.src = x; p.out = w; p.M = O; p.NC = KH * KW * C; p.ldc = (long long)KH * KW * C;
-    p.taps = 1;
     p.kblocks = (int)((mpix + BK - 1) / BK);
-    bn = p.NC > 128 ? 256 : (p.NC > 64 ? 128 : 64);
+    const int bn = p.NC > 128 ? 256 : (p.NC > 64 ? 128 : 64);
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.NC + bn - 1) / bn;
+    CUtensorMap tm, tmi;
     uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
     uint32_t bx[2] = {32, BK};
     rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
-  }
-  if (rc) return rc;
-  p.tiles_m = (p.M + BM - 1) / BM;
-  p.tiles_n = (p.NC + bn - 1) / bn;
-  if (kind == 2) {
+    if (rc) return rc;
     // split the pixel reduction so that the work items fill whole waves of CTAs
     const long long tiles = (long long)p.tiles_m * p.tiles_n * p.taps;
     const int sms = sm_count();
     int splits = 1;
     double best_eff = 0.0;
     for (int waves = 1; waves <= 4; ++waves) {
-      int s = (int)((long long)waves * sms / tiles);
-      if (s < 1) s = 1;
-      if (s > p.kblocks / 4) s = p.kblocks / 4 > 0 ? p.kblocks / 4 : 1;
-      if (s > 64) s = 64;
-      const long long items = tiles * s;
+      int sp = (int)((long long)waves * sms / tiles);
+      if (sp < 1) sp = 1;
+      if (sp > p.kblocks / 4) sp = p.kblocks / 4 > 0 ? p.kblocks / 4 : 1;
+      if (sp > 64) sp = 64;
+      const long long items = tiles * sp;
       const double eff = (double)items / (double)(((items + sms - 1) / sms) * sms);
       // prefer more waves only when they are clearly better balanced (each split costs a partial-sum pass)
-      if (eff > best_eff + 0.04) { best_eff = eff; splits = s; }
+      if (eff > best_eff + 0.04) { best_eff = eff; splits = sp; }
     }
     const int per = (p.kblocks + splits - 1) / splits;
     p.splits = (p.kblocks + per - 1) / per;
     if (p.splits > 1) {
       const size_t need = (size_t)p.splits * O * KH * KW * C * sizeof(float);
-      p.ws = get_ws(need);
+      p.ws = get_ws(st, 0, need, size_t(128) << 20);
       if (!p.ws) return TSB_ERR_OOM;
     }
+    rc = im2col_map(&tmi, x, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BK, true);
+    if (rc == TSB_OK) rc = launch_bn<2, true>(bn, tm, tmi, p, st);
+    else if (rc == TSB_ERR_UNSUPPORTED) rc = launch_bn<2, false>(bn, tm, tm, p, st);
+    if (rc) return rc;
+    if (p.splits > 1) {
+      const long long per_split = (long long)O * KH * KW * C;
+      int blocks = (int)((per_split + 255) / 256);
+      if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+      conv_splitk_reduce<<<blocks, 256, 0, st>>>(p.ws, p.out, p.splits, per_split, 0);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+    }
   }
-  if (kind == 0) rc = launch_bn<0>(bn, tm, p, st);
-  else if (kind == 1) rc = launch_bn<1>(bn, tm, p, st);
-  else rc = launch_bn<2>(bn, tm, p, st);
   if (rc) return rc;
-  if (p.splits > 1) {
-    const long long per_split = (long long)O * KH * KW * C;
-    int blocks = (int)((per_split + 255) / 256);
-    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
-    conv_splitk_reduce<<<blocks, 256, 0, st>>>(p.ws, p.out, p.splits, per_split, 0);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
-  }
   const int late = tsb_host::peek_status();
   return late ? TSB_ERR_TIMEOUT | (late << 8) : TSB_OK;
 }

@@ -354,6 +354,72 @@ int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* 
   return TSB_OK;
 }
 
+int make_tmap_im2col_f32(CUtensorMap* out, const void* base, int C, int W, int H, int N, const int* lower,
+                         const int* upper, int channels, int pixels, int stride_w, int stride_h, bool atom32) {
+  typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                     const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeIm2colFn fn = nullptr;
+  static int driver_version = 0;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeIm2colFn>(p);
+    cudaDriverGetVersion(&driver_version);
+  });
+  if (!fn) return TSB_ERR_TMAP;
+  for (int i = 0; i < 2; ++i)
+    if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return TSB_ERR_UNSUPPORTED;
+  struct Key {
+    const void* base; int v[13];
+    bool operator==(const Key& o) const { return std::memcmp(this, &o, sizeof(Key)) == 0; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&k);
+      size_t h = 1469598103934665603ull;
+      for (size_t i = 0; i < sizeof(Key) / 4; ++i) h = (h ^ w[i]) * 1099511628211ull;
+      return h;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  Key key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base;
+  const int vals[13] = {C, W, H, N, lower[0], lower[1], upper[0], upper[1], channels, pixels, stride_w, stride_h,
+                        atom32 ? 1 : 0};
+  std::memcpy(key.v, vals, sizeof(vals));
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return TSB_OK; }
+  }
+  cuuint64_t gd[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t gs[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
+  cuuint32_t es[4] = {1, (cuuint32_t)stride_w, (cuuint32_t)stride_h, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), gd, gs, lower, upper,
+                  (cuuint32_t)channels, (cuuint32_t)pixels, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return TSB_ERR_TMAP | ((int)r << 8);
+  // Drivers up to CUDA 13.1 encode im2col maps of tensors smaller than 128 KiB with a flag that
+  // makes the load misbehave; CUTLASS clears it the same way
+  // (cute/atom/copy_traits_sm90_im2col.hpp, make_im2col_tma_copy_desc).
+  if (driver_version <= 13010 && (size_t)C * W * H * N * 4 < 131072)
+    reinterpret_cast<uint64_t*>(out)[1] &= ~(1ull << 21);
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache[key] = *out;
+  }
+  return TSB_OK;
+}
+
 static int* g_status_host = nullptr;   // pinned, mapped: one word per device
 static int* g_status_dev[64] = {nullptr};
 

@@ -26,7 +26,8 @@
 namespace {
 
 constexpr int MAX_CHUNKS = 128;
-constexpr long long SCRATCH_FLOATS = 2ll * MAX_CHUNKS * 8192;   // two partial planes, up to 8192 channels
+constexpr long long PLANE_FLOATS = (long long)MAX_CHUNKS * 8192;   // one partial plane: chunks x channels
+constexpr long long SCRATCH_FLOATS = 2 * PLANE_FLOATS;              // two planes (up to 8192 channels at MAX_CHUNKS)
 
 float* g_scratch[64] = {nullptr};
 float* scratch() {
@@ -57,75 +58,127 @@ int done() {
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
-// Column partial sums over a chunk of rows.  Block = 32 (float4 columns) x 8 (row lanes).
+// Column partial sums over a chunk of rows.  A block of 256 threads covers `cw` float4 columns
+// (cw = min(32, C/4)) with 256/cw row lanes, so narrow tensors (64 channels) still keep every
+// thread busy; each thread has four independent rows in flight.
 // MODE 0: p0 = sum x, p1 = sum x^2.   MODE 1: p0 = sum dy, p1 = sum dy * (x - mean) * invstd.
 // `mask` (MODE 1 only, may be null): output of a fused ReLU; dy counts only where mask > 0.
+constexpr int STAT_THREADS = 256;
+constexpr int STAT_UNROLL = 4;
+
+__device__ __forceinline__ void stat_accum0(float4& a0, float4& a1, const float4 v) {
+  a0.x += v.x; a0.y += v.y; a0.z += v.z; a0.w += v.w;
+  a1.x += v.x * v.x; a1.y += v.y * v.y; a1.z += v.z * v.z; a1.w += v.w * v.w;
+}
+__device__ __forceinline__ void stat_accum1(float4& a0, float4& a1, float4 g, const float4 x, const float4 mu,
+                                            const float4 is) {
+  a0.x += g.x; a0.y += g.y; a0.z += g.z; a0.w += g.w;
+  a1.x += g.x * (x.x - mu.x) * is.x; a1.y += g.y * (x.y - mu.y) * is.y;
+  a1.z += g.z * (x.z - mu.z) * is.z; a1.w += g.w * (x.w - mu.w) * is.w;
+}
+__device__ __forceinline__ float4 relu_mask(float4 g, const float4 m) {
+  g.x = m.x > 0.f ? g.x : 0.f; g.y = m.y > 0.f ? g.y : 0.f;
+  g.z = m.z > 0.f ? g.z : 0.f; g.w = m.w > 0.f ? g.w : 0.f;
+  return g;
+}
+
 template <int MODE>
-__global__ void col_partial(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mean,
-                            const float* __restrict__ invstd, float* __restrict__ part, long long rows, int C,
-                            long long lda, long long ldb, int chunks, const float* __restrict__ mask = nullptr,
-                            long long ldm = 0) {
-  __shared__ float4 s0[8][32], s1[8][32];
-  const int c4 = blockIdx.x * 32 + threadIdx.x;   // float4 column
-  const int c = c4 * 4;
+__global__ void __launch_bounds__(STAT_THREADS)
+col_partial(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mean,
+            const float* __restrict__ invstd, float* __restrict__ part, long long rows, int C,
+            long long lda, long long ldb, int chunks, int cw, const float* __restrict__ mask = nullptr,
+            long long ldm = 0) {
+  __shared__ float4 s0[STAT_THREADS], s1[STAT_THREADS];
+  const int rl = STAT_THREADS / cw;               // row lanes
+  const int cx = threadIdx.x % cw, ry = threadIdx.x / cw;
+  const int c = (blockIdx.x * cw + cx) * 4;
   const int ch = blockIdx.y;
   const long long per = (rows + chunks - 1) / chunks;
   const long long r0 = ch * per, r1 = min(rows, r0 + per);
   float4 acc0 = make_float4(0, 0, 0, 0), acc1 = make_float4(0, 0, 0, 0);
-  if (c < C) {
+  const bool active = ry < rl && c < C;
+  if (active) {
     float4 mu = make_float4(0, 0, 0, 0), is = make_float4(1, 1, 1, 1);
     if (MODE == 1) {
       mu = *reinterpret_cast<const float4*>(mean + c);
       is = *reinterpret_cast<const float4*>(invstd + c);
     }
-    for (long long r = r0 + threadIdx.y; r < r1; r += 8) {
-      float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
-      if (MODE == 1 && mask) {
-        const float4 m = *reinterpret_cast<const float4*>(mask + r * ldm + c);
-        v.x = m.x > 0.f ? v.x : 0.f; v.y = m.y > 0.f ? v.y : 0.f;
-        v.z = m.z > 0.f ? v.z : 0.f; v.w = m.w > 0.f ? v.w : 0.f;
+    long long r = r0 + ry;
+    for (; r + (STAT_UNROLL - 1) * rl < r1; r += STAT_UNROLL * rl) {
+      float4 v[STAT_UNROLL], x[STAT_UNROLL], m[STAT_UNROLL];
+#pragma unroll
+      for (int u = 0; u < STAT_UNROLL; ++u) {
+        v[u] = *reinterpret_cast<const float4*>(a + (r + u * rl) * lda + c);
+        if (MODE == 1) x[u] = *reinterpret_cast<const float4*>(b + (r + u * rl) * ldb + c);
+        if (MODE == 1 && mask) m[u] = *reinterpret_cast<const float4*>(mask + (r + u * rl) * ldm + c);
       }
+#pragma unroll
+      for (int u = 0; u < STAT_UNROLL; ++u) {
+        if (MODE == 0) {
+          stat_accum0(acc0, acc1, v[u]);
+        } else {
+          if (mask) v[u] = relu_mask(v[u], m[u]);
+          stat_accum1(acc0, acc1, v[u], x[u], mu, is);
+        }
+      }
+    }
+    for (; r < r1; r += rl) {
+      float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
       if (MODE == 0) {
-        acc0.x += v.x; acc0.y += v.y; acc0.z += v.z; acc0.w += v.w;
-        acc1.x += v.x * v.x; acc1.y += v.y * v.y; acc1.z += v.z * v.z; acc1.w += v.w * v.w;
+        stat_accum0(acc0, acc1, v);
       } else {
-        const float4 x = *reinterpret_cast<const float4*>(b + r * ldb + c);
-        acc0.x += v.x; acc0.y += v.y; acc0.z += v.z; acc0.w += v.w;
-        acc1.x += v.x * (x.x - mu.x) * is.x; acc1.y += v.y * (x.y - mu.y) * is.y;
-        acc1.z += v.z * (x.z - mu.z) * is.z; acc1.w += v.w * (x.w - mu.w) * is.w;
+        if (mask) v = relu_mask(v, *reinterpret_cast<const float4*>(mask + r * ldm + c));
+        stat_accum1(acc0, acc1, v, *reinterpret_cast<const float4*>(b + r * ldb + c), mu, is);
       }
     }
   }
-  s0[threadIdx.y][threadIdx.x] = acc0;
-  s1[threadIdx.y][threadIdx.x] = acc1;
+  s0[threadIdx.x] = acc0;
+  s1[threadIdx.x] = acc1;
   __syncthreads();
-  if (threadIdx.y == 0 && c < C) {
-    float4 t0 = s0[0][threadIdx.x], t1 = s1[0][threadIdx.x];
-#pragma unroll
-    for (int j = 1; j < 8; ++j) {
-      const float4 u0 = s0[j][threadIdx.x], u1 = s1[j][threadIdx.x];
+  if (ry == 0 && c < C) {
+    float4 t0 = s0[cx], t1 = s1[cx];
+    for (int j = 1; j < rl; ++j) {               // fixed order: the result does not depend on scheduling
+      const float4 u0 = s0[j * cw + cx], u1 = s1[j * cw + cx];
       t0.x += u0.x; t0.y += u0.y; t0.z += u0.z; t0.w += u0.w;
       t1.x += u1.x; t1.y += u1.y; t1.z += u1.z; t1.w += u1.w;
     }
     float* p0 = part + (long long)ch * C + c;
-    float* p1 = part + (long long)MAX_CHUNKS * 8192 + (long long)ch * C + c;   // second plane
+    float* p1 = part + PLANE_FLOATS + (long long)ch * C + c;   // second plane
     *reinterpret_cast<float4*>(p0) = t0;
     *reinterpret_cast<float4*>(p1) = t1;
   }
 }
 
-// Forward finalise: mean / invstd from the partial sums (+ running statistics).
-// accumulate != 0 adds the partials into sum/sumsq planes instead (micro-batches).
+// Sum of the chunk partials of one channel, in double and in a fixed order: block = 32 channels
+// x 8 lanes, lane y adds chunks y, y+8, ...; lane 0 then adds the eight lane sums.
+__device__ __forceinline__ void reduce_partials(const float* __restrict__ part, int chunks, int C, int c,
+                                                double& s, double& ss) {
+  __shared__ double sh0[8][32], sh1[8][32];
+  double a = 0.0, b = 0.0;
+  if (c < C) {
+    for (int ch = threadIdx.y; ch < chunks; ch += 8) {
+      a += part[(long long)ch * C + c];
+      b += part[PLANE_FLOATS + (long long)ch * C + c];
+    }
+  }
+  sh0[threadIdx.y][threadIdx.x] = a;
+  sh1[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  s = 0.0; ss = 0.0;
+  if (threadIdx.y == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { s += sh0[j][threadIdx.x]; ss += sh1[j][threadIdx.x]; }
+  }
+}
+
+// Forward finalise: mean / invstd from the partial sums (+ running statistics).  Block (32, 8).
 __global__ void bn_finalize_fwd(const float* __restrict__ part, int chunks, int C, double count, float eps,
                                 float momentum, float* __restrict__ mean, float* __restrict__ invstd,
                                 float* __restrict__ run_mean, float* __restrict__ run_var) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0.0, ss = 0.0;
-  for (int ch = 0; ch < chunks; ++ch) {
-    s += part[(long long)ch * C + c];
-    ss += part[(long long)MAX_CHUNKS * 8192 + (long long)ch * C + c];
-  }
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  double s, ss;
+  reduce_partials(part, chunks, C, c, s, ss);
+  if (threadIdx.y != 0 || c >= C) return;
   const double m = s / count;
   double var = ss / count - m * m;
   if (var < 0.0) var = 0.0;
@@ -139,13 +192,10 @@ __global__ void bn_finalize_fwd(const float* __restrict__ part, int chunks, int 
 
 __global__ void bn_finalize_bwd(const float* __restrict__ part, int chunks, int C, float* __restrict__ dscale,
                                 float* __restrict__ dbias) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0.0, ss = 0.0;
-  for (int ch = 0; ch < chunks; ++ch) {
-    s += part[(long long)ch * C + c];
-    ss += part[(long long)MAX_CHUNKS * 8192 + (long long)ch * C + c];
-  }
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  double s, ss;
+  reduce_partials(part, chunks, C, c, s, ss);
+  if (threadIdx.y != 0 || c >= C) return;
   dbias[c] = (float)s;
   dscale[c] = (float)ss;
 }
@@ -227,13 +277,29 @@ int static_scratch(float** out) {
   return TSB_OK;
 }
 
-int pick_chunks(long long rows, int C) {
-  const int col_blocks = (C / 4 + 31) / 32;
-  long long want = (4ll * sm_count() + col_blocks - 1) / col_blocks;
-  if (want > MAX_CHUNKS) want = MAX_CHUNKS;
-  if (want > (rows + 63) / 64) want = (rows + 63) / 64;
-  return want < 1 ? 1 : (int)want;
+// Launch geometry of the column statistics: columns per block, row chunks, grid.  Aims at eight
+// blocks per SM; narrow tensors get more chunks (a plane holds chunks x C partials).
+struct StatGeom {
+  int cw, chunks;
+  dim3 grid;
+};
+StatGeom stat_geom(long long rows, int C) {
+  StatGeom g;
+  const int c4 = C / 4;
+  g.cw = c4 < 32 ? c4 : 32;
+  const int rl = STAT_THREADS / g.cw;
+  const int col_blocks = (c4 + g.cw - 1) / g.cw;
+  long long want = (8ll * sm_count() + col_blocks - 1) / col_blocks;
+  const long long cap = PLANE_FLOATS / C;
+  if (want > cap) want = cap;
+  if (want > 4096) want = 4096;
+  const long long by_rows = (rows + (long long)rl * STAT_UNROLL - 1) / ((long long)rl * STAT_UNROLL);
+  if (want > by_rows) want = by_rows;
+  g.chunks = want < 1 ? 1 : (int)want;
+  g.grid = dim3((unsigned)col_blocks, (unsigned)g.chunks);
+  return g;
 }
+inline unsigned fin_blocks(long long C) { return (unsigned)((C + 31) / 32); }
 
 int ew_grid(long long work) {
   long long blocks = (work + 255) / 256;
@@ -300,7 +366,7 @@ __global__ void ln_bwd_params_partial(const float* __restrict__ dy, const float*
     b += g * (x[r * D + c] - mean[r]) * invstd[r];
   }
   part[(long long)ch * D + c] = a;
-  part[(long long)MAX_CHUNKS * 8192 + (long long)ch * D + c] = b;
+  part[PLANE_FLOATS + (long long)ch * D + c] = b;
 }
 
 }  // namespace
@@ -315,11 +381,10 @@ int tsb_bn_forward(const float* x, const float* scale, const float* bias, float*
   if ((C % 4) || (ldx % 4) || (ldy % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
   float* part = scratch();
   if (!part) return TSB_ERR_OOM;
-  const int chunks = pick_chunks(rows, (int)C);
-  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
-  col_partial<0><<<grid, blk, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, chunks);
-  bn_finalize_fwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, (double)rows, eps, momentum,
-                                                               save_mean, save_invstd, run_mean, run_var);
+  const StatGeom sg = stat_geom(rows, (int)C);
+  col_partial<0><<<sg.grid, STAT_THREADS, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, sg.chunks, sg.cw);
+  bn_finalize_fwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
+                                                         save_invstd, run_mean, run_var);
   bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
                                                         ldx, ldy, relu);
   return done();
@@ -336,13 +401,12 @@ int tsb_bn_forward_static(const float* x, const float* scale, const float* bias,
   float* part = nullptr;
   const int rc = static_scratch(&part);
   if (rc) return rc;
-  const int chunks = pick_chunks(rows, (int)C);
-  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
+  const StatGeom sg = stat_geom(rows, (int)C);
   // every partial word that the finalise step reads is written by the statistics step of the
   // same call, so nothing in the shared array has to be cleared between calls
-  col_partial<0><<<grid, blk, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, chunks);
-  bn_finalize_fwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, (double)rows, eps, momentum,
-                                                               save_mean, save_invstd, run_mean, run_var);
+  col_partial<0><<<sg.grid, STAT_THREADS, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, sg.chunks, sg.cw);
+  bn_finalize_fwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
+                                                         save_invstd, run_mean, run_var);
   bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
                                                         ldx, ldy, relu);
   return done();
@@ -356,10 +420,10 @@ int tsb_bn_backward(const float* dy, const float* x, const float* scale, const f
   if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
   float* part = scratch();
   if (!part) return TSB_ERR_OOM;
-  const int chunks = pick_chunks(rows, (int)C);
-  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
-  col_partial<1><<<grid, blk, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, chunks);
-  bn_finalize_bwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, dscale, dbias);
+  const StatGeom sg = stat_geom(rows, (int)C);
+  col_partial<1><<<sg.grid, STAT_THREADS, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, sg.chunks,
+                                                   sg.cw);
+  bn_finalize_bwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
                                                         rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows);
   return done();
@@ -377,10 +441,10 @@ int tsb_bn_relu_backward(const float* dy, const float* x, const float* y, const 
   if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4) || (ldy % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
   float* part = scratch();
   if (!part) return TSB_ERR_OOM;
-  const int chunks = pick_chunks(rows, (int)C);
-  dim3 grid((unsigned)((C / 4 + 31) / 32), chunks), blk(32, 8);
-  col_partial<1><<<grid, blk, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, chunks, y, ldy);
-  bn_finalize_bwd<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(part, chunks, (int)C, dscale, dbias);
+  const StatGeom sg = stat_geom(rows, (int)C);
+  col_partial<1><<<sg.grid, STAT_THREADS, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, sg.chunks,
+                                                   sg.cw, y, ldy);
+  bn_finalize_bwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
                                                         rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows, y, ldy);
   return done();
@@ -409,7 +473,7 @@ int tsb_layer_norm_grad(const float* dy, const float* x, const float* scale, con
   if (chunks > MAX_CHUNKS) chunks = MAX_CHUNKS;
   dim3 grid((unsigned)((D + 127) / 128), chunks);
   ln_bwd_params_partial<<<grid, 128, 0, st>>>(dy, x, mean, invstd, part, rows, (int)D, chunks);
-  bn_finalize_bwd<<<(unsigned)((D + 127) / 128), 128, 0, st>>>(part, chunks, (int)D, dscale, dbias);
+  bn_finalize_bwd<<<fin_blocks(D), dim3(32, 8), 0, st>>>(part, chunks, (int)D, dscale, dbias);
   return done();
 }
 

@@ -140,6 +140,59 @@ __global__ void pool_bwd(const float* __restrict__ x, const float* __restrict__ 
   }
 }
 
+// Backward for windows that tile the input exactly (kernel == stride, no padding, h = oh*stride):
+// one thread owns one output window and four channels, reads its K x K inputs and one gradient,
+// and writes the K x K input gradients -- x and dx cross HBM once each and y is not read at all.
+// Ties go to the first maximum in scan order, as in the general kernel.
+template <int KIND, int K>
+__global__ void pool_bwd_tiled(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx,
+                               const PoolP p) {
+  const int C4 = p.c >> 2;
+  const long long total = (long long)p.n * p.oh * p.ow * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C4) * 4;
+    long long r = i / C4;
+    const int ox = (int)(r % p.ow); r /= p.ow;
+    const int oy = (int)(r % p.oh);
+    const int n = (int)(r / p.oh);
+    const float4 g = *reinterpret_cast<const float4*>(dy + n * p.ysn + oy * p.ysh + ox * p.ysw + c);
+    const long long base = n * p.xsn + (long long)(oy * K) * p.xsh + (long long)(ox * K) * p.xsw + c;
+    if (KIND == 1) {
+      const float s = 1.f / (float)(K * K);
+      const float4 o = make_float4(g.x * s, g.y * s, g.z * s, g.w * s);
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int b = 0; b < K; ++b) *reinterpret_cast<float4*>(dx + base + a * p.xsh + b * p.xsw) = o;
+      continue;
+    }
+    float4 v[K * K];
+#pragma unroll
+    for (int a = 0; a < K; ++a)
+#pragma unroll
+      for (int b = 0; b < K; ++b) v[a * K + b] = *reinterpret_cast<const float4*>(x + base + a * p.xsh + b * p.xsw);
+    int ax = 0, ay = 0, az = 0, aw = 0;          // index of the first maximum per channel
+    float4 m = v[0];
+#pragma unroll
+    for (int q = 1; q < K * K; ++q) {
+      if (v[q].x > m.x) { m.x = v[q].x; ax = q; }
+      if (v[q].y > m.y) { m.y = v[q].y; ay = q; }
+      if (v[q].z > m.z) { m.z = v[q].z; az = q; }
+      if (v[q].w > m.w) { m.w = v[q].w; aw = q; }
+    }
+#pragma unroll
+    for (int a = 0; a < K; ++a)
+#pragma unroll
+      for (int b = 0; b < K; ++b) {
+        const int q = a * K + b;
+        const float4 o = make_float4(ax == q ? g.x : 0.f, ay == q ? g.y : 0.f, az == q ? g.z : 0.f,
+                                     aw == q ? g.w : 0.f);
+        *reinterpret_cast<float4*>(dx + base + a * p.xsh + b * p.xsw) = o;
+      }
+  }
+}
+
 // ------------------------------------------------------------------ softmax family
 __device__ __forceinline__ float block_max(float v, float* sh) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -266,6 +319,14 @@ int tsb_pool_bwd(int kind, const float* x, const float* y, const float* dy, floa
   if (kind == 0 && (!x || !y)) return TSB_ERR_ARG;
   PoolP p{n, c, h, w, oh, ow, kh, kw, pad, stride, xsn, xsh, xsw, ysn, ysh, ysw};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kh == stride && kw == stride && pad == 0 && oh * stride == h && ow * stride == w && (stride == 2 || stride == 3)) {
+    const int tg = ew_grid((long long)n * oh * ow * (c / 4));
+    if (kind == 0 && stride == 2) pool_bwd_tiled<0, 2><<<tg, 256, 0, st>>>(x, dy, dx, p);
+    else if (kind == 0) pool_bwd_tiled<0, 3><<<tg, 256, 0, st>>>(x, dy, dx, p);
+    else if (stride == 2) pool_bwd_tiled<1, 2><<<tg, 256, 0, st>>>(x, dy, dx, p);
+    else pool_bwd_tiled<1, 3><<<tg, 256, 0, st>>>(x, dy, dx, p);
+    return done();
+  }
   const int grid = ew_grid((long long)n * h * w * (c / 4));
   if (kind == 0) pool_bwd<0><<<grid, 256, 0, st>>>(x, y, dy, dx, p);
   else pool_bwd<1><<<grid, 256, 0, st>>>(x, y, dy, dx, p);

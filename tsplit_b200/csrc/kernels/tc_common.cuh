@@ -75,13 +75,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   long long t0 = clock64();
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 255u) == 0) {
-      if (*(volatile int*)status != 0) return false;
+    if ((++polls & 1023u) == 0) {
       if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
         *(volatile int*)status = code;     // mapped host word: plain store, then make it visible
         __threadfence_system();
         return false;
       }
+      // the status word lives in host memory (a read crosses PCIe), so look at it rarely: it only
+      // shortens the exit of the other roles after one of them has already given up
+      if ((polls & 0xffffu) == 0 && *(volatile int*)status != 0) return false;
     }
   }
   return true;
@@ -103,6 +105,19 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], "
       "[%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// im2col-mode load of a channels-last activation [N][H][W][C]: `pixels` consecutive positions of
+// the traversal (along W, then H, then N, inside the bounding box that the tensor map was encoded
+// with) starting at base position (w, h, n), each read at the filter offset (off_w, off_h), `c`
+// onward.  Positions that fall outside the image read zero.  c * 4 bytes must be a multiple of 16.
+__device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c, int w,
+                                                   int h, int n, uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6}], [%2], {%7, %8};"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+      "h"(off_w), "h"(off_h)
       : "memory");
 }
 
@@ -183,6 +198,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= (uint64_t)layout_type << 61;
   return d;
 }
+// The same descriptor in two halves, for issue loops that must stay short: the high word is a
+// compile-time constant and the low word moves with the address only, so stepping along K or to
+// the next stage is one 32-bit add (the address field cannot carry out of its 14 bits while the
+// operand stays inside shared memory).
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes, uint32_t layout_type = LAYOUT_SW128) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (layout_type << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t hi, uint32_t lo) {
+  return ((uint64_t)hi << 32) | lo;
+}
 // Instruction descriptor for kind::tf32, fp32 accumulate.
 __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4)                 // D format: f32
@@ -208,6 +236,13 @@ EncodeTiledFn encode_fn();
 // atom32 selects SWIZZLE_128B_ATOM_32B (MN-major tf32 operands) instead of SWIZZLE_128B.
 int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_b,
                   const uint32_t* box, bool atom32 = false);
+
+// im2col-mode fp32 tensor map over a dense channels-last activation [N][H][W][C].  A load yields
+// `pixels` rows of `channels` floats (128-byte rows, 128B swizzle; atom32 as above).  lower/upper
+// are the bounding-box corners in (W, H) order: base positions run from lower to dim-1+upper in
+// steps of `stride`.  Corners must lie in [-128, 127].
+int make_tmap_im2col_f32(CUtensorMap* out, const void* base, int C, int W, int H, int N, const int* lower,
+                         const int* upper, int channels, int pixels, int stride_w, int stride_h, bool atom32);
 
 int* status_word(cudaStream_t stream);   // zeroed device int used by bounded waits (per device)
 int read_status(cudaStream_t stream);    // sync + read + reset; 0 when clean
