@@ -226,13 +226,33 @@ class MemoryExecutor(Executor):
             if nxt > best_next:
                 best, best_next = t, nxt
         if best is None:
-            return False
+            return self._cancel_prefetch()
         if best not in self.host:
             self._swap_out(best)
         a = self.arr[best]
         a.gpu2cpu_event.sync()
         self._release(best)
         self._reap(True)
+        self.stats["evictions"] += 1
+        return True
+
+    def _cancel_prefetch(self):
+        """Give back the prefetched tensor whose use is farthest away: its host copy
+        stays valid, so it returns on demand (or by a later trigger)."""
+        cur = self._cursor
+        best, best_next = None, -1
+        for t, ev in self.swapin_event.items():
+            if t in self.locked or t not in self.arr:
+                continue
+            nxt = min((self.index[u] for u in self.users[t] if self.index[u] >= cur), default=None)
+            if nxt is None or nxt == cur:
+                continue
+            if nxt > best_next:
+                best, best_next = t, nxt
+        if best is None:
+            return False
+        self.swapin_event[best].sync()            # the copy must not land in a freed block
+        self._release(best)
         self.stats["evictions"] += 1
         return True
 
