@@ -47,6 +47,7 @@ struct ConvParams {
   int splits;
   int accumulate;
   long long ldc;
+  int a3d;             // wgrad: dy arrives through the 3-D (32 channels, pixel, chunk) view
   int* status;
   unsigned long long* prof;   // role-time counters (only written when built with -DTSB_CONV_PROF)
 };
@@ -113,7 +114,7 @@ __device__ __forceinline__ Item decode_item(const ConvParams& p, long long item,
 // gather warps at all; needs the gathered tensor's channel count to be a multiple of 32 and is not
 // used for strided dgrad.  Otherwise the eight cp.async warps below gather it.
 template <int MODE, int BN, bool IM2COL>
-__global__ void __launch_bounds__(IM2COL ? 192 : NUM_THREADS, 1)
+__global__ void __launch_bounds__(IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS, 1)
 conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi, const ConvParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -157,6 +158,72 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
   constexpr bool TMA_IS_A = (MODE == 2);
   constexpr int TMA_BYTES = TMA_IS_A ? A_STAGE_BYTES : C::B_STAGE_BYTES;
 
+  // wgrad with both operands by TMA.  Issuing a TMA costs the issuing thread on the order of a
+  // hundred cycles, and a k-block needs up to nine boxes, so four producer threads (one lane each
+  // of warp 0 and of the three extra warps) share them: producer q fetches chunks q and q+4 of the
+  // patch tile (a chunk = 32 pixels x 32 channels of the filter tap its columns belong to), and
+  // producer 0 also posts the byte count and fetches the dy tile.  Transfers of the other
+  // producers may complete before producer 0 posts the count; the barrier's phase cannot complete
+  // before that arrival.
+  auto wgrad_producer = [&](int q) {
+    constexpr int NCH = BN / 32;
+    uint32_t it = 0;
+    bool ok = true;
+    PROF_DECL(tw); PROF_DECL(tt);
+    PROF_BEGIN(tt);
+    for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const Item w = decode_item(p, item, BN);
+      int c0[2], kh[2], kw[2];
+      bool cv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int ci = q + 4 * u;
+        const int col = w.n0 + ci * 32;
+        cv[u] = ci < NCH && col < p.NC;
+        const int tap = col / p.C;
+        c0[u] = col - tap * p.C;
+        kh[u] = tap / p.KW; kw[u] = tap - kh[u] * p.KW;
+      }
+      int nv = (p.NC - w.n0 + 31) / 32;
+      if (nv > NCH) nv = NCH;
+      const uint32_t tx = A_STAGE_BYTES + nv * (BK * 128);
+      // position of the first pixel of the first k-block
+      const int pix0 = w.kb0 * BK;
+      int n = pix0 / (p.OH * p.OW);
+      const int rem = pix0 - n * (p.OH * p.OW);
+      int oy = rem / p.OW, ox = rem - oy * p.OW;
+      for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        PROF_BEGIN(tw);
+        if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x207 + q)) { ok = false; break; }
+        PROF_END(tw);
+        if (q == 0) {
+          mbar_expect_tx(&full[s], tx);
+          if (p.a3d) {           // dy viewed (32 channels, pixel, channel chunk): four chunks in one box
+            tma_load_3d(smem_a + s * A_STAGE_BYTES, &tm, &full[s], 0, kb * BK, w.m0 >> 5);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 32; ++c)
+              tma_load_2d(smem_a + s * A_STAGE_BYTES + c * (BK * 128), &tm, &full[s], w.m0 + c * 32, kb * BK);
+          }
+        }
+        const int bw = ox * p.stride - p.pw, bh = oy * p.stride - p.ph;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          if (cv[u])
+            tma_load_im2col_4d(smem_b + s * C::B_STAGE_BYTES + (q + 4 * u) * (BK * 128), &tmi, &full[s], c0[u], bw,
+                               bh, n, (uint16_t)kw[u], (uint16_t)kh[u]);
+        ox += BK;
+        while (ox >= p.OW) { ox -= p.OW; ++oy; }
+        while (oy >= p.OH) { oy -= p.OH; ++n; }
+      }
+    }
+    PROF_END(tt);
+    if (q == 0) { PROF_FLUSH(4, tw); PROF_FLUSH(5, tt); }
+    if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  };
+
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (IM2COL && MODE == 0) {
@@ -197,57 +264,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
         if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
     } else if (IM2COL && MODE == 2) {
-      // wgrad with both operands by TMA, one box per lane so that the issue cost of the twelve
-      // boxes of a k-block overlaps: lanes 0-3 fetch the dy tile (four chunks of 32 output
-      // channels), lane 4+i fetches chunk i of the patch tile = 32 pixels x 32 channels of the
-      // filter tap that the chunk's columns belong to.
-      constexpr int NCH = BN / 32;
-      const int ci = lane - 4;
-      uint32_t it = 0;
-      bool ok = true;
-      PROF_DECL(tw); PROF_DECL(tt);
-      PROF_BEGIN(tt);
-      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
-        const Item w = decode_item(p, item, BN);
-        int c0 = 0, kh = 0, kw = 0;
-        bool cvalid = false;
-        if (ci >= 0 && ci < NCH) {
-          const int col = w.n0 + ci * 32;
-          cvalid = col < p.NC;
-          const int tap = col / p.C;
-          c0 = col - tap * p.C;
-          kh = tap / p.KW; kw = tap - kh * p.KW;
-        }
-        int nv = (p.NC - w.n0 + 31) / 32;
-        if (nv > NCH) nv = NCH;
-        const uint32_t tx = A_STAGE_BYTES + nv * (BK * 128);
-        // position of the first pixel of the first k-block
-        const int pix0 = w.kb0 * BK;
-        int n = pix0 / (p.OH * p.OW);
-        const int rem = pix0 - n * (p.OH * p.OW);
-        int oy = rem / p.OW, ox = rem - oy * p.OW;
-        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
-          const int s = it % C::STAGES;
-          const uint32_t ph = (it / C::STAGES) & 1;
-          PROF_BEGIN(tw);
-          const bool got = mbar_wait(&empty[s], ph ^ 1, p.status, 0x201);
-          PROF_END(tw);
-          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-          if (lane == 0) mbar_expect_tx(&full[s], tx);
-          __syncwarp();
-          if (lane < 4)
-            tma_load_2d(smem_a + s * A_STAGE_BYTES + lane * (BK * 128), &tm, &full[s], w.m0 + lane * 32, kb * BK);
-          else if (cvalid)
-            tma_load_im2col_4d(smem_b + s * C::B_STAGE_BYTES + ci * (BK * 128), &tmi, &full[s], c0,
-                               ox * p.stride - p.pw, oy * p.stride - p.ph, n, (uint16_t)kw, (uint16_t)kh);
-          ox += BK;
-          while (ox >= p.OW) { ox -= p.OW; ++oy; }
-          while (oy >= p.OH) { oy -= p.OH; ++n; }
-        }
-      }
-      PROF_END(tt);
-      if (lane == 0) { PROF_FLUSH(4, tw); PROF_FLUSH(5, tt); }
-      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      if (lane == 0) wgrad_producer(0);
     } else if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -392,7 +409,10 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
     }
     PROF_END(et);
     if (warp == 2 && lane == 0) { PROF_FLUSH(11, ew); PROF_FLUSH(12, et); }
-  } else if (!IM2COL) {
+  } else if (IM2COL) {
+    // ---------------------------------------------------------------- extra TMA producers (wgrad only)
+    if (MODE == 2 && lane == 0) wgrad_producer(warp - 5);
+  } else {
     // ---------------------------------------------------------------- gather producers (warps 6..)
     // The loop over k-blocks is kept short on purpose: with few warps per scheduler the chain of
     // dependent address instructions, not the memory system, bounds the rate of k-blocks.  So
@@ -665,7 +685,7 @@ template <int MODE, int BN, bool IM2COL>
 int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
   using C = Cfg<BN>;
   auto kern = conv_tf32_kernel<MODE, BN, IM2COL>;
-  constexpr int threads = IM2COL ? 192 : NUM_THREADS;
+  constexpr int threads = IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS;   // wgrad: three extra producer warps
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
@@ -712,7 +732,7 @@ ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH
   p.N = N; p.C = C; p.H = H; p.W = W; p.O = O; p.KH = KH; p.KW = KW; p.OH = OH; p.OW = OW;
   p.ph = ph; p.pw = pw; p.stride = stride;
   p.src = nullptr; p.out = nullptr; p.ws = nullptr; p.accumulate = 0; p.splits = 1; p.taps = 1;
-  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr;
+  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr; p.a3d = 0;
   p.M = 0; p.NC = 0; p.kblocks = 0; p.tiles_m = 0; p.tiles_n = 0; p.ldc = 0;
   return p;
 }
@@ -808,9 +828,18 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.NC + bn - 1) / bn;
     CUtensorMap tm, tmi;
-    uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
-    uint32_t bx[2] = {32, BK};
-    rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
+    const bool want_im2col = (C % 32) == 0;
+    if (want_im2col && (O % 32) == 0) {
+      // chunk-outermost view of dy: one box brings the four 32-channel chunks of a k-block
+      uint64_t d[3] = {32, (uint64_t)mpix, (uint64_t)O / 32}, s[2] = {(uint64_t)O * 4, 128};
+      uint32_t bx[3] = {32, BK, BM / 32};
+      rc = tsb_host::make_tmap_f32(&tm, y, 3, d, s, bx, true);
+      p.a3d = 1;
+    } else {
+      uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
+      uint32_t bx[2] = {32, BK};
+      rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
+    }
     if (rc) return rc;
     // split the pixel reduction so that the work items fill whole waves of CTAs
     const long long tiles = (long long)p.tiles_m * p.tiles_n * p.taps;
@@ -835,8 +864,18 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
       if (!p.ws) return TSB_ERR_OOM;
     }
     rc = im2col_map(&tmi, x, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BK, true);
-    if (rc == TSB_OK) rc = launch_bn<2, true>(bn, tm, tmi, p, st);
-    else if (rc == TSB_ERR_UNSUPPORTED) rc = launch_bn<2, false>(bn, tm, tm, p, st);
+    if (rc == TSB_OK) {
+      rc = launch_bn<2, true>(bn, tm, tmi, p, st);
+    } else if (rc == TSB_ERR_UNSUPPORTED) {
+      if (p.a3d) {               // the gather kernel reads dy through the 2-D view
+        uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
+        uint32_t bx[2] = {32, BK};
+        rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
+        if (rc) return rc;
+        p.a3d = 0;
+      }
+      rc = launch_bn<2, false>(bn, tm, tm, p, st);
+    }
     if (rc) return rc;
     if (p.splits > 1) {
       const long long per_split = (long long)O * KH * KW * C;

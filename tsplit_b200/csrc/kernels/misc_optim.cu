@@ -161,8 +161,28 @@ __global__ void opt_kernel(const OptArgs a) {
   float* s1 = a.s1[t];
   float* s2 = a.s2[t];
   const long long n = a.n[t];
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  // 16 bytes per access when every array of this tensor is 16-byte aligned; scalar tail / fallback
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                     (KIND >= 1 ? reinterpret_cast<uintptr_t>(s1) : 0) |
+                     (KIND == 4 ? reinterpret_cast<uintptr_t>(s2) : 0)) & 15) == 0;
+  const long long n4 = vec ? n / 4 : 0;
+  for (long long i = tid; i < n4; i += nthreads) {
+    float4 pv = reinterpret_cast<float4*>(p)[i];
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    float4 v1 = make_float4(0, 0, 0, 0), v2 = make_float4(0, 0, 0, 0);
+    if (KIND >= 1) v1 = reinterpret_cast<float4*>(s1)[i];
+    if (KIND == 4) v2 = reinterpret_cast<float4*>(s2)[i];
+    opt_one<KIND>(pv.x, gv.x, v1.x, v2.x, a.h);
+    opt_one<KIND>(pv.y, gv.y, v1.y, v2.y, a.h);
+    opt_one<KIND>(pv.z, gv.z, v1.z, v2.z, a.h);
+    opt_one<KIND>(pv.w, gv.w, v1.w, v2.w, a.h);
+    reinterpret_cast<float4*>(p)[i] = pv;
+    if (KIND >= 1) reinterpret_cast<float4*>(s1)[i] = v1;
+    if (KIND == 4) reinterpret_cast<float4*>(s2)[i] = v2;
+  }
+  for (long long i = n4 * 4 + tid; i < n; i += nthreads) {
     float pv = p[i], v1 = (KIND >= 1) ? s1[i] : 0.f, v2 = (KIND == 4) ? s2[i] : 0.f;
     opt_one<KIND>(pv, g[i], v1, v2, a.h);
     p[i] = pv;
@@ -235,8 +255,8 @@ int tsb_optimizer_step(int kind, int count, float** params, const float** grads,
     if (kind == 4 && !a.s2[i]) return TSB_ERR_ARG;
   }
   for (int i = 0; i < 8; ++i) a.h[i] = hyper[i];
-  long long bx = (biggest + 255) / 256;
-  if (bx > 2 * sm_count()) bx = 2 * sm_count();
+  long long bx = (biggest / 4 + 255) / 256;
+  if (bx > 8 * sm_count()) bx = 8 * sm_count();
   if (bx < 1) bx = 1;
   dim3 grid((unsigned)bx, count);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -150,13 +150,26 @@ col_partial(const float* __restrict__ a, const float* __restrict__ b, const floa
 }
 
 // Sum of the chunk partials of one channel, in double and in a fixed order: block = 32 channels
-// x 8 lanes, lane y adds chunks y, y+8, ...; lane 0 then adds the eight lane sums.
+// x FIN_LANES lanes; lane y adds chunks y, y+FIN_LANES, ... (four independent loads in flight),
+// lane 0 then adds the lane sums.
+constexpr int FIN_LANES = 32;
 __device__ __forceinline__ void reduce_partials(const float* __restrict__ part, int chunks, int C, int c,
                                                 double& s, double& ss) {
-  __shared__ double sh0[8][32], sh1[8][32];
+  __shared__ double sh0[FIN_LANES][33], sh1[FIN_LANES][33];
   double a = 0.0, b = 0.0;
   if (c < C) {
-    for (int ch = threadIdx.y; ch < chunks; ch += 8) {
+    int ch = threadIdx.y;
+    for (; ch + 3 * FIN_LANES < chunks; ch += 4 * FIN_LANES) {
+      float x[4], y[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        x[u] = part[(long long)(ch + u * FIN_LANES) * C + c];
+        y[u] = part[PLANE_FLOATS + (long long)(ch + u * FIN_LANES) * C + c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { a += x[u]; b += y[u]; }
+    }
+    for (; ch < chunks; ch += FIN_LANES) {
       a += part[(long long)ch * C + c];
       b += part[PLANE_FLOATS + (long long)ch * C + c];
     }
@@ -166,12 +179,12 @@ __device__ __forceinline__ void reduce_partials(const float* __restrict__ part, 
   __syncthreads();
   s = 0.0; ss = 0.0;
   if (threadIdx.y == 0) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { s += sh0[j][threadIdx.x]; ss += sh1[j][threadIdx.x]; }
+#pragma unroll 8
+    for (int j = 0; j < FIN_LANES; ++j) { s += sh0[j][threadIdx.x]; ss += sh1[j][threadIdx.x]; }
   }
 }
 
-// Forward finalise: mean / invstd from the partial sums (+ running statistics).  Block (32, 8).
+// Forward finalise: mean / invstd from the partial sums (+ running statistics).  Block (32, FIN_LANES).
 __global__ void bn_finalize_fwd(const float* __restrict__ part, int chunks, int C, double count, float eps,
                                 float momentum, float* __restrict__ mean, float* __restrict__ invstd,
                                 float* __restrict__ run_mean, float* __restrict__ run_var) {
@@ -277,7 +290,7 @@ int static_scratch(float** out) {
   return TSB_OK;
 }
 
-// Launch geometry of the column statistics: columns per block, row chunks, grid.  Aims at eight
+// Launch geometry of the column statistics: columns per block, row chunks, grid.  Aims at four
 // blocks per SM; narrow tensors get more chunks (a plane holds chunks x C partials).
 struct StatGeom {
   int cw, chunks;
@@ -289,7 +302,7 @@ StatGeom stat_geom(long long rows, int C) {
   g.cw = c4 < 32 ? c4 : 32;
   const int rl = STAT_THREADS / g.cw;
   const int col_blocks = (c4 + g.cw - 1) / g.cw;
-  long long want = (8ll * sm_count() + col_blocks - 1) / col_blocks;
+  long long want = (4ll * sm_count() + col_blocks - 1) / col_blocks;
   const long long cap = PLANE_FLOATS / C;
   if (want > cap) want = cap;
   if (want > 4096) want = 4096;
@@ -383,7 +396,7 @@ int tsb_bn_forward(const float* x, const float* scale, const float* bias, float*
   if (!part) return TSB_ERR_OOM;
   const StatGeom sg = stat_geom(rows, (int)C);
   col_partial<0><<<sg.grid, STAT_THREADS, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, sg.chunks, sg.cw);
-  bn_finalize_fwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
+  bn_finalize_fwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
                                                          save_invstd, run_mean, run_var);
   bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
                                                         ldx, ldy, relu);
@@ -405,7 +418,7 @@ int tsb_bn_forward_static(const float* x, const float* scale, const float* bias,
   // every partial word that the finalise step reads is written by the statistics step of the
   // same call, so nothing in the shared array has to be cleared between calls
   col_partial<0><<<sg.grid, STAT_THREADS, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, sg.chunks, sg.cw);
-  bn_finalize_fwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
+  bn_finalize_fwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
                                                          save_invstd, run_mean, run_var);
   bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
                                                         ldx, ldy, relu);
@@ -423,7 +436,7 @@ int tsb_bn_backward(const float* dy, const float* x, const float* scale, const f
   const StatGeom sg = stat_geom(rows, (int)C);
   col_partial<1><<<sg.grid, STAT_THREADS, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, sg.chunks,
                                                    sg.cw);
-  bn_finalize_bwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
+  bn_finalize_bwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
                                                         rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows);
   return done();
@@ -444,7 +457,7 @@ int tsb_bn_relu_backward(const float* dy, const float* x, const float* y, const 
   const StatGeom sg = stat_geom(rows, (int)C);
   col_partial<1><<<sg.grid, STAT_THREADS, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, sg.chunks,
                                                    sg.cw, y, ldy);
-  bn_finalize_bwd<<<fin_blocks(C), dim3(32, 8), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
+  bn_finalize_bwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
                                                         rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows, y, ldy);
   return done();
@@ -473,7 +486,7 @@ int tsb_layer_norm_grad(const float* dy, const float* x, const float* scale, con
   if (chunks > MAX_CHUNKS) chunks = MAX_CHUNKS;
   dim3 grid((unsigned)((D + 127) / 128), chunks);
   ln_bwd_params_partial<<<grid, 128, 0, st>>>(dy, x, mean, invstd, part, rows, (int)D, chunks);
-  bn_finalize_bwd<<<fin_blocks(D), dim3(32, 8), 0, st>>>(part, chunks, (int)D, dscale, dbias);
+  bn_finalize_bwd<<<fin_blocks(D), dim3(32, FIN_LANES), 0, st>>>(part, chunks, (int)D, dscale, dbias);
   return done();
 }
 
