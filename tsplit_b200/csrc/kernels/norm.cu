@@ -62,7 +62,9 @@ int done() {
 // (cw = min(32, C/4)) with 256/cw row lanes, so narrow tensors (64 channels) still keep every
 // thread busy; each thread has four independent rows in flight.
 // MODE 0: p0 = sum x, p1 = sum x^2.   MODE 1: p0 = sum dy, p1 = sum dy * (x - mean) * invstd.
-// `mask` (MODE 1 only, may be null): output of a fused ReLU; dy counts only where mask > 0.
+// `rscale` / `rbias` (MODE 1 only, may be null): scale and shift of a fused BN+ReLU forward; dy then
+// counts only where the forward output (x - mean) * invstd * scale + bias was positive.  The sign is
+// recomputed from x, which this pass reads anyway, instead of reading the forward output.
 constexpr int STAT_THREADS = 256;
 constexpr int STAT_UNROLL = 4;
 
@@ -76,9 +78,13 @@ __device__ __forceinline__ void stat_accum1(float4& a0, float4& a1, float4 g, co
   a1.x += g.x * (x.x - mu.x) * is.x; a1.y += g.y * (x.y - mu.y) * is.y;
   a1.z += g.z * (x.z - mu.z) * is.z; a1.w += g.w * (x.w - mu.w) * is.w;
 }
-__device__ __forceinline__ float4 relu_mask(float4 g, const float4 m) {
-  g.x = m.x > 0.f ? g.x : 0.f; g.y = m.y > 0.f ? g.y : 0.f;
-  g.z = m.z > 0.f ? g.z : 0.f; g.w = m.w > 0.f ? g.w : 0.f;
+// dy where the fused forward output was positive, else 0 (same expression as bn_apply_fwd)
+__device__ __forceinline__ float4 relu_mask(float4 g, const float4 x, const float4 mu, const float4 is,
+                                            const float4 sc, const float4 bi) {
+  g.x = ((x.x - mu.x) * is.x * sc.x + bi.x) > 0.f ? g.x : 0.f;
+  g.y = ((x.y - mu.y) * is.y * sc.y + bi.y) > 0.f ? g.y : 0.f;
+  g.z = ((x.z - mu.z) * is.z * sc.z + bi.z) > 0.f ? g.z : 0.f;
+  g.w = ((x.w - mu.w) * is.w * sc.w + bi.w) > 0.f ? g.w : 0.f;
   return g;
 }
 
@@ -86,8 +92,8 @@ template <int MODE>
 __global__ void __launch_bounds__(STAT_THREADS)
 col_partial(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mean,
             const float* __restrict__ invstd, float* __restrict__ part, long long rows, int C,
-            long long lda, long long ldb, int chunks, int cw, const float* __restrict__ mask = nullptr,
-            long long ldm = 0) {
+            long long lda, long long ldb, int chunks, int cw, const float* __restrict__ rscale = nullptr,
+            const float* __restrict__ rbias = nullptr) {
   __shared__ float4 s0[STAT_THREADS], s1[STAT_THREADS];
   const int rl = STAT_THREADS / cw;               // row lanes
   const int cx = threadIdx.x % cw, ry = threadIdx.x / cw;
@@ -99,25 +105,30 @@ col_partial(const float* __restrict__ a, const float* __restrict__ b, const floa
   const bool active = ry < rl && c < C;
   if (active) {
     float4 mu = make_float4(0, 0, 0, 0), is = make_float4(1, 1, 1, 1);
+    float4 sc = make_float4(0, 0, 0, 0), bi = make_float4(0, 0, 0, 0);
+    const bool relu = MODE == 1 && rscale != nullptr;
     if (MODE == 1) {
       mu = *reinterpret_cast<const float4*>(mean + c);
       is = *reinterpret_cast<const float4*>(invstd + c);
+      if (relu) {
+        sc = *reinterpret_cast<const float4*>(rscale + c);
+        bi = *reinterpret_cast<const float4*>(rbias + c);
+      }
     }
     long long r = r0 + ry;
     for (; r + (STAT_UNROLL - 1) * rl < r1; r += STAT_UNROLL * rl) {
-      float4 v[STAT_UNROLL], x[STAT_UNROLL], m[STAT_UNROLL];
+      float4 v[STAT_UNROLL], x[STAT_UNROLL];
 #pragma unroll
       for (int u = 0; u < STAT_UNROLL; ++u) {
         v[u] = *reinterpret_cast<const float4*>(a + (r + u * rl) * lda + c);
         if (MODE == 1) x[u] = *reinterpret_cast<const float4*>(b + (r + u * rl) * ldb + c);
-        if (MODE == 1 && mask) m[u] = *reinterpret_cast<const float4*>(mask + (r + u * rl) * ldm + c);
       }
 #pragma unroll
       for (int u = 0; u < STAT_UNROLL; ++u) {
         if (MODE == 0) {
           stat_accum0(acc0, acc1, v[u]);
         } else {
-          if (mask) v[u] = relu_mask(v[u], m[u]);
+          if (relu) v[u] = relu_mask(v[u], x[u], mu, is, sc, bi);
           stat_accum1(acc0, acc1, v[u], x[u], mu, is);
         }
       }
@@ -127,8 +138,9 @@ col_partial(const float* __restrict__ a, const float* __restrict__ b, const floa
       if (MODE == 0) {
         stat_accum0(acc0, acc1, v);
       } else {
-        if (mask) v = relu_mask(v, *reinterpret_cast<const float4*>(mask + r * ldm + c));
-        stat_accum1(acc0, acc1, v, *reinterpret_cast<const float4*>(b + r * ldb + c), mu, is);
+        const float4 xv = *reinterpret_cast<const float4*>(b + r * ldb + c);
+        if (relu) v = relu_mask(v, xv, mu, is, sc, bi);
+        stat_accum1(acc0, acc1, v, xv, mu, is);
       }
     }
   }
@@ -241,7 +253,7 @@ __global__ void bn_apply_bwd(const float* __restrict__ dy, const float* __restri
                              const float* __restrict__ invstd, const float* __restrict__ dscale,
                              const float* __restrict__ dbias, float* __restrict__ dx, long long rows, int C,
                              long long lddy, long long ldx, long long lddx, float inv_count,
-                             const float* __restrict__ mask = nullptr, long long ldm = 0) {
+                             const float* __restrict__ rbias = nullptr) {
   const int C4 = C >> 2;
   const long long total = rows * C4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -249,15 +261,11 @@ __global__ void bn_apply_bwd(const float* __restrict__ dy, const float* __restri
     const long long r = i / C4;
     const int c = (int)(i - r * C4) * 4;
     float4 g = *reinterpret_cast<const float4*>(dy + r * lddy + c);
-    if (mask) {
-      const float4 m = *reinterpret_cast<const float4*>(mask + r * ldm + c);
-      g.x = m.x > 0.f ? g.x : 0.f; g.y = m.y > 0.f ? g.y : 0.f;
-      g.z = m.z > 0.f ? g.z : 0.f; g.w = m.w > 0.f ? g.w : 0.f;
-    }
     const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
     const float4 mu = *reinterpret_cast<const float4*>(mean + c);
     const float4 is = *reinterpret_cast<const float4*>(invstd + c);
     const float4 sc = *reinterpret_cast<const float4*>(scale + c);
+    if (rbias) g = relu_mask(g, v, mu, is, sc, *reinterpret_cast<const float4*>(rbias + c));   // fused ReLU
     const float4 ds = *reinterpret_cast<const float4*>(dscale + c);
     const float4 db = *reinterpret_cast<const float4*>(dbias + c);
     float4 o;
@@ -442,24 +450,23 @@ int tsb_bn_backward(const float* dy, const float* x, const float* scale, const f
   return done();
 }
 
-// Backward of the fused batch-norm + ReLU: `y` is the fused forward output; the incoming
-// gradient is masked by y > 0 on the fly in both passes, so no separate ReLU-gradient pass
-// (and no gradient tensor for the batch-norm output) exists.
-int tsb_bn_relu_backward(const float* dy, const float* x, const float* y, const float* scale,
+// Backward of the fused batch-norm + ReLU.  The incoming gradient is masked on the fly in both
+// passes by the sign of the forward output, which is recomputed from x, scale and bias: no separate
+// ReLU-gradient pass exists and the forward output is not read at all.
+int tsb_bn_relu_backward(const float* dy, const float* x, const float* scale, const float* bias,
                          const float* save_mean, const float* save_invstd, float* dx, float* dscale, float* dbias,
-                         long long rows, long long C, long long ldx, long long lddy, long long ldy, long long lddx,
-                         void* stream) {
+                         long long rows, long long C, long long ldx, long long lddy, long long lddx, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (rows <= 0 || C <= 0) return TSB_ERR_ARG;
-  if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4) || (ldy % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
+  if (rows <= 0 || C <= 0 || !bias) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4) || C > 8192) return TSB_ERR_UNSUPPORTED;
   float* part = scratch();
   if (!part) return TSB_ERR_OOM;
   const StatGeom sg = stat_geom(rows, (int)C);
   col_partial<1><<<sg.grid, STAT_THREADS, 0, st>>>(dy, x, save_mean, save_invstd, part, rows, (int)C, lddy, ldx, sg.chunks,
-                                                   sg.cw, y, ldy);
+                                                   sg.cw, scale, bias);
   bn_finalize_bwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
-                                                        rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows, y, ldy);
+                                                        rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows, bias);
   return done();
 }
 

@@ -114,8 +114,8 @@ def single(op, batch, channel, hw, iters):
                 ds, db = ndarray.empty((1, c, 1, 1), ctx), ndarray.empty((1, c, 1, 1), ctx)
                 g = ndarray.empty((n, c, hw, hw), ctx)
                 g.t.normal_()
-                fn = lambda: G.bn_relu_backward(g, x, y, s_, stats[0], stats[1], dx, ds, db, stream=st)
-                work, unit = 7.0 * x.nbytes / 1e6, "GB/s"
+                fn = lambda: G.bn_relu_backward(g, x, s_, b_, stats[0], stats[1], dx, ds, db, stream=st)
+                work, unit = 5.0 * x.nbytes / 1e6, "GB/s"   # dy and x read twice, dx written once
     ms = _time(fn, iters)
     print("%s batch=%d channel=%d hw=%d: %.4f ms, %.1f %s" % (op, batch, channel, hw, ms, work / ms, unit))
     return ms

@@ -236,14 +236,13 @@ def bn_backward(dy, x, scale, save_mean, save_invstd, dx, dscale, dbias, stream)
                                  c_int64(lddy), c_int64(lddx), _s(stream)), "bn_backward")
 
 
-def bn_relu_backward(dy, x, y, scale, save_mean, save_invstd, dx, dscale, dbias, stream):
+def bn_relu_backward(dy, x, scale, bias, save_mean, save_invstd, dx, dscale, dbias, stream):
     rows, c, ldx = _rows_c(x)
     _, _, lddy = _rows_c(dy)
-    _, _, ldy = _rows_c(y)
     _, _, lddx = _rows_c(dx)
-    _check(lib().tsb_bn_relu_backward(_p(dy), _p(x), _p(y), _p(scale), _p(save_mean), _p(save_invstd), _p(dx),
+    _check(lib().tsb_bn_relu_backward(_p(dy), _p(x), _p(scale), _p(bias), _p(save_mean), _p(save_invstd), _p(dx),
                                       _p(dscale), _p(dbias), c_int64(rows), c_int64(c), c_int64(ldx),
-                                      c_int64(lddy), c_int64(ldy), c_int64(lddx), _s(stream)), "bn_relu_backward")
+                                      c_int64(lddy), c_int64(lddx), _s(stream)), "bn_relu_backward")
 
 
 def layer_norm(x, scale, bias, y, mean, invstd, eps, stream):
