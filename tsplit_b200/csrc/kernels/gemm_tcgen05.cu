@@ -40,6 +40,7 @@ struct GemmParams {
   int accumulate;
   int tiles_m, tiles_n;
   int kblocks;        // ceil(K / BK)
+  int a_chunked, b_chunked;   // MN-major operand mapped (32 cols, k, chunk of 32 cols, batch): one box per stage
   int* status;
 };
 
@@ -121,12 +122,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * BK;
           if (!A_MN) {
             tma_load_3d(sa, &tmA, &full[s], k0, m0, b);
+          } else if (p.a_chunked) {
+            tma_load_4d(sa, &tmA, &full[s], 0, k0, m0 >> 5, b);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 32; ++c) tma_load_3d(sa + c * (BK * 128), &tmA, &full[s], m0 + c * 32, k0, b);
           }
           if (!B_MN) {
             tma_load_3d(sb, &tmB, &full[s], k0, n0, b);
+          } else if (p.b_chunked) {
+            tma_load_4d(sb, &tmB, &full[s], 0, k0, n0 >> 5, b);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) tma_load_3d(sb + c * (BK * 128), &tmB, &full[s], n0 + c * 32, k0, b);
@@ -141,6 +146,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_tf32(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // descriptor halves: K-major operands step 32 bytes per MMA inside the 128B swizzle row,
+      // MN-major ones (32-byte-atom swizzle, chunks of 32 columns BK*128 bytes apart) 1024 bytes
+      constexpr uint32_t A_HI = A_MN ? smem_desc_hi(512, LAYOUT_SW128_BASE32B) : smem_desc_hi(1024);
+      constexpr uint32_t B_HI = B_MN ? smem_desc_hi(512, LAYOUT_SW128_BASE32B) : smem_desc_hi(1024);
+      constexpr uint32_t A_KSTEP = (A_MN ? 1024 : UMMA_K * 4) >> 4, B_KSTEP = (B_MN ? 1024 : UMMA_K * 4) >> 4;
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), A_MN ? BK * 128 : 16);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), B_MN ? BK * 128 : 16);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
@@ -158,16 +170,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&full[s], ph, p.status, 0x103)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
-          const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
+          const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (C::B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? make_smem_desc(sa + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
-                                     : make_smem_desc(sa + k * (UMMA_K * 4), 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc(sb + k * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B)
-                                     : make_smem_desc(sb + k * (UMMA_K * 4), 16, 1024);
-            umma_tf32(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_tf32(d_tmem, smem_desc_join(A_HI, a_lo + k * A_KSTEP), smem_desc_join(B_HI, b_lo + k * B_KSTEP),
+                      idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);     // frees the smem stage when these MMAs retire
         }
         if (ok) umma_commit(&tfull[acc]);
@@ -579,6 +587,7 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
   }
   // tensor maps (dims innermost first)
   CUtensorMap ta, tb;
+  p.a_chunked = p.b_chunked = 0;
   const uint64_t sab = (uint64_t)(batch > 1 ? sa : (long long)(trans_a ? k : m) * lda) * 4;
   const uint64_t sbb = (uint64_t)(batch > 1 ? sb : (long long)(trans_b ? n : k) * ldb) * 4;
   int rc;
@@ -586,7 +595,12 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     uint64_t d[3] = {(uint64_t)k, (uint64_t)m, (uint64_t)batch}, s[2] = {(uint64_t)lda * 4, sab};
     uint32_t bx[3] = {BK, BM, 1};
     rc = tsb_host::make_tmap_f32(&ta, a, 3, d, s, bx);
-  } else {          // A stored [k][m], M contiguous -> MN-major
+  } else if (m % 32 == 0) {   // A stored [k][m], M contiguous -> MN-major; all chunks of a stage in one box
+    uint64_t d[4] = {32, (uint64_t)k, (uint64_t)m / 32, (uint64_t)batch}, s[3] = {(uint64_t)lda * 4, 128, sab};
+    uint32_t bx[4] = {32, BK, BM / 32, 1};
+    rc = tsb_host::make_tmap_f32(&ta, a, 4, d, s, bx, true);
+    p.a_chunked = 1;
+  } else {
     uint64_t d[3] = {(uint64_t)m, (uint64_t)k, (uint64_t)batch}, s[2] = {(uint64_t)lda * 4, sab};
     uint32_t bx[3] = {32, BK, 1};
     rc = tsb_host::make_tmap_f32(&ta, a, 3, d, s, bx, true);
@@ -596,7 +610,12 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     uint64_t d[3] = {(uint64_t)k, (uint64_t)n, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
     uint32_t bx[3] = {BK, (uint32_t)bn, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx);
-  } else {          // B[k][n], N contiguous -> MN-major
+  } else if (n % 32 == 0) {   // B[k][n], N contiguous -> MN-major; all chunks of a stage in one box
+    uint64_t d[4] = {32, (uint64_t)k, (uint64_t)n / 32, (uint64_t)batch}, s[3] = {(uint64_t)ldb * 4, 128, sbb};
+    uint32_t bx[4] = {32, BK, (uint32_t)bn / 32, 1};
+    rc = tsb_host::make_tmap_f32(&tb, b, 4, d, s, bx, true);
+    p.b_chunked = 1;
+  } else {
     uint64_t d[3] = {(uint64_t)n, (uint64_t)k, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
     uint32_t bx[3] = {32, BK, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx, true);
