@@ -52,11 +52,16 @@ struct ConvParams {
   unsigned long long* prof;   // role-time counters (only written when built with -DTSB_CONV_PROF)
 };
 
-template <int BN>
+// Narrow tiles (BN <= 128) of the TMA-only kernels run two CTAs per SM: a stage's four MMAs cost
+// the single issuing thread about as much time for a 64-wide tile as for a 256-wide one, so a second
+// CTA's issue thread fills the tensor pipe that one CTA leaves idle.  Each of the two gets half the
+// stages (2 x ~97 KB of shared memory) and its own TMEM columns (2 x 128 or 2 x 256 of 512).
+template <int BN, bool IM2COL>
 struct Cfg {
+  static constexpr int OCC = (IM2COL && BN <= 128) ? 2 : 1;       // CTAs per SM
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = ((BN == 256) ? 4 : (BN == 128 ? 6 : 8)) / OCC;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
 };
@@ -114,9 +119,9 @@ __device__ __forceinline__ Item decode_item(const ConvParams& p, long long item,
 // gather warps at all; needs the gathered tensor's channel count to be a multiple of 32 and is not
 // used for strided dgrad.  Otherwise the eight cp.async warps below gather it.
 template <int MODE, int BN, bool IM2COL>
-__global__ void __launch_bounds__(IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS, 1)
+__global__ void __launch_bounds__(IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS, Cfg<BN, IM2COL>::OCC)
 conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi, const ConvParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, IM2COL>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -311,7 +316,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
       const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), A_MN ? BK * 128 : 16);
       const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), B_MN ? BK * 128 : 16);
       uint32_t it = 0, acc_it = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       PROF_DECL(mf); PROF_DECL(me); PROF_DECL(mi); PROF_DECL(mt);
       PROF_BEGIN(mt);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
@@ -327,9 +332,13 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           PROF_BEGIN(mf);
-          if (!mbar_wait(&full[s], ph, p.status, 0x203)) { ok = false; break; }
+          if (!ready && !mbar_wait(&full[s], ph, p.status, 0x203)) { ok = false; break; }
           PROF_END(mf);
           PROF_BEGIN(mi);
+          {   // probe the next stage now; the answer arrives while this stage's MMAs are issued
+            const uint32_t it2 = it + 1;
+            ready = mbar_test(&full[it2 % C::STAGES], (it2 / C::STAGES) & 1);
+          }
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + s * (C::B_STAGE_BYTES >> 4);
@@ -683,7 +692,7 @@ int sm_count() {
 
 template <int MODE, int BN, bool IM2COL>
 int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, IM2COL>;
   auto kern = conv_tf32_kernel<MODE, BN, IM2COL>;
   constexpr int threads = IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS;   // wgrad: three extra producer warps
   static bool attr_set = false;
@@ -693,7 +702,8 @@ int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, c
     attr_set = true;
   }
   const long long items = (long long)p.tiles_m * p.tiles_n * p.taps * p.splits;
-  const int grid = (int)(items < sm_count() ? items : sm_count());
+  const long long slots = (long long)sm_count() * C::OCC;
+  const int grid = (int)(items < slots ? items : slots);
 #ifdef TSB_CONV_PROF
   static unsigned long long* prof = nullptr;
   if (!prof) cudaMalloc(reinterpret_cast<void**>(&prof), 16 * sizeof(unsigned long long));

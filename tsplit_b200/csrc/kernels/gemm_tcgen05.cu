@@ -154,7 +154,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), A_MN ? BK * 128 : 16);
       const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), B_MN ? BK * 128 : 16);
       uint32_t it = 0, acc_it = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
         const long long rest = item / tiles;
         const int split = (int)(rest / p.batch);
@@ -168,7 +168,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, p.status, 0x103)) { ok = false; break; }
+          if (!ready && !mbar_wait(&full[s], ph, p.status, 0x103)) { ok = false; break; }
+          {   // probe the next stage now; the answer arrives while this stage's MMAs are issued
+            const uint32_t it2 = it + 1;
+            ready = mbar_test(&full[it2 % C::STAGES], (it2 / C::STAGES) & 1);
+          }
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + s * (C::B_STAGE_BYTES >> 4);
