@@ -126,40 +126,63 @@ __device__ bool exchange(const Args& a, int phase) {
   return ok;
 }
 
+// One thread handles U 16-byte pieces per trip and issues the U peer loads of a rank back to
+// back, so U * 16 bytes per thread are in flight on NVLink at any time (a peer load takes a few
+// microseconds; with one load in flight per thread the links ran at well under half their rate).
+constexpr int U = 8;
+
 template <int KIND>
 __device__ void reduce_update_shard(const Args& a, long long tid, long long nthreads) {
   const float inv = 1.f / (float)a.world;
   const long long lo4 = a.lo >> 2, hi4 = a.hi >> 2;
-  for (long long i4 = lo4 + tid; i4 < hi4; i4 += nthreads) {
-    const long long i = i4 << 2;
-    float4 g;
+  for (long long base = lo4 + tid; base < hi4; base += nthreads * U) {
+    float4 g[U];
     if (a.grad_mc) {
-      g = multimem_ld_reduce(a.grad_mc + i);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i4 = base + u * nthreads;
+        g[u] = i4 < hi4 ? multimem_ld_reduce(a.grad_mc + (i4 << 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     } else {
-      g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < U; ++u) g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
       for (int r = 0; r < a.world; ++r) {       // fixed order: bitwise identical on every rank
-        const float4 v = ld_peer(a.grad[r] + i);
-        g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
+        const float* src = a.grad[r];
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i4 = base + u * nthreads;
+          v[u] = i4 < hi4 ? ld_peer(src + (i4 << 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) { g[u].x += v[u].x; g[u].y += v[u].y; g[u].z += v[u].z; g[u].w += v[u].w; }
       }
     }
-    g.x *= inv; g.y *= inv; g.z *= inv; g.w *= inv;
-    float4 p = *reinterpret_cast<const float4*>(a.param[a.rank] + i);
-    const long long li = i - a.lo;
-    float4 s1 = make_float4(0, 0, 0, 0), s2 = make_float4(0, 0, 0, 0);
-    if (KIND >= 1) s1 = *reinterpret_cast<const float4*>(a.slot1 + li);
-    if (KIND == 4) s2 = *reinterpret_cast<const float4*>(a.slot2 + li);
-    opt_one<KIND>(p.x, g.x, s1.x, s2.x, a.h);
-    opt_one<KIND>(p.y, g.y, s1.y, s2.y, a.h);
-    opt_one<KIND>(p.z, g.z, s1.z, s2.z, a.h);
-    opt_one<KIND>(p.w, g.w, s1.w, s2.w, a.h);
-    if (KIND >= 1) *reinterpret_cast<float4*>(a.slot1 + li) = s1;
-    if (KIND == 4) *reinterpret_cast<float4*>(a.slot2 + li) = s2;
-    if (a.param_mc) {
-      multimem_st(a.param_mc + i, p);
-    } else {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i4 = base + u * nthreads;
+      if (i4 >= hi4) break;
+      const long long i = i4 << 2;
+      float4 gv = g[u];
+      gv.x *= inv; gv.y *= inv; gv.z *= inv; gv.w *= inv;
+      float4 p = *reinterpret_cast<const float4*>(a.param[a.rank] + i);
+      const long long li = i - a.lo;
+      float4 s1 = make_float4(0, 0, 0, 0), s2 = make_float4(0, 0, 0, 0);
+      if (KIND >= 1) s1 = *reinterpret_cast<const float4*>(a.slot1 + li);
+      if (KIND == 4) s2 = *reinterpret_cast<const float4*>(a.slot2 + li);
+      opt_one<KIND>(p.x, gv.x, s1.x, s2.x, a.h);
+      opt_one<KIND>(p.y, gv.y, s1.y, s2.y, a.h);
+      opt_one<KIND>(p.z, gv.z, s1.z, s2.z, a.h);
+      opt_one<KIND>(p.w, gv.w, s1.w, s2.w, a.h);
+      if (KIND >= 1) *reinterpret_cast<float4*>(a.slot1 + li) = s1;
+      if (KIND == 4) *reinterpret_cast<float4*>(a.slot2 + li) = s2;
+      if (a.param_mc) {
+        multimem_st(a.param_mc + i, p);
+      } else {
 #pragma unroll 1
-      for (int r = 0; r < a.world; ++r) st_peer(a.param[r] + i, p);
+        for (int r = 0; r < a.world; ++r) st_peer(a.param[r] + i, p);
+      }
     }
   }
 }

@@ -5,11 +5,13 @@ replaces.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
         --master-port 29555 -m tsplit_b200.parallel.bench_allreduce --mb 100 400
 
-For a bucket of S bytes on N GPUs the fused kernel moves S*(N-1)/N bytes in
-(gradient shards read from peers) and S*(N-1)/N bytes out (new parameters stored
-to peers) per GPU; both directions run concurrently, so the link-time floor is
-S*(N-1)/N divided by the per-direction peer bandwidth (770 GB/s measured copy,
-900 GB/s nominal).  Timed on the device with CUDA events, max over ranks.
+For a bucket of S bytes on N GPUs every GPU receives 2*S*(N-1)/N bytes (the
+peers' gradients for its own shard, which it reads, and the peers' updated
+shards, which they store into it) and sends as many (the answers to the peers'
+reads of its gradients and its own updated shard stored to the peers).  The two
+directions run concurrently, so the link-time floor is 2*S*(N-1)/N divided by
+the per-direction peer bandwidth (770 GB/s measured copy, 900 GB/s nominal).
+Timed on the device with CUDA events, max over ranks.
 """
 from __future__ import annotations
 
@@ -105,7 +107,7 @@ def main():
         comm.check(st)
         if rank == 0:
             s_bytes = n * 4
-            floor_ms = s_bytes * (world - 1) / world / (LINK_GBS_MEASURED * 1e6)
+            floor_ms = 2.0 * s_bytes * (world - 1) / world / (LINK_GBS_MEASURED * 1e6)
             bus = 2.0 * s_bytes * (world - 1) / world / (results["fused"] * 1e6)
             print(json.dumps({"bucket_mb": round(s_bytes / 2**20, 1), "world": world, "nvls": args.nvls,
                               "fused_ms": round(results["fused"], 4), "nccl_plus_update_ms":
