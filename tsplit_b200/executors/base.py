@@ -29,41 +29,56 @@ def _shape_of(v):
 
 class FeedStager(object):
     """Host -> device feed path: a pinned staging buffer and a device buffer per
-    fed node, reused across runs while the shape stays the same."""
+    fed node, reused across runs while the shape stays the same.  A feed that is
+    already a pinned host ``NDArray`` (``ndarray.empty(shape, ndarray.cpu(0),
+    pinned=True)``) is copied to the device straight from the caller's buffer."""
 
     def __init__(self, ctx):
         self.ctx = ctx
         self.slots = {}
 
     def put(self, node, value, stream, channels_last=None):
+        user_pinned = None
         if isinstance(value, ndarray.NDArray):
             if value.ctx == self.ctx or value.ctx.device_type == self.ctx.device_type:
                 return value
-            value = value.asnumpy()
-        value = np.asarray(value)
-        if not ndarray.is_gpu_ctx(self.ctx) or self.ctx.device_type == 3:
-            return ndarray.array(value, self.ctx, use_pool=False)
+            t = getattr(value, "t", None)
+            if (ndarray.is_gpu_ctx(self.ctx) and self.ctx.device_type == 2 and t is not None and not t.is_cuda
+                    and t.is_pinned() and t.is_contiguous() and t.dtype == torch.float32):
+                user_pinned = t.reshape(-1)       # the caller's own pinned buffer: no staging copy
+            else:
+                value = value.asnumpy()
+        if user_pinned is None:
+            value = np.asarray(value)
+            if not ndarray.is_gpu_ctx(self.ctx) or self.ctx.device_type == 3:
+                return ndarray.array(value, self.ctx, use_pool=False)
         shape = tuple(value.shape)
         slot = self.slots.get(node)
         if slot is None or slot[0] != shape or slot[2].is_channels_last() != bool(
                 len(shape) == 4 and (channels_last is None or channels_last)):
             n = int(np.prod(shape)) if shape else 1
-            pinned = torch.empty(max(n, 1), dtype=torch.float32, pin_memory=True)
+            pinned = None
             dev = ndarray.empty(shape, self.ctx, use_pool=False, channels_last=channels_last)
             raw = None
             if dev.is_channels_last() and not dev.t.is_contiguous():   # land row-major bytes first
                 raw = torch.empty(max(n, 1), dtype=torch.float32, device=self.ctx.torch_device)
-            slot = (shape, pinned, dev, raw)
+            slot = [shape, pinned, dev, raw]
             self.slots[node] = slot
         _, pinned, dev, raw = slot
         n = int(np.prod(shape)) if shape else 1
-        pinned[:n].numpy()[...] = value.reshape(-1)
+        if user_pinned is not None:
+            src = user_pinned
+        else:
+            if pinned is None:
+                pinned = slot[1] = torch.empty(max(n, 1), dtype=torch.float32, pin_memory=True)
+            pinned[:n].numpy()[...] = value.reshape(-1)
+            src = pinned
         with torch.cuda.stream(stream.torch_stream):
             if raw is None:
-                dev.t.view(-1)[:n].copy_(pinned[:n], non_blocking=True) if dev.t.is_contiguous() \
-                    else dev.t.copy_(pinned[:n].view(shape), non_blocking=True)
+                dev.t.view(-1)[:n].copy_(src[:n], non_blocking=True) if dev.t.is_contiguous() \
+                    else dev.t.copy_(src[:n].view(shape), non_blocking=True)
             else:
-                raw[:n].copy_(pinned[:n], non_blocking=True)
+                raw[:n].copy_(src[:n], non_blocking=True)
                 from ..ops import _gpu as G
                 rm = []
                 acc = 1
@@ -74,8 +89,8 @@ class FeedStager(object):
         return dev
 
     def bytes_per_step(self, feed_dict):
-        return sum(int(np.prod(np.asarray(v).shape)) * 4 for v in feed_dict.values()
-                   if not isinstance(v, ndarray.NDArray))
+        return sum(int(np.prod(v.shape)) * 4 for v in feed_dict.values()
+                   if not (isinstance(v, ndarray.NDArray) and ndarray.is_gpu_ctx(v.ctx)))
 
 
 class Executor(object):
