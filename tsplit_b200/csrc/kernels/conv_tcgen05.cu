@@ -29,6 +29,7 @@ constexpr int BM = 128;
 constexpr int BK = 32;
 constexpr int UMMA_K = 8;
 constexpr int A_STAGE_BYTES = BM * BK * 4;
+constexpr int STORE_STAGING_BYTES = 4 * 2048;   // per epilogue warp: 32 rows x 16 columns on their way to a TMA store
 constexpr int GATHER_WARPS = 8;        // two per scheduler, so one warp's address arithmetic hides the other's
 constexpr int GATHER_THREADS = GATHER_WARPS * 32;
 constexpr int NUM_THREADS = 6 * 32 + GATHER_THREADS;   // warp0 TMA, warp1 MMA, warps2-5 epilogue, then gather
@@ -47,6 +48,7 @@ struct ConvParams {
   int splits;
   int accumulate;
   long long ldc;
+  int tma_store;       // the output tile leaves through shared memory and TMA stores (map `tmo`)
   int a3d;             // wgrad: dy arrives through the 3-D (32 channels, pixel, chunk) view
   int* status;
   unsigned long long* prof;   // role-time counters (only written when built with -DTSB_CONV_PROF)
@@ -62,7 +64,7 @@ struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGES = ((BN == 256) ? 4 : (BN == 128 ? 6 : 8)) / OCC;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STORE_STAGING_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
 };
 
@@ -120,13 +122,15 @@ __device__ __forceinline__ Item decode_item(const ConvParams& p, long long item,
 // used for strided dgrad.  Otherwise the eight cp.async warps below gather it.
 template <int MODE, int BN, bool IM2COL>
 __global__ void __launch_bounds__(IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS, Cfg<BN, IM2COL>::OCC)
-conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi, const ConvParams p) {
+conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi,
+                 const __grid_constant__ CUtensorMap tmo, const ConvParams p) {
   using C = Cfg<BN, IM2COL>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + C::STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* smem_stg = smem;
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES;
+  uint8_t* smem_b = smem_a + C::STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + C::STAGES * C::STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
   uint64_t* tfull = bars + 2 * C::STAGES;
@@ -148,6 +152,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
     fence_barrier_init();
     tma_prefetch_desc(&tm);
     if (IM2COL) tma_prefetch_desc(&tmi);
+    if (p.tma_store) tma_prefetch_desc(&tmo);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -317,7 +322,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
       const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), B_MN ? BK * 128 : 16);
       uint32_t it = 0, acc_it = 0;
       bool ok = true, ready = false;
-      PROF_DECL(mf); PROF_DECL(me); PROF_DECL(mi); PROF_DECL(mt);
+      PROF_DECL(mf); PROF_DECL(me); PROF_DECL(mi); PROF_DECL(mt); PROF_DECL(mm); PROF_DECL(mc);
       PROF_BEGIN(mt);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
         const Item w = decode_item(p, item, BN);
@@ -342,17 +347,21 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + s * (C::B_STAGE_BYTES >> 4);
+          PROF_BEGIN(mm);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_tf32(d_tmem, smem_desc_join(A_HI, a_lo + k * A_KSTEP), smem_desc_join(B_HI, b_lo + k * B_KSTEP),
                       idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+          PROF_END(mm);
+          PROF_BEGIN(mc);
           umma_commit(&empty[s]);
+          PROF_END(mc);
           PROF_END(mi);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
       PROF_END(mt);
-      PROF_FLUSH(0, mf); PROF_FLUSH(1, me); PROF_FLUSH(2, mi); PROF_FLUSH(3, mt);
+      PROF_FLUSH(0, mf); PROF_FLUSH(1, me); PROF_FLUSH(2, mi); PROF_FLUSH(3, mt); PROF_FLUSH(13, mm); PROF_FLUSH(14, mc);
     }
   } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue
@@ -392,6 +401,35 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
         const int col = w.n0 + c0;
+        if (p.tma_store) {
+          // Each lane holds one output row; written straight to global that is 32 scattered 16-byte
+          // pieces per instruction.  Instead the warp parks 32 rows x 16 columns in shared memory
+          // (64-byte rows, 64B swizzle: conflict-free) and one TMA store writes them as full lines;
+          // the TMA unit also clips rows / columns that lie outside the tensor.
+          uint8_t* stg = smem_stg + q * 2048;
+          const uint32_t srow = smem_u32(stg) + lane * 64;
+          const uint32_t sx = (uint32_t)(lane >> 1) & 3;
+          const int row0 = w.m0 + q * 32;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (lane == 0) bulk_wait_read();       // the previous store has finished reading the buffer
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int j = half * 16 + c * 4;
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(srow + (((uint32_t)c ^ sx) << 4)),
+                           "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
+                           : "memory");
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M && col + half * 16 < p.NC) {
+              tma_store_2d(&tmo, stg, col + half * 16, row0);
+              bulk_commit();
+            }
+          }
+          continue;
+        }
         if (row < p.M && col < p.NC) {
           float* dst = crow + col;
           const bool vec_ok = (col + 32 <= p.NC) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
@@ -416,6 +454,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+    if (p.tma_store && lane == 0) bulk_wait_all();     // this lane's stores are complete before the CTA exits
     PROF_END(et);
     if (warp == 2 && lane == 0) { PROF_FLUSH(11, ew); PROF_FLUSH(12, et); }
   } else if (IM2COL) {
@@ -691,7 +730,8 @@ int sm_count() {
 }
 
 template <int MODE, int BN, bool IM2COL>
-int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
+int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo, const ConvParams& p,
+           cudaStream_t st) {
   using C = Cfg<BN, IM2COL>;
   auto kern = conv_tf32_kernel<MODE, BN, IM2COL>;
   constexpr int threads = IM2COL ? (MODE == 2 ? 288 : 192) : NUM_THREADS;   // wgrad: three extra producer warps
@@ -710,30 +750,31 @@ int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, c
   cudaMemsetAsync(prof, 0, 16 * sizeof(unsigned long long), st);
   ConvParams pp = p;
   pp.prof = prof;
-  kern<<<grid, threads, C::SMEM_BYTES, st>>>(tm, tmi, pp);
+  kern<<<grid, threads, C::SMEM_BYTES, st>>>(tm, tmi, tmo, pp);
   unsigned long long h[16];
   cudaMemcpyAsync(h, prof, sizeof(h), cudaMemcpyDeviceToHost, st);
   cudaStreamSynchronize(st);
   const double kbs = (double)items / grid * ((p.kblocks + p.splits - 1) / p.splits);   // k-blocks per CTA
   fprintf(stderr,
           "[conv prof] mode %d bn %d im2col %d grid %d kblocks/cta %.0f | cycles per k-block: mma total %.0f (wait "
-          "full %.0f, wait tmem %.0f, issue %.0f) | tma total %.0f (wait empty %.0f) | gather total %.0f (wait empty "
+          "full %.0f, wait tmem %.0f, issue %.0f = 4 mma %.0f + commit %.0f + rest) | tma total %.0f (wait empty %.0f) | gather total %.0f (wait empty "
           "%.0f) | epilogue total %.0f (wait tmem-full %.0f)\n",
           MODE, BN, (int)IM2COL, grid, kbs, h[3] / kbs / grid, h[0] / kbs / grid, h[1] / kbs / grid,
-          h[2] / kbs / grid, h[5] / kbs / grid, h[4] / kbs / grid, h[9] / kbs / grid, h[6] / kbs / grid,
+          h[2] / kbs / grid, h[13] / kbs / grid, h[14] / kbs / grid, h[5] / kbs / grid, h[4] / kbs / grid, h[9] / kbs / grid, h[6] / kbs / grid,
           h[12] / kbs / grid, h[11] / kbs / grid);
 #else
-  kern<<<grid, threads, C::SMEM_BYTES, st>>>(tm, tmi, p);
+  kern<<<grid, threads, C::SMEM_BYTES, st>>>(tm, tmi, tmo, p);
 #endif
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
 template <int MODE, bool IM2COL>
-int launch_bn(int bn, const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
-  if (bn == 256) return launch<MODE, 256, IM2COL>(tm, tmi, p, st);
-  if (bn == 128) return launch<MODE, 128, IM2COL>(tm, tmi, p, st);
-  return launch<MODE, 64, IM2COL>(tm, tmi, p, st);
+int launch_bn(int bn, const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo, const ConvParams& p,
+              cudaStream_t st) {
+  if (bn == 256) return launch<MODE, 256, IM2COL>(tm, tmi, tmo, p, st);
+  if (bn == 128) return launch<MODE, 128, IM2COL>(tm, tmi, tmo, p, st);
+  return launch<MODE, 64, IM2COL>(tm, tmi, tmo, p, st);
 }
 
 ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH, int OW, int ph, int pw,
@@ -742,7 +783,7 @@ ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH
   p.N = N; p.C = C; p.H = H; p.W = W; p.O = O; p.KH = KH; p.KW = KW; p.OH = OH; p.OW = OW;
   p.ph = ph; p.pw = pw; p.stride = stride;
   p.src = nullptr; p.out = nullptr; p.ws = nullptr; p.accumulate = 0; p.splits = 1; p.taps = 1;
-  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr; p.a3d = 0;
+  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr; p.a3d = 0; p.tma_store = 0;
   p.M = 0; p.NC = 0; p.kblocks = 0; p.tiles_m = 0; p.tiles_n = 0; p.ldc = 0;
   return p;
 }
@@ -778,10 +819,19 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
   uint32_t bx[2] = {BK, (uint32_t)bn};
   int rc = tsb_host::make_tmap_f32(&tm, wts, 2, d, s, bx, false);
   if (rc) return rc;
+  // output [M][O] leaves through TMA stores of 32 rows x 16 columns (64-byte rows, 64B swizzle)
+  CUtensorMap tmo;
+  {
+    uint64_t od[2] = {(uint64_t)O, (uint64_t)p.M}, os[1] = {(uint64_t)O * 4};
+    uint32_t ob[2] = {16, 32};
+    rc = tsb_host::make_tmap_f32_swz(&tmo, out, 2, od, os, ob, 2);
+    if (rc) return rc;
+    p.tma_store = 1;
+  }
   rc = im2col_map(&tmi, src, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BM, false);
-  if (rc == TSB_OK) return launch_bn<0, true>(bn, tm, tmi, p, st);
+  if (rc == TSB_OK) return launch_bn<0, true>(bn, tm, tmi, tmo, p, st);
   if (rc != TSB_ERR_UNSUPPORTED) return rc;
-  return launch_bn<0, false>(bn, tm, tm, p, st);
+  return launch_bn<0, false>(bn, tm, tm, tmo, p, st);
 }
 
 }  // namespace
@@ -826,7 +876,7 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     uint32_t bx[3] = {32, 1, BK};
     rc = tsb_host::make_tmap_f32(&tm, w, 3, d, s, bx, true);
     if (rc) return rc;
-    rc = launch_bn<1, false>(bn, tm, tm, p, st);
+    rc = launch_bn<1, false>(bn, tm, tm, tm, p, st);
   } else {
     ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
     p.status = tsb_host::status_word(st);
@@ -875,7 +925,7 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     }
     rc = im2col_map(&tmi, x, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BK, true);
     if (rc == TSB_OK) {
-      rc = launch_bn<2, true>(bn, tm, tmi, p, st);
+      rc = launch_bn<2, true>(bn, tm, tmi, tm, p, st);
     } else if (rc == TSB_ERR_UNSUPPORTED) {
       if (p.a3d) {               // the gather kernel reads dy through the 2-D view
         uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
@@ -884,7 +934,7 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
         if (rc) return rc;
         p.a3d = 0;
       }
-      rc = launch_bn<2, false>(bn, tm, tm, p, st);
+      rc = launch_bn<2, false>(bn, tm, tm, tm, p, st);
     }
     if (rc) return rc;
     if (p.splits > 1) {

@@ -321,6 +321,12 @@ EncodeTiledFn encode_fn() {
 
 int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_b,
                   const uint32_t* box, bool atom32) {
+  return make_tmap_f32_swz(out, base, rank, dims, strides_b, box, atom32 ? 1 : 0);
+}
+
+int make_tmap_f32_swz(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_b,
+                      const uint32_t* box, int swizzle) {
+  const int atom32 = swizzle;      // cache key field: the swizzle code
   EncodeTiledFn fn = encode_fn();
   if (!fn) return TSB_ERR_TMAP;
   // cache: identical descriptors are re-used across steps (addresses are stable under the pool)
@@ -340,7 +346,7 @@ int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* 
   static std::mutex mu;
   Key key;
   std::memset(&key, 0, sizeof(key));
-  key.base = base; key.rank = rank; key.atom32 = atom32 ? 1 : 0;
+  key.base = base; key.rank = rank; key.atom32 = atom32;
   for (int i = 0; i < rank; ++i) { key.d[i] = dims[i]; key.b[i] = box[i]; }
   for (int i = 0; i + 1 < rank; ++i) key.s[i] = strides_b[i];
   {
@@ -354,7 +360,8 @@ int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* 
   for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_b[i];
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base), gd, gs, bx, es,
                   CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                               : (swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return TSB_ERR_TMAP | ((int)r << 8);

@@ -130,6 +130,18 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// Tiled store shared -> global (bulk async group of the issuing thread).  Parts of the box outside
+// the tensor are not written.  x * element size must be a multiple of 16 bytes and x, y >= 0.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all bulk groups of this thread have finished READING shared memory (the buffer may be rewritten)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all bulk groups of this thread are complete (writes performed)
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // im2col-mode load of a channels-last activation [N][H][W][C]: `pixels` consecutive positions of
 // the traversal (along W, then H, then N, inside the bounding box that the tensor map was encoded
 // with) starting at base position (w, h, n), each read at the filter offset (off_w, off_h), `c`
@@ -259,6 +271,9 @@ EncodeTiledFn encode_fn();
 // atom32 selects SWIZZLE_128B_ATOM_32B (MN-major tf32 operands) instead of SWIZZLE_128B.
 int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_b,
                   const uint32_t* box, bool atom32 = false);
+// Same with the swizzle spelled out: 0 = 128B, 1 = 128B with 32-byte atoms, 2 = 64B (box rows of 64 bytes).
+int make_tmap_f32_swz(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_b,
+                      const uint32_t* box, int swizzle);
 
 // im2col-mode fp32 tensor map over a dense channels-last activation [N][H][W][C].  A load yields
 // `pixels` rows of `channels` floats (128-byte rows, 128B swizzle; atom32 as above).  lower/upper
