@@ -70,3 +70,17 @@ def test_gemm_unaligned_falls_back_to_simt():
 
 def test_gemm_large_many_tiles():
     assert _run(4096, 4096, 1024, 0, 0) < 5e-3
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(2048, 2048, 320), (2304, 2560, 96), (2112, 4128, 40)])
+def test_gemm_cta_pair_tiles(m, n, k, ta, tb):
+    """Problems with many 256 x 256 tiles and no split-K run the cta_group::2 kernel."""
+    assert _run(m, n, k, ta, tb) < 5e-3
+
+
+def test_gemm_cta_pair_ragged_batched_accumulate():
+    assert _run(3000, 1800, 72, 0, 1) < 5e-3                     # rows / columns that are not tile multiples
+    assert _run(1024, 1024, 128, 0, 0, batch=8) < 5e-3
+    assert _run(1024, 768, 64, 1, 1, batch=16) < 5e-3
+    assert _run(2048, 2048, 64, 0, 1, accumulate=True) < 5e-3

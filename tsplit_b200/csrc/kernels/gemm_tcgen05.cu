@@ -20,6 +20,7 @@
 #include <unordered_map>
 #include <string>
 #include <cstring>
+#include <cstdlib>
 
 using namespace tsb;
 
@@ -255,6 +256,189 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): a cluster of two CTAs on an SM pair computes one 256 x 256 tile.
+// Each CTA stages its own 128 rows of A and its own 128 columns of B (32 KB per k-block instead of
+// 48 KB, so six stages fit and each byte of B crosses L2 -> SM once per pair); the leader's elected
+// thread issues 256 x 256 x 8 MMAs that run on both SMs; each CTA drains its own 128 x 256
+// accumulator half from its own TMEM.  Barriers:
+//   full[s]   leader only: 1 arrival (its producer, with the byte count of BOTH CTAs' boxes)
+//   empty[s]  per CTA: 1 arrival, by the multicast commit of the leader's MMAs
+//   tfull[a]  per CTA: 1 arrival, multicast commit after the last k-block of a tile
+//   tempty[a] leader only: 8 arrivals (four epilogue warps of each CTA)
+// ---------------------------------------------------------------------------------------------
+constexpr int P2_BN = 256;                               // tile columns of the pair
+constexpr int P2_BNH = P2_BN / 2;                        // columns of B staged per CTA
+constexpr int P2_B_STAGE_BYTES = P2_BNH * BK * 4;
+constexpr int P2_STAGE_BYTES = A_STAGE_BYTES + P2_B_STAGE_BYTES;   // 32 KB
+constexpr int P2_STAGES = 6;
+constexpr int P2_SMEM_BYTES = P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + P2_STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P2_STAGES * P2_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + P2_STAGES;
+  uint64_t* tfull = bars + 2 * P2_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0 = leader
+  const long long pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P2_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], 8);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {                                    // the same warp in both CTAs, as the pair allocation requires
+    tmem_alloc_2sm(tmem_slot, 512);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                 // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int ptm = (p.m + 255) / 256, ptn = (p.n + P2_BN - 1) / P2_BN;
+  const int tiles = ptm * ptn;
+  const long long items = (long long)tiles * p.batch;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long item = pair; item < items && ok; item += npairs) {
+        const int tile = (int)(item % tiles);
+        const int b = (int)(item / tiles);
+        const int m0 = (tile / ptn) * 256 + (int)rank * 128;     // this CTA's rows of A
+        const int n0 = (tile % ptn) * P2_BN + (int)rank * P2_BNH;   // this CTA's columns of B
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          const uint32_t ph = (it / P2_STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x111)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * P2_STAGE_BYTES);
+          uint8_t* sa = smem_a + s * A_STAGE_BYTES;
+          uint8_t* sb = smem_b + s * P2_B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (!A_MN) tma_load_3d_2sm(sa, &tmA, &full[s], k0, m0, b);
+          else tma_load_4d_2sm(sa, &tmA, &full[s], 0, k0, m0 >> 5, b);
+          if (!B_MN) tma_load_3d_2sm(sb, &tmB, &full[s], k0, n0, b);
+          else tma_load_4d_2sm(sb, &tmB, &full[s], 0, k0, n0 >> 5, b);
+        }
+      }
+      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(256, P2_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t A_HI = A_MN ? smem_desc_hi(512, LAYOUT_SW128_BASE32B) : smem_desc_hi(1024);
+      constexpr uint32_t B_HI = B_MN ? smem_desc_hi(512, LAYOUT_SW128_BASE32B) : smem_desc_hi(1024);
+      constexpr uint32_t A_KSTEP = (A_MN ? 1024 : UMMA_K * 4) >> 4, B_KSTEP = (B_MN ? 1024 : UMMA_K * 4) >> 4;
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), A_MN ? BK * 128 : 16);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), B_MN ? BK * 128 : 16);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (long long item = pair; item < items && ok; item += npairs, ++acc_it) {
+        const int acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x112)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * P2_BN;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          const uint32_t ph = (it / P2_STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, p.status, 0x113)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (P2_B_STAGE_BYTES >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_tf32_2sm(d_tmem, smem_desc_join(A_HI, a_lo + k * A_KSTEP), smem_desc_join(B_HI, b_lo + k * B_KSTEP),
+                          idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_2sm(&empty[s], 3);      // both CTAs may refill this stage once the MMAs retire
+        }
+        if (ok) umma_commit_2sm(&tfull[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own TMEM half)
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (long long item = pair; item < items && ok; item += npairs, ++acc_it) {
+      const int tile = (int)(item % tiles);
+      const int b = (int)(item / tiles);
+      const int m0 = (tile / ptn) * 256 + (int)rank * 128;
+      const int n0 = (tile % ptn) * P2_BN;
+      const int acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x114)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      float* crow = p.c + (long long)b * p.sc + (long long)row * p.ldc;
+      const bool accumulate = p.accumulate != 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < P2_BN; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(tmem_base + acc * P2_BN + ((uint32_t)(q * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        const int col = n0 + c0;
+        if (row < p.m && col < p.n) {
+          float* dst = crow + col;
+          const bool vec_ok = (col + 32 <= p.n) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.n) dst[j] = accumulate ? dst[j] + v[j] : v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty[acc]);   // the leader's MMA thread counts both CTAs' warps
+    }
+  }
+
+  // Nobody leaves (and nobody frees TMEM) while the partner may still signal or read.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
   }
 }
 
@@ -539,6 +723,42 @@ int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMa
   return launch_tc<BN, true, true>(ta, tb, p, st);
 }
 
+template <bool A_MN, bool B_MN>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  auto kern = gemm_tf32_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES) != cudaSuccess)
+      return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
+    attr_set = true;
+  }
+  const long long items = (long long)((p.m + 255) / 256) * ((p.n + P2_BN - 1) / P2_BN) * p.batch;
+  long long pairs = sm_count() / 2;
+  if (pairs > items) pairs = items;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = P2_SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                  cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_pair<false, false>(ta, tb, p, st);
+  if (!a_mn && b_mn) return launch_pair<false, true>(ta, tb, p, st);
+  if (a_mn && !b_mn) return launch_pair<true, false>(ta, tb, p, st);
+  return launch_pair<true, true>(ta, tb, p, st);
+}
+
 }  // namespace
 
 // Chooses the split-K factor: enough work items to fill the SMs when the tile
@@ -596,6 +816,16 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
       return TSB_ERR_SCRATCH;
     }
   }
+  // CTA pairs (256 x 256 tiles on SM pairs) when the problem has enough of them and no split-K
+  bool use_pair = false;
+  {
+    const long long pair_items = (long long)((m + 255) / 256) * ((n + 255) / 256) * batch;
+    const char* e = getenv("TSB_GEMM_PAIR");              // "0" selects the one-CTA tiles everywhere
+    const bool enabled = !(e && e[0] == '0');
+    use_pair = enabled && bn == 256 && p.splits == 1 && m >= 256 && pair_items * 4 >= sm_count() &&
+               (!trans_a || m % 32 == 0) && (trans_b || n % 32 == 0);
+  }
+  const uint32_t bbox = use_pair ? P2_BNH : (uint32_t)bn;   // columns of B that one CTA stages
   // tensor maps (dims innermost first)
   CUtensorMap ta, tb;
   p.a_chunked = p.b_chunked = 0;
@@ -619,11 +849,11 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
   if (rc) return rc;
   if (trans_b) {    // B stored [n][k], K contiguous -> K-major
     uint64_t d[3] = {(uint64_t)k, (uint64_t)n, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
-    uint32_t bx[3] = {BK, (uint32_t)bn, 1};
+    uint32_t bx[3] = {BK, bbox, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx);
   } else if (n % 32 == 0) {   // B[k][n], N contiguous -> MN-major; all chunks of a stage in one box
     uint64_t d[4] = {32, (uint64_t)k, (uint64_t)n / 32, (uint64_t)batch}, s[3] = {(uint64_t)ldb * 4, 128, sbb};
-    uint32_t bx[4] = {32, BK, (uint32_t)bn / 32, 1};
+    uint32_t bx[4] = {32, BK, bbox / 32, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 4, d, s, bx, true);
     p.b_chunked = 1;
   } else {
@@ -633,7 +863,8 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
   }
   if (rc) return rc;
   const bool a_mn = trans_a != 0, b_mn = trans_b == 0;
-  if (bn == 256) rc = dispatch_major<256>(a_mn, b_mn, ta, tb, p, st);
+  if (use_pair) rc = dispatch_pair(a_mn, b_mn, ta, tb, p, st);
+  else if (bn == 256) rc = dispatch_major<256>(a_mn, b_mn, ta, tb, p, st);
   else if (bn == 128) rc = dispatch_major<128>(a_mn, b_mn, ta, tb, p, st);
   else rc = dispatch_major<64>(a_mn, b_mn, ta, tb, p, st);
   if (rc) return rc;
