@@ -100,6 +100,10 @@ CONVS = [
     (1, 32, 40, 40, 32, 3, 0, 1),      # no padding, several tiles of pixels
     (3, 96, 6, 6, 160, 3, 1, 1),       # pixel tiles that span images
     (5, 128, 7, 9, 64, 3, 1, 1),
+    # enough 256-pixel x 256-channel tiles for the CTA-pair (cta_group::2) kernel
+    (10, 32, 32, 32, 256, 3, 1, 1),    # forward on pairs
+    (10, 256, 32, 32, 64, 3, 1, 1),    # dgrad on pairs (forward kernel with flipped filters)
+    (12, 64, 56, 56, 320, 3, 1, 2),    # strided, ragged channel tile
 ]
 
 

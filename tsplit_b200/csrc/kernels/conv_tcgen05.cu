@@ -15,6 +15,7 @@
 // Role in the reference: cudnnConvolutionForward / BackwardData / BackwardFilter
 // (src/ops/CudnnConv2d.cu:127-602).
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -665,6 +666,187 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair forward kernel (cta_group::2): a cluster of two CTAs on an SM pair computes 256 pixels x
+// 256 output channels.  Each CTA stages the im2col box of its own 128 pixels and its own 128 filter
+// rows (32 KB per k-block instead of 48 KB: six stages, and the filters cross L2 -> SM once per
+// pair); the leader's elected thread issues 256 x 256 x 8 MMAs that run on both SMs; each CTA
+// drains and stores its own 128 x 256 half.  Barrier roles as in the pair GEMM: full[] and
+// tempty[] live in the leader, empty[] and tfull[] in both CTAs (multicast commit).
+// Used for forward and stride-1 dgrad when C % 32 == 0 and there are more than 128 output channels.
+// ---------------------------------------------------------------------------------------------
+constexpr int P2_BN = 256;
+constexpr int P2_B_STAGE_BYTES = (P2_BN / 2) * BK * 4;
+constexpr int P2_STAGE_BYTES = A_STAGE_BYTES + P2_B_STAGE_BYTES;
+constexpr int P2_STAGES = 6;
+constexpr int P2_SMEM_BYTES = STORE_STAGING_BYTES + P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(192, 1)
+conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi,
+                     const __grid_constant__ CUtensorMap tmo, const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_stg = smem;
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES;
+  uint8_t* smem_b = smem_a + P2_STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + P2_STAGES * P2_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + P2_STAGES;
+  uint64_t* tfull = bars + 2 * P2_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P2_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], 8);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm);
+    tma_prefetch_desc(&tmi);
+    tma_prefetch_desc(&tmo);
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(tmem_slot, 512);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int ptm = (p.M + 255) / 256, ptn = (p.NC + P2_BN - 1) / P2_BN;
+  const int items = ptm * ptn;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      const int cpb = p.C >> 5;
+      for (int item = pair; item < items && ok; item += npairs) {
+        const int m0 = (item / ptn) * 256 + (int)rank * 128;          // this CTA's pixels
+        const int n0 = (item % ptn) * P2_BN + (int)rank * (P2_BN / 2);  // this CTA's filter rows
+        const int n = m0 / (p.OH * p.OW);
+        const int rem = m0 - n * (p.OH * p.OW);
+        const int oy = rem / p.OW, ox = rem - oy * p.OW;
+        const int bw = ox * p.stride - p.pw, bh = oy * p.stride - p.ph;
+        int cb = 0, kh = 0, kw = 0;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          const uint32_t ph = (it / P2_STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x211)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * P2_STAGE_BYTES);
+          tma_load_im2col_4d_2sm(smem_a + s * A_STAGE_BYTES, &tmi, &full[s], cb * 32, bw, bh, n, (uint16_t)kw,
+                                 (uint16_t)kh);
+          tma_load_2d_2sm(smem_b + s * P2_B_STAGE_BYTES, &tm, &full[s], kb * BK, n0);
+          if (++cb == cpb) {
+            cb = 0;
+            if (++kw == p.KW) { kw = 0; ++kh; }
+          }
+        }
+      }
+      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(256, P2_BN, 0, 0);
+      constexpr uint32_t HI = smem_desc_hi(1024);
+      constexpr uint32_t KSTEP = (UMMA_K * 4) >> 4;
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), 16);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), 16);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int item = pair; item < items && ok; item += npairs, ++acc_it) {
+        const int acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x212)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * P2_BN;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          const uint32_t ph = (it / P2_STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, p.status, 0x213)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (P2_B_STAGE_BYTES >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_tf32_2sm(d_tmem, smem_desc_join(HI, a_lo + k * KSTEP), smem_desc_join(HI, b_lo + k * KSTEP), idesc,
+                          (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_2sm(&empty[s], 3);
+        }
+        if (ok) umma_commit_2sm(&tfull[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs): TMEM -> smem -> TMA store
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    uint8_t* stg = smem_stg + q * 2048;
+    const uint32_t srow = smem_u32(stg) + lane * 64;
+    const uint32_t sx = (uint32_t)(lane >> 1) & 3;
+    for (int item = pair; item < items && ok; item += npairs, ++acc_it) {
+      const int m0 = (item / ptn) * 256 + (int)rank * 128;
+      const int n0 = (item % ptn) * P2_BN;
+      const int acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x214)) { ok = false; break; }
+      tc_fence_after();
+      const int row0 = m0 + q * 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < P2_BN; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(tmem_base + acc * P2_BN + ((uint32_t)(q * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        const int col = n0 + c0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (lane == 0) bulk_wait_read();
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int j = half * 16 + c * 4;
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(srow + (((uint32_t)c ^ sx) << 4)),
+                         "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
+                         : "memory");
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M && col + half * 16 < p.NC) {
+            tma_store_2d(&tmo, stg, col + half * 16, row0);
+            bulk_commit();
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // nobody leaves or frees TMEM while the partner may still signal or read
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
+  }
+}
+
 __global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restrict__ out, int splits,
                                    long long per_split, int accumulate) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_split;
@@ -777,6 +959,34 @@ int launch_bn(int bn, const CUtensorMap& tm, const CUtensorMap& tmi, const CUten
   return launch<MODE, 64, IM2COL>(tm, tmi, tmo, p, st);
 }
 
+int launch_fwd_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo, const ConvParams& p,
+                    cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(conv_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES) !=
+        cudaSuccess)
+      return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
+    attr_set = true;
+  }
+  const long long items = (long long)((p.M + 255) / 256) * ((p.NC + P2_BN - 1) / P2_BN);
+  long long pairs = sm_count() / 2;
+  if (pairs > items) pairs = items;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = P2_SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, conv_fwd_pair_kernel, tm, tmi, tmo, p);
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
 ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH, int OW, int ph, int pw,
                        int stride) {
   ConvParams p;
@@ -829,7 +1039,18 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
     p.tma_store = 1;
   }
   rc = im2col_map(&tmi, src, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BM, false);
-  if (rc == TSB_OK) return launch_bn<0, true>(bn, tm, tmi, tmo, p, st);
+  if (rc == TSB_OK) {
+    const char* e = getenv("TSB_CONV_PAIR");              // "0" selects the one-CTA tiles everywhere
+    const long long pair_items = (long long)((p.M + 255) / 256) * ((p.NC + P2_BN - 1) / P2_BN);
+    if (!(e && e[0] == '0') && bn == 256 && pair_items * 4 >= sm_count()) {
+      CUtensorMap tmh;          // filters, 128 rows per CTA
+      uint32_t hb[2] = {BK, P2_BN / 2};
+      rc = tsb_host::make_tmap_f32(&tmh, wts, 2, d, s, hb, false);
+      if (rc) return rc;
+      return launch_fwd_pair(tmh, tmi, tmo, p, st);
+    }
+    return launch_bn<0, true>(bn, tm, tmi, tmo, p, st);
+  }
   if (rc != TSB_ERR_UNSUPPORTED) return rc;
   return launch_bn<0, false>(bn, tm, tm, tmo, p, st);
 }
