@@ -847,6 +847,186 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
   }
 }
 
+// CTA-pair wgrad (cta_group::2): the pair computes 256 output channels x 256 (tap, channel) columns
+// of dw over a range of pixels.  Each CTA stages its own 128 rows of dy (one chunked box) and its
+// own 128 columns of the patch tile (four im2col boxes of 32 pixels x 32 channels); four producer
+// threads per CTA share the boxes as in the one-CTA kernel.  Needs O >= 256 (else half of the
+// pair's rows would be padding), C % 32 == 0 and the chunked dy view (O % 32 == 0).
+__global__ void __launch_bounds__(288, 1)
+conv_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi,
+                       const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES;
+  uint8_t* smem_b = smem_a + P2_STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + P2_STAGES * P2_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + P2_STAGES;
+  uint64_t* tfull = bars + 2 * P2_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P2_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], 8);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm);
+    tma_prefetch_desc(&tmi);
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(tmem_slot, 512);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int ptm = (p.M + 255) / 256, ptn = (p.NC + P2_BN - 1) / P2_BN;
+  const int tiles = ptm * ptn;
+  const int items = tiles * p.splits;
+  const int per_split = (p.kblocks + p.splits - 1) / p.splits;
+
+  // producer q of this CTA: chunk q of this CTA's four patch chunks; q == 0 also the dy box and, in the
+  // leader, the byte count of both CTAs' boxes
+  auto producer = [&](int q) {
+    uint32_t it = 0;
+    bool ok = true;
+    for (int item = pair; item < items && ok; item += npairs) {
+      const int tile = item % tiles, split = item / tiles;
+      const int m0 = (tile / ptn) * 256 + (int)rank * 128;     // this CTA's rows (output channels)
+      const int nt0 = (tile % ptn) * P2_BN;                    // first column of the pair's tile
+      const int col = nt0 + ((int)rank * 4 + q) * 32;          // first column of this producer's chunk
+      const bool cvalid = col < p.NC;
+      const int tap = col / p.C, c0 = col - tap * p.C;
+      const int kh = tap / p.KW, kw = tap - kh * p.KW;
+      int nv = (p.NC - nt0 + 31) / 32;
+      if (nv > 8) nv = 8;
+      const uint32_t tx = 2 * A_STAGE_BYTES + nv * (BK * 128);
+      const int kb0 = split * per_split, kb1 = min(p.kblocks, kb0 + per_split);
+      const int pix0 = kb0 * BK;
+      int n = pix0 / (p.OH * p.OW);
+      const int rem = pix0 - n * (p.OH * p.OW);
+      int oy = rem / p.OW, ox = rem - oy * p.OW;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % P2_STAGES;
+        const uint32_t ph = (it / P2_STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x221 + q)) { ok = false; break; }
+        if (q == 0) {
+          if (rank == 0) mbar_expect_tx(&full[s], tx);
+          tma_load_3d_2sm(smem_a + s * A_STAGE_BYTES, &tm, &full[s], 0, kb * BK, m0 >> 5);
+        }
+        if (cvalid)
+          tma_load_im2col_4d_2sm(smem_b + s * P2_B_STAGE_BYTES + q * (BK * 128), &tmi, &full[s], c0,
+                                 ox * p.stride - p.pw, oy * p.stride - p.ph, n, (uint16_t)kw, (uint16_t)kh);
+        ox += BK;
+        while (ox >= p.OW) { ox -= p.OW; ++oy; }
+        while (oy >= p.OH) { oy -= p.OH; ++n; }
+      }
+    }
+    if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) producer(0);
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(256, P2_BN, 1, 1);
+      constexpr uint32_t HI = smem_desc_hi(512, LAYOUT_SW128_BASE32B);
+      constexpr uint32_t KSTEP = 1024 >> 4;
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), BK * 128);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), BK * 128);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int item = pair; item < items && ok; item += npairs, ++acc_it) {
+        const int split = item / tiles;
+        const int kb0 = split * per_split, kb1 = min(p.kblocks, kb0 + per_split);
+        const int acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x225)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * P2_BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          const uint32_t ph = (it / P2_STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, p.status, 0x226)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (P2_B_STAGE_BYTES >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_tf32_2sm(d_tmem, smem_desc_join(HI, a_lo + k * KSTEP), smem_desc_join(HI, b_lo + k * KSTEP), idesc,
+                          (kb > kb0 || k > 0) ? 1u : 0u);
+          umma_commit_2sm(&empty[s], 3);
+        }
+        if (ok) umma_commit_2sm(&tfull[acc], 3);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int item = pair; item < items && ok; item += npairs, ++acc_it) {
+      const int tile = item % tiles, split = item / tiles;
+      const int m0 = (tile / ptn) * 256 + (int)rank * 128;
+      const int n0 = (tile % ptn) * P2_BN;
+      const int kb0 = split * per_split, kb1 = min(p.kblocks, kb0 + per_split);
+      const bool has_k = kb0 < kb1;
+      const int acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x227)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      float* crow = p.splits > 1 ? p.ws + ((long long)split * p.M + row) * p.ldc : p.out + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c0 = 0; c0 < P2_BN; c0 += 32) {
+        float v[32];
+        if (has_k) {
+          tmem_ld_32x32(tmem_base + acc * P2_BN + ((uint32_t)(q * 32) << 16) + c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        const int col = n0 + c0;
+        if (row < p.M && col < p.NC) {     // NC is a multiple of 32 here and ldc * 4 of 16: whole chunks, aligned
+          float* dst = crow + col;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+    }
+  } else {
+    if (lane == 0) producer(warp - 5);      // warps 6, 7, 8: patch chunks 1, 2, 3
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
+  }
+}
+
 __global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restrict__ out, int splits,
                                    long long per_split, int accumulate) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_split;
@@ -987,6 +1167,33 @@ int launch_fwd_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtenso
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
+int launch_wgrad_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(conv_wgrad_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES) !=
+        cudaSuccess)
+      return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
+    attr_set = true;
+  }
+  const long long items = (long long)((p.M + 255) / 256) * ((p.NC + P2_BN - 1) / P2_BN) * p.splits;
+  long long pairs = sm_count() / 2;
+  if (pairs > items) pairs = items;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(288);
+  cfg.dynamicSmemBytes = P2_SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, conv_wgrad_pair_kernel, tm, tmi, p);
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
 ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH, int OW, int ph, int pw,
                        int stride) {
   ConvParams p;
@@ -1122,9 +1329,16 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
       rc = tsb_host::make_tmap_f32(&tm, y, 2, d, s, bx, true);
     }
     if (rc) return rc;
-    // split the pixel reduction so that the work items fill whole waves of CTAs
-    const long long tiles = (long long)p.tiles_m * p.tiles_n * p.taps;
-    const int sms = sm_count();
+    // CTA pairs when there are at least 256 output channels (a pair's 256 rows) and both operands go by TMA
+    bool use_pair = false;
+    {
+      const char* e = getenv("TSB_CONV_PAIR");
+      use_pair = !(e && e[0] == '0') && p.a3d && O >= 256 && bn == 256;
+    }
+    // split the pixel reduction so that the work items fill whole waves of CTAs (or CTA pairs)
+    const long long tiles = use_pair ? (long long)((p.M + 255) / 256) * ((p.NC + P2_BN - 1) / P2_BN)
+                                     : (long long)p.tiles_m * p.tiles_n * p.taps;
+    const int sms = use_pair ? sm_count() / 2 : sm_count();
     int splits = 1;
     double best_eff = 0.0;
     for (int waves = 1; waves <= 4; ++waves) {
@@ -1146,7 +1360,7 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     }
     rc = im2col_map(&tmi, x, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BK, true);
     if (rc == TSB_OK) {
-      rc = launch_bn<2, true>(bn, tm, tmi, tm, p, st);
+      rc = use_pair ? launch_wgrad_pair(tm, tmi, p, st) : launch_bn<2, true>(bn, tm, tmi, tm, p, st);
     } else if (rc == TSB_ERR_UNSUPPORTED) {
       if (p.a3d) {               // the gather kernel reads dy through the 2-D view
         uint64_t d[2] = {(uint64_t)O, (uint64_t)mpix}, s[1] = {(uint64_t)O * 4};
