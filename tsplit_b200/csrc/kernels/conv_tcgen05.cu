@@ -1027,6 +1027,55 @@ conv_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_cons
   }
 }
 
+// ---- few-channel stems (RGB) through the TMA kernels --------------------------------------------
+// A stride-1 "same" convolution over x[N,H,W,4] (3 real channels) has K = 9 * 4: far too short for
+// a 32-wide k-block.  Reading the same memory as x'[N,H,W/8,32] (eight pixels of a row = one packed
+// pixel with 32 channels) and y[N,H,W,O] as y'[N,H,W/8,8*O] turns it into an ordinary 3-wide
+// convolution with 32 input and 8*O output channels whose filters are mostly zero:
+//   w'[(po, o)][kh][dx + 1][(pi, c)] = w[o][kh][kw][c]  with  kw = 8 * dx + pi - po + pw,  if 0 <= kw < KW.
+// Eight times the arithmetic, but on the tensor cores at full rate instead of on the gather path.
+__global__ void stem_pack_filters(const float* __restrict__ w, long long so, long long sc, long long sh,
+                                  long long sw, float* __restrict__ out, int O, int C, int KH, int KW, int pw) {
+  const long long total = 8ll * O * KH * 3 * 32;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int pc = (int)(i % 32);
+    long long r = i / 32;
+    const int dxi = (int)(r % 3); r /= 3;
+    const int kh = (int)(r % KH); r /= KH;
+    const int o = (int)(r % O);
+    const int po = (int)(r / O);
+    const int pi = pc >> 2, c = pc & 3;
+    const int kw = 8 * (dxi - 1) + pi - po + pw;
+    float v = 0.f;
+    if (c < C && kw >= 0 && kw < KW) v = w[o * so + c * sc + kh * sh + kw * sw];
+    out[i] = v;
+  }
+}
+
+// dw[o][kh][kw][c] = sum of the packed gradient entries that alias this filter tap
+__global__ void stem_unpack_filter_grads(const float* __restrict__ gp, float* __restrict__ dw, long long so,
+                                         long long sc, long long sh, long long sw, int O, int C, int KH, int KW,
+                                         int pw) {
+  const int total = O * KH * KW * C;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int c = i % C;
+    int r = i / C;
+    const int kw = r % KW; r /= KW;
+    const int kh = r % KH;
+    const int o = r / KH;
+    float acc = 0.f;
+    for (int po = 0; po < 8; ++po) {
+      const int t = kw - pw + po;                 // = 8 * dx + pi
+      const int dx = (t >= 0) ? t / 8 : -((7 - t) / 8);
+      const int pi = t - 8 * dx;
+      if (dx < -1 || dx > 1) continue;
+      acc += gp[((((long long)po * O + o) * KH + kh) * 3 + (dx + 1)) * 32 + pi * 4 + c];
+    }
+    dw[o * so + c * sc + kh * sh + kw * sw] = acc;
+  }
+}
+
 __global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restrict__ out, int splits,
                                    long long per_split, int accumulate) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_split;
@@ -1384,6 +1433,29 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
   if (rc) return rc;
   const int late = tsb_host::peek_status();
   return late ? TSB_ERR_TIMEOUT | (late << 8) : TSB_OK;
+}
+
+// Packed-stem helpers (see stem_pack_filters).  w / dw are addressed through element strides
+// (output channel, input channel, kh, kw) so any filter layout works; the packed array is dense
+// [8*O][KH][3][32].
+int tsb_stem_pack_filters(const float* w, long long so, long long sc, long long sh, long long sw, float* packed,
+                          int O, int C, int KH, int KW, int pw, void* stream) {
+  if (C > 4 || KW > 9 || pw > 8 || KW - 1 - pw > 8) return TSB_ERR_UNSUPPORTED;
+  const long long total = 8ll * O * KH * 3 * 32;
+  stem_pack_filters<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      w, so, sc, sh, sw, packed, O, C, KH, KW, pw);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+int tsb_stem_unpack_filter_grads(const float* packed, float* dw, long long so, long long sc, long long sh,
+                                 long long sw, int O, int C, int KH, int KW, int pw, void* stream) {
+  if (C > 4 || KW > 9 || pw > 8 || KW - 1 - pw > 8) return TSB_ERR_UNSUPPORTED;
+  const int total = O * KH * KW * C;
+  stem_unpack_filter_grads<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      packed, dw, so, sc, sh, sw, O, C, KH, KW, pw);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
 }  // extern "C"

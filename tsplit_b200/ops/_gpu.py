@@ -352,9 +352,16 @@ def _padded(arr, c4, tag):
 
 def _conv2d_padded_channels(kind, x, w, y, ph, pw, stride, stream):
     """Input-channel count not a multiple of 4 (the RGB stem): run the kernel on
-    zero-padded copies of x and w; only the real channels are copied back."""
+    zero-padded copies of x and w; only the real channels are copied back.
+
+    Stride-1 "same" convolutions with at most 4 channels take the packed route
+    instead: eight pixels of a row are read as one pixel with 32 channels (same
+    memory), which turns the stem into an ordinary 32 -> 8*O channel convolution
+    for the TMA kernels (see ``stem_pack_filters`` in the kernel source)."""
     c = x.shape[1]
     c4 = (c + 3) // 4 * 4
+    if kind in (0, 2) and _packed_stem_ok(x, w, y, c4, pw, stride):
+        return _conv2d_packed_stem(kind, x, w, y, ph, pw, stream)
     x4, w4 = _padded(x, c4, "x"), _padded(w, c4, "w")
     xs, ws = x4.strides, w4.strides
     if kind in (0, 2):
@@ -366,6 +373,38 @@ def _conv2d_padded_channels(kind, x, w, y, ph, pw, stride, stream):
         copy_raw(x4.ptr, xs, x.ptr, x.strides, x.shape, stream)
     elif kind == 2:
         copy_raw(w4.ptr, ws, w.ptr, w.strides, w.shape, stream)
+
+
+def _packed_stem_ok(x, w, y, c4, pw, stride):
+    kw = w.shape[3]
+    return (stride == 1 and c4 == 4 and x.shape[3] % 8 == 0 and y.shape[3] == x.shape[3] and kw <= 9 and pw <= 8
+            and kw - 1 - pw <= 8 and y.shape[1] % 4 == 0)
+
+
+def _conv2d_packed_stem(kind, x, w, y, ph, pw, stream):
+    from .. import ndarray
+    n, c, h, wd = x.shape
+    o, _, kh, kw = w.shape
+    _, _, oh, ow = y.shape
+    x4 = _padded(x, 4, "x")
+    copy_raw(x.ptr, x.strides, x4.ptr, x4.strides, x.shape, stream)
+    key = ("stem_w", (o, kh), x.ctx.device_id)
+    packed = _PAD_CACHE.get(key)
+    if packed is None:
+        packed = _PAD_CACHE[key] = ndarray.empty((8 * o * kh * 3 * 32,), x.ctx, use_pool=False)
+    so, sc, sh, sw = w.strides
+    if kind == 0:
+        _check(lib().tsb_stem_pack_filters(_p(w), c_int64(so), c_int64(sc), c_int64(sh), c_int64(sw), _p(packed),
+                                           c_int(o), c_int(c), c_int(kh), c_int(kw), c_int(pw), _s(stream)),
+               "stem_pack_filters")
+    rc = lib().tsb_conv2d(c_int(kind), _p(x4), _p(packed), _p(y), c_int(n), c_int(32), c_int(h), c_int(wd // 8),
+                          c_int(8 * o), c_int(kh), c_int(3), c_int(oh), c_int(ow // 8), c_int(ph), c_int(1),
+                          c_int(1), _s(stream))
+    _check(rc, "conv2d (packed stem) kind %d" % kind)
+    if kind == 2:
+        _check(lib().tsb_stem_unpack_filter_grads(_p(packed), _p(w), c_int64(so), c_int64(sc), c_int64(sh),
+                                                  c_int64(sw), c_int(o), c_int(c), c_int(kh), c_int(kw), c_int(pw),
+                                                  _s(stream)), "stem_unpack_filter_grads")
 
 
 def csrmm(vals, rowptr, colidx, nrow, ncol, dense, out, trans_a, ncols_dense, stream):
