@@ -179,11 +179,6 @@ class MemoryExecutor(Executor):
                 if self._compact(nbytes(shape)):
                     continue
                 raise
-        pool = ndarray.get_pool(self.ctx)
-        if pool is not None:
-            used = pool.stats()["used"]
-            if used > self.stats["peak_bytes"]:
-                self.stats["peak_bytes"] = used
         return a
 
     def _compact(self, need):
@@ -384,9 +379,14 @@ class MemoryExecutor(Executor):
         self._reset_state()
         for n, v in node_to_val.items():
             self.arr[n] = v
+        pool = ndarray.get_pool(self.ctx)
+        if pool is not None:
+            pool.reset_peak()
         self._execute()
         self.stream.sync()
         self._reap(True)
+        if pool is not None:
+            self.stats["peak_bytes"] = pool.stats()["peak"]
         outs = [self.arr.get(n) for n in self.eval_node_list]
         if convert_to_numpy_ret_vals:
             outs = [o.asnumpy() if isinstance(o, ndarray.NDArray) else o for o in outs]

@@ -330,8 +330,8 @@ def empty(shape, ctx=cpu(0), pinned=False, use_pool=True, channels_last=None, lo
     pool = _POOLS.get(ctx) if use_pool else None
     cl = is_cuda_ctx(ctx) if channels_last is None else (bool(channels_last) and is_cuda_ctx(ctx))
     if pool is not None:
-        blk, flat = pool.alloc(n * 4, long_lived) if long_lived else pool.alloc(n * 4)
-        return NDArray(_make_view(flat[:n], shape, cl), ctx, block=blk, pool=pool)
+        blk, view = pool.alloc_view(n * 4, shape, cl and len(shape) == 4, long_lived)
+        return NDArray(view, ctx, block=blk, pool=pool)
     if ctx.device_type == 2:
         flat = torch.empty(max(n, 1), dtype=torch.float32, device=ctx.torch_device)
     else:

@@ -44,6 +44,7 @@ class MemoryPool(object):
         n_floats = self.capacity // 4
         dev = ctx.torch_device if ctx.device_type == 2 else torch.device("cpu")
         self.arena = torch.empty(n_floats, dtype=torch.float32, device=dev)
+        self._views = {}
         self.lib = _lib()
         self.handle = self.lib.tsb_pool_create(self.capacity, _ALIGN)
         assert self.handle, "pool creation failed"
@@ -75,6 +76,33 @@ class MemoryPool(object):
         o = off.value // 4
         n = max((int(nbytes) + 3) // 4, 1)
         return off.value, self.arena[o:o + n]
+
+    def alloc_view(self, nbytes, shape, channels_last, long_lived=False):
+        """``alloc`` plus the shaped tensor view of the block.  A training step asks for the
+        same (offset, shape, layout) combinations every iteration, so the views are cached:
+        the steady state costs one native call and a dictionary lookup per tensor."""
+        off = c_int64()
+        high = long_lived or nbytes * 256 < self.capacity
+        fn = self.lib.tsb_pool_alloc_high if high else self.lib.tsb_pool_alloc
+        rc = fn(self.handle, int(nbytes), ctypes.byref(off))
+        if rc != 0:
+            if rc == 5:
+                st = self.stats()
+                raise ndarray.OutOfHBMBudget(
+                    "GPU available memory is not enough! need %.1f MB, free %.1f MB (largest block %.1f MB) "
+                    "of a %.1f MB budget" % (nbytes / 2**20, st["free"] / 2**20, st["largest_free"] / 2**20,
+                                             st["capacity"] / 2**20))
+            raise AssertionError("pool alloc error %d" % rc)
+        key = (off.value, shape, channels_last)
+        view = self._views.get(key)
+        if view is None:
+            if len(self._views) > 65536:
+                self._views.clear()
+            o = off.value // 4
+            n = max((int(nbytes) + 3) // 4, 1)
+            view = self._views[key] = ndarray._make_view(self.arena[o:o + n][:ndarray._numel(shape)], shape,
+                                                         channels_last)
+        return off.value, view
 
     def free(self, block):
         if self.handle:
