@@ -126,13 +126,38 @@ __device__ bool exchange(const Args& a, int phase) {
   return ok;
 }
 
-// One thread handles U 16-byte pieces per trip and issues the U peer loads of a rank back to
-// back, so U * 16 bytes per thread are in flight on NVLink at any time (a peer load takes a few
-// microseconds; with one load in flight per thread the links ran at well under half their rate).
-constexpr int U = 8;
-
+// One thread handles U 16-byte pieces per trip and issues ALL its peer loads of the trip (every
+// rank, every piece: W * U = 16 loads of 16 bytes) before it adds anything, so 256 bytes per thread
+// are in flight on NVLink at any time.  A peer load takes a few microseconds: with one load in
+// flight per thread the links ran at well under half their rate, and with the ranks visited one
+// after the other each trip paid the latency once per rank.  The sum still runs in rank order, so
+// every rank computes bitwise the same value.
 template <int KIND>
-__device__ void reduce_update_shard(const Args& a, long long tid, long long nthreads) {
+__device__ __forceinline__ void update_piece(const Args& a, long long i, float4 gv, float inv) {
+  gv.x *= inv; gv.y *= inv; gv.z *= inv; gv.w *= inv;
+  float4 p = *reinterpret_cast<const float4*>(a.param[a.rank] + i);
+  const long long li = i - a.lo;
+  float4 s1 = make_float4(0, 0, 0, 0), s2 = make_float4(0, 0, 0, 0);
+  if (KIND >= 1) s1 = *reinterpret_cast<const float4*>(a.slot1 + li);
+  if (KIND == 4) s2 = *reinterpret_cast<const float4*>(a.slot2 + li);
+  opt_one<KIND>(p.x, gv.x, s1.x, s2.x, a.h);
+  opt_one<KIND>(p.y, gv.y, s1.y, s2.y, a.h);
+  opt_one<KIND>(p.z, gv.z, s1.z, s2.z, a.h);
+  opt_one<KIND>(p.w, gv.w, s1.w, s2.w, a.h);
+  if (KIND >= 1) *reinterpret_cast<float4*>(a.slot1 + li) = s1;
+  if (KIND == 4) *reinterpret_cast<float4*>(a.slot2 + li) = s2;
+  if (a.param_mc) {
+    multimem_st(a.param_mc + i, p);
+  } else {
+#pragma unroll 1
+    for (int r = 0; r < a.world; ++r) st_peer(a.param[r] + i, p);
+  }
+}
+
+// W = number of ranks when it is 2, 4 or 8 (all loads of a trip in flight), 0 = any (rank by rank)
+template <int KIND, int W>
+__device__ void reduce_update_shard_w(const Args& a, long long tid, long long nthreads) {
+  constexpr int U = W ? 16 / W : 8;
   const float inv = 1.f / (float)a.world;
   const long long lo4 = a.lo >> 2, hi4 = a.hi >> 2;
   for (long long base = lo4 + tid; base < hi4; base += nthreads * U) {
@@ -142,6 +167,23 @@ __device__ void reduce_update_shard(const Args& a, long long tid, long long nthr
       for (int u = 0; u < U; ++u) {
         const long long i4 = base + u * nthreads;
         g[u] = i4 < hi4 ? multimem_ld_reduce(a.grad_mc + (i4 << 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else if (W) {
+      float4 v[W ? W : 1][U];
+#pragma unroll
+      for (int r = 0; r < W; ++r) {
+        const float* src = a.grad[r];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i4 = base + u * nthreads;
+          v[r][u] = i4 < hi4 ? ld_peer(src + (i4 << 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        g[u] = v[0][u];
+#pragma unroll
+        for (int r = 1; r < W; ++r) { g[u].x += v[r][u].x; g[u].y += v[r][u].y; g[u].z += v[r][u].z; g[u].w += v[r][u].w; }
       }
     } else {
 #pragma unroll
@@ -162,29 +204,17 @@ __device__ void reduce_update_shard(const Args& a, long long tid, long long nthr
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long i4 = base + u * nthreads;
-      if (i4 >= hi4) break;
-      const long long i = i4 << 2;
-      float4 gv = g[u];
-      gv.x *= inv; gv.y *= inv; gv.z *= inv; gv.w *= inv;
-      float4 p = *reinterpret_cast<const float4*>(a.param[a.rank] + i);
-      const long long li = i - a.lo;
-      float4 s1 = make_float4(0, 0, 0, 0), s2 = make_float4(0, 0, 0, 0);
-      if (KIND >= 1) s1 = *reinterpret_cast<const float4*>(a.slot1 + li);
-      if (KIND == 4) s2 = *reinterpret_cast<const float4*>(a.slot2 + li);
-      opt_one<KIND>(p.x, gv.x, s1.x, s2.x, a.h);
-      opt_one<KIND>(p.y, gv.y, s1.y, s2.y, a.h);
-      opt_one<KIND>(p.z, gv.z, s1.z, s2.z, a.h);
-      opt_one<KIND>(p.w, gv.w, s1.w, s2.w, a.h);
-      if (KIND >= 1) *reinterpret_cast<float4*>(a.slot1 + li) = s1;
-      if (KIND == 4) *reinterpret_cast<float4*>(a.slot2 + li) = s2;
-      if (a.param_mc) {
-        multimem_st(a.param_mc + i, p);
-      } else {
-#pragma unroll 1
-        for (int r = 0; r < a.world; ++r) st_peer(a.param[r] + i, p);
-      }
+      if (i4 < hi4) update_piece<KIND>(a, i4 << 2, g[u], inv);
     }
   }
+}
+
+template <int KIND>
+__device__ void reduce_update_shard(const Args& a, long long tid, long long nthreads) {
+  if (a.world == 2) reduce_update_shard_w<KIND, 2>(a, tid, nthreads);
+  else if (a.world == 4) reduce_update_shard_w<KIND, 4>(a, tid, nthreads);
+  else if (a.world == 8) reduce_update_shard_w<KIND, 8>(a, tid, nthreads);
+  else reduce_update_shard_w<KIND, 0>(a, tid, nthreads);
 }
 
 template <int KIND>
