@@ -104,6 +104,8 @@ CONVS = [
     (10, 32, 32, 32, 256, 3, 1, 1),    # forward on pairs
     (10, 256, 32, 32, 64, 3, 1, 1),    # dgrad on pairs (forward kernel with flipped filters)
     (12, 64, 56, 56, 320, 3, 1, 2),    # strided, ragged channel tile
+    (4, 64, 14, 14, 128, 1, 0, 2),     # 1x1 stride-2 projection (strided dgrad through zero insertion)
+    (2, 32, 15, 17, 64, 3, 1, 3),      # stride 3, sizes that leave a remainder
 ]
 
 
@@ -128,6 +130,29 @@ def test_conv_asymmetric_kernel_and_padding(ctx):
         gx, gf = ad.gradients(loss, [x, f])
         return {"x": x, "w": f}, [y, gx, gf]
     both(build, {"x": f32(2, 16, 10, 10), "w": f32(24, 16, 1, 7, scale=0.2)}, ctx, rtol=6e-3)
+
+
+@pytest.mark.parametrize("n,c,hw,o,relu", [
+    (4, 32, 16, 64, True),        # one-CTA tiles of 64 columns, two CTAs per SM
+    (3, 64, 12, 128, False),      # tiles of 128 columns
+    (6, 64, 24, 512, True),       # one-CTA tiles of 256 columns, two column tiles
+    (10, 32, 32, 256, True),      # CTA pairs
+    (16, 64, 32, 512, False),     # CTA pairs, two column tiles
+    (2, 8, 10, 24, True),         # channel count off the TMA path: statistics from the separate kernel
+])
+def test_conv_then_batch_norm_takes_statistics_from_the_conv_epilogue(n, c, hw, o, relu, ctx):
+    xv, wv = f32(n, c, hw, hw), f32(o, c, 3, 3, scale=0.2)
+    sv, bv = 1.0 + 0.1 * f32(1, o, 1, 1), 0.1 * f32(1, o, 1, 1)
+
+    def build():
+        x, f = ad.Variable("x"), ad.Variable("w")
+        s, b = ad.Variable("s"), ad.Variable("b")
+        y = ad.conv2d_op(x, f, padding=1, stride=1)
+        z = ad.batch_normalization_relu_op(y, s, b) if relu else ad.batch_normalization_op(y, s, b)
+        loss = ad.reduce_sum_op(ad.mul_op(z, z), [0, 1, 2, 3])
+        gx, gf, gs, gb = ad.gradients(loss, [x, f, s, b])
+        return {"x": x, "w": f, "s": s, "b": b}, [z, gx, gf, gs, gb]
+    both(build, {"x": xv, "w": wv, "s": sv, "b": bv}, ctx, rtol=2e-2)
 
 
 def test_conv_bias_helpers(ctx):

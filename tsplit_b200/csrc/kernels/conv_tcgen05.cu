@@ -50,6 +50,8 @@ struct ConvParams {
   int accumulate;
   long long ldc;
   int tma_store;       // the output tile leaves through shared memory and TMA stores (map `tmo`)
+  float* stats;        // forward only, may be null: per-CTA column sums / sums of squares of the output
+  long long stats_plane;   // floats between the plane of sums and the plane of sums of squares
   int a3d;             // wgrad: dy arrives through the 3-D (32 channels, pixel, chunk) view
   int* status;
   unsigned long long* prof;   // role-time counters (only written when built with -DTSB_CONV_PROF)
@@ -65,7 +67,8 @@ struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGES = ((BN == 256) ? 4 : (BN == 128 ? 6 : 8)) / OCC;
-  static constexpr int SMEM_BYTES = STORE_STAGING_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int STAT_BYTES = 4 * 2 * BN * 4;          // per epilogue warp: (sum, sum of squares) per tile column
+  static constexpr int SMEM_BYTES = STORE_STAGING_BYTES + STAT_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
 };
 
@@ -98,6 +101,52 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 #define PROF_FLUSH(idx, n)
 #endif
 
+// ---- column statistics of the output, taken in the epilogue (for a batch norm that follows) -------
+// The 32 x 16 block that a warp has parked in its staging buffer (64-byte rows, 64B swizzle) is read
+// back column-wise: lanes 0-15 take rows 0-15 of column (lane & 15), lanes 16-31 rows 16-31, the two
+// halves meet by shuffle and lanes 0-15 add (sum, sum of squares) to the warp's accumulators in
+// shared memory.  Rows past the end of the tensor hold zeros (their patches were zero-filled) and
+// add nothing.  Tiles are visited in a fixed order, so the result does not depend on scheduling.
+__device__ __forceinline__ void stat_accumulate(const uint8_t* stg, float* acc, int colbase, int lane) {
+  const int colh = lane & 15, rh = lane >> 4;
+  const uint32_t base = smem_u32(stg) + (uint32_t)(colh & 3) * 4;
+  const uint32_t c4 = (uint32_t)(colh >> 2);
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const uint32_t row = (uint32_t)(rh * 16 + r);
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(base + row * 64 + ((c4 ^ ((row >> 1) & 3)) << 4)) : "memory");
+    s += v;
+    ss += v * v;
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 16);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+  if (lane < 16) {
+    acc[2 * (colbase + lane)] += s;
+    acc[2 * (colbase + lane) + 1] += ss;
+  }
+}
+// After the last tile: the four epilogue warps (128 threads, named barrier 1) add their accumulators
+// in warp order and write the CTA's partial sums for its column tile to slot `slot` of the two planes.
+__device__ __forceinline__ void stat_flush(const ConvParams& p, const float* stat, int bn, int q, int lane, int slot,
+                                           int col0) {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  for (int col = q * 32 + lane; col < bn; col += 128) {
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      s += stat[w * 2 * bn + 2 * col];
+      ss += stat[w * 2 * bn + 2 * col + 1];
+    }
+    const int gc = col0 + col;
+    if (gc < p.NC) {
+      p.stats[(long long)slot * p.NC + gc] = s;
+      p.stats[p.stats_plane + (long long)slot * p.NC + gc] = ss;
+    }
+  }
+}
+
 struct Item {
   int m0, n0, tap, split, kb0, kb1;
 };
@@ -129,7 +178,8 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_stg = smem;
-  uint8_t* smem_a = smem + STORE_STAGING_BYTES;
+  float* smem_stat = reinterpret_cast<float*>(smem + STORE_STAGING_BYTES);
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES + C::STAT_BYTES;
   uint8_t* smem_b = smem_a + C::STAGES * A_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + C::STAGES * C::STAGE_BYTES);
   uint64_t* full = bars;
@@ -369,6 +419,9 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
     const int q = warp & 3;
     uint32_t acc_it = 0;
     bool ok = true;
+    float* my_stat = smem_stat + q * 2 * BN;
+    if (MODE == 0 && p.stats)
+      for (int i = lane; i < 2 * BN; i += 32) my_stat[i] = 0.f;
     PROF_DECL(ew); PROF_DECL(et);
     PROF_BEGIN(et);
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++acc_it) {
@@ -428,6 +481,7 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
               tma_store_2d(&tmo, stg, col + half * 16, row0);
               bulk_commit();
             }
+            if (MODE == 0 && p.stats) stat_accumulate(stg, my_stat, c0 + half * 16, lane);
           }
           continue;
         }
@@ -456,6 +510,8 @@ conv_tf32_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
     if (p.tma_store && lane == 0) bulk_wait_all();     // this lane's stores are complete before the CTA exits
+    if (MODE == 0 && p.stats)            // grid is a multiple of tiles_n: this CTA saw one column tile only
+      stat_flush(p, smem_stat, BN, q, lane, blockIdx.x / p.tiles_n, (blockIdx.x % p.tiles_n) * BN);
     PROF_END(et);
     if (warp == 2 && lane == 0) { PROF_FLUSH(11, ew); PROF_FLUSH(12, et); }
   } else if (IM2COL) {
@@ -679,7 +735,8 @@ constexpr int P2_BN = 256;
 constexpr int P2_B_STAGE_BYTES = (P2_BN / 2) * BK * 4;
 constexpr int P2_STAGE_BYTES = A_STAGE_BYTES + P2_B_STAGE_BYTES;
 constexpr int P2_STAGES = 6;
-constexpr int P2_SMEM_BYTES = STORE_STAGING_BYTES + P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
+constexpr int P2_STAT_BYTES = 4 * 2 * P2_BN * 4;
+constexpr int P2_SMEM_BYTES = STORE_STAGING_BYTES + P2_STAT_BYTES + P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
 
 __global__ void __launch_bounds__(192, 1)
 conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi,
@@ -687,7 +744,8 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_stg = smem;
-  uint8_t* smem_a = smem + STORE_STAGING_BYTES;
+  float* smem_stat = reinterpret_cast<float*>(smem + STORE_STAGING_BYTES);
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES + P2_STAT_BYTES;
   uint8_t* smem_b = smem_a + P2_STAGES * A_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + P2_STAGES * P2_STAGE_BYTES);
   uint64_t* full = bars;
@@ -798,6 +856,9 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
     uint8_t* stg = smem_stg + q * 2048;
     const uint32_t srow = smem_u32(stg) + lane * 64;
     const uint32_t sx = (uint32_t)(lane >> 1) & 3;
+    float* my_stat = smem_stat + q * 2 * P2_BN;
+    if (p.stats)
+      for (int i = lane; i < 2 * P2_BN; i += 32) my_stat[i] = 0.f;
     for (int item = pair; item < items && ok; item += npairs, ++acc_it) {
       const int m0 = (item / ptn) * 256 + (int)rank * 128;
       const int n0 = (item % ptn) * P2_BN;
@@ -829,6 +890,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
             tma_store_2d(&tmo, stg, col + half * 16, row0);
             bulk_commit();
           }
+          if (p.stats) stat_accumulate(stg, my_stat, c0 + half * 16, lane);
         }
       }
       tc_fence_before();
@@ -836,6 +898,8 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
       if (lane == 0) mbar_arrive_leader(&tempty[acc]);
     }
     if (lane == 0) bulk_wait_all();
+    if (p.stats)                         // the pair count is a multiple of ptn: one column tile per pair
+      stat_flush(p, smem_stat, P2_BN, q, lane, (pair / ptn) * 2 + (int)rank, (pair % ptn) * P2_BN);
   }
 
   tc_fence_before();
@@ -857,7 +921,7 @@ conv_wgrad_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_cons
                        const ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_a = smem + STORE_STAGING_BYTES;
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES + P2_STAT_BYTES;
   uint8_t* smem_b = smem_a + P2_STAGES * A_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + P2_STAGES * P2_STAGE_BYTES);
   uint64_t* full = bars;
@@ -1076,6 +1140,28 @@ __global__ void stem_unpack_filter_grads(const float* __restrict__ gp, float* __
   }
 }
 
+// Strided dgrad runs as a stride-1 forward convolution over dy with zeros inserted between its
+// pixels: up[n][s*i][s*j][:] = dy[n][i][j][:], zero elsewhere (Hup x Wup positions).  The inserted
+// zeros cost s*s times the arithmetic of the strided layer, but on the TMA kernels.
+__global__ void upsample_zero_insert(const float* __restrict__ dy, float* __restrict__ up, int N, int OH, int OW,
+                                     int O, int Hup, int Wup, int stride) {
+  const int O4 = O >> 2;
+  const long long total = (long long)N * Hup * Wup * O4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % O4) * 4;
+    long long r = i / O4;
+    const int xx = (int)(r % Wup); r /= Wup;
+    const int yy = (int)(r % Hup);
+    const int n = (int)(r / Hup);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int iy = yy / stride, ix = xx / stride;
+    if (iy * stride == yy && ix * stride == xx && iy < OH && ix < OW)
+      v = *reinterpret_cast<const float4*>(dy + (((long long)n * OH + iy) * OW + ix) * O + c);
+    *reinterpret_cast<float4*>(up + i * 4) = v;
+  }
+}
+
 __global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restrict__ out, int splits,
                                    long long per_split, int accumulate) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_split;
@@ -1154,7 +1240,8 @@ int launch(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo
   }
   const long long items = (long long)p.tiles_m * p.tiles_n * p.taps * p.splits;
   const long long slots = (long long)sm_count() * C::OCC;
-  const int grid = (int)(items < slots ? items : slots);
+  int grid = (int)(items < slots ? items : slots);
+  if (p.stats && grid > p.tiles_n) grid -= grid % p.tiles_n;    // every CTA then sees one column tile only
 #ifdef TSB_CONV_PROF
   static unsigned long long* prof = nullptr;
   if (!prof) cudaMalloc(reinterpret_cast<void**>(&prof), 16 * sizeof(unsigned long long));
@@ -1197,9 +1284,11 @@ int launch_fwd_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtenso
       return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
     attr_set = true;
   }
-  const long long items = (long long)((p.M + 255) / 256) * ((p.NC + P2_BN - 1) / P2_BN);
+  const int ptn = (p.NC + P2_BN - 1) / P2_BN;
+  const long long items = (long long)((p.M + 255) / 256) * ptn;
   long long pairs = sm_count() / 2;
   if (pairs > items) pairs = items;
+  if (p.stats && pairs > ptn) pairs -= pairs % ptn;              // every pair then sees one column tile only
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(192);
@@ -1249,7 +1338,7 @@ ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH
   p.N = N; p.C = C; p.H = H; p.W = W; p.O = O; p.KH = KH; p.KW = KW; p.OH = OH; p.OW = OW;
   p.ph = ph; p.pw = pw; p.stride = stride;
   p.src = nullptr; p.out = nullptr; p.ws = nullptr; p.accumulate = 0; p.splits = 1; p.taps = 1;
-  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr; p.a3d = 0; p.tma_store = 0;
+  p.K = KH * KW * C; p.ocb = (O + 31) / 32; p.status = nullptr; p.prof = nullptr; p.a3d = 0; p.tma_store = 0; p.stats = nullptr; p.stats_plane = 0;
   p.M = 0; p.NC = 0; p.kblocks = 0; p.tiles_m = 0; p.tiles_n = 0; p.ldc = 0;
   return p;
 }
@@ -1270,8 +1359,13 @@ int im2col_map(CUtensorMap* out, const float* a, int N, int C, int H, int W, int
 
 // out[N,OH,OW,O] = conv(src[N,H,W,C], wts[O,KH,KW,C]).  Serves forward, and stride-1 dgrad with
 // flipped and transposed filters.
+// stats / stats_plane / max_chunks / chunks_out (optional): also leave per-CTA column sums and sums of
+// squares of the output in `stats` ([chunks][O] in each of two planes `stats_plane` floats apart) and
+// report the number of chunks; 0 chunks = statistics not produced (the caller computes them itself).
 int run_forward(const float* src, const float* wts, float* out, int N, int C, int H, int W, int O, int KH, int KW,
-                int OH, int OW, int ph, int pw, int stride, cudaStream_t st) {
+                int OH, int OW, int ph, int pw, int stride, cudaStream_t st, float* stats = nullptr,
+                long long stats_plane = 0, int max_chunks = 0, int* chunks_out = nullptr) {
+  if (chunks_out) *chunks_out = 0;
   ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
   p.status = tsb_host::status_word(st);
   if (!p.status) return TSB_ERR_LAUNCH;
@@ -1303,7 +1397,29 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
       uint32_t hb[2] = {BK, P2_BN / 2};
       rc = tsb_host::make_tmap_f32(&tmh, wts, 2, d, s, hb, false);
       if (rc) return rc;
+      if (stats) {              // same grid arithmetic as launch_fwd_pair
+        const int ptn = (p.NC + P2_BN - 1) / P2_BN;
+        long long pairs = sm_count() / 2;
+        if (pairs > pair_items) pairs = pair_items;
+        if (pairs > ptn) pairs -= pairs % ptn;
+        const int chunks = (int)(2 * pairs / ptn);
+        if (pairs % ptn == 0 && chunks <= max_chunks) {
+          p.stats = stats; p.stats_plane = stats_plane;
+          if (chunks_out) *chunks_out = chunks;
+        }
+      }
       return launch_fwd_pair(tmh, tmi, tmo, p, st);
+    }
+    if (stats) {                // same grid arithmetic as launch<>
+      const long long items = (long long)p.tiles_m * p.tiles_n;
+      const long long slots = (long long)sm_count() * (bn <= 128 ? 2 : 1);
+      int grid = (int)(items < slots ? items : slots);
+      if (grid > p.tiles_n) grid -= grid % p.tiles_n;
+      const int chunks = grid / p.tiles_n;
+      if (grid % p.tiles_n == 0 && chunks <= max_chunks) {
+        p.stats = stats; p.stats_plane = stats_plane;
+        if (chunks_out) *chunks_out = chunks;
+      }
     }
     return launch_bn<0, true>(bn, tm, tmi, tmo, p, st);
   }
@@ -1338,6 +1454,24 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
     rc = run_forward(y, wt, x, N, O, OH, OW, C, KH, KW, H, W, KH - 1 - ph, KW - 1 - pw, 1, st);
+  } else if (kind == 1 && stride > 1 && (O % 32) == 0 && ph <= KH - 1 && pw <= KW - 1 &&
+             (long long)N * (H - KH + 1 + 2 * ph) * (W - KW + 1 + 2 * pw) * O * 4 <= (4ll << 30)) {
+    // strided dgrad = stride-1 forward convolution of the zero-inserted dy with the flipped, transposed filters
+    const int Hup = H - KH + 1 + 2 * ph, Wup = W - KW + 1 + 2 * pw;
+    const size_t wbytes = (size_t)C * KH * KW * O * sizeof(float);
+    const size_t ubytes = (size_t)N * Hup * Wup * O * sizeof(float);
+    float* wt = get_ws(st, 1, wbytes, size_t(16) << 20);
+    float* up = get_ws(st, 2, ubytes, size_t(64) << 20);
+    if (!wt || !up) return TSB_ERR_OOM;
+    dim3 grid((C + 31) / 32, (O + 31) / 32, KH * KW);
+    flip_transpose_filters<<<grid, dim3(32, 8), 0, st>>>(w, wt, O, C, KH, KW);
+    const long long work = (long long)N * Hup * Wup * (O / 4);
+    long long blocks = (work + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    upsample_zero_insert<<<(unsigned)blocks, 256, 0, st>>>(y, up, N, OH, OW, O, Hup, Wup, stride);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+    rc = run_forward(up, wt, x, N, O, Hup, Wup, C, KH, KW, H, W, KH - 1 - ph, KW - 1 - pw, 1, st);
   } else if (kind == 1) {
     ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
     p.status = tsb_host::status_word(st);
@@ -1430,6 +1564,26 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
       if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
     }
   }
+  if (rc) return rc;
+  const int late = tsb_host::peek_status();
+  return late ? TSB_ERR_TIMEOUT | (late << 8) : TSB_OK;
+}
+
+// Forward convolution that also leaves the column statistics of y for a batch norm that follows
+// (see run_forward).  *chunks_out == 0 on return means "no statistics": unsupported shape for the
+// fused path, or more chunks than the caller's buffer holds.
+int tsb_conv2d_fwd_stats(float* x, float* w, float* y, int N, int C, int H, int W, int O, int KH, int KW, int OH,
+                         int OW, int ph, int pw, int stride, float* stats, long long stats_plane, int max_chunks,
+                         int* chunks_out, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (N <= 0 || stride <= 0 || !chunks_out) return TSB_ERR_ARG;
+  *chunks_out = 0;
+  if ((C % 4) || (O % 4)) return TSB_ERR_UNSUPPORTED;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
+    return TSB_ERR_UNSUPPORTED;
+  if ((long long)N * OH * OW >= (1ll << 31) || (long long)N * H * W >= (1ll << 31)) return TSB_ERR_UNSUPPORTED;
+  int rc = run_forward(x, w, y, N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride, st, stats, stats_plane, max_chunks,
+                       chunks_out);
   if (rc) return rc;
   const int late = tsb_host::peek_status();
   return late ? TSB_ERR_TIMEOUT | (late << 8) : TSB_OK;

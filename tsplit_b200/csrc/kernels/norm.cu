@@ -166,7 +166,7 @@ col_partial(const float* __restrict__ a, const float* __restrict__ b, const floa
 // lane 0 then adds the lane sums.
 constexpr int FIN_LANES = 32;
 __device__ __forceinline__ void reduce_partials(const float* __restrict__ part, int chunks, int C, int c,
-                                                double& s, double& ss) {
+                                                double& s, double& ss, long long plane = PLANE_FLOATS) {
   __shared__ double sh0[FIN_LANES][33], sh1[FIN_LANES][33];
   double a = 0.0, b = 0.0;
   if (c < C) {
@@ -176,14 +176,14 @@ __device__ __forceinline__ void reduce_partials(const float* __restrict__ part, 
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         x[u] = part[(long long)(ch + u * FIN_LANES) * C + c];
-        y[u] = part[PLANE_FLOATS + (long long)(ch + u * FIN_LANES) * C + c];
+        y[u] = part[plane + (long long)(ch + u * FIN_LANES) * C + c];
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) { a += x[u]; b += y[u]; }
     }
     for (; ch < chunks; ch += FIN_LANES) {
       a += part[(long long)ch * C + c];
-      b += part[PLANE_FLOATS + (long long)ch * C + c];
+      b += part[plane + (long long)ch * C + c];
     }
   }
   sh0[threadIdx.y][threadIdx.x] = a;
@@ -199,10 +199,11 @@ __device__ __forceinline__ void reduce_partials(const float* __restrict__ part, 
 // Forward finalise: mean / invstd from the partial sums (+ running statistics).  Block (32, FIN_LANES).
 __global__ void bn_finalize_fwd(const float* __restrict__ part, int chunks, int C, double count, float eps,
                                 float momentum, float* __restrict__ mean, float* __restrict__ invstd,
-                                float* __restrict__ run_mean, float* __restrict__ run_var) {
+                                float* __restrict__ run_mean, float* __restrict__ run_var,
+                                long long plane = PLANE_FLOATS) {
   const int c = blockIdx.x * 32 + threadIdx.x;
   double s, ss;
-  reduce_partials(part, chunks, C, c, s, ss);
+  reduce_partials(part, chunks, C, c, s, ss, plane);
   if (threadIdx.y != 0 || c >= C) return;
   const double m = s / count;
   double var = ss / count - m * m;
@@ -406,6 +407,36 @@ int tsb_bn_forward(const float* x, const float* scale, const float* bias, float*
   col_partial<0><<<sg.grid, STAT_THREADS, 0, st>>>(x, nullptr, nullptr, nullptr, part, rows, (int)C, ldx, 0, sg.chunks, sg.cw);
   bn_finalize_fwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, (double)rows, eps, momentum, save_mean,
                                                          save_invstd, run_mean, run_var);
+  bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
+                                                        ldx, ldy, relu);
+  return done();
+}
+
+// Batch-norm forward whose column partial sums were produced by the convolution that wrote x
+// (tsb_conv2d_fwd_stats): finalise + one normalise pass; x is read once instead of twice.
+int tsb_bn_forward_from_partials(const float* part, int chunks, long long plane, const float* x, const float* scale,
+                                 const float* bias, float* y, float* save_mean, float* save_invstd, float* run_mean,
+                                 float* run_var, long long rows, long long C, long long ldx, long long ldy,
+                                 float momentum, float eps, int relu, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0 || chunks <= 0 || !part) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (ldy % 4)) return TSB_ERR_UNSUPPORTED;
+  bn_finalize_fwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, chunks, (int)C, (double)rows, eps, momentum,
+                                                                 save_mean, save_invstd, run_mean, run_var, plane);
+  bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
+                                                        ldx, ldy, relu);
+  return done();
+}
+
+// Normalise / scale / shift (/ReLU) with statistics that are already known: what a rematerialised
+// batch-norm output needs (the statistics of the step were computed by the first forward pass, and
+// the running statistics must not be updated a second time).
+int tsb_bn_apply(const float* x, const float* scale, const float* bias, float* y, const float* save_mean,
+                 const float* save_invstd, long long rows, long long C, long long ldx, long long ldy, int relu,
+                 void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (ldy % 4)) return TSB_ERR_UNSUPPORTED;
   bn_apply_fwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(x, scale, bias, save_mean, save_invstd, y, rows, (int)C,
                                                         ldx, ldy, relu);
   return done();

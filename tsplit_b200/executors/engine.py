@@ -356,7 +356,14 @@ class MemoryExecutor(Executor):
             self.locked.add(i)
         out = self._alloc(node)
         self.arr[node] = out
-        self._launch(node, out)
+        state = getattr(node, "state", None)
+        if isinstance(state, dict):
+            state["rematerialise"] = True      # ops with per-step side results (batch-norm statistics) reuse them
+        try:
+            self._launch(node, out)
+        finally:
+            if isinstance(state, dict):
+                state.pop("rematerialise", None)
         for i in node.inputs:
             self.locked.discard(i)
         self.stats["recomputed_nodes"] += 1

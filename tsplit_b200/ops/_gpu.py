@@ -236,6 +236,14 @@ def bn_backward(dy, x, scale, save_mean, save_invstd, dx, dscale, dbias, stream)
                                  c_int64(lddy), c_int64(lddx), _s(stream)), "bn_backward")
 
 
+def bn_apply(x, scale, bias, y, save_mean, save_invstd, relu, stream):
+    """Normalise with known statistics (rematerialisation of a batch-norm output)."""
+    rows, c, ldx = _rows_c(x)
+    _, _, ldy = _rows_c(y)
+    _check(lib().tsb_bn_apply(_p(x), _p(scale), _p(bias), _p(y), _p(save_mean), _p(save_invstd), c_int64(rows),
+                              c_int64(c), c_int64(ldx), c_int64(ldy), c_int(int(relu)), _s(stream)), "bn_apply")
+
+
 def bn_relu_backward(dy, x, scale, bias, save_mean, save_invstd, dx, dscale, dbias, stream):
     rows, c, ldx = _rows_c(x)
     _, _, lddy = _rows_c(dy)
@@ -320,6 +328,39 @@ def conv2d(kind, x, w, y, ph, pw, stride, stream):
                           c_int(o), c_int(kh), c_int(kw), c_int(oh), c_int(ow), c_int(ph), c_int(pw),
                           c_int(stride), _s(stream))
     _check(rc, "conv2d kind %d" % kind)
+
+
+CONV_STAT_MAX_CHUNKS = 304      # upper bound of per-CTA partial-sum slots a forward convolution may fill
+
+
+def conv2d_fwd_stats(x, w, y, ph, pw, stride, part, stream):
+    """Forward convolution that also leaves per-CTA column sums / sums of squares of ``y`` in
+    ``part`` (flat array of 2 * CONV_STAT_MAX_CHUNKS * O floats) for the batch norm that follows.
+    Returns the number of chunks written; 0 = no statistics (the plain kernel ran)."""
+    n, c, h, wd = x.shape
+    o, _, kh, kw = w.shape
+    _, _, oh, ow = y.shape
+    if c % 4 or not (x.is_channels_last() and w.is_channels_last() and y.is_channels_last()):
+        conv2d(0, x, w, y, ph, pw, stride, stream)
+        return 0
+    chunks = c_int(0)
+    rc = lib().tsb_conv2d_fwd_stats(_p(x), _p(w), _p(y), c_int(n), c_int(c), c_int(h), c_int(wd), c_int(o),
+                                    c_int(kh), c_int(kw), c_int(oh), c_int(ow), c_int(ph), c_int(pw),
+                                    c_int(stride), _p(part), c_int64(CONV_STAT_MAX_CHUNKS * o),
+                                    c_int(CONV_STAT_MAX_CHUNKS), ctypes.byref(chunks), _s(stream))
+    _check(rc, "conv2d_fwd_stats")
+    return int(chunks.value)
+
+
+def bn_forward_from_partials(part, chunks, x, scale, bias, y, save_mean, save_invstd, run_mean, run_var, momentum,
+                             eps, relu, stream):
+    rows, c, ldx = _rows_c(x)
+    _, _, ldy = _rows_c(y)
+    _check(lib().tsb_bn_forward_from_partials(_p(part), c_int(chunks), c_int64(CONV_STAT_MAX_CHUNKS * c), _p(x),
+                                              _p(scale), _p(bias), _p(y), _p(save_mean), _p(save_invstd),
+                                              _p(run_mean), _p(run_var), c_int64(rows), c_int64(c), c_int64(ldx),
+                                              c_int64(ldy), c_float(momentum), c_float(eps), c_int(int(relu)),
+                                              _s(stream)), "bn_forward_from_partials")
 
 
 _PAD_CACHE = {}

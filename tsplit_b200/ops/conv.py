@@ -17,6 +17,7 @@ from __future__ import annotations
 import numpy as np
 
 from ..graph import Op
+from .. import ndarray
 from . import _gpu as G
 
 
@@ -77,6 +78,17 @@ class Conv2dOp(Op):
 
     def gpu_compute(self, node, iv, out, stream):
         ph, pw = _pads(node)
+        bn = node.attrs.get("bn_consumer")
+        if bn is not None:
+            # a batch norm reads this output: take its column statistics in the epilogue
+            st = bn.state
+            o = out.shape[1]
+            part = st.get("conv_part")
+            if part is None or part.shape != (2 * G.CONV_STAT_MAX_CHUNKS * o,):
+                part = st["conv_part"] = ndarray.empty((2 * G.CONV_STAT_MAX_CHUNKS * o,), out.ctx, use_pool=False)
+            st["conv_chunks"] = G.conv2d_fwd_stats(iv[0], iv[1], out, ph, pw, node.attrs["stride"], part, stream)
+            st["conv_rows"] = out.shape[0] * out.shape[2] * out.shape[3]
+            return
         G.conv2d(0, iv[0], iv[1], out, ph, pw, node.attrs["stride"], stream)
 
     def gradient(self, node, g):

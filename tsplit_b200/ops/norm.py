@@ -60,7 +60,26 @@ class BatchNormOp(Op):
     def __call__(self, x, scale, bias, momentum=0.99, eps=0.01):
         node = Op.__call__(self, x, scale, bias, momentum=momentum, eps=eps)
         node.state = {}
+        if getattr(x.op, "name", None) == "Conv2d" and x.attrs.get("bn_consumer") is None:
+            x.attrs["bn_consumer"] = node      # the convolution's epilogue then supplies the column statistics
         return node
+
+    def _forward(self, node, iv, out, stream, relu):
+        x, scale, bias = iv
+        st = node.state
+        c = x.shape[1]
+        if "mean" not in st or st["mean"].shape != (c,):
+            st["mean"], st["invstd"] = _small((c,), x.ctx), _small((c,), x.ctx)
+            st["run_mean"], st["run_var"] = _small((c,), x.ctx, 0.0), _small((c,), x.ctx, 1.0)
+        if st.get("rematerialise"):      # same step, statistics known: normalise only, leave running stats alone
+            return G.bn_apply(x, scale, bias, out, st["mean"], st["invstd"], relu, stream)
+        chunks = st.pop("conv_chunks", 0)
+        if chunks and st.get("conv_rows") == x.shape[0] * x.shape[2] * x.shape[3]:
+            return G.bn_forward_from_partials(st["conv_part"], chunks, x, scale, bias, out, st["mean"], st["invstd"],
+                                              st["run_mean"], st["run_var"], node.attrs["momentum"],
+                                              node.attrs["eps"], relu, stream)
+        G.bn_forward(x, scale, bias, out, st["mean"], st["invstd"], st["run_mean"], st["run_var"],
+                     node.attrs["momentum"], node.attrs["eps"], relu, stream)
 
     def np_compute(self, node, iv):
         x, scale, bias = iv
@@ -73,14 +92,7 @@ class BatchNormOp(Op):
         return y
 
     def gpu_compute(self, node, iv, out, stream):
-        x, scale, bias = iv
-        st = node.state
-        c = x.shape[1]
-        if "mean" not in st or st["mean"].shape != (c,):
-            st["mean"], st["invstd"] = _small((c,), x.ctx), _small((c,), x.ctx)
-            st["run_mean"], st["run_var"] = _small((c,), x.ctx, 0.0), _small((c,), x.ctx, 1.0)
-        G.bn_forward(x, scale, bias, out, st["mean"], st["invstd"], st["run_mean"], st["run_var"],
-                     node.attrs["momentum"], node.attrs["eps"], False, stream)
+        self._forward(node, iv, out, stream, False)
 
     def gradient(self, node, g):
         x, scale, bias = node.inputs
@@ -109,14 +121,7 @@ class BatchNormReluOp(BatchNormOp):
         return np.maximum(BatchNormOp.np_compute(self, node, iv), 0)
 
     def gpu_compute(self, node, iv, out, stream):
-        x, scale, bias = iv
-        st = node.state
-        c = x.shape[1]
-        if "mean" not in st or st["mean"].shape != (c,):
-            st["mean"], st["invstd"] = _small((c,), x.ctx), _small((c,), x.ctx)
-            st["run_mean"], st["run_var"] = _small((c,), x.ctx, 0.0), _small((c,), x.ctx, 1.0)
-        G.bn_forward(x, scale, bias, out, st["mean"], st["invstd"], st["run_mean"], st["run_var"],
-                     node.attrs["momentum"], node.attrs["eps"], True, stream)
+        self._forward(node, iv, out, stream, True)
 
     def gradient(self, node, g):
         x, scale, bias = node.inputs
