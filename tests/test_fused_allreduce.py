@@ -74,3 +74,36 @@ def test_two_gpu_training_matches_nccl_baseline():
     res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-4000:]
     assert "DDP_OK" in res.stdout, res.stdout[-4000:]
+
+
+@pytest.mark.gpu
+def test_bounded_wait_reports_a_peer_that_never_signals():
+    """Failure detection on the device: rank 0 of a 2-rank exchange whose peer never writes its flag.
+    The kernel's flag wait gives up after about a second, leaves a status code that the host turns
+    into an error, and the context stays usable (a following launch works)."""
+    from ctypes import c_int, c_void_p, c_longlong, c_float, c_uint
+    from tsplit_b200.parallel import fused_allreduce as fa
+    lib = fa._lib()
+    dev = torch.device("cuda", 0)
+    n = 4096
+    grads = [torch.ones(n, device=dev), torch.ones(n, device=dev)]
+    params = [torch.zeros(n, device=dev), torch.zeros(n, device=dev)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev), torch.zeros(64, dtype=torch.int32, device=dev)]
+    slot1, slot2 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    PT = c_void_p * 2
+    hv = (c_float * 8)(0.1, 0, 0, 0, 0, 0, 0, 0)
+    torch.cuda.synchronize()
+    rc = lib.tsb_fused_allreduce_update(
+        c_int(0), c_int(0), c_int(2), PT(*[g.data_ptr() for g in grads]), PT(*[p.data_ptr() for p in params]),
+        PT(*[f.data_ptr() for f in flags]), c_void_p(0), c_void_p(0), c_void_p(slot1.data_ptr()),
+        c_void_p(slot2.data_ptr()), c_longlong(n), hv, c_uint(1), c_void_p(0))
+    assert rc & 0xFF in (0, 4), rc          # the launch itself succeeds; a late status may already be visible
+    status = lib.tsb_comm_status(c_void_p(0))          # synchronises, reads and clears the status word
+    assert (status & 0xF00) == 0x300, hex(status)      # a flag wait of the exchange ran out
+    # the context is still healthy: the one-GPU emulation of two ranks runs and gives the SGD result
+    g2 = [torch.full((n,), 1.0, device=dev), torch.full((n,), 3.0, device=dev)]
+    p2 = [torch.zeros(n, device=dev), torch.zeros(n, device=dev)]
+    fa.emulate(0, g2, p2, torch.zeros(n, device=dev), torch.zeros(n, device=dev), [0.1])
+    torch.cuda.synchronize()
+    assert lib.tsb_comm_status(c_void_p(0)) == 0
+    np.testing.assert_allclose(p2[0].cpu().numpy(), np.full(n, -0.2, np.float32), rtol=1e-6)

@@ -738,19 +738,33 @@ constexpr int P2_STAGES = 6;
 constexpr int P2_STAT_BYTES = 4 * 2 * P2_BN * 4;
 constexpr int P2_SMEM_BYTES = STORE_STAGING_BYTES + P2_STAT_BYTES + P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
 
+// Forward pair kernel, written for tiles of BN = 64 / 128 / 256 output channels; only BN = 256 is
+// dispatched (see run_forward for the measurement that keeps narrow tiles on the one-CTA kernel).
+template <int BN>
+struct PairCfg {
+  static constexpr int B_STAGE_BYTES = (BN / 2) * BK * 4;       // this CTA's half of the filter rows
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = BN == 256 ? 6 : 8;
+  static constexpr int STAT_BYTES = 4 * 2 * BN * 4;
+  static constexpr int SMEM_BYTES = STORE_STAGING_BYTES + STAT_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;    // two accumulators; 128, 256 or 512 columns
+};
+
+template <int BN>
 __global__ void __launch_bounds__(192, 1)
 conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmi,
                      const __grid_constant__ CUtensorMap tmo, const ConvParams p) {
+  using PC = PairCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_stg = smem;
   float* smem_stat = reinterpret_cast<float*>(smem + STORE_STAGING_BYTES);
-  uint8_t* smem_a = smem + STORE_STAGING_BYTES + P2_STAT_BYTES;
-  uint8_t* smem_b = smem_a + P2_STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + P2_STAGES * P2_STAGE_BYTES);
+  uint8_t* smem_a = smem + STORE_STAGING_BYTES + PC::STAT_BYTES;
+  uint8_t* smem_b = smem_a + PC::STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_a + PC::STAGES * PC::STAGE_BYTES);
   uint64_t* full = bars;
-  uint64_t* empty = bars + P2_STAGES;
-  uint64_t* tfull = bars + 2 * P2_STAGES;
+  uint64_t* empty = bars + PC::STAGES;
+  uint64_t* tfull = bars + 2 * PC::STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
 
@@ -760,7 +774,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < P2_STAGES; ++s) {
+    for (int s = 0; s < PC::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -774,7 +788,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
     tma_prefetch_desc(&tmo);
   }
   if (warp == 1) {
-    tmem_alloc_2sm(tmem_slot, 512);
+    tmem_alloc_2sm(tmem_slot, PC::TMEM_COLS);
     tmem_relinquish_2sm();
   }
   tc_fence_before();
@@ -783,7 +797,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int ptm = (p.M + 255) / 256, ptn = (p.NC + P2_BN - 1) / P2_BN;
+  const int ptm = (p.M + 255) / 256, ptn = (p.NC + BN - 1) / BN;
   const int items = ptm * ptn;
 
   if (warp == 0) {
@@ -794,20 +808,20 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
       const int cpb = p.C >> 5;
       for (int item = pair; item < items && ok; item += npairs) {
         const int m0 = (item / ptn) * 256 + (int)rank * 128;          // this CTA's pixels
-        const int n0 = (item % ptn) * P2_BN + (int)rank * (P2_BN / 2);  // this CTA's filter rows
+        const int n0 = (item % ptn) * BN + (int)rank * (BN / 2);  // this CTA's filter rows
         const int n = m0 / (p.OH * p.OW);
         const int rem = m0 - n * (p.OH * p.OW);
         const int oy = rem / p.OW, ox = rem - oy * p.OW;
         const int bw = ox * p.stride - p.pw, bh = oy * p.stride - p.ph;
         int cb = 0, kh = 0, kw = 0;
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % P2_STAGES;
-          const uint32_t ph = (it / P2_STAGES) & 1;
+          const int s = it % PC::STAGES;
+          const uint32_t ph = (it / PC::STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, 0x211)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(&full[s], 2 * P2_STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * PC::STAGE_BYTES);
           tma_load_im2col_4d_2sm(smem_a + s * A_STAGE_BYTES, &tmi, &full[s], cb * 32, bw, bh, n, (uint16_t)kw,
                                  (uint16_t)kh);
-          tma_load_2d_2sm(smem_b + s * P2_B_STAGE_BYTES, &tm, &full[s], kb * BK, n0);
+          tma_load_2d_2sm(smem_b + s * PC::B_STAGE_BYTES, &tm, &full[s], kb * BK, n0);
           if (++cb == cpb) {
             cb = 0;
             if (++kw == p.KW) { kw = 0; ++kh; }
@@ -819,7 +833,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_tf32(256, P2_BN, 0, 0);
+      constexpr uint32_t idesc = make_idesc_tf32(256, BN, 0, 0);
       constexpr uint32_t HI = smem_desc_hi(1024);
       constexpr uint32_t KSTEP = (UMMA_K * 4) >> 4;
       const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), 16);
@@ -831,14 +845,14 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
         const uint32_t acc_ph = (acc_it >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, 0x212)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * P2_BN;
+        const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % P2_STAGES;
-          const uint32_t ph = (it / P2_STAGES) & 1;
+          const int s = it % PC::STAGES;
+          const uint32_t ph = (it / PC::STAGES) & 1;
           if (!mbar_wait(&full[s], ph, p.status, 0x213)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * (A_STAGE_BYTES >> 4);
-          const uint32_t b_lo = b_lo0 + s * (P2_B_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (PC::B_STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_tf32_2sm(d_tmem, smem_desc_join(HI, a_lo + k * KSTEP), smem_desc_join(HI, b_lo + k * KSTEP), idesc,
@@ -856,21 +870,21 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
     uint8_t* stg = smem_stg + q * 2048;
     const uint32_t srow = smem_u32(stg) + lane * 64;
     const uint32_t sx = (uint32_t)(lane >> 1) & 3;
-    float* my_stat = smem_stat + q * 2 * P2_BN;
+    float* my_stat = smem_stat + q * 2 * BN;
     if (p.stats)
-      for (int i = lane; i < 2 * P2_BN; i += 32) my_stat[i] = 0.f;
+      for (int i = lane; i < 2 * BN; i += 32) my_stat[i] = 0.f;
     for (int item = pair; item < items && ok; item += npairs, ++acc_it) {
       const int m0 = (item / ptn) * 256 + (int)rank * 128;
-      const int n0 = (item % ptn) * P2_BN;
+      const int n0 = (item % ptn) * BN;
       const int acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x214)) { ok = false; break; }
       tc_fence_after();
       const int row0 = m0 + q * 32;
 #pragma unroll 1
-      for (int c0 = 0; c0 < P2_BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
-        tmem_ld_32x32(tmem_base + acc * P2_BN + ((uint32_t)(q * 32) << 16) + c0, v);
+        tmem_ld_32x32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + c0, v);
         tmem_ld_wait();
         const int col = n0 + c0;
 #pragma unroll
@@ -899,7 +913,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
     }
     if (lane == 0) bulk_wait_all();
     if (p.stats)                         // the pair count is a multiple of ptn: one column tile per pair
-      stat_flush(p, smem_stat, P2_BN, q, lane, (pair / ptn) * 2 + (int)rank, (pair % ptn) * P2_BN);
+      stat_flush(p, smem_stat, BN, q, lane, (pair / ptn) * 2 + (int)rank, (pair % ptn) * BN);
   }
 
   tc_fence_before();
@@ -907,7 +921,7 @@ conv_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
   cluster_sync_all();          // nobody leaves or frees TMEM while the partner may still signal or read
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc_2sm(tmem_base, 512);
+    tmem_dealloc_2sm(tmem_base, PC::TMEM_COLS);
   }
 }
 
@@ -1275,16 +1289,18 @@ int launch_bn(int bn, const CUtensorMap& tm, const CUtensorMap& tmi, const CUten
   return launch<MODE, 64, IM2COL>(tm, tmi, tmo, p, st);
 }
 
-int launch_fwd_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo, const ConvParams& p,
-                    cudaStream_t st) {
+template <int BN>
+int launch_fwd_pair_bn(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo, const ConvParams& p,
+                       cudaStream_t st) {
+  using PC = PairCfg<BN>;
+  auto kern = conv_fwd_pair_kernel<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(conv_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::SMEM_BYTES) != cudaSuccess)
       return TSB_ERR_LAUNCH | ((int)cudaGetLastError() << 8);
     attr_set = true;
   }
-  const int ptn = (p.NC + P2_BN - 1) / P2_BN;
+  const int ptn = (p.NC + BN - 1) / BN;
   const long long items = (long long)((p.M + 255) / 256) * ptn;
   long long pairs = sm_count() / 2;
   if (pairs > items) pairs = items;
@@ -1292,7 +1308,7 @@ int launch_fwd_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtenso
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(192);
-  cfg.dynamicSmemBytes = P2_SMEM_BYTES;
+  cfg.dynamicSmemBytes = PC::SMEM_BYTES;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1301,8 +1317,15 @@ int launch_fwd_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const CUtenso
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, conv_fwd_pair_kernel, tm, tmi, tmo, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm, tmi, tmo, p);
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
+}
+
+int launch_fwd_pair(int bn, const CUtensorMap& tm, const CUtensorMap& tmi, const CUtensorMap& tmo,
+                    const ConvParams& p, cudaStream_t st) {
+  if (bn == 256) return launch_fwd_pair_bn<256>(tm, tmi, tmo, p, st);
+  if (bn == 128) return launch_fwd_pair_bn<128>(tm, tmi, tmo, p, st);
+  return launch_fwd_pair_bn<64>(tm, tmi, tmo, p, st);
 }
 
 int launch_wgrad_pair(const CUtensorMap& tm, const CUtensorMap& tmi, const ConvParams& p, cudaStream_t st) {
@@ -1391,14 +1414,16 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
   rc = im2col_map(&tmi, src, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BM, false);
   if (rc == TSB_OK) {
     const char* e = getenv("TSB_CONV_PAIR");              // "0" selects the one-CTA tiles everywhere
-    const long long pair_items = (long long)((p.M + 255) / 256) * ((p.NC + P2_BN - 1) / P2_BN);
+    const int ptn = (p.NC + bn - 1) / bn;
+    const long long pair_items = (long long)((p.M + 255) / 256) * ptn;
+    // narrow tiles measured slower on pairs (one CTA per SM, one issuing thread per two SMs) than on the
+    // one-CTA kernel with two CTAs per SM: 64 -> 64 channels at 224x224, batch 64: 0.90 ms against 0.61 ms
     if (!(e && e[0] == '0') && bn == 256 && pair_items * 4 >= sm_count()) {
-      CUtensorMap tmh;          // filters, 128 rows per CTA
-      uint32_t hb[2] = {BK, P2_BN / 2};
+      CUtensorMap tmh;          // filters, bn / 2 rows per CTA
+      uint32_t hb[2] = {BK, (uint32_t)bn / 2};
       rc = tsb_host::make_tmap_f32(&tmh, wts, 2, d, s, hb, false);
       if (rc) return rc;
-      if (stats) {              // same grid arithmetic as launch_fwd_pair
-        const int ptn = (p.NC + P2_BN - 1) / P2_BN;
+      if (stats) {              // same grid arithmetic as launch_fwd_pair_bn
         long long pairs = sm_count() / 2;
         if (pairs > pair_items) pairs = pair_items;
         if (pairs > ptn) pairs -= pairs % ptn;
@@ -1408,7 +1433,7 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
           if (chunks_out) *chunks_out = chunks;
         }
       }
-      return launch_fwd_pair(tmh, tmi, tmo, p, st);
+      return launch_fwd_pair(bn, tmh, tmi, tmo, p, st);
     }
     if (stats) {                // same grid arithmetic as launch<>
       const long long items = (long long)p.tiles_m * p.tiles_n;
