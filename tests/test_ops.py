@@ -62,6 +62,25 @@ def test_scalar_broadcast_add_mul(ctx):
     both(build, {"x": f32(4, 9), "s": np.array([2.5], np.float32)}, ctx)
 
 
+def test_fused_add_relu_matches_add_then_relu(ctx):
+    av, bv = f32(3, 8, 5, 7), f32(3, 8, 5, 7)
+
+    def build():
+        a, b = ad.Variable("a"), ad.Variable("b")
+        y = ad.add_relu_op(a, b)
+        ref = ad.relu_op(ad.add_op(a, b))
+        w = ad.Variable("w")
+        ga, gb = ad.gradients(ad.reduce_sum_op(ad.mul_op(y, w), [0, 1, 2, 3]), [a, b])
+        ra, rb = ad.gradients(ad.reduce_sum_op(ad.mul_op(ref, w), [0, 1, 2, 3]), [a, b])
+        return {"a": a, "b": b, "w": w}, [y, ref, ga, gb, ra, rb]
+    feeds = {"a": av, "b": bv, "w": f32(3, 8, 5, 7)}
+    both(build, feeds, ctx)
+    y, ref, ga, gb, ra, rb = [np.asarray(o) for o in run_graph(build, feeds, ctx)]
+    np.testing.assert_allclose(y, ref, rtol=1e-6)
+    np.testing.assert_allclose(ga, ra, rtol=1e-6)
+    np.testing.assert_allclose(gb, rb, rtol=1e-6)
+
+
 @pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
 def test_matmul_and_grads(ta, tb, ctx):
     m, k, n = 96, 64, 80

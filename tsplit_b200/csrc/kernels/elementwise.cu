@@ -20,7 +20,7 @@
 namespace {
 
 enum { UN_COPY, UN_RELU, UN_SIGMOID, UN_TANH, UN_SQRT, UN_RSQRT, UN_NEG, UN_ADDC, UN_MULC, UN_CDIV, UN_FILL };
-enum { BIN_ADD, BIN_MUL, BIN_DIV, BIN_RELU_GRAD, BIN_SUB };
+enum { BIN_ADD, BIN_MUL, BIN_DIV, BIN_RELU_GRAD, BIN_SUB, BIN_ADD_RELU, BIN_RELU_GRAD_OUT };
 
 constexpr int MAXD = 8;
 struct Dims {
@@ -54,6 +54,8 @@ __device__ __forceinline__ float bin(float a, float b) {
     case BIN_MUL: return a * b;
     case BIN_DIV: return a / b;
     case BIN_RELU_GRAD: return a > 0.f ? b : (a == 0.f ? 0.5f * b : 0.f);
+    case BIN_ADD_RELU: return fmaxf(a + b, 0.f);              // residual add + ReLU in one pass
+    case BIN_RELU_GRAD_OUT: return a > 0.f ? b : 0.f;         // a = the ReLU OUTPUT: gradient passes where it is positive
     default: return a - b;
   }
 }
@@ -305,6 +307,7 @@ int tsb_ew_binary(int op, const float* a, const float* b, float* y, long long n,
   const int grid = grid_for((n + 3) / 4, 256);
   switch (op) {
     BIN_CASE(BIN_ADD) BIN_CASE(BIN_MUL) BIN_CASE(BIN_DIV) BIN_CASE(BIN_RELU_GRAD) BIN_CASE(BIN_SUB)
+    BIN_CASE(BIN_ADD_RELU) BIN_CASE(BIN_RELU_GRAD_OUT)
     default: return TSB_ERR_ARG;
   }
   return done();
@@ -374,6 +377,7 @@ int tsb_strided_binary(int op, const float* a, const float* b, float* y, int nd,
   const int grid = grid_for(n, 256);
   switch (op) {
     BINS_CASE(BIN_ADD) BINS_CASE(BIN_MUL) BINS_CASE(BIN_DIV) BINS_CASE(BIN_RELU_GRAD) BINS_CASE(BIN_SUB)
+    BINS_CASE(BIN_ADD_RELU) BINS_CASE(BIN_RELU_GRAD_OUT)
     default: return TSB_ERR_ARG;
   }
   return done();

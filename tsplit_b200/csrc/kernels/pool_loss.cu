@@ -193,6 +193,88 @@ __global__ void pool_bwd_tiled(const float* __restrict__ x, const float* __restr
   }
 }
 
+// Max-pool backward for windows that overlap (e.g. 3x3 stride 2), in two passes without scans:
+//   pass 1, one thread per output window and four channels: position (a * kw + b) of the first
+//           maximum inside the window, one byte per channel;
+//   pass 2, one thread per input pixel and four channels: add dy of every window that contains the
+//           pixel and whose recorded position is this pixel, in a fixed order.
+// After a ReLU most windows tie at zero, which made the scan-for-earlier-maximum form of the general
+// kernel expensive; here every tensor is read once.
+__global__ void pool_argmax(const float* __restrict__ x, unsigned char* __restrict__ idx, const PoolP p) {
+  const int C4 = p.c >> 2;
+  const long long total = (long long)p.n * p.oh * p.ow * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C4) * 4;
+    long long r = i / C4;
+    const int ox = (int)(r % p.ow); r /= p.ow;
+    const int oy = (int)(r % p.oh);
+    const int n = (int)(r / p.oh);
+    float4 m = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+    uchar4 q = make_uchar4(255, 255, 255, 255);
+    for (int a = 0; a < p.kh; ++a) {
+      const int iy = oy * p.stride - p.pad + a;
+      if ((unsigned)iy >= (unsigned)p.h) continue;
+      for (int b = 0; b < p.kw; ++b) {
+        const int ix = ox * p.stride - p.pad + b;
+        if ((unsigned)ix >= (unsigned)p.w) continue;
+        const float4 v = *reinterpret_cast<const float4*>(x + n * p.xsn + iy * p.xsh + ix * p.xsw + c);
+        const unsigned char pos = (unsigned char)(a * p.kw + b);
+        if (v.x > m.x || q.x == 255) { m.x = v.x; q.x = pos; }
+        if (v.y > m.y || q.y == 255) { m.y = v.y; q.y = pos; }
+        if (v.z > m.z || q.z == 255) { m.z = v.z; q.z = pos; }
+        if (v.w > m.w || q.w == 255) { m.w = v.w; q.w = pos; }
+      }
+    }
+    *reinterpret_cast<uchar4*>(idx + i * 4) = q;
+  }
+}
+
+__global__ void pool_bwd_from_argmax(const unsigned char* __restrict__ idx, const float* __restrict__ dy,
+                                     float* __restrict__ dx, const PoolP p) {
+  const int C4 = p.c >> 2;
+  const long long total = (long long)p.n * p.h * p.w * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c4 = (int)(i % C4);
+    const int c = c4 * 4;
+    long long r = i / C4;
+    const int ix = (int)(r % p.w); r /= p.w;
+    const int iy = (int)(r % p.h);
+    const int n = (int)(r / p.h);
+    const int oy0 = ceil_div_pos(iy + p.pad - p.kh + 1, p.stride), oy1 = min(p.oh - 1, (iy + p.pad) / p.stride);
+    const int ox0 = ceil_div_pos(ix + p.pad - p.kw + 1, p.stride), ox1 = min(p.ow - 1, (ix + p.pad) / p.stride);
+    float4 acc = make_float4(0, 0, 0, 0);
+    for (int oy = oy0; oy <= oy1; ++oy) {
+      for (int ox = ox0; ox <= ox1; ++ox) {
+        const int pos = (iy - (oy * p.stride - p.pad)) * p.kw + (ix - (ox * p.stride - p.pad));
+        const uchar4 q = *reinterpret_cast<const uchar4*>(idx + ((((long long)n * p.oh + oy) * p.ow + ox) * C4 + c4) * 4);
+        const float4 g = *reinterpret_cast<const float4*>(dy + n * p.ysn + oy * p.ysh + ox * p.ysw + c);
+        if (q.x == pos) acc.x += g.x;
+        if (q.y == pos) acc.y += g.y;
+        if (q.z == pos) acc.z += g.z;
+        if (q.w == pos) acc.w += g.w;
+      }
+    }
+    *reinterpret_cast<float4*>(dx + n * p.xsn + iy * p.xsh + ix * p.xsw + c) = acc;
+  }
+}
+
+unsigned char* g_argmax[64] = {nullptr};
+size_t g_argmax_bytes[64] = {0};
+unsigned char* argmax_scratch(size_t bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (g_argmax_bytes[dev] < bytes) {
+    if (g_argmax[dev]) cudaFree(g_argmax[dev]);
+    g_argmax[dev] = nullptr; g_argmax_bytes[dev] = 0;
+    const size_t want = bytes < (size_t(32) << 20) ? (size_t(32) << 20) : bytes;
+    if (cudaMalloc(reinterpret_cast<void**>(&g_argmax[dev]), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    g_argmax_bytes[dev] = want;
+  }
+  return g_argmax[dev];
+}
+
 // ------------------------------------------------------------------ softmax family
 __device__ __forceinline__ float block_max(float v, float* sh) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -328,6 +410,16 @@ int tsb_pool_bwd(int kind, const float* x, const float* y, const float* dy, floa
     return done();
   }
   const int grid = ew_grid((long long)n * h * w * (c / 4));
+  if (kind == 0 && kh * kw < 255) {
+    // overlapping windows: positions of the maxima first, then a gather per input pixel (one scratch
+    // buffer per device: pooling backward passes of one device must not overlap on different streams)
+    unsigned char* idx = argmax_scratch((size_t)n * oh * ow * c);
+    if (idx) {
+      pool_argmax<<<ew_grid((long long)n * oh * ow * (c / 4)), 256, 0, st>>>(x, idx, p);
+      pool_bwd_from_argmax<<<grid, 256, 0, st>>>(idx, dy, dx, p);
+      return done();
+    }
+  }
   if (kind == 0) pool_bwd<0><<<grid, 256, 0, st>>>(x, y, dy, dx, p);
   else pool_bwd<1><<<grid, 256, 0, st>>>(x, y, dy, dx, p);
   return done();

@@ -6,7 +6,7 @@ does not ship (``microopExecutor``, ``capuchinExecutor``)."""
 from ..graph import Node, Op, gradients, find_topo_sort, find_topo_sort2, sum_node_list, broadcast_rule
 from ..ops.elementwise import (add_op, addbyconst_op, mul_op, mul_byconst_op, div_op, div_const_op,
                                opposite_op, sqrt_op, rsqrt_op, sigmoid_op, tanh_op, relu_op,
-                               relu_gradient_op, where_op)
+                               relu_gradient_op, where_op, add_relu_op, relu_out_gradient_op)
 from ..ops.linalg import matmul_op, batch_matmul_op, csrmv_op, csrmm_op
 from ..ops.conv import (conv2d_op, conv2d_gradient_of_data_op, conv2d_gradient_of_filter_op,
                         conv2d_broadcastto_op, conv2d_reducesum_op)

@@ -23,7 +23,7 @@ def bottleneck(p, x, cin, mid, stride, name):
     y = conv_bn(p, y, mid, cout, 1, 1, 0, name + "_c", relu=False)
     if stride != 1 or cin != cout:
         x = conv_bn(p, x, cin, cout, 1, stride, 0, name + "_proj", relu=False)
-    return ad.relu_op(ad.add_op(x, y)), cout
+    return ad.add_relu_op(x, y), cout
 
 
 def resnet(num_layers=50, num_classes=1000, image=224, width_div=1, seed=123):

@@ -19,7 +19,7 @@ from .. import _base
 (UN_COPY, UN_RELU, UN_SIGMOID, UN_TANH, UN_SQRT, UN_RSQRT, UN_NEG, UN_ADDC, UN_MULC, UN_CDIV,
  UN_FILL) = range(11)
 # binary codes
-BIN_ADD, BIN_MUL, BIN_DIV, BIN_RELU_GRAD, BIN_SUB = range(5)
+BIN_ADD, BIN_MUL, BIN_DIV, BIN_RELU_GRAD, BIN_SUB, BIN_ADD_RELU, BIN_RELU_GRAD_OUT = range(7)
 
 MAX_DIMS = 8
 _I64x8 = c_int64 * MAX_DIMS

@@ -96,6 +96,32 @@ class ReluGradientOp(_Binary):
         raise NotImplementedError("second-order gradient of relu")
 
 
+class AddReluOp(_Binary):
+    """``relu(a + b)`` in one pass (the residual join of a ResNet block).  No counterpart in the
+    reference, which runs ``AddOp`` then ``ReluOp`` (``examples/imagenet_resnet.py``): two extra passes
+    over the tensor forward, and a backward that needs the pre-activation.  Here the backward masks
+    by the OUTPUT (positive output = positive pre-activation) and both inputs share one gradient node."""
+    name, gpu_code, cheap = "AddRelu", G.BIN_ADD_RELU, True
+
+    def _np(self, a, b):
+        return np.maximum(a + b, 0)
+
+    def gradient(self, node, g):
+        r = relu_out_gradient_op(node, g)
+        return [r, r]
+
+
+class ReluOutGradientOp(_Binary):
+    """``g`` where the ReLU output ``y`` is positive, else 0."""
+    name, gpu_code, cheap = "ReluOutGradient", G.BIN_RELU_GRAD_OUT, True
+
+    def _np(self, y, g):
+        return np.where(y > 0, g, 0).astype(np.float32)
+
+    def gradient(self, node, g):
+        raise NotImplementedError("second-order gradient of relu")
+
+
 class _Unary(Op):
     gpu_code = 0
     cheap = True
@@ -237,6 +263,7 @@ class WhereOp(Op):
 
 
 _add, _mul, _div, _relu_grad = AddOp(), MulOp(), DivOp(), ReluGradientOp()
+_add_relu, _relu_out_grad = AddReluOp(), ReluOutGradientOp()
 _addc, _mulc, _divc = AddConstOp(), MulConstOp(), DivConstOp()
 _neg, _sqrt, _rsqrt, _sig, _tanh, _relu, _where = (OppositeOp(), SqrtOp(), RsqrtOp(), SigmoidOp(),
                                                    TanhOp(), ReluOp(), WhereOp())
@@ -292,6 +319,14 @@ def relu_op(node):
 
 def relu_gradient_op(node, grad_node):
     return _relu_grad(node, grad_node)
+
+
+def add_relu_op(node_A, node_B):
+    return _add_relu(node_A, node_B)
+
+
+def relu_out_gradient_op(out_node, grad_node):
+    return _relu_out_grad(out_node, grad_node)
 
 
 def where_op(cond, node_A, node_B):
