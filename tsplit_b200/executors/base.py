@@ -36,8 +36,35 @@ class FeedStager(object):
     def __init__(self, ctx):
         self.ctx = ctx
         self.slots = {}
+        self.staged = {}          # node -> {id(value): (value object, device array, event)} copied ahead of its step
+                                  # (at most two per node: one per device buffer)
+        self._flip = {}           # node -> which of the two device buffers the next copy uses
+
+    def stage(self, node, value, copy_stream, channels_last=None):
+        """Copy the NEXT step's feed while the current step computes: the copy goes to the other of
+        two device buffers on ``copy_stream`` and leaves an event; ``put`` with the same value
+        object later only waits for that event.  The caller must not modify ``value`` in between."""
+        if not (ndarray.is_gpu_ctx(self.ctx) and self.ctx.device_type == 2):
+            return
+        if isinstance(value, ndarray.NDArray) and value.ctx.device_type == self.ctx.device_type:
+            return
+        self._flip[node] = 1 - self._flip.get(node, 0)
+        dev = self._copy(("ahead", node, self._flip[node]), value, copy_stream, channels_last)
+        ev = Event(self.ctx)
+        ev.record(copy_stream)
+        self.staged.setdefault(node, {})[id(value)] = (value, dev, ev)
 
     def put(self, node, value, stream, channels_last=None):
+        ahead = self.staged.get(node, {}).pop(id(value), None)
+        if ahead is not None and ahead[0] is value:
+            stream.wait_event(ahead[2])
+            return ahead[1]
+        if isinstance(value, ndarray.NDArray) and (
+                value.ctx == self.ctx or value.ctx.device_type == self.ctx.device_type):
+            return value
+        return self._copy(node, value, stream, channels_last)
+
+    def _copy(self, node, value, stream, channels_last=None):
         user_pinned = None
         if isinstance(value, ndarray.NDArray):
             if value.ctx == self.ctx or value.ctx.device_type == self.ctx.device_type:
@@ -155,6 +182,22 @@ class Executor(object):
                 assert isinstance(value, (np.ndarray, ndarray.NDArray)), "feed_dict value type not supported"
                 vals[node] = self.stager.put(node, value, self.stream, self._feed_layout(node, value))
         return vals
+
+    def prefetch_feeds(self, feed_dict):
+        """Start the host -> device copies of the NEXT step's feeds now, on the copy stream, so that
+        they overlap the step that is about to run: ``ex.prefetch_feeds(next); ex.run(cur)``.  The
+        next ``run`` must be given the same value objects, unmodified.  No-op off the GPU."""
+        if not self.on_device or self.stager is None:
+            return
+        stream = getattr(self, "h2d_stream", None)
+        if stream is None:
+            stream = self.__dict__.get("_prefetch_stream")
+            if stream is None:
+                stream = self._prefetch_stream = create_stream_handle(self.ctx)
+        for node, value in feed_dict.items():
+            if isinstance(value, ndarray.ND_Sparse_Array):
+                continue
+            self.stager.stage(node, value, stream, self._feed_layout(node, value))
 
     def _feed_layout(self, node, value):
         """Channels-last only for 4-D feeds consumed by an image operator."""
