@@ -52,6 +52,8 @@ def parse_args():
     p.add_argument("--max-batch", type=int, default=256, help="upper bound of the max-batch search")
     p.add_argument("--host-link-gbs", type=float, default=45.0)
     p.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    p.add_argument("--graph", type=int, default=0,
+                   help="1 = replay the step from a CUDA graph when the plan has no swaps (single GPU)")
     p.add_argument("--plan-frac", type=float, default=0.9,
                    help="fraction of the cap the planner may fill (the rest absorbs fragmentation)")
     return p.parse_args()
@@ -124,11 +126,12 @@ def make_executor(args, model, train_op, ctx):
     from tsplit_b200 import gpu_ops as ad
     nodes = [model.loss, train_op]
     pol = args.policy
+    graph = bool(getattr(args, "graph", 0))
     if pol == "base":
-        return ad.MemoryExecutor(nodes, ctx=ctx)
+        return ad.MemoryExecutor(nodes, ctx=ctx, use_graph=graph)
     if pol == "tsplit":
         return ad.microopExecutor(nodes, ctx=ctx, host_link_gbs=args.host_link_gbs,
-                                  budget_bytes=int(args.cap_gib * 2**30 * args.plan_frac))
+                                  budget_bytes=int(args.cap_gib * 2**30 * args.plan_frac), use_graph=graph)
     if pol in ("vdnnall", "vdnnconv"):
         return ad.vdnnExecutor(nodes, ctx=ctx, policy=pol[4:])
     if pol.startswith("recompute"):

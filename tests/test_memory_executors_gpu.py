@@ -72,3 +72,24 @@ def test_training_with_graph_replay_matches_eager():
         losses[use_graph] = [float(ex.run({m.X: xd, m.y_: yd})[0].asnumpy()[0]) for _ in range(5)]
     assert_close(np.array(losses[True]), np.array(losses[False]), rtol=5e-3)
     assert losses[False][-1] < losses[False][0]
+
+
+def test_graph_replay_of_a_swap_free_step_matches_eager():
+    """The engine replays a step without swaps from a CUDA graph after two eager steps; the losses
+    of six training steps equal those of the eager executor step by step."""
+    ctx = ndarray.gpu(0)
+    outs = []
+    for use_graph in (False, True):
+        m = net()
+        opt = optimizer.MomentumOptimizer(learning_rate=0.01, momentum=0.9, ctx=ctx)
+        train = opt.minimize(m.loss)
+        x, y = m.synthetic_batch(16, seed=2)
+        with use_pool(ctx, 4 << 30):
+            ex = ad.MemoryExecutor([m.loss, train], ctx=ctx, use_graph=use_graph)
+            vals = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0].reshape(-1)[0])
+                    for _ in range(6)]
+        outs.append(vals)
+        if use_graph:
+            assert ex._step_graph is not None, "the step was not captured"
+    np.testing.assert_allclose(outs[1], outs[0], rtol=1e-5)
+    assert outs[0][-1] < outs[0][0]

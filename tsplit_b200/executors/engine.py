@@ -30,6 +30,7 @@ from .. import ndarray
 from ..ndarray import OutOfHBMBudget
 from ..stream import create_stream_handle, Event
 from ..ops.misc import PlaceholderOp
+from ..ops import _gpu as G
 from .base import Executor
 
 KEEP, SWAP, DROP = 0, 1, 2
@@ -49,8 +50,13 @@ class MemoryExecutor(Executor):
     lazy_evict = False           # swap-class tensors stay resident until memory is needed (LRU)
     recompute_mode = "speed"     # "speed": keep rematerialised intermediates; "memory": free them at once
 
-    def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None, trace=None):
+    def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None, trace=None,
+                 use_graph=False):
         Executor.__init__(self, eval_node_list, ctx=ctx, policy=policy)
+        # CUDA-graph replay of the whole step (plans without swaps only, see _graph_eligible)
+        self.use_graph = bool(use_graph) and self.on_device
+        self._step_graph = None
+        self._graph_steps_seen = 0
         assert ctx is not None and ndarray.is_gpu_ctx(ctx), "memory executors need a (simulated) GPU context"
         if streams is None:
             streams = [self.stream, create_stream_handle(ctx), create_stream_handle(ctx)]
@@ -383,6 +389,11 @@ class MemoryExecutor(Executor):
             self.feed_shapes = feed_shapes
             self.infer_shape(feed_shapes)
             self.memory_plan(feed_shapes)
+        if self.use_graph and self._graph_eligible():
+            return self._run_graphed(node_to_val, convert_to_numpy_ret_vals)
+        return self._run_with_values(node_to_val, convert_to_numpy_ret_vals)
+
+    def _run_with_values(self, node_to_val, convert_to_numpy_ret_vals):
         self._reset_state()
         for n, v in node_to_val.items():
             self.arr[n] = v
@@ -403,6 +414,73 @@ class MemoryExecutor(Executor):
                 self._release(n, final=True)
         self._reap(True)
         return outs
+
+    # ------------------------------------------------------------------ CUDA-graph replay
+    def _graph_eligible(self):
+        """A step can be replayed from a captured graph when its launch list is fixed: no swaps (their
+        event queries and host-side frees cannot be captured), no lazily evicted cache, no trace, no
+        collective (its epoch counter is a kernel argument), no optimizer or op whose kernel arguments
+        change from step to step (Adam's bias correction, dropout seeds)."""
+        ok = self.__dict__.get("_graph_ok")
+        if ok is None:
+            ok = self.trace is None and not self.lazy_evict
+            ok = ok and not any(c == SWAP for c in getattr(self, "cls", {}).values())
+            for n in self.topo_order:
+                if n.op.name in ("Dropout", "DropoutGradient"):
+                    ok = False
+                if n.op.name == "Optimizer":
+                    opt = n.attrs.get("optimizer")
+                    if opt is None or getattr(opt, "kind", 4) == 4 or getattr(opt, "communicator", None) is not None:
+                        ok = False
+            self._graph_ok = bool(ok)
+        return self._graph_ok
+
+    def _run_graphed(self, node_to_val, convert):
+        """Two eager steps (they size every library scratch buffer, tensor map and side buffer and let
+        the pool settle), then one capture, then replays.  Feeds are copied into fixed device arrays
+        first, because staged feeds alternate between two buffers."""
+        from ..runtime import cudagraph
+        if self._step_graph is None and self._graph_steps_seen < 2:
+            self._graph_steps_seen += 1
+            return self._run_eager_step(node_to_val, convert)
+        if self._step_graph is None:
+            self._graph_feeds = {n: ndarray.empty(v.shape, self.ctx, use_pool=False,
+                                                  channels_last=v.is_channels_last() if len(v.shape) == 4 else None)
+                                 for n, v in node_to_val.items() if isinstance(v, ndarray.NDArray)}
+        fixed = dict(node_to_val)
+        for n, buf in self._graph_feeds.items():
+            G.copy(node_to_val[n], buf, self.stream)
+            fixed[n] = buf
+        if self._step_graph is None:
+            self._reset_state()
+            for n, v in fixed.items():
+                self.arr[n] = v
+            self.stream.sync()
+            try:
+                self._step_graph = cudagraph.capture(self.stream, self._execute)
+            except Exception:
+                # something in this step cannot be captured (an allocation path that synchronises, a
+                # library buffer that had to grow): stay on the eager path for good
+                self.use_graph = False
+                self._step_graph = None
+                return self._run_with_values(node_to_val, convert)
+            self._graph_outs = [self.arr.get(n) for n in self.eval_node_list]
+            for n in list(self.arr.keys()):
+                if n not in self.eval_node_list and not isinstance(n.op, PlaceholderOp) and n not in fixed:
+                    self._release(n, final=True)
+        self._step_graph.launch(self.stream)
+        self.stream.sync()
+        outs = self._graph_outs
+        if convert:
+            outs = [o.asnumpy() if isinstance(o, ndarray.NDArray) else o for o in outs]
+        return outs
+
+    def _run_eager_step(self, node_to_val, convert):
+        saved, self.use_graph = self.use_graph, False
+        try:
+            return self._run_with_values(node_to_val, convert)
+        finally:
+            self.use_graph = saved
 
     def _execute(self):
         order = self.topo_order
@@ -501,8 +579,8 @@ class MemoryExecutor(Executor):
                 self._release(node, final=True)
 
     # ------------------------------------------------------------------ cost model
-    TF32_FLOP_PER_MS = 3.0e11       # sustained tensor-core rate assumed by the static model
-    HBM_BYTES_PER_MS = 5.0e9
+    TF32_FLOP_PER_MS = 7.0e11       # sustained tensor-core rate of the wide-tile convolution / GEMM kernels
+    HBM_BYTES_PER_MS = 5.5e9        # what the batch-norm / pooling / elementwise passes reach
     LAUNCH_MS = 0.004
 
     def profile_ops(self):

@@ -68,9 +68,9 @@ class microopExecutor(MemoryExecutor):
     spill_on_pressure = True
 
     def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None,
-                 host_link_gbs=50.0, max_split=8, trace=None):
+                 host_link_gbs=50.0, max_split=8, trace=None, use_graph=False):
         MemoryExecutor.__init__(self, eval_node_list, ctx=ctx, streams=streams, policy=policy,
-                                budget_bytes=budget_bytes, trace=trace)
+                                budget_bytes=budget_bytes, trace=trace, use_graph=use_graph)
         self.host_link_gbs = float(host_link_gbs)
         self.max_split = int(max_split)
         self.plan_result = None
