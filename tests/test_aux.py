@@ -162,3 +162,17 @@ def test_micro_tensor_helpers():
     inp, out = ndarray.tensor_reuse((8, 4), (8, 4), pieces=4, overlap_pieces=3, ctx=ndarray.cpu(0))
     assert inp._holder.shape[0] == 32 + 8 * (4 - 3)       # output + one un-overlapped input piece
     assert inp.shape == (8, 4) and out.shape == (8, 4)
+
+
+def test_dropout_draws_a_new_mask_every_step_and_backward_reuses_it():
+    from tsplit_b200 import gpu_ops as ad
+    x = ad.Variable("x")
+    y = ad.dropout_op(x, 0.5, seed=11)
+    (gx,) = ad.gradients(ad.reduce_sum_op(y, [0, 1]), [x])
+    ex = ad.Executor([y, gx], ctx=None)
+    xv = np.ones((8, 64), np.float32)
+    y0, g0 = ex.run({x: xv})
+    y1, g1 = ex.run({x: xv})
+    assert np.array_equal(y0 != 0, g0 != 0) and np.array_equal(y1 != 0, g1 != 0)    # same mask within a step
+    assert not np.array_equal(y0 != 0, y1 != 0)                                     # a new one the next step
+    assert 0.3 < (y0 != 0).mean() < 0.7

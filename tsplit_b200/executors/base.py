@@ -226,7 +226,14 @@ class Executor(object):
         return arr.numpy_view() if isinstance(arr, ndarray.NDArray) else arr
 
     # -- run ---------------------------------------------------------------------
+    def _begin_step(self):
+        """Publish this executor's step index to the ops that draw per-step random numbers."""
+        from ..ops import misc
+        misc.STEP[0] = self.__dict__.get("_run_index", 0)
+        self._run_index = misc.STEP[0] + 1
+
     def run(self, feed_dict, convert_to_numpy_ret_vals=False):
+        self._begin_step()
         node_to_val = self._ingest(feed_dict)
         feed_shapes = {n: _shape_of(v) for n, v in node_to_val.items()}
         if feed_shapes != self.feed_shapes:
@@ -237,8 +244,8 @@ class Executor(object):
             self._graph = None
             self._graph_warm = False
 
-        if self.use_graph:
-            self._run_graph(node_to_val)
+        if self.use_graph and not any(n.op.name == "Dropout" for n in self.topo_order):
+            self._run_graph(node_to_val)          # (a captured step would replay one step's dropout masks)
         else:
             self._run_eager(node_to_val)
 

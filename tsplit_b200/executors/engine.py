@@ -383,6 +383,7 @@ class MemoryExecutor(Executor):
         self.plan()
 
     def run(self, feed_dict, convert_to_numpy_ret_vals=False):
+        self._begin_step()
         node_to_val = self._ingest(feed_dict)
         feed_shapes = {n: tuple(v.shape) for n, v in node_to_val.items()}
         if feed_shapes != self.feed_shapes:

@@ -201,9 +201,19 @@ def philox_like_mask(shape, keep_prob, seed):
     return (u < np.float32(keep_prob)).reshape(shape)
 
 
+#: index of the training step that is executing; executors set it at the start of ``run`` so that
+#: dropout draws a fresh mask every step while forward, recompute and backward of one step agree
+STEP = [0]
+
+
+def step_seed(node):
+    return (int(node.attrs["seed"]) + 0x632BE5AB * int(STEP[0])) & 0x7FFFFFFFFFFFFFFF
+
+
 class DropoutOp(Op):
     """``x * mask / keep_prob`` with a mask that is a pure function of
-    (node seed, element index), so forward, recompute and backward agree."""
+    (node seed, step index, element index), so forward, recompute and backward
+    of one step agree and every step draws a new mask."""
     name = "Dropout"
 
     def __call__(self, x, keep_prob, seed=None):
@@ -213,12 +223,12 @@ class DropoutOp(Op):
 
     def np_compute(self, node, iv):
         kp = node.attrs["keep_prob"]
-        m = philox_like_mask(iv[0].shape, kp, node.attrs["seed"])
+        m = philox_like_mask(iv[0].shape, kp, step_seed(node))
         return (iv[0] * m / kp).astype(np.float32)
 
     def gpu_compute(self, node, iv, out, stream):
         assert iv[0].is_dense() and iv[0].same_layout(out)
-        G.dropout(iv[0], out, node.attrs["keep_prob"], node.attrs["seed"], stream)
+        G.dropout(iv[0], out, node.attrs["keep_prob"], step_seed(node), stream)
 
     def gradient(self, node, g):
         return [dropout_gradient_op(g, node.attrs["keep_prob"], node)]
