@@ -93,3 +93,22 @@ def test_graph_replay_of_a_swap_free_step_matches_eager():
             assert ex._step_graph is not None, "the step was not captured"
     np.testing.assert_allclose(outs[1], outs[0], rtol=1e-5)
     assert outs[0][-1] < outs[0][0]
+
+
+def test_graph_replay_with_adam_keeps_the_bias_correction_in_step():
+    ctx = ndarray.gpu(0)
+    outs = []
+    for use_graph in (False, True):
+        m = net()
+        opt = optimizer.AdamOptimizer(learning_rate=0.001, ctx=ctx)
+        train = opt.minimize(m.loss)
+        x, y = m.synthetic_batch(16, seed=2)
+        with use_pool(ctx, 4 << 30):
+            ex = ad.MemoryExecutor([m.loss, train], ctx=ctx, use_graph=use_graph)
+            vals = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0].reshape(-1)[0])
+                    for _ in range(6)]
+        outs.append(vals)
+        assert opt.step_count == 6
+        if use_graph:
+            assert ex._step_graph is not None, "the step was not captured"
+    np.testing.assert_allclose(outs[1], outs[0], rtol=1e-4)

@@ -126,6 +126,7 @@ struct OptArgs {
   float* s2[MAX_TENSORS];
   long long n[MAX_TENSORS];
   float h[8];
+  const float* hdev;     // Adam only, may be null: {beta1^t, beta2^t} kept on the device (see tsb_adam_advance)
   int count;
 };
 
@@ -156,6 +157,10 @@ template <int KIND>
 __global__ void opt_kernel(const OptArgs a) {
   const int t = blockIdx.y;
   if (t >= a.count) return;
+  float hloc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) hloc[i] = a.h[i];
+  if (KIND == 4 && a.hdev) { hloc[3] = a.hdev[0]; hloc[4] = a.hdev[1]; }
   float* p = a.p[t];
   const float* g = a.g[t];
   float* s1 = a.s1[t];
@@ -174,26 +179,39 @@ __global__ void opt_kernel(const OptArgs a) {
     float4 v1 = make_float4(0, 0, 0, 0), v2 = make_float4(0, 0, 0, 0);
     if (KIND >= 1) v1 = reinterpret_cast<float4*>(s1)[i];
     if (KIND == 4) v2 = reinterpret_cast<float4*>(s2)[i];
-    opt_one<KIND>(pv.x, gv.x, v1.x, v2.x, a.h);
-    opt_one<KIND>(pv.y, gv.y, v1.y, v2.y, a.h);
-    opt_one<KIND>(pv.z, gv.z, v1.z, v2.z, a.h);
-    opt_one<KIND>(pv.w, gv.w, v1.w, v2.w, a.h);
+    opt_one<KIND>(pv.x, gv.x, v1.x, v2.x, hloc);
+    opt_one<KIND>(pv.y, gv.y, v1.y, v2.y, hloc);
+    opt_one<KIND>(pv.z, gv.z, v1.z, v2.z, hloc);
+    opt_one<KIND>(pv.w, gv.w, v1.w, v2.w, hloc);
     reinterpret_cast<float4*>(p)[i] = pv;
     if (KIND >= 1) reinterpret_cast<float4*>(s1)[i] = v1;
     if (KIND == 4) reinterpret_cast<float4*>(s2)[i] = v2;
   }
   for (long long i = n4 * 4 + tid; i < n; i += nthreads) {
     float pv = p[i], v1 = (KIND >= 1) ? s1[i] : 0.f, v2 = (KIND == 4) ? s2[i] : 0.f;
-    opt_one<KIND>(pv, g[i], v1, v2, a.h);
+    opt_one<KIND>(pv, g[i], v1, v2, hloc);
     p[i] = pv;
     if (KIND >= 1) s1[i] = v1;
     if (KIND == 4) s2[i] = v2;
   }
 }
 
+// Adam's bias-correction powers live on the device so that a captured step (CUDA graph) advances
+// them by itself: one thread multiplies {beta1^t, beta2^t} by {beta1, beta2} before the update.
+__global__ void adam_advance_kernel(float* hdev, float b1, float b2) {
+  hdev[0] *= b1;
+  hdev[1] *= b2;
+}
+
 }  // namespace
 
 extern "C" {
+
+int tsb_adam_advance(float* hdev, float b1, float b2, void* stream) {
+  if (!hdev) return TSB_ERR_ARG;
+  adam_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(hdev, b1, b2);
+  return done();
+}
 
 int tsb_one_hot(const float* idx, float* y, long long n, long long k, void* stream) {
   if (n <= 0 || k <= 0) return TSB_ERR_ARG;
@@ -239,11 +257,21 @@ int tsb_csrmm(const float* vals, const float* rowptr, const float* colidx, long 
   return done();
 }
 
+int tsb_optimizer_step_dev(int kind, int count, float** params, const float** grads, float** slot1, float** slot2,
+                           const long long* sizes, const float* hyper, const float* hyper_dev, void* stream);
+
 int tsb_optimizer_step(int kind, int count, float** params, const float** grads, float** slot1, float** slot2,
                        const long long* sizes, const float* hyper, void* stream) {
+  return tsb_optimizer_step_dev(kind, count, params, grads, slot1, slot2, sizes, hyper, nullptr, stream);
+}
+
+// hyper_dev (Adam, optional): device array {beta1^t, beta2^t} that overrides hyper[3], hyper[4]
+int tsb_optimizer_step_dev(int kind, int count, float** params, const float** grads, float** slot1, float** slot2,
+                           const long long* sizes, const float* hyper, const float* hyper_dev, void* stream) {
   if (count <= 0 || count > MAX_TENSORS || kind < 0 || kind > 4) return TSB_ERR_ARG;
   OptArgs a;
   a.count = count;
+  a.hdev = hyper_dev;
   long long biggest = 0;
   for (int i = 0; i < count; ++i) {
     a.p[i] = params[i]; a.g[i] = grads[i];

@@ -420,8 +420,8 @@ class MemoryExecutor(Executor):
     def _graph_eligible(self):
         """A step can be replayed from a captured graph when its launch list is fixed: no swaps (their
         event queries and host-side frees cannot be captured), no lazily evicted cache, no trace, no
-        collective (its epoch counter is a kernel argument), no optimizer or op whose kernel arguments
-        change from step to step (Adam's bias correction, dropout seeds)."""
+        collective (its epoch counter is a kernel argument), no op whose kernel arguments change from
+        step to step (dropout seeds; Adam's bias-correction powers live on the device for this reason)."""
         ok = self.__dict__.get("_graph_ok")
         if ok is None:
             ok = self.trace is None and not self.lazy_evict
@@ -431,7 +431,7 @@ class MemoryExecutor(Executor):
                     ok = False
                 if n.op.name == "Optimizer":
                     opt = n.attrs.get("optimizer")
-                    if opt is None or getattr(opt, "kind", 4) == 4 or getattr(opt, "communicator", None) is not None:
+                    if opt is None or getattr(opt, "communicator", None) is not None:
                         ok = False
             self._graph_ok = bool(ok)
         return self._graph_ok
@@ -465,12 +465,22 @@ class MemoryExecutor(Executor):
                 self.use_graph = False
                 self._step_graph = None
                 return self._run_with_values(node_to_val, convert)
+            self._just_captured = True          # this step's Python side (optimizer bookkeeping) ran during capture
             self._graph_outs = [self.arr.get(n) for n in self.eval_node_list]
             for n in list(self.arr.keys()):
                 if n not in self.eval_node_list and not isinstance(n.op, PlaceholderOp) and n not in fixed:
                     self._release(n, final=True)
+        captured_now = self.__dict__.pop("_just_captured", False)
         self._step_graph.launch(self.stream)
         self.stream.sync()
+        if not captured_now:
+            # the optimizer's Python side did not run: keep its host-side step bookkeeping (checkpoints) in step.
+            # Hyper-parameters are kernel arguments of the captured launch: a changed learning rate needs a new capture.
+            for n in self.topo_order:
+                if n.op.name == "Optimizer":
+                    opt = n.attrs["optimizer"]
+                    opt.step_count += 1
+                    opt._begin_step()
         outs = self._graph_outs
         if convert:
             outs = [o.asnumpy() if isinstance(o, ndarray.NDArray) else o for o in outs]

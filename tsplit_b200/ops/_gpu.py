@@ -454,7 +454,11 @@ def csrmm(vals, rowptr, colidx, nrow, ncol, dense, out, trans_a, ncols_dense, st
 
 
 # -- optimizers (multi-tensor) ----------------------------------------------------------
-def optimizer_step(kind, params, grads, slot1, slot2, hyper, stream):
+def adam_advance(hdev, beta1, beta2, stream):
+    _check(lib().tsb_adam_advance(_p(hdev), c_float(beta1), c_float(beta2), _s(stream)), "adam_advance")
+
+
+def optimizer_step(kind, params, grads, slot1, slot2, hyper, stream, hyper_dev=None):
     """One launch per chunk of up to 64 tensors.  kind: 0 sgd, 1 momentum,
     2 nesterov, 3 adagrad, 4 adam.  ``hyper`` is up to 6 floats."""
     n = len(params)
@@ -462,9 +466,10 @@ def optimizer_step(kind, params, grads, slot1, slot2, hyper, stream):
     SZ = c_int64 * n
     z = [None] * n
     hv = (c_float * 8)(*(list(hyper) + [0.0] * (8 - len(hyper))))
-    rc = lib().tsb_optimizer_step(
+    rc = lib().tsb_optimizer_step_dev(
         c_int(kind), c_int(n), PT(*[p.ptr for p in params]), PT(*[g.ptr for g in grads]),
         PT(*[(s.ptr if s is not None else None) for s in (slot1 or z)]),
         PT(*[(s.ptr if s is not None else None) for s in (slot2 or z)]),
-        SZ(*[_numel(p.shape) for p in params]), hv, _s(stream))
+        SZ(*[_numel(p.shape) for p in params]), hv, c_void_p(hyper_dev.ptr if hyper_dev is not None else None),
+        _s(stream))
     _check(rc, "optimizer_step")

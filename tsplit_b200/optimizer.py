@@ -102,11 +102,12 @@ class Optimizer(object):
         params = self.params
         if on_device and not use_numpy:
             s1, s2 = self.slots()
+            hdev = self._device_hyper(stream_handle)
             for lo in range(0, len(grads), 64):
                 hi = lo + 64
                 G.optimizer_step(self.kind, params[lo:hi], grads[lo:hi],
                                  s1[lo:hi] if s1 else None, s2[lo:hi] if s2 else None,
-                                 self.hyper(), stream_handle)
+                                 self.hyper(), stream_handle, hyper_dev=hdev)
             return
         for i, g in enumerate(grads):
             p = params[i]
@@ -116,6 +117,10 @@ class Optimizer(object):
 
     def _begin_step(self):
         pass
+
+    def _device_hyper(self, stream):
+        """Device-resident per-step scalars of the update kernel (Adam); None otherwise."""
+        return None
 
     def _np(self, arr):
         return arr.numpy_view() if isinstance(arr, ndarray.NDArray) else arr
@@ -263,6 +268,18 @@ class AdamOptimizer(Optimizer):
     def _restore_step(self):
         self.beta1_t = self.beta1 ** self.step_count
         self.beta2_t = self.beta2 ** self.step_count
+        self._bt_dev = None                  # rebuilt from the restored powers on the next device step
+
+    def _device_hyper(self, stream):
+        """{beta1^t, beta2^t} on the device, advanced by a one-thread kernel every step, so that a step
+        captured in a CUDA graph keeps the right bias correction when it is replayed."""
+        bt = getattr(self, "_bt_dev", None)
+        if bt is None:
+            prev1 = self.beta1_t / self.beta1      # _begin_step already advanced the host copies
+            prev2 = self.beta2_t / self.beta2
+            bt = self._bt_dev = ndarray.array(np.array([prev1, prev2], np.float32), self.ctx, use_pool=False)
+        G.adam_advance(bt, self.beta1, self.beta2, stream)
+        return bt
 
     def hyper(self):
         return [self.learning_rate, self.beta1, self.beta2, self.beta1_t, self.beta2_t, self.epsilon]
