@@ -20,9 +20,13 @@ POLICIES = ["None", "base", "vdnnconv", "vdnnall", "superneurons", "recompute_me
             "capuchin", "simulator", "profiler", "planner", "tsplit"]
 
 
+USE_GRAPH = [False]       # set by ``--graph 1``: replay fixed (swap-free) steps from a CUDA graph
+
+
 def make_executor(policy, nodes, ctx):
+    g = USE_GRAPH[0]
     if policy in ("None", "base"):
-        return ad.Executor(nodes, ctx=ctx)
+        return ad.Executor(nodes, ctx=ctx, use_graph=g)
     if policy == "vdnnconv":
         return ad.vdnnExecutor(nodes, ctx=ctx, policy="conv")
     if policy == "vdnnall":
@@ -30,9 +34,9 @@ def make_executor(policy, nodes, ctx):
     if policy == "superneurons":
         return ad.superNeuronsExecutor(nodes, ctx=ctx)
     if policy == "recompute_memory":
-        return ad.recomputeExecutor(nodes, ctx=ctx, policy="memory")
+        return ad.recomputeExecutor(nodes, ctx=ctx, policy="memory", use_graph=g)
     if policy == "recompute_speed":
-        return ad.recomputeExecutor(nodes, ctx=ctx, policy="speed")
+        return ad.recomputeExecutor(nodes, ctx=ctx, policy="speed", use_graph=g)
     if policy == "capuchin":
         return ad.capuchinExecutor(nodes, ctx=ctx)
     if policy == "simulator":
@@ -42,7 +46,7 @@ def make_executor(policy, nodes, ctx):
     if policy == "planner":
         return ad.microopPlanner(nodes, ctx=ctx)
     if policy == "tsplit":
-        return ad.microopExecutor(nodes, ctx=ctx)
+        return ad.microopExecutor(nodes, ctx=ctx, use_graph=g)
     raise NotImplementedError(policy)
 
 
@@ -86,9 +90,12 @@ def parse(description, extra=None):
     p.add_argument("-b", "--batch", type=int, default=0, help="single batch size (0 = sweep)")
     p.add_argument("--cap-gib", type=float, default=16.0, help="HBM budget of the activation pool")
     p.add_argument("--out", default=None, help="append results to this file")
+    p.add_argument("--graph", type=int, default=0, help="1 = replay swap-free steps from a CUDA graph")
     if extra:
         extra(p)
-    return p.parse_args()
+    args = p.parse_args()
+    USE_GRAPH[0] = bool(args.graph)
+    return args
 
 
 def with_pool(ctx, cap_gib):

@@ -75,8 +75,11 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
   return (float)(x >> 40) * (1.0f / 16777216.0f);
 }
 
+// step_dev (may be null): index of the training step, kept on the device by the executor so that a
+// step replayed from a CUDA graph still draws a new mask; the seed is mixed exactly as on the host.
 __global__ void dropout_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float keep,
-                               unsigned long long seed) {
+                               unsigned long long seed, const unsigned long long* __restrict__ step_dev) {
+  if (step_dev) seed = (seed + 0x632BE5ABull * *step_dev) & 0x7FFFFFFFFFFFFFFFull;
   const float inv = 1.f / keep;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
@@ -198,6 +201,8 @@ __global__ void opt_kernel(const OptArgs a) {
 
 // Adam's bias-correction powers live on the device so that a captured step (CUDA graph) advances
 // them by itself: one thread multiplies {beta1^t, beta2^t} by {beta1, beta2} before the update.
+__global__ void step_advance_kernel(unsigned long long* step_dev) { *step_dev += 1ull; }
+
 __global__ void adam_advance_kernel(float* hdev, float b1, float b2) {
   hdev[0] *= b1;
   hdev[1] *= b2;
@@ -234,10 +239,18 @@ int tsb_embedding_grad(const float* g, const float* idx, float* dtable, long lon
   return done();
 }
 
-int tsb_dropout(const float* x, float* y, long long n, float keep, unsigned long long seed, void* stream) {
+int tsb_dropout(const float* x, float* y, long long n, float keep, unsigned long long seed,
+                const unsigned long long* step_dev, void* stream) {
   if (n <= 0) return TSB_OK;
   if (!(keep > 0.f)) return TSB_ERR_ARG;
-  dropout_kernel<<<ew_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n, keep, seed);
+  dropout_kernel<<<ew_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n, keep, seed, step_dev);
+  return done();
+}
+
+// ++*step_dev on the stream (one thread): the executor's step counter, advanced at the start of a step
+int tsb_step_advance(unsigned long long* step_dev, void* stream) {
+  if (!step_dev) return TSB_ERR_ARG;
+  step_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(step_dev);
   return done();
 }
 

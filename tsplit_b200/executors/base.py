@@ -231,6 +231,20 @@ class Executor(object):
         from ..ops import misc
         misc.STEP[0] = self.__dict__.get("_run_index", 0)
         self._run_index = misc.STEP[0] + 1
+        if self.on_device:
+            # the same index on the device, advanced by a one-thread kernel at the start of every step
+            # (see _advance_device_step), so that a step replayed from a CUDA graph still moves on
+            if self.__dict__.get("_step_dev") is None:
+                self._step_dev = torch.full((1,), misc.STEP[0] - 1, dtype=torch.int64,
+                                            device=self.ctx.torch_device)
+            misc.STEP_DEV[0] = self._step_dev.data_ptr()
+        else:
+            misc.STEP_DEV[0] = 0
+
+    def _advance_device_step(self):
+        if self.on_device and self.__dict__.get("_step_dev") is not None:
+            from ..ops import _gpu as G
+            G.step_advance(self._step_dev.data_ptr(), self.stream)
 
     def run(self, feed_dict, convert_to_numpy_ret_vals=False):
         self._begin_step()
@@ -244,8 +258,8 @@ class Executor(object):
             self._graph = None
             self._graph_warm = False
 
-        if self.use_graph and not any(n.op.name == "Dropout" for n in self.topo_order):
-            self._run_graph(node_to_val)          # (a captured step would replay one step's dropout masks)
+        if self.use_graph:
+            self._run_graph(node_to_val)
         else:
             self._run_eager(node_to_val)
 
@@ -257,6 +271,7 @@ class Executor(object):
         return outs
 
     def _run_eager(self, node_to_val):
+        self._advance_device_step()
         host_like = not self.on_device
         for node in self.topo_order:
             if node in node_to_val:

@@ -421,14 +421,12 @@ class MemoryExecutor(Executor):
         """A step can be replayed from a captured graph when its launch list is fixed: no swaps (their
         event queries and host-side frees cannot be captured), no lazily evicted cache, no trace, no
         collective (its epoch counter is a kernel argument), no op whose kernel arguments change from
-        step to step (dropout seeds; Adam's bias-correction powers live on the device for this reason)."""
+        step to step (the step index of dropout and Adam's bias-correction powers live on the device for this reason)."""
         ok = self.__dict__.get("_graph_ok")
         if ok is None:
             ok = self.trace is None and not self.lazy_evict
             ok = ok and not any(c == SWAP for c in getattr(self, "cls", {}).values())
             for n in self.topo_order:
-                if n.op.name in ("Dropout", "DropoutGradient"):
-                    ok = False
                 if n.op.name == "Optimizer":
                     opt = n.attrs.get("optimizer")
                     if opt is None or getattr(opt, "communicator", None) is not None:
@@ -494,6 +492,7 @@ class MemoryExecutor(Executor):
             self.use_graph = saved
 
     def _execute(self):
+        self._advance_device_step()
         order = self.topo_order
         self._cursor = 0
         for idx, node in enumerate(order):

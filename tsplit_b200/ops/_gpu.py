@@ -199,9 +199,14 @@ def embedding_grad(g, idx, dtable, stream):
            "embedding_grad")
 
 
-def dropout(x, y, keep_prob, seed, stream):
+def dropout(x, y, keep_prob, seed, stream, step_dev=0):
+    """``step_dev``: device address of the executor's step counter (0 = ``seed`` is already step-mixed)."""
     _check(lib().tsb_dropout(_p(x), _p(y), c_int64(_numel(x.shape)), c_float(keep_prob),
-                             ctypes.c_uint64(seed), _s(stream)), "dropout")
+                             ctypes.c_uint64(seed), c_void_p(step_dev or None), _s(stream)), "dropout")
+
+
+def step_advance(step_dev, stream):
+    _check(lib().tsb_step_advance(c_void_p(step_dev), _s(stream)), "step_advance")
 
 
 # -- normalisation ------------------------------------------------------------

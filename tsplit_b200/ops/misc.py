@@ -204,6 +204,8 @@ def philox_like_mask(shape, keep_prob, seed):
 #: index of the training step that is executing; executors set it at the start of ``run`` so that
 #: dropout draws a fresh mask every step while forward, recompute and backward of one step agree
 STEP = [0]
+#: device address of the running executor's step counter (0 = none: the host index above is used)
+STEP_DEV = [0]
 
 
 def step_seed(node):
@@ -228,7 +230,10 @@ class DropoutOp(Op):
 
     def gpu_compute(self, node, iv, out, stream):
         assert iv[0].is_dense() and iv[0].same_layout(out)
-        G.dropout(iv[0], out, node.attrs["keep_prob"], step_seed(node), stream)
+        if STEP_DEV[0]:
+            G.dropout(iv[0], out, node.attrs["keep_prob"], int(node.attrs["seed"]), stream, step_dev=STEP_DEV[0])
+        else:
+            G.dropout(iv[0], out, node.attrs["keep_prob"], step_seed(node), stream)
 
     def gradient(self, node, g):
         return [dropout_gradient_op(g, node.attrs["keep_prob"], node)]
