@@ -112,3 +112,37 @@ def test_graph_replay_with_adam_keeps_the_bias_correction_in_step():
         if use_graph:
             assert ex._step_graph is not None, "the step was not captured"
     np.testing.assert_allclose(outs[1], outs[0], rtol=1e-4)
+
+
+def test_prefetched_pinned_feeds_give_the_same_steps():
+    """``prefetch_feeds`` copies the next step's pinned host arrays on the copy stream into the second
+    device buffer; results equal those of feeding the same arrays step by step."""
+    import torch
+    ctx = ndarray.gpu(0)
+    batches = []
+    m0 = net()
+    for seed in (2, 9):
+        x, y = m0.synthetic_batch(16, seed=seed)
+        xp = ndarray.empty(x.shape, ndarray.cpu(0), pinned=True)
+        yp = ndarray.empty(y.shape, ndarray.cpu(0), pinned=True)
+        xp.t.copy_(torch.from_numpy(x))
+        yp.t.copy_(torch.from_numpy(y))
+        batches.append((xp, yp))
+    outs = []
+    for ahead in (False, True):
+        m = net()
+        opt = optimizer.MomentumOptimizer(learning_rate=0.01, momentum=0.9, ctx=ctx)
+        train = opt.minimize(m.loss)
+        with use_pool(ctx, 4 << 30):
+            ex = ad.MemoryExecutor([m.loss, train], ctx=ctx)
+            feeds = [{m.X: b[0], m.y_: b[1]} for b in batches]
+            vals = []
+            if ahead:
+                ex.prefetch_feeds(feeds[0])
+            for i in range(5):
+                if ahead and i + 1 < 5:
+                    ex.prefetch_feeds(feeds[(i + 1) % 2])
+                vals.append(float(ex.run(feeds[i % 2], convert_to_numpy_ret_vals=True)[0].reshape(-1)[0]))
+        outs.append(vals)
+    np.testing.assert_allclose(outs[1], outs[0], rtol=1e-5)
+    assert abs(outs[0][0] - outs[0][1]) > 1e-6        # the two batches really differ
