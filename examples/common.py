@@ -56,10 +56,14 @@ def default_ctx():
 
 
 def timed_run(executor, feed, iters=3):
-    """One warm-up run, then ``iters`` timed runs; seconds per iteration."""
+    """Warm-up (one run; three with ``--graph``, whose capture happens on the third), then ``iters``
+    timed runs; seconds per iteration."""
     out = executor.run(feed)
     if not isinstance(out, list):
         return out
+    if USE_GRAPH[0]:
+        executor.run(feed)
+        executor.run(feed)
     t0 = time.time()
     for _ in range(iters):
         executor.run(feed)
