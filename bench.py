@@ -150,7 +150,9 @@ def find_max_batch(args, model, train_op, ctx, cap_bytes):
         return args.max_batch
 
     def fits(b):
-        sim = ad.microopOptimizer(nodes, ctx=ctx, budget_bytes=int(cap_bytes * args.plan_frac),
+        # 4 % below the executor's own planning budget: a plan whose peak touches the budget tends to
+        # need an unplanned spill at run time (fragmentation), which the warm-up check would then reject
+        sim = ad.microopOptimizer(nodes, ctx=ctx, budget_bytes=int(cap_bytes * args.plan_frac * 0.96),
                                   host_link_gbs=args.host_link_gbs)
         x = np.empty((b,) + model.input_shape, dtype=np.float32)
         y = np.empty((b, model.num_classes), dtype=np.float32)
@@ -209,24 +211,46 @@ def main():
         batch = int(t.item())
     assert batch > 0, "no batch fits the cap"
 
-    pool = MemoryPool(ctx, cap_bytes)
-    ndarray.set_pool(ctx, pool)
-    ex = make_executor(args, model, train_op, ctx)
-
-    x_np, y_np = model.synthetic_batch(batch, seed=rank)
-    x_dev = ndarray.array(x_np, ctx, use_pool=False)
-    y_dev = ndarray.array(y_np, ctx, use_pool=False)
-    feed_dev = {model.X: x_dev, model.y_: y_dev}
-    feed_np = {model.X: x_np, model.y_: y_np}
-
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (also builds the plan, tensor maps, side buffers)
-    for _ in range(max(args.warmup, 3)):
-        loss = ex.run(feed_dev)[0]
+    # ---- warm-up (also builds the plan, tensor maps, side buffers).  A batch chosen by the planner's
+    # simulator is then checked against reality: if the steps needed an unplanned spill, a pool
+    # compaction or an on-demand swap-in (fragmentation the simulator does not model), the batch is
+    # stepped down and the executor rebuilt, so that the timed steps run the plan and nothing else.
+    attempts = 0
+    while True:
+        pool = MemoryPool(ctx, cap_bytes)          # a fresh arena per attempt: an aborted step may leave blocks behind
+        ndarray.set_pool(ctx, pool)
+        ex = make_executor(args, model, train_op, ctx)
+        x_np, y_np = model.synthetic_batch(batch, seed=rank)
+        x_dev = ndarray.array(x_np, ctx, use_pool=False)
+        y_dev = ndarray.array(y_np, ctx, use_pool=False)
+        feed_dev = {model.X: x_dev, model.y_: y_dev}
+        feed_np = {model.X: x_np, model.y_: y_np}
+        unplanned = 0
+        try:
+            for _ in range(max(args.warmup, 3)):
+                loss = ex.run(feed_dev)[0]
+            if args.policy == "tsplit":
+                st_ = ex.stats
+                unplanned = int(st_.get("evictions", 0)) + int(st_.get("on_demand_swapins", 0)) + \
+                    int(st_.get("compactions", 0))
+        except ndarray.OutOfHBMBudget:
+            if args.batch:
+                raise
+            unplanned = 1
+        if dist is not None:
+            t = torch.tensor([unplanned], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            unplanned = int(t.item())
+        if not unplanned or args.batch or attempts >= 6 or batch <= 8:
+            break
+        attempts += 1
+        batch = max(8, (int(batch * 0.94) // 8) * 8)
+        del ex, x_dev, y_dev, feed_dev
     barrier()
 
     # ---- device-timed region
