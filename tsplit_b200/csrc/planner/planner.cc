@@ -24,6 +24,7 @@
 #include <cstdint>
 #include <cstring>
 #include <limits>
+#include <utility>
 #include <vector>
 
 namespace {
@@ -328,6 +329,37 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
   }
   place_prefetch(g, cls, prefetch, min_trigger);
   r = simulate(g, cls, split, prefetch);
+  // The greedy loop takes the biggest savers first and usually overshoots: give tensors back while the
+  // plan still fits, the ones that cost the most step time first.
+  if (r.first_over < 0) {
+    std::vector<std::pair<double, int>> evicted;
+    for (int t = 0; t < n; ++t) {
+      if (cls[t] == KEEP) continue;
+      const double cost = cls[t] == DROP ? rebuild_ms(g, cls, t) : 2.0 * (double)out_bytes[t] / g.bw;
+      evicted.push_back({cost, t});
+    }
+    std::sort(evicted.begin(), evicted.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) {
+      return a.first > b.first;
+    });
+    for (auto& e : evicted) {
+      const int t = e.second, was = cls[t], was_split = split[t];
+      cls[t] = KEEP;
+      split[t] = 1;
+      place_prefetch(g, cls, prefetch, min_trigger);
+      Result trial = simulate(g, cls, split, prefetch);
+      // leave 5 % of the budget free: a plan whose peak touches the budget tends to need an unplanned
+      // spill at run time (the simulator does not model fragmentation)
+      if (trial.first_over < 0 && trial.time_ms <= r.time_ms + 1e-9 &&
+          (double)trial.peak <= 0.95 * (double)budget) {
+        r = trial;
+      } else {
+        cls[t] = was;
+        split[t] = was_split;
+      }
+    }
+    place_prefetch(g, cls, prefetch, min_trigger);
+    r = simulate(g, cls, split, prefetch);
+  }
   std::memcpy(cls_out, cls.data(), sizeof(int) * n);
   std::memcpy(split_out, split.data(), sizeof(int) * n);
   std::memcpy(prefetch_out, prefetch.data(), sizeof(int) * n);
