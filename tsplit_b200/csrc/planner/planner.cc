@@ -347,10 +347,10 @@ int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, cons
       split[t] = 1;
       place_prefetch(g, cls, prefetch, min_trigger);
       Result trial = simulate(g, cls, split, prefetch);
-      // leave 5 % of the budget free: a plan whose peak touches the budget tends to need an unplanned
-      // spill at run time (the simulator does not model fragmentation)
+      // leave 12 % of the budget free: measured peaks run about 5 % above the simulated ones (allocation
+      // granularity, fragmentation), and a plan whose peak touches the budget needs an unplanned spill
       if (trial.first_over < 0 && trial.time_ms <= r.time_ms + 1e-9 &&
-          (double)trial.peak <= 0.95 * (double)budget) {
+          (double)trial.peak <= 0.88 * (double)budget) {
         r = trial;
       } else {
         cls[t] = was;
