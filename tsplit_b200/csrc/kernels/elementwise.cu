@@ -135,6 +135,19 @@ __device__ __forceinline__ void offsets3(const Dims& d, long long idx, long long
   }
 }
 
+// Strided copy whose innermost dimension is contiguous on both sides and a multiple of four floats
+// (a channel range of a channels-last tensor: concat / slice along channels, padded feeds): the same
+// index walk as unary_strided, but in units of 16 bytes.  `d` holds the shape and strides already
+// divided by four in the innermost dimension / for the outer strides.
+__global__ void copy_strided_v4(const float4* __restrict__ x, float4* __restrict__ y, const Dims d, long long n4) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+    long long ox, oy;
+    offsets2(d, i, ox, oy);
+    y[oy] = x[ox];
+  }
+}
+
 template <int OP>
 __global__ void unary_strided(const float* __restrict__ x, float* __restrict__ y, const Dims d, long long n,
                               float a) {
@@ -328,6 +341,21 @@ int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long*
   long long n = 1;
   for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = xs[i]; d.s1[i] = ys[i]; d.s2[i] = 0; n *= shape[i]; }
   if (n <= 0) return TSB_OK;
+  // 16-byte path: innermost dimension contiguous on both sides, everything a multiple of four floats
+  if (op == UN_COPY && xs[nd - 1] == 1 && ys[nd - 1] == 1 && (shape[nd - 1] & 3) == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    bool ok = true;
+    for (int i = 0; i < nd - 1; ++i) ok = ok && (xs[i] & 3) == 0 && (ys[i] & 3) == 0;
+    if (ok) {
+      Dims v = d;
+      v.shape[nd - 1] = shape[nd - 1] / 4;
+      for (int i = 0; i < nd - 1; ++i) { v.s0[i] = xs[i] / 4; v.s1[i] = ys[i] / 4; }
+      const long long n4 = n / 4;
+      copy_strided_v4<<<grid_for(n4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(x),
+                                                          reinterpret_cast<float4*>(y), v, n4);
+      return done();
+    }
+  }
   // coalesced tiled path: copy where src is contiguous along the last dim and dst along another one
   if (op == UN_COPY && nd >= 2 && nd <= 3 && xs[nd - 1] == 1 && ys[nd - 1] != 1) {
     int rdim = -1;
