@@ -341,15 +341,24 @@ int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long*
   long long n = 1;
   for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = xs[i]; d.s1[i] = ys[i]; d.s2[i] = 0; n *= shape[i]; }
   if (n <= 0) return TSB_OK;
-  // 16-byte path: innermost dimension contiguous on both sides, everything a multiple of four floats
-  if (op == UN_COPY && xs[nd - 1] == 1 && ys[nd - 1] == 1 && (shape[nd - 1] & 3) == 0 &&
-      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
-    bool ok = true;
-    for (int i = 0; i < nd - 1; ++i) ok = ok && (xs[i] & 3) == 0 && (ys[i] & 3) == 0;
+  // 16-byte path: some dimension is contiguous on both sides (the channel range of a channels-last
+  // tensor given in logical N, C, H, W order) and everything is a multiple of four floats.  The order
+  // of the dimensions does not matter to a copy, so that dimension is moved last.
+  if (op == UN_COPY && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    int cd = -1;
+    for (int i = nd - 1; i >= 0; --i)
+      if (xs[i] == 1 && ys[i] == 1 && (shape[i] & 3) == 0) { cd = i; break; }
+    bool ok = cd >= 0;
+    for (int i = 0; i < nd && ok; ++i)
+      if (i != cd) ok = (xs[i] & 3) == 0 && (ys[i] & 3) == 0;
     if (ok) {
       Dims v = d;
-      v.shape[nd - 1] = shape[nd - 1] / 4;
-      for (int i = 0; i < nd - 1; ++i) { v.s0[i] = xs[i] / 4; v.s1[i] = ys[i] / 4; }
+      // rotate dimension cd to the end
+      for (int i = cd; i + 1 < nd; ++i) {
+        v.shape[i] = d.shape[i + 1]; v.s0[i] = d.s0[i + 1]; v.s1[i] = d.s1[i + 1];
+      }
+      v.shape[nd - 1] = shape[cd] / 4; v.s0[nd - 1] = 1; v.s1[nd - 1] = 1;
+      for (int i = 0; i < nd - 1; ++i) { v.s0[i] /= 4; v.s1[i] /= 4; }
       const long long n4 = n / 4;
       copy_strided_v4<<<grid_for(n4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(x),
                                                           reinterpret_cast<float4*>(y), v, n4);
