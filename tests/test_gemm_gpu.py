@@ -63,9 +63,9 @@ def test_gemm_splitk_and_accumulate():
     assert _run(128, 256, 8192, 1, 0) < 5e-3        # auto split-K (few tiles, long K)
 
 
-def test_gemm_unaligned_falls_back_to_simt():
-    assert _run(37, 10, 256, 0, 0) < 1e-4           # ldb = 10 floats: not TMA-addressable
-    assert _run(128, 10, 255, 0, 0) < 1e-4
+def test_gemm_row_strides_that_tma_cannot_address():
+    assert _run(37, 10, 256, 0, 0) < 5e-3           # ldb = 10 floats: padded into scratch, then tensor cores
+    assert _run(128, 10, 255, 0, 0) < 5e-3
 
 
 def test_gemm_large_many_tiles():
@@ -84,3 +84,12 @@ def test_gemm_cta_pair_ragged_batched_accumulate():
     assert _run(1024, 1024, 128, 0, 0, batch=8) < 5e-3
     assert _run(1024, 768, 64, 1, 1, batch=16) < 5e-3
     assert _run(2048, 2048, 64, 0, 1, accumulate=True) < 5e-3
+
+
+def test_gemm_odd_row_stride_is_padded_not_simt():
+    """Row strides that are not multiples of four floats (255-wide attention matrices) are padded
+    into scratch and still run on the tensor cores; results match in every transpose mode."""
+    assert _run(255, 64, 255, 0, 0, batch=16) < 5e-3
+    assert _run(255, 64, 255, 1, 0, batch=16) < 5e-3
+    assert _run(130, 255, 64, 0, 1, batch=3) < 5e-3
+    assert _run(100, 37, 72, 0, 0) < 5e-3            # ldb = 37

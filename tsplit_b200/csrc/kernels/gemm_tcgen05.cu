@@ -19,6 +19,7 @@
 #include <mutex>
 #include <unordered_map>
 #include <string>
+#include <cstdio>
 #include <cstring>
 #include <cstdlib>
 
@@ -751,6 +752,35 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
+// Copy of a [batch][rows][cols] operand whose row stride is not a multiple of four floats into a
+// scratch array with the row stride rounded up (pad columns zero), so that TMA can address it.
+__global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int batch, int rows,
+                                int cols, long long lds, long long ss, long long ldd, long long sd) {
+  const long long total = (long long)batch * rows * ldd;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ldd);
+    const long long r = i / ldd;
+    const int row = (int)(r % rows);
+    const long long b = r / rows;
+    dst[b * sd + row * ldd + c] = c < cols ? src[b * ss + row * lds + c] : 0.f;
+  }
+}
+
+Workspace g_pad[64][2];
+float* pad_workspace(int slot, size_t bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Workspace& w = g_pad[dev][slot];
+  if (w.bytes < bytes) {
+    if (w.ptr) cudaFree(w.ptr);
+    w.ptr = nullptr; w.bytes = 0;
+    if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    w.bytes = bytes;
+  }
+  return w.ptr;
+}
+
 int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                   cudaStream_t st) {
   if (!a_mn && !b_mn) return launch_pair<false, false>(ta, tb, p, st);
@@ -782,7 +812,52 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
   if (m <= 0 || n <= 0 || k <= 0 || batch <= 0) return TSB_ERR_ARG;
   const bool aligned = (lda % 4 == 0) && (ldb % 4 == 0) && (sa % 4 == 0) && (sb % 4 == 0) &&
                        ((reinterpret_cast<uintptr_t>(a) & 15) == 0) && ((reinterpret_cast<uintptr_t>(b) & 15) == 0);
+  // Only the row strides are off (e.g. 255-wide attention matrices): pad the operand rows into scratch
+  // once (one pass over the operand) and run the tensor-core kernel on the padded copy.
+  if (!aligned && may_alloc && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0) {
+    const float* ap = a;
+    const float* bp = b;
+    long long lda2 = lda, ldb2 = ldb, sa2 = sa, sb2 = sb;
+    const int rows_a = trans_a ? k : m, cols_a = trans_a ? m : k;
+    const int rows_b = trans_b ? n : k, cols_b = trans_b ? k : n;
+    bool okpad = true;
+    if ((lda % 4) || (batch > 1 && (sa % 4))) {
+      lda2 = (cols_a + 3) / 4 * 4;
+      sa2 = (long long)rows_a * lda2;
+      float* buf = pad_workspace(0, (size_t)batch * sa2 * sizeof(float));
+      if (!buf) okpad = false;
+      else {
+        const long long total = (long long)batch * rows_a * lda2;
+        long long blocks = (total + 255) / 256;
+        if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+        pad_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(a, buf, batch, rows_a, cols_a, lda, batch > 1 ? sa : 0, lda2,
+                                                         sa2);
+        ap = buf;
+      }
+    }
+    if (okpad && ((ldb % 4) || (batch > 1 && (sb % 4)))) {
+      ldb2 = (cols_b + 3) / 4 * 4;
+      sb2 = (long long)rows_b * ldb2;
+      float* buf = pad_workspace(1, (size_t)batch * sb2 * sizeof(float));
+      if (!buf) okpad = false;
+      else {
+        const long long total = (long long)batch * rows_b * ldb2;
+        long long blocks = (total + 255) / 256;
+        if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+        pad_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(b, buf, batch, rows_b, cols_b, ldb, batch > 1 ? sb : 0, ldb2,
+                                                         sb2);
+        bp = buf;
+      }
+    }
+    if (okpad)
+      return tsb_gemm_tf32_impl(ap, bp, c, m, n, k, lda2, ldb2, ldc, trans_a, trans_b, batch, sa2, sb2, sc, accumulate,
+                                forced_splits, ws, ws_bytes, may_alloc, st);
+  }
   if (!aligned) {
+    if (getenv("TSB_GEMM_TRACE"))
+      fprintf(stderr, "[gemm] SIMT fallback m %d n %d k %d lda %lld ldb %lld ta %d tb %d batch %d sa %lld sb %lld a%%16 %d b%%16 %d\n",
+              m, n, k, lda, ldb, trans_a, trans_b, batch, sa, sb, (int)(reinterpret_cast<uintptr_t>(a) & 15),
+              (int)(reinterpret_cast<uintptr_t>(b) & 15));
     dim3 blk(16, 16), grd((n + 15) / 16, (m + 15) / 16, batch);
     gemm_simt_kernel<<<grd, blk, 0, st>>>(a, b, c, m, n, k, lda, ldb, ldc, trans_a, trans_b, sa, sb, sc,
                                           accumulate);
