@@ -214,9 +214,12 @@ def test_layer_norm(ctx):
     both(build, {"x": f32(3, 5, 64), "s": f32(64) + 1, "b": f32(64)}, ctx, rtol=5e-3)
 
 
-def test_softmax_and_cross_entropy(ctx):
-    logits = f32(32, 1000)
-    labels = np.eye(1000, dtype=np.float32)[R.randint(0, 1000, 32)]
+@pytest.mark.parametrize("rows,cols", [(32, 1000), (70, 256), (19, 64), (5, 1023), (9, 4100), (6, 33000)])
+def test_softmax_and_cross_entropy(ctx, rows, cols):
+    # short rows take the warp-per-row kernel, rows whose length is no multiple of 4 the scalar one,
+    # long rows the 16-byte one-pass kernels
+    logits = f32(rows, cols) * 3
+    labels = np.eye(cols, dtype=np.float32)[R.randint(0, cols, rows)]
 
     def build():
         y, y_ = ad.Variable("y"), ad.Variable("y_")

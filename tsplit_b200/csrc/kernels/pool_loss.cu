@@ -4,8 +4,9 @@
 // gradient is a gather over the windows containing an input pixel and gives the
 // gradient to the FIRST maximum of each window (row-major), so it is
 // deterministic, needs no atomics and no zero-fill pass.
-// Softmax family: one CTA per row with warp-shuffle reductions; the mean of the
-// row losses is a fixed-order second stage.
+// Softmax family: one warp per row for short rows (the row stays in registers), one
+// CTA per row with 16-byte lanes and a one-pass running (max, sum) for long rows; the
+// mean of the row losses is a fixed-order second stage.
 //
 // Roles in the reference: cudnnPoolingForward/Backward (src/ops/CudnnMaxPool.cu,
 // CudnnAvgPool.cu) and the <<<1,1024>>> kernels of src/ops/Softmax.cu:3-22 and
@@ -314,6 +315,128 @@ __global__ void softmax_rows(const float* __restrict__ x, float* __restrict__ y,
   }
 }
 
+// Short rows (cols <= 1024, a multiple of 4): one warp per row, the row held in registers between the
+// maximum, the sum and the store, so it is read once and no block barrier is involved.
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_warp_rows(const float4* __restrict__ x, float4* __restrict__ y,
+                                                         long long rows, int nvec) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float4* xr = x + row * nvec;
+    float4 v[NV];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      v[j] = i < nvec ? __ldg(xr + i) : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+      m = fmaxf(m, fmaxf(fmaxf(v[j].x, v[j].y), fmaxf(v[j].z, v[j].w)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      v[j].x = __expf(v[j].x - m); v[j].y = __expf(v[j].y - m);
+      v[j].z = __expf(v[j].z - m); v[j].w = __expf(v[j].w - m);
+      s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.f / s;
+    float4* yr = y + row * nvec;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec) yr[i] = make_float4(v[j].x * inv, v[j].y * inv, v[j].z * inv, v[j].w * inv);
+    }
+  }
+}
+
+// Running (maximum, sum of exponentials) of a row in one pass: the sum is rescaled when the maximum moves.
+struct MaxSum { float m, s; };
+__device__ __forceinline__ MaxSum ms_join(MaxSum a, MaxSum b) {
+  const float m = fmaxf(a.m, b.m);
+  return {m, a.s * __expf(a.m - m) + b.s * __expf(b.m - m)};
+}
+__device__ __forceinline__ void ms_add4(MaxSum& a, const float4 v) {
+  const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+  if (m4 > a.m) { a.s *= __expf(a.m - m4); a.m = m4; }
+  a.s += (__expf(v.x - a.m) + __expf(v.y - a.m)) + (__expf(v.z - a.m) + __expf(v.w - a.m));
+}
+// Block-wide join; sh holds 2 floats per warp.
+__device__ __forceinline__ MaxSum block_max_sum(MaxSum a, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum b{__shfl_xor_sync(0xffffffffu, a.m, o), __shfl_xor_sync(0xffffffffu, a.s, o)};
+    a = ms_join(a, b);
+  }
+  if (lane == 0) { sh[2 * w] = a.m; sh[2 * w + 1] = a.s; }
+  __syncthreads();
+  MaxSum r{sh[0], sh[1]};
+  for (int i = 1; i < nw; ++i) r = ms_join(r, MaxSum{sh[2 * i], sh[2 * i + 1]});
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ MaxSum row_max_sum(const float4* __restrict__ xr, int nvec, float* sh) {
+  MaxSum a{-FLT_MAX, 0.f};
+  int i = threadIdx.x;
+  for (; i + 3 * (int)blockDim.x < nvec; i += 4 * blockDim.x) {
+    const float4 v0 = __ldg(xr + i), v1 = __ldg(xr + i + blockDim.x), v2 = __ldg(xr + i + 2 * blockDim.x),
+                 v3 = __ldg(xr + i + 3 * blockDim.x);
+    ms_add4(a, v0); ms_add4(a, v1); ms_add4(a, v2); ms_add4(a, v3);
+  }
+  for (; i < nvec; i += blockDim.x) ms_add4(a, __ldg(xr + i));
+  return block_max_sum(a, sh);
+}
+
+// Long rows, 16-byte lanes: the logits come from DRAM once (the second pass finds the row in L2, the
+// rows in flight being kept below its size by the block size chosen at launch).
+__global__ void __launch_bounds__(512) ce_rows_v4(const float4* __restrict__ x, const float4* __restrict__ lab,
+                                                  float* __restrict__ row_loss, long long rows, int nvec) {
+  __shared__ float sh[64];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float4* xr = x + row * nvec;
+    const float4* lr = lab + row * nvec;
+    const MaxSum ms = row_max_sum(xr, nvec, sh);
+    const float lse = ms.m + logf(ms.s);
+    float l = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const float4 t = __ldcs(lr + i);
+      const float4 v = __ldg(xr + i);
+      l -= (t.x * (v.x - lse) + t.y * (v.y - lse)) + (t.z * (v.z - lse) + t.w * (v.w - lse));
+    }
+    l = block_sum(l, sh);
+    if (threadIdx.x == 0) row_loss[row] = l;
+  }
+}
+
+__global__ void __launch_bounds__(512) ce_grad_rows_v4(const float4* __restrict__ x, const float4* __restrict__ lab,
+                                                       const float* __restrict__ g, float4* __restrict__ dx,
+                                                       long long rows, int nvec) {
+  __shared__ float sh[64];
+  const float scale = g[0] / (float)rows;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float4* xr = x + row * nvec;
+    const float4* lr = lab + row * nvec;
+    float4* dr = dx + row * nvec;
+    const MaxSum ms = row_max_sum(xr, nvec, sh);
+    const float inv = 1.f / ms.s, m = ms.m;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const float4 t = __ldcs(lr + i);
+      const float4 v = __ldg(xr + i);
+      float4 o;
+      o.x = (__expf(v.x - m) * inv - t.x) * scale;
+      o.y = (__expf(v.y - m) * inv - t.y) * scale;
+      o.z = (__expf(v.z - m) * inv - t.z) * scale;
+      o.w = (__expf(v.w - m) * inv - t.w) * scale;
+      __stcs(dr + i, o);
+    }
+  }
+}
+
 __global__ void ce_rows(const float* __restrict__ x, const float* __restrict__ lab, float* __restrict__ row_loss,
                         long long rows, long long cols) {
   __shared__ float sh[8];
@@ -359,6 +482,8 @@ __global__ void ce_grad_rows(const float* __restrict__ x, const float* __restric
       dx[row * cols + i] = (expf(xr[i] - m) * inv - lab[row * cols + i]) * scale;
   }
 }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 float* g_rows[64] = {nullptr};
 long long g_rows_cap[64] = {0};
@@ -427,8 +552,21 @@ int tsb_pool_bwd(int kind, const float* x, const float* y, const float* dy, floa
 
 int tsb_softmax(const float* x, float* y, long long rows, long long cols, void* stream) {
   if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cols <= 1024 && cols % 4 == 0 && aligned16(x) && aligned16(y)) {
+    const int nvec = (int)(cols / 4);
+    const long long blocks = (rows + 7) / 8;
+    const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+    const float4* xv = reinterpret_cast<const float4*>(x);
+    float4* yv = reinterpret_cast<float4*>(y);
+    if (nvec <= 32) softmax_warp_rows<1><<<wgrid, 256, 0, st>>>(xv, yv, rows, nvec);
+    else if (nvec <= 64) softmax_warp_rows<2><<<wgrid, 256, 0, st>>>(xv, yv, rows, nvec);
+    else if (nvec <= 128) softmax_warp_rows<4><<<wgrid, 256, 0, st>>>(xv, yv, rows, nvec);
+    else softmax_warp_rows<8><<<wgrid, 256, 0, st>>>(xv, yv, rows, nvec);
+    return done();
+  }
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
-  softmax_rows<<<grid, cols >= 1024 ? 256 : 128, 0, static_cast<cudaStream_t>(stream)>>>(x, y, rows, cols);
+  softmax_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, rows, cols);
   return done();
 }
 
@@ -438,6 +576,13 @@ int tsb_softmax_ce(const float* x, const float* labels, float* loss, long long r
   if (!rl) return TSB_ERR_OOM;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  if (cols >= 512 && cols % 4 == 0 && cols / 4 < (1ll << 30) && aligned16(x) && aligned16(labels)) {
+    ce_rows_v4<<<grid, cols >= 8192 ? 512 : 256, 0, st>>>(reinterpret_cast<const float4*>(x),
+                                                         reinterpret_cast<const float4*>(labels), rl, rows,
+                                                         (int)(cols / 4));
+    mean_rows<<<1, 1024, 0, st>>>(rl, loss, rows);
+    return done();
+  }
   ce_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(x, labels, rl, rows, cols);
   mean_rows<<<1, 1024, 0, st>>>(rl, loss, rows);
   return done();
@@ -447,6 +592,12 @@ int tsb_softmax_ce_grad(const float* x, const float* labels, const float* g, flo
                         long long cols, void* stream) {
   if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  if (cols >= 512 && cols % 4 == 0 && cols / 4 < (1ll << 30) && aligned16(x) && aligned16(labels) && aligned16(dx)) {
+    ce_grad_rows_v4<<<grid, cols >= 8192 ? 512 : 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(labels), g,
+        reinterpret_cast<float4*>(dx), rows, (int)(cols / 4));
+    return done();
+  }
   ce_grad_rows<<<grid, cols >= 1024 ? 256 : 128, 0, static_cast<cudaStream_t>(stream)>>>(x, labels, g, dx, rows,
                                                                                          cols);
   return done();
