@@ -229,6 +229,18 @@ def test_softmax_and_cross_entropy(ctx, rows, cols):
     both(build, {"y": logits, "y_": labels}, ctx)
 
 
+@pytest.mark.parametrize("shape", [(2, 4, 24, 256), (3, 2, 7, 64), (5, 1030), (4, 4100)])
+def test_softmax_backward(ctx, shape):
+    # rows up to 1024 long take the warp-per-row kernel, others the CTA-per-row one
+    def build():
+        x, w = ad.Variable("x"), ad.Variable("w")
+        y = ad.softmax_op(x)
+        loss = ad.reduce_sum_op(ad.mul_op(y, w), list(range(len(shape))))
+        gx, = ad.gradients(loss, [x])
+        return {"x": x, "w": w}, [y, gx]
+    both(build, {"x": f32(*shape) * 2, "w": f32(*shape)}, ctx)
+
+
 def test_shape_family(ctx):
     def build():
         x, z = ad.Variable("x"), ad.Variable("z")

@@ -354,6 +354,53 @@ __global__ void __launch_bounds__(256) softmax_warp_rows(const float4* __restric
   }
 }
 
+// Softmax backward, dx = y * (dy - sum(dy * y)): one warp per row, y and dy read once.
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_grad_warp_rows(const float4* __restrict__ y,
+                                                              const float4* __restrict__ dy,
+                                                              float4* __restrict__ dx, long long rows, int nvec) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float4* yr = y + row * nvec;
+    const float4* gr = dy + row * nvec;
+    float4 a[NV], g[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      a[j] = i < nvec ? __ldg(yr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      g[j] = i < nvec ? __ldg(gr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s += (a[j].x * g[j].x + a[j].y * g[j].y) + (a[j].z * g[j].z + a[j].w * g[j].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    float4* dr = dx + row * nvec;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec)
+        dr[i] = make_float4(a[j].x * (g[j].x - s), a[j].y * (g[j].y - s), a[j].z * (g[j].z - s),
+                            a[j].w * (g[j].w - s));
+    }
+  }
+}
+
+// Any row length: one CTA per row, the second pass finds the row in L2.
+__global__ void softmax_grad_rows(const float* __restrict__ y, const float* __restrict__ dy, float* __restrict__ dx,
+                                  long long rows, long long cols) {
+  __shared__ float sh[8];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* yr = y + row * cols;
+    const float* gr = dy + row * cols;
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) s += yr[i] * gr[i];
+    s = block_sum(s, sh);
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) dx[row * cols + i] = yr[i] * (gr[i] - s);
+  }
+}
+
 // Running (maximum, sum of exponentials) of a row in one pass: the sum is rescaled when the maximum moves.
 struct MaxSum { float m, s; };
 __device__ __forceinline__ MaxSum ms_join(MaxSum a, MaxSum b) {
@@ -567,6 +614,27 @@ int tsb_softmax(const float* x, float* y, long long rows, long long cols, void* 
   }
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
   softmax_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, rows, cols);
+  return done();
+}
+
+int tsb_softmax_grad(const float* y, const float* dy, float* dx, long long rows, long long cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cols <= 1024 && cols % 4 == 0 && aligned16(y) && aligned16(dy) && aligned16(dx)) {
+    const int nvec = (int)(cols / 4);
+    const long long blocks = (rows + 7) / 8;
+    const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+    const float4* yv = reinterpret_cast<const float4*>(y);
+    const float4* gv = reinterpret_cast<const float4*>(dy);
+    float4* dv = reinterpret_cast<float4*>(dx);
+    if (nvec <= 32) softmax_grad_warp_rows<1><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
+    else if (nvec <= 64) softmax_grad_warp_rows<2><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
+    else if (nvec <= 128) softmax_grad_warp_rows<4><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
+    else softmax_grad_warp_rows<8><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
+    return done();
+  }
+  const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+  softmax_grad_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(y, dy, dx, rows, cols);
   return done();
 }
 

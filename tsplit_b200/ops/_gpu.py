@@ -171,6 +171,12 @@ def softmax(x, y, stream):
     _check(lib().tsb_softmax(_p(x), _p(y), c_int64(rows), c_int64(cols), _s(stream)), "softmax")
 
 
+def softmax_grad(y, dy, dx, stream):
+    rows, cols = _numel(y.shape[:-1]), y.shape[-1]
+    _check(lib().tsb_softmax_grad(_p(y), _p(dy), _p(dx), c_int64(rows), c_int64(cols), _s(stream)),
+           "softmax_grad")
+
+
 def softmax_ce(logits, labels, loss, stream):
     rows, cols = logits.shape
     _check(lib().tsb_softmax_ce(_p(logits), _p(labels), _p(loss), c_int64(rows), c_int64(cols),

@@ -34,18 +34,39 @@ class SoftmaxOp(Op):
         G.softmax(iv[0], out, stream)
 
     def gradient(self, node, g):
-        # dx = y * (g - sum(g * y, axis=-1, keepdims))  (the reference leaves this undefined)
-        from .elementwise import mul_op, add_op, opposite_op
-        from .shape import reduce_sum_op, broadcasttoTF_op
-        gy = mul_op(g, node)
-        s = reduce_sum_op(gy, [-1], keepdims=True)
-        return [mul_op(node, add_op(g, opposite_op(broadcasttoTF_op(s, g))))]
+        # the reference leaves this undefined (src/ops/Softmax.cu has no backward kernel)
+        return [softmax_gradient_op(node, g)]
 
     def infer_shape(self, node, s):
         return tuple(s[0])
 
     def flops(self, node, s, out):
         return 5.0 * np.prod(out)
+
+
+class SoftmaxGradientOp(Op):
+    """``dx = y * (dy - sum(dy * y, axis=-1, keepdims=True))`` in one kernel (y and dy read once)."""
+    name = "SoftmaxGradient"
+
+    def __call__(self, y, dy):
+        return Op.__call__(self, y, dy)
+
+    def np_compute(self, node, iv):
+        y, dy = iv
+        return (y * (dy - np.sum(dy * y, axis=-1, keepdims=True))).astype(np.float32)
+
+    def gpu_compute(self, node, iv, out, stream):
+        G.softmax_grad(iv[0], iv[1], out, stream)
+
+    def gradient(self, node, g):
+        raise NotImplementedError
+
+    def infer_shape(self, node, s):
+        assert tuple(s[0]) == tuple(s[1])
+        return tuple(s[0])
+
+    def flops(self, node, s, out):
+        return 4.0 * np.prod(out)
 
 
 class SoftmaxCrossEntropyOp(Op):
@@ -102,10 +123,15 @@ class SoftmaxCrossEntropyGradientOp(Op):
 
 
 _sm, _ce, _ceg = SoftmaxOp(), SoftmaxCrossEntropyOp(), SoftmaxCrossEntropyGradientOp()
+_smg = SoftmaxGradientOp()
 
 
 def softmax_op(node):
     return _sm(node)
+
+
+def softmax_gradient_op(node_y, node_dy):
+    return _smg(node_y, node_dy)
 
 
 def softmaxcrossentropy_op(node_A, node_B):
