@@ -204,14 +204,17 @@ def test_batch_norm_forward_backward(ctx):
     both(build, {"x": f32(4, 16, 6, 6) + 0.5, "s": f32(1, 16, 1, 1) + 1, "b": f32(1, 16, 1, 1)}, ctx, rtol=5e-3)
 
 
-def test_layer_norm(ctx):
+@pytest.mark.parametrize("shape", [(3, 5, 64), (40, 33, 512), (7, 9, 30)])
+def test_layer_norm(ctx, shape):
+    d = shape[-1]
+
     def build():
         x, s, b = ad.Variable("x"), ad.Variable("s"), ad.Variable("b")
         y = ad.layer_normalization_op(x, s, b)
         loss = ad.reduce_sum_op(ad.mul_op(y, y), [0, 1, 2])
         gx, gs, gb = ad.gradients(loss, [x, s, b])
         return {"x": x, "s": s, "b": b}, [y, gx, gs, gb]
-    both(build, {"x": f32(3, 5, 64), "s": f32(64) + 1, "b": f32(64)}, ctx, rtol=5e-3)
+    both(build, {"x": f32(*shape), "s": f32(d) + 1, "b": f32(d)}, ctx, rtol=5e-3)
 
 
 @pytest.mark.parametrize("rows,cols", [(32, 1000), (70, 256), (19, 64), (5, 1023), (9, 4100), (6, 33000)])
@@ -229,7 +232,7 @@ def test_softmax_and_cross_entropy(ctx, rows, cols):
     both(build, {"y": logits, "y_": labels}, ctx)
 
 
-@pytest.mark.parametrize("shape", [(2, 4, 24, 256), (3, 2, 7, 64), (5, 1030), (4, 4100)])
+@pytest.mark.parametrize("shape", [(2, 4, 24, 256), (3, 2, 7, 64), (2, 3, 9, 255), (11, 100), (5, 1030), (4, 4100)])
 def test_softmax_backward(ctx, shape):
     # rows up to 1024 long take the warp-per-row kernel, others the CTA-per-row one
     def build():
@@ -239,6 +242,31 @@ def test_softmax_backward(ctx, shape):
         gx, = ad.gradients(loss, [x])
         return {"x": x, "w": w}, [y, gx]
     both(build, {"x": f32(*shape) * 2, "w": f32(*shape)}, ctx)
+
+
+@pytest.mark.parametrize("xs,bs", [((6, 10, 64), (64,)), ((5, 30), (30,)), ((3, 4, 9, 15), (3, 1, 1, 15)),
+                                   ((4, 8, 12), (8, 1)), ((7, 36), (7, 36))])
+def test_add_of_a_broadcast_is_one_op(ctx, xs, bs):
+    # x + broadcasttoTF_op(b, x) is built as one AddBroadcast node; b's gradient sums over the broadcast axes
+    def build():
+        x, b, w = ad.Variable("x"), ad.Variable("b"), ad.Variable("w")
+        y = x + ad.broadcasttoTF_op(b, x)
+        assert y.op.name == "AddBroadcast"
+        z = ad.broadcasttoTF_op(b, x) + x
+        assert z.op.name == "AddBroadcast"
+        loss = ad.reduce_sum_op(ad.mul_op(y, w), list(range(len(xs))))
+        gx, gb = ad.gradients(loss, [x, b])
+        return {"x": x, "b": b, "w": w}, [y, z, gx, gb]
+    both(build, {"x": f32(*xs), "b": f32(*bs), "w": f32(*xs)}, ctx)
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 128), (2050, 36), (100, 30), (64, 4)])
+def test_column_sums(ctx, rows, cols):
+    # [rows, cols] -> [cols]: the two-stage kernels (16-byte lanes when cols is a multiple of 4)
+    def build():
+        x = ad.Variable("x")
+        return {"x": x}, [ad.reduce_sum_op(x, [0]), ad.reducesumaxiszero_op(x)]
+    both(build, {"x": f32(rows, cols)}, ctx)
 
 
 def test_shape_family(ctx):

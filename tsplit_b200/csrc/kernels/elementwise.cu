@@ -15,6 +15,7 @@
 
 #define TSB_OK 0
 #define TSB_ERR_ARG 1
+#define TSB_ERR_UNSUPPORTED 2
 #define TSB_ERR_LAUNCH 3
 
 namespace {
@@ -29,6 +30,7 @@ struct Dims {
   long long s1[MAXD];
   long long s2[MAXD];
   int nd;
+  int small;   // the element count is below 2^32: index arithmetic may run in 32 bits
 };
 
 template <int OP>
@@ -107,9 +109,38 @@ __global__ void where_flat(const float* __restrict__ c, const float* __restrict_
     y[i] = c[i] != 0.f ? a[i] : b[i];
 }
 
+// y[r, c] = x[r, c] + b[c] on a dense row-major [rows, cols] view, 16 bytes per thread (the bias of a
+// dense layer added without materialising the broadcast).
+__global__ void bias_add_v4(const float4* __restrict__ x, const float4* __restrict__ b, float4* __restrict__ y,
+                            long long n4, unsigned cols4) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const unsigned c = (n4 >> 32) == 0 ? (unsigned)i % cols4 : (unsigned)(i % cols4);
+    const float4 v = x[i], w = __ldg(b + c);
+    y[i] = make_float4(v.x + w.x, v.y + w.y, v.z + w.z, v.w + w.w);
+  }
+}
+
 // index decomposition: the LAST dim varies fastest across threads
+// (tensors of fewer than 2^32 elements are decomposed with 32-bit divisions, several times cheaper
+// than 64-bit ones)
 __device__ __forceinline__ void offsets2(const Dims& d, long long idx, long long& o0, long long& o1) {
   o0 = 0; o1 = 0;
+  if (d.small) {
+    unsigned r = (unsigned)idx;
+#pragma unroll
+    for (int k = MAXD - 1; k >= 0; --k) {
+      if (k < d.nd) {
+        const unsigned sh = (unsigned)d.shape[k];
+        const unsigned q = r / sh;
+        const long long c = r - q * sh;
+        r = q;
+        o0 += c * d.s0[k];
+        o1 += c * d.s1[k];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int k = MAXD - 1; k >= 0; --k) {
     if (k < d.nd) {
@@ -123,6 +154,22 @@ __device__ __forceinline__ void offsets2(const Dims& d, long long idx, long long
 __device__ __forceinline__ void offsets3(const Dims& d, long long idx, long long& o0, long long& o1,
                                          long long& o2) {
   o0 = 0; o1 = 0; o2 = 0;
+  if (d.small) {
+    unsigned r = (unsigned)idx;
+#pragma unroll
+    for (int k = MAXD - 1; k >= 0; --k) {
+      if (k < d.nd) {
+        const unsigned sh = (unsigned)d.shape[k];
+        const unsigned q = r / sh;
+        const long long c = r - q * sh;
+        r = q;
+        o0 += c * d.s0[k];
+        o1 += c * d.s1[k];
+        o2 += c * d.s2[k];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int k = MAXD - 1; k >= 0; --k) {
     if (k < d.nd) {
@@ -248,6 +295,49 @@ __global__ void colsum_partial(const float* __restrict__ x, float* __restrict__ 
   for (long long r = r0; r < r1; ++r) acc += x[r * ld + c];
   part[(long long)ch * cols + c] = acc;
 }
+// 16-byte variant: a thread owns four adjacent columns and keeps four rows in flight.
+__global__ void colsum_partial_v4(const float4* __restrict__ x, float4* __restrict__ part, long long rows,
+                                  int cols4, long long ld4, int chunks) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int ch = blockIdx.y;
+  if (c >= cols4) return;
+  const long long per = (rows + chunks - 1) / chunks;
+  const long long r0 = ch * per, r1 = min(rows, r0 + per);
+  float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+  long long r = r0;
+  for (; r + 3 < r1; r += 4) {
+    const float4 v0 = __ldg(x + r * ld4 + c), v1 = __ldg(x + (r + 1) * ld4 + c), v2 = __ldg(x + (r + 2) * ld4 + c),
+                 v3 = __ldg(x + (r + 3) * ld4 + c);
+    a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
+    a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
+    a2.x += v2.x; a2.y += v2.y; a2.z += v2.z; a2.w += v2.w;
+    a3.x += v3.x; a3.y += v3.y; a3.z += v3.z; a3.w += v3.w;
+  }
+  for (; r < r1; ++r) {
+    const float4 v = __ldg(x + r * ld4 + c);
+    a0.x += v.x; a0.y += v.y; a0.z += v.z; a0.w += v.w;
+  }
+  part[(long long)ch * cols4 + c] =
+      make_float4((a0.x + a1.x) + (a2.x + a3.x), (a0.y + a1.y) + (a2.y + a3.y), (a0.z + a1.z) + (a2.z + a3.z),
+                  (a0.w + a1.w) + (a2.w + a3.w));
+}
+// Second stage for many chunks: 32 columns x 8 chunk lanes per block, lanes joined in a fixed order.
+__global__ void colsum_final_lanes(const float* __restrict__ part, float* __restrict__ y, long long cols, int chunks,
+                                   long long ys) {
+  __shared__ float sh[8][33];
+  const long long c = blockIdx.x * 32ll + threadIdx.x;
+  float acc = 0.f;
+  if (c < cols)
+    for (int ch = threadIdx.y; ch < chunks; ch += 8) acc += part[(long long)ch * cols + c];
+  sh[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += sh[j][threadIdx.x];
+    y[c * ys] = t;
+  }
+}
 __global__ void colsum_final(const float* __restrict__ part, float* __restrict__ y, long long cols, int chunks,
                              long long ys) {
   const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -341,6 +431,7 @@ int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long*
   long long n = 1;
   for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = xs[i]; d.s1[i] = ys[i]; d.s2[i] = 0; n *= shape[i]; }
   if (n <= 0) return TSB_OK;
+  d.small = n < (1ll << 32);
   // 16-byte path: some dimension is contiguous on both sides (the channel range of a channels-last
   // tensor given in logical N, C, H, W order) and everything is a multiple of four floats.  The order
   // of the dimensions does not matter to a copy, so that dimension is moved last.
@@ -402,6 +493,18 @@ int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long*
   return done();
 }
 
+int tsb_bias_add(const float* x, const float* b, float* y, long long rows, long long cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return TSB_OK;
+  if ((cols & 3) || cols >= (1ll << 32) ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(y)) & 15))
+    return TSB_ERR_UNSUPPORTED;
+  const long long n4 = rows * (cols / 4);
+  bias_add_v4<<<grid_for(n4, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(b), reinterpret_cast<float4*>(y), n4,
+      (unsigned)(cols / 4));
+  return done();
+}
+
 int tsb_strided_binary(int op, const float* a, const float* b, float* y, int nd, const long long* shape,
                        const long long* as, const long long* bs, const long long* ys, void* stream) {
   if (nd < 1 || nd > MAXD) return TSB_ERR_ARG;
@@ -411,6 +514,7 @@ int tsb_strided_binary(int op, const float* a, const float* b, float* y, int nd,
   long long n = 1;
   for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = as[i]; d.s1[i] = bs[i]; d.s2[i] = ys[i]; n *= shape[i]; }
   if (n <= 0) return TSB_OK;
+  d.small = n < (1ll << 32);
   const int grid = grid_for(n, 256);
   switch (op) {
     BINS_CASE(BIN_ADD) BINS_CASE(BIN_MUL) BINS_CASE(BIN_DIV) BINS_CASE(BIN_RELU_GRAD) BINS_CASE(BIN_SUB)
@@ -435,6 +539,20 @@ int tsb_reduce_sum(const float* x, float* y, int nk, const long long* kshape, co
   if (nk == 1 && nr == 1 && kxs[0] == 1 && nkeep <= 65536 && nred >= 64) {
     float* part = colsum_scratch();
     if (part) {
+      if ((nkeep & 3) == 0 && (rxs[0] & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        // scratch: 64 x 65536 floats, so up to 256 chunks for 16384 columns or fewer
+        long long cmax = (64ll * 65536) / nkeep;
+        if (cmax > 256) cmax = 256;
+        long long want = nred / 32;
+        if (want < 1) want = 1;
+        const int chunks = (int)(want < cmax ? want : cmax);
+        const int cols4 = (int)(nkeep / 4);
+        dim3 g1((unsigned)((cols4 + 127) / 128), chunks);
+        colsum_partial_v4<<<g1, 128, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(part),
+                                              nred, cols4, rxs[0] / 4, chunks);
+        colsum_final_lanes<<<(unsigned)((nkeep + 31) / 32), dim3(32, 8), 0, st>>>(part, y, nkeep, chunks, kys[0]);
+        return done();
+      }
       int chunks = (int)(nred / 64 < 64 ? (nred / 64 < 1 ? 1 : nred / 64) : 64);
       dim3 g1((unsigned)((nkeep + 127) / 128), chunks);
       colsum_partial<<<g1, 128, 0, st>>>(x, part, nred, nkeep, rxs[0], chunks);

@@ -391,6 +391,40 @@ __global__ void ln_bwd_params_partial(const float* __restrict__ dy, const float*
   part[PLANE_FLOATS + (long long)ch * D + c] = b;
 }
 
+// 16-byte variant (D a multiple of 4): a thread owns four adjacent columns, two rows in flight.
+__global__ void ln_bwd_params_partial_v4(const float4* __restrict__ dy, const float4* __restrict__ x,
+                                         const float* __restrict__ mean, const float* __restrict__ invstd,
+                                         float* __restrict__ part, long long rows, int D4, int chunks) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int ch = blockIdx.y;
+  if (c >= D4) return;
+  const long long per = (rows + chunks - 1) / chunks;
+  const long long r0 = ch * per, r1 = min(rows, r0 + per);
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, a2 = a, b2 = a;
+  long long r = r0;
+  for (; r + 1 < r1; r += 2) {
+    const float4 g0 = __ldg(dy + r * D4 + c), g1 = __ldg(dy + (r + 1) * D4 + c);
+    const float4 v0 = __ldg(x + r * D4 + c), v1 = __ldg(x + (r + 1) * D4 + c);
+    const float m0 = __ldg(mean + r), m1 = __ldg(mean + r + 1), i0 = __ldg(invstd + r), i1 = __ldg(invstd + r + 1);
+    a.x += g0.x; a.y += g0.y; a.z += g0.z; a.w += g0.w;
+    a2.x += g1.x; a2.y += g1.y; a2.z += g1.z; a2.w += g1.w;
+    b.x += g0.x * (v0.x - m0) * i0; b.y += g0.y * (v0.y - m0) * i0;
+    b.z += g0.z * (v0.z - m0) * i0; b.w += g0.w * (v0.w - m0) * i0;
+    b2.x += g1.x * (v1.x - m1) * i1; b2.y += g1.y * (v1.y - m1) * i1;
+    b2.z += g1.z * (v1.z - m1) * i1; b2.w += g1.w * (v1.w - m1) * i1;
+  }
+  for (; r < r1; ++r) {
+    const float4 g0 = __ldg(dy + r * D4 + c), v0 = __ldg(x + r * D4 + c);
+    const float m0 = __ldg(mean + r), i0 = __ldg(invstd + r);
+    a.x += g0.x; a.y += g0.y; a.z += g0.z; a.w += g0.w;
+    b.x += g0.x * (v0.x - m0) * i0; b.y += g0.y * (v0.y - m0) * i0;
+    b.z += g0.z * (v0.z - m0) * i0; b.w += g0.w * (v0.w - m0) * i0;
+  }
+  const long long o = (long long)ch * (D4 * 4) + 4 * c;
+  *reinterpret_cast<float4*>(part + o) = make_float4(a.x + a2.x, a.y + a2.y, a.z + a2.z, a.w + a2.w);
+  *reinterpret_cast<float4*>(part + PLANE_FLOATS + o) = make_float4(b.x + b2.x, b.y + b2.y, b.z + b2.z, b.w + b2.w);
+}
+
 }  // namespace
 
 extern "C" {
@@ -522,6 +556,21 @@ int tsb_layer_norm_grad(const float* dy, const float* x, const float* scale, con
   ln_bwd_dx<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(dy, x, scale, mean, invstd, dx, rows, (int)D);
   int chunks = (int)((rows + 31) / 32);
   if (chunks > MAX_CHUNKS) chunks = MAX_CHUNKS;
+  if ((D & 3) == 0 && ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+    const int D4 = (int)(D / 4);
+    const int bt = D4 >= 128 ? 128 : (D4 >= 64 ? 64 : 32);
+    // about 16 rows per thread; a plane of partials holds PLANE_FLOATS / D chunks
+    long long c4 = (rows + 15) / 16;
+    if (c4 > PLANE_FLOATS / D) c4 = PLANE_FLOATS / D;
+    if (c4 > 1024) c4 = 1024;
+    chunks = (int)(c4 < 1 ? 1 : c4);
+    dim3 grid4((unsigned)((D4 + bt - 1) / bt), chunks);
+    ln_bwd_params_partial_v4<<<grid4, bt, 0, st>>>(reinterpret_cast<const float4*>(dy),
+                                                   reinterpret_cast<const float4*>(x), mean, invstd, part, rows, D4,
+                                                   chunks);
+    bn_finalize_bwd<<<fin_blocks(D), dim3(32, FIN_LANES), 0, st>>>(part, chunks, (int)D, dscale, dbias);
+    return done();
+  }
   dim3 grid((unsigned)((D + 127) / 128), chunks);
   ln_bwd_params_partial<<<grid, 128, 0, st>>>(dy, x, mean, invstd, part, rows, (int)D, chunks);
   bn_finalize_bwd<<<fin_blocks(D), dim3(32, FIN_LANES), 0, st>>>(part, chunks, (int)D, dscale, dbias);

@@ -354,6 +354,72 @@ __global__ void __launch_bounds__(256) softmax_warp_rows(const float4* __restric
   }
 }
 
+// The same for rows whose length is no multiple of 4 (or whose base is not 16-byte aligned): scalar,
+// still coalesced, lanes; NE elements per lane.
+template <int NE>
+__global__ void __launch_bounds__(256) softmax_warp_rows_scalar(const float* __restrict__ x, float* __restrict__ y,
+                                                                long long rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float* xr = x + row * cols;
+    float v[NE];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      v[j] = i < cols ? __ldg(xr + i) : -FLT_MAX;
+      m = fmaxf(m, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) { v[j] = __expf(v[j] - m); s += v[j]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.f / s;
+    float* yr = y + row * cols;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      if (i < cols) yr[i] = v[j] * inv;
+    }
+  }
+}
+
+template <int NE>
+__global__ void __launch_bounds__(256) softmax_grad_warp_rows_scalar(const float* __restrict__ y,
+                                                                     const float* __restrict__ dy,
+                                                                     float* __restrict__ dx, long long rows,
+                                                                     int cols) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float* yr = y + row * cols;
+    const float* gr = dy + row * cols;
+    float a[NE], g[NE];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      a[j] = i < cols ? __ldg(yr + i) : 0.f;
+      g[j] = i < cols ? __ldg(gr + i) : 0.f;
+      s += a[j] * g[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    float* dr = dx + row * cols;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      if (i < cols) dr[i] = a[j] * (g[j] - s);
+    }
+  }
+}
+
 // Softmax backward, dx = y * (dy - sum(dy * y)): one warp per row, y and dy read once.
 template <int NV>
 __global__ void __launch_bounds__(256) softmax_grad_warp_rows(const float4* __restrict__ y,
@@ -612,6 +678,17 @@ int tsb_softmax(const float* x, float* y, long long rows, long long cols, void* 
     else softmax_warp_rows<8><<<wgrid, 256, 0, st>>>(xv, yv, rows, nvec);
     return done();
   }
+  if (cols <= 1024) {
+    const long long blocks = (rows + 7) / 8;
+    const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+    const int c = (int)cols;
+    if (c <= 64) softmax_warp_rows_scalar<2><<<wgrid, 256, 0, st>>>(x, y, rows, c);
+    else if (c <= 128) softmax_warp_rows_scalar<4><<<wgrid, 256, 0, st>>>(x, y, rows, c);
+    else if (c <= 256) softmax_warp_rows_scalar<8><<<wgrid, 256, 0, st>>>(x, y, rows, c);
+    else if (c <= 512) softmax_warp_rows_scalar<16><<<wgrid, 256, 0, st>>>(x, y, rows, c);
+    else softmax_warp_rows_scalar<32><<<wgrid, 256, 0, st>>>(x, y, rows, c);
+    return done();
+  }
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
   softmax_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, rows, cols);
   return done();
@@ -631,6 +708,17 @@ int tsb_softmax_grad(const float* y, const float* dy, float* dx, long long rows,
     else if (nvec <= 64) softmax_grad_warp_rows<2><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
     else if (nvec <= 128) softmax_grad_warp_rows<4><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
     else softmax_grad_warp_rows<8><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec);
+    return done();
+  }
+  if (cols <= 1024) {
+    const long long blocks = (rows + 7) / 8;
+    const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+    const int c = (int)cols;
+    if (c <= 64) softmax_grad_warp_rows_scalar<2><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c);
+    else if (c <= 128) softmax_grad_warp_rows_scalar<4><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c);
+    else if (c <= 256) softmax_grad_warp_rows_scalar<8><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c);
+    else if (c <= 512) softmax_grad_warp_rows_scalar<16><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c);
+    else softmax_grad_warp_rows_scalar<32><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c);
     return done();
   }
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);

@@ -37,7 +37,7 @@ BATCH_SEPARABLE = {"Conv2d", "Conv2dGradData", "Relu", "ReluGradient", "Add", "M
 #: ops that are cheap enough to rebuild instead of moving their output over the host link
 RECOMPUTABLE = {"Relu", "BatchNorm", "BatchNormRelu", "MaxPool2d", "AvgPool2d", "Add", "Mul", "AddConst", "MulConst", "Reshape",
                 "Transpose", "Dropout", "Concat", "Slice", "Pad", "Sigmoid", "Tanh", "BroadcastTo",
-                "BroadcastShape", "BroadcastToTF", "Conv2dBroadcastTo", "LayerNorm", "Softmax", "Opposite"}
+                "BroadcastShape", "BroadcastToTF", "AddBroadcast", "Conv2dBroadcastTo", "LayerNorm", "Softmax", "Opposite"}
 
 
 def _arr(ctype, values):

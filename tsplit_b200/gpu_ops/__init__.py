@@ -17,7 +17,7 @@ from ..ops.norm import (batch_normalization_op, batch_normalization_gradient_op,
                         batch_normalization_relu_op)
 from ..ops.shape import (array_reshape_op, array_reshape_gradient_op, transpose_op, slice_op,
                          slice_gradient_op, concat_op, concat_gradient_op, pad_op, pad_gradient_op,
-                         broadcastto_op, broadcast_shape_op, broadcasttoTF_op, reduce_sum_op,
+                         broadcastto_op, broadcast_shape_op, broadcasttoTF_op, add_broadcast_op, reduce_sum_op,
                          reducesumaxiszero_op)
 from ..ops.loss import (softmax_func, softmax_op, softmax_gradient_op, softmaxcrossentropy_op,
                         softmaxcrossentropy_gradient_op)

@@ -14,7 +14,7 @@ IMAGE_OPS = {
     "BatchNormGradScale", "BatchNormGradBias", "BatchNormRelu", "BatchNormReluGradient",
 }
 FOLLOW_OPS = {
-    "Add", "Mul", "Div", "ReluGradient", "AddRelu", "ReluOutGradient", "AddConst", "MulConst", "DivConst", "Opposite", "Sqrt", "Rsqrt",
+    "Add", "AddBroadcast", "Mul", "Div", "ReluGradient", "AddRelu", "ReluOutGradient", "AddConst", "MulConst", "DivConst", "Opposite", "Sqrt", "Rsqrt",
     "Sigmoid", "Tanh", "Relu", "Where", "OnesLike", "ZerosLike", "Dropout", "DropoutGradient", "Concat",
     "ConcatGradient", "Slice", "SliceGradient", "Pad", "PadGradient", "Split", "SwapIn", "SwapOut",
 }

@@ -127,6 +127,19 @@ def binary(code, a, b, y, stream):
     _check(rc, "binary")
 
 
+def add_broadcast(x, b, b_strides, y, stream):
+    """y <- x + b, b seen through ``b_strides`` (zeros where it is broadcast) in y's index space."""
+    cols = y.shape[-1]
+    if (x.is_contiguous() and y.is_contiguous() and cols % 4 == 0 and b_strides[-1] == 1
+            and all(s == 0 for s in b_strides[:-1])):
+        rc = lib().tsb_bias_add(_p(x), _p(b), _p(y), c_int64(_numel(y.shape) // cols), c_int64(cols), _s(stream))
+        if rc == 0:
+            return
+        if rc != 2:      # 2: operands not 16-byte aligned, take the strided kernel
+            _check(rc, "bias_add")
+    binary_bcast(BIN_ADD, x.ptr, x.strides, b.ptr, b_strides, y, stream)
+
+
 def binary_bcast(code, a_ptr, a_strides, b_ptr, b_strides, y, stream):
     """Binary op where operand strides (possibly 0) are given for y's shape."""
     shape, (sa, sb, sy) = _collapse(list(y.shape), list(a_strides), list(b_strides), list(y.strides))

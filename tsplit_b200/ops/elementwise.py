@@ -270,6 +270,11 @@ _neg, _sqrt, _rsqrt, _sig, _tanh, _relu, _where = (OppositeOp(), SqrtOp(), Rsqrt
 
 
 def add_op(node_A, node_B):
+    # x + broadcasttoTF_op(b, x): one kernel that reads b through broadcast strides
+    for x, bc in ((node_A, node_B), (node_B, node_A)):
+        if bc.op.name == "BroadcastToTF" and bc.inputs[1] is x and x.op.name != "BroadcastToTF":
+            from .shape import add_broadcast_op
+            return add_broadcast_op(x, bc.inputs[0])
     return _add(node_A, node_B)
 
 

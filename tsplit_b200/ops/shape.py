@@ -445,6 +445,43 @@ class BroadcastToTFOp(Op):
         return tuple(shape)
 
 
+class AddBroadcastOp(Op):
+    """``x + broadcast(b)`` in one kernel.  ``add_op`` builds it for ``x + broadcasttoTF_op(b, x)`` (the
+    bias of a dense layer, an attention mask), so the broadcast is never materialised."""
+    name, cheap = "AddBroadcast", True
+
+    def __call__(self, x, b):
+        return Op.__call__(self, x, b, grad_node=None)
+
+    def np_compute(self, node, iv):
+        return (iv[0] + np.broadcast_to(iv[1], iv[0].shape)).astype(np.float32)
+
+    def gpu_compute(self, node, iv, out, stream):
+        x, b = iv
+        G.add_broadcast(x, b, _bcast_strides(b.shape, b.strides, out.shape), out, stream)
+
+    def gradient(self, node, g):
+        gn = reduce_sum_op(g, None, None)
+        node.attrs["grad_node"] = gn
+        return [g, gn]
+
+    def infer_shape(self, node, s):
+        shape, in_shape = list(s[0]), list(s[1])
+        diff = len(shape) - len(in_shape)
+        assert diff >= 0, "AddBroadcast: %s does not broadcast to %s" % (in_shape, shape)
+        axes, keep = list(range(diff)), [False] * diff
+        padded = [1] * diff + in_shape
+        for i in range(diff, len(shape)):
+            assert padded[i] in (1, shape[i])
+            if padded[i] == 1 and shape[i] > 1:
+                axes.append(i)
+                keep.append(True)
+        gn = node.attrs.get("grad_node")
+        if gn is not None:
+            gn.attrs["axes"], gn.attrs["keepdims"] = axes, keep
+        return tuple(shape)
+
+
 # -- reductions ---------------------------------------------------------------------------------
 class ReduceSumOp(Op):
     name = "ReduceSum"
@@ -520,6 +557,7 @@ _slice, _slice_g, _concat, _concat_g, _pad, _pad_g = (SliceOp(), SliceGradientOp
                                                       ConcatGradientOp(), PadOp(), PadGradientOp())
 _bto, _bshape, _btf, _rsum, _rsum0 = (BroadcastToOp(), BroadcastShapeOp(), BroadcastToTFOp(), ReduceSumOp(),
                                       ReduceSumAxisZeroOp())
+_addb = AddBroadcastOp()
 
 
 def array_reshape_op(node, output_shape):
@@ -568,6 +606,10 @@ def broadcast_shape_op(node_A, shape, add_axes=None):
 
 def broadcasttoTF_op(node_A, node_B):
     return _btf(node_A, node_B)
+
+
+def add_broadcast_op(node_x, node_b):
+    return _addb(node_x, node_b)
 
 
 def reduce_sum_op(node, axes, keepdims=False):
