@@ -297,7 +297,8 @@ def test_embedding_onehot_dropout(ctx):
         gt, = ad.gradients(loss, [t])
         d = ad.dropout_op(x, 0.7, seed=1234)
         gd, = ad.gradients(ad.reduce_sum_op(d, [0, 1]), [x])
-        return {"t": t, "i": i, "x": x}, [e, gt, ad.one_hot_op(i, 50), d, gd]
+        # 50 classes: scalar one-hot kernel; 1032: the 16-byte row kernel
+        return {"t": t, "i": i, "x": x}, [e, gt, ad.one_hot_op(i, 50), d, gd, ad.one_hot_op(i, 1032)]
     both(build, {"t": f32(50, 16), "i": idx, "x": f32(8, 32)}, ctx)
 
 

@@ -44,6 +44,20 @@ __global__ void one_hot_kernel(const float* __restrict__ idx, float* __restrict_
   }
 }
 
+// Rows that are a multiple of four classes long: one block row-slice per row, 16-byte stores, no division
+// per element (grid.y walks the rows, grid.x * blockDim.x the 4-class groups of a row).
+__global__ void one_hot_rows_v4(const float* __restrict__ idx, float4* __restrict__ y, long long n, int k4) {
+  for (long long r = blockIdx.y; r < n; r += gridDim.y) {
+    const long long id = (long long)idx[r];
+    float4* yr = y + r * k4;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < k4; c += gridDim.x * blockDim.x) {
+      const long long c0 = 4ll * c;
+      yr[c] = make_float4(id == c0 ? 1.f : 0.f, id == c0 + 1 ? 1.f : 0.f, id == c0 + 2 ? 1.f : 0.f,
+                          id == c0 + 3 ? 1.f : 0.f);
+    }
+  }
+}
+
 __global__ void embedding_kernel(const float* __restrict__ table, const float* __restrict__ idx,
                                  float* __restrict__ y, long long n, long long vocab, long long dim) {
   const long long total = n * dim;
@@ -220,6 +234,15 @@ int tsb_adam_advance(float* hdev, float b1, float b2, void* stream) {
 
 int tsb_one_hot(const float* idx, float* y, long long n, long long k, void* stream) {
   if (n <= 0 || k <= 0) return TSB_ERR_ARG;
+  if ((k & 3) == 0 && k / 4 < (1ll << 30) && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    const int k4 = (int)(k / 4);
+    int gx = (k4 + 255) / 256;
+    if (gx > 32) gx = 32;
+    long long gy = n < 65535 ? n : 65535;
+    one_hot_rows_v4<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        idx, reinterpret_cast<float4*>(y), n, k4);
+    return done();
+  }
   one_hot_kernel<<<ew_grid(n * k), 256, 0, static_cast<cudaStream_t>(stream)>>>(idx, y, n, k);
   return done();
 }
