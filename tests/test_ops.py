@@ -245,7 +245,8 @@ def test_softmax_backward(ctx, shape):
 
 
 @pytest.mark.parametrize("xs,bs", [((6, 10, 64), (64,)), ((5, 30), (30,)), ((3, 4, 9, 15), (3, 1, 1, 15)),
-                                   ((4, 8, 12), (8, 1)), ((7, 36), (7, 36))])
+                                   ((4, 8, 12), (8, 1)), ((7, 36), (7, 36)), ((3, 2, 5, 100), (3, 1, 1, 100)),
+                                   ((2, 3, 66, 70), (66, 70)), ((2, 3, 9, 255), (2, 1, 1, 255))])
 def test_add_of_a_broadcast_is_one_op(ctx, xs, bs):
     # x + broadcasttoTF_op(b, x) is built as one AddBroadcast node; b's gradient sums over the broadcast axes
     def build():
@@ -256,7 +257,10 @@ def test_add_of_a_broadcast_is_one_op(ctx, xs, bs):
         assert z.op.name == "AddBroadcast"
         loss = ad.reduce_sum_op(ad.mul_op(y, w), list(range(len(xs))))
         gx, gb = ad.gradients(loss, [x, b])
-        return {"x": x, "b": b, "w": w}, [y, z, gx, gb]
+        # the bare broadcast and a product with it run the strided copy / binary kernels (row form when the
+        # innermost dimension is long)
+        bc = ad.broadcasttoTF_op(b, x)
+        return {"x": x, "b": b, "w": w}, [y, z, gx, gb, bc, ad.mul_op(x, bc)]
     both(build, {"x": f32(*xs), "b": f32(*bs), "w": f32(*xs)}, ctx)
 
 

@@ -245,6 +245,30 @@ __global__ void binary_strided(const float* __restrict__ p, const float* __restr
   }
 }
 
+// Row forms of the strided kernels for a long innermost dimension: a warp walks one row, so the outer
+// index is decomposed once per row instead of once per element.  Block = 32 lanes x 8 rows.
+template <int OP>
+__global__ void binary_rows(const float* __restrict__ p, const float* __restrict__ q, float* __restrict__ y,
+                            const Dims o, long long outer, int inner, long long sa, long long sb,
+                            long long sy) {
+  for (long long r = blockIdx.x * (long long)blockDim.y + threadIdx.y; r < outer;
+       r += (long long)gridDim.x * blockDim.y) {
+    long long oa, ob, oy;
+    offsets3(o, r, oa, ob, oy);
+    for (int c = threadIdx.x; c < inner; c += 32) y[oy + c * sy] = bin<OP>(p[oa + c * sa], q[ob + c * sb]);
+  }
+}
+template <int OP>
+__global__ void unary_rows(const float* __restrict__ x, float* __restrict__ y, const Dims o, long long outer,
+                           int inner, float a, long long sx, long long sy) {
+  for (long long r = blockIdx.x * (long long)blockDim.y + threadIdx.y; r < outer;
+       r += (long long)gridDim.x * blockDim.y) {
+    long long ox, oy;
+    offsets2(o, r, ox, oy);
+    for (int c = threadIdx.x; c < inner; c += 32) y[oy + c * sy] = un<OP>(OP == UN_FILL ? 0.f : x[ox + c * sx], a);
+  }
+}
+
 // y[keep] = sum_red x[keep, red].  One warp per output element when the reduced
 // extent is long, otherwise one thread.  Deterministic (fixed order + shuffles).
 struct RDims {
@@ -383,6 +407,10 @@ float* colsum_scratch() {   // 64 chunks x up to 64K columns
 
 #define UN_CASE(OPC) \
   case OPC: unary_flat<OPC><<<grid, 256, 0, st>>>(x, y, n, alpha); break;
+#define UNR_CASE(OPC) \
+  case OPC: unary_rows<OPC><<<rgrid, dim3(32, 8), 0, st>>>(x, y, dr, outer, inner, alpha, xs[nd - 1], ys[nd - 1]); break;
+#define BINR_CASE(OPC) \
+  case OPC: binary_rows<OPC><<<rgrid, dim3(32, 8), 0, st>>>(a, b, y, dr, outer, inner, as[nd - 1], bs[nd - 1], ys[nd - 1]); break;
 #define UNS_CASE(OPC) \
   case OPC: unary_strided<OPC><<<grid, 256, 0, st>>>(x, y, d, n, alpha); break;
 #define BIN_CASE(OPC) \
@@ -484,6 +512,19 @@ int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long*
       return done();
     }
   }
+  if (nd >= 2 && shape[nd - 1] >= 64 && shape[nd - 1] < (1ll << 31)) {
+    const long long outer = n / shape[nd - 1];
+    const int inner = (int)shape[nd - 1];
+    const int rgrid = grid_for(outer * 32, 256);
+    Dims dr = d;
+    dr.nd = nd - 1;
+    switch (op) {
+      UNR_CASE(UN_COPY) UNR_CASE(UN_RELU) UNR_CASE(UN_SIGMOID) UNR_CASE(UN_TANH) UNR_CASE(UN_SQRT)
+      UNR_CASE(UN_RSQRT) UNR_CASE(UN_NEG) UNR_CASE(UN_ADDC) UNR_CASE(UN_MULC) UNR_CASE(UN_CDIV) UNR_CASE(UN_FILL)
+      default: return TSB_ERR_ARG;
+    }
+    return done();
+  }
   const int grid = grid_for(n, 256);
   switch (op) {
     UNS_CASE(UN_COPY) UNS_CASE(UN_RELU) UNS_CASE(UN_SIGMOID) UNS_CASE(UN_TANH) UNS_CASE(UN_SQRT)
@@ -515,6 +556,19 @@ int tsb_strided_binary(int op, const float* a, const float* b, float* y, int nd,
   for (int i = 0; i < nd; ++i) { d.shape[i] = shape[i]; d.s0[i] = as[i]; d.s1[i] = bs[i]; d.s2[i] = ys[i]; n *= shape[i]; }
   if (n <= 0) return TSB_OK;
   d.small = n < (1ll << 32);
+  if (nd >= 2 && shape[nd - 1] >= 64 && shape[nd - 1] < (1ll << 31)) {
+    const long long outer = n / shape[nd - 1];
+    const int inner = (int)shape[nd - 1];
+    const int rgrid = grid_for(outer * 32, 256);
+    Dims dr = d;
+    dr.nd = nd - 1;
+    switch (op) {
+      BINR_CASE(BIN_ADD) BINR_CASE(BIN_MUL) BINR_CASE(BIN_DIV) BINR_CASE(BIN_RELU_GRAD) BINR_CASE(BIN_SUB)
+      BINR_CASE(BIN_ADD_RELU) BINR_CASE(BIN_RELU_GRAD_OUT)
+      default: return TSB_ERR_ARG;
+    }
+    return done();
+  }
   const int grid = grid_for(n, 256);
   switch (op) {
     BINS_CASE(BIN_ADD) BINS_CASE(BIN_MUL) BINS_CASE(BIN_DIV) BINS_CASE(BIN_RELU_GRAD) BINS_CASE(BIN_SUB)
