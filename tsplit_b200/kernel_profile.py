@@ -91,6 +91,26 @@ def single(op, batch, channel, hw, iters):
         a.t.normal_(), b.t.normal_()
         fn = lambda: G.gemm(a, b, out, False, False, st, m=m, n=c * 8, k=c * 8, lda=c * 8, ldb=c * 8, ldc=c * 8)
         work, unit = 2.0 * m * (c * 8) ** 2 / 1e9, "TFLOP/s"
+    elif op in ("softmax", "softmax_grad", "ce_grad"):
+        # rows = batch * channel, row length = hw
+        rows, cols = n * c, hw
+        x, y, z = (ndarray.empty((rows, cols), ctx) for _ in range(3))
+        x.t.normal_(), y.t.normal_()
+        if op == "softmax":
+            fn = lambda: G.softmax(x, z, st)
+            work = 2.0 * x.nbytes / 1e6
+        elif op == "softmax_grad":
+            G.softmax(x, y, st)
+            fn = lambda: G.softmax_grad(y, x, z, st)
+            work = 3.0 * x.nbytes / 1e6
+        else:
+            y.t.zero_()
+            y.t[:, 0] = 1.0
+            g = ndarray.empty((1,), ctx)
+            g.t.fill_(1.0)
+            fn = lambda: G.softmax_ce_grad(x, y, g, z, st)
+            work = 3.0 * x.nbytes / 1e6
+        unit = "GB/s"
     else:
         x = ndarray.empty((n, c, hw, hw), ctx)
         y = ndarray.empty((n, c, hw, hw), ctx)
@@ -124,7 +144,7 @@ def single(op, batch, channel, hw, iters):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu", "conv_fwd", "conv_dgrad",
-                                  "conv_wgrad", "bnrelu_bwd"])
+                                  "conv_wgrad", "bnrelu_bwd", "softmax", "softmax_grad", "ce_grad"])
     p.add_argument("--sweep", default="batch", choices=["batch", "channel", "hw"])
     p.add_argument("--single", action="store_true", help="one configuration (for profiler captures)")
     p.add_argument("--batch", type=int, default=32)
