@@ -106,46 +106,110 @@ def test_optimizer_inside_memory_executor_trains():
     assert losses[-1] < losses[0]
 
 
-def test_tsplit_plan_fits_budget_and_matches_base():
-    batch = 8
-    ref = reference_run(small_cnn, batch, steps=1)
-    peak_keep = base_peak_bytes(small_cnn, batch)
+def _tsplit_case(frac, ref, peak_keep, **kw):
     ctx = ndarray.simgpu(0)
     m = small_cnn()
     grads = ad.gradients(m.loss, m.variables)
-    x, y = m.synthetic_batch(batch, seed=1)
-    cap = int(peak_keep * 0.8)
+    x, y = m.synthetic_batch(8, seed=1)
+    cap = int(peak_keep * frac)
     with use_pool(ctx, cap) as pool:
-        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, host_link_gbs=0.05, max_split=4)
-        outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
-        plan = ex.plan_result
-        assert plan.fits and plan.predicted_peak_bytes <= cap
-        assert pool.stats()["peak"] <= cap
-        c = plan.counts()
-        assert c["swap"] + c["recompute"] > 0
+        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, min_split_bytes=1, **kw)
+        for _ in range(2):
+            pool.reset_peak()
+            outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
+        peak = pool.stats()["peak"]
     for i, (o, r) in enumerate(zip(outs, ref)):
-        assert_close(o, r, rtol=1e-4, what="tsplit output %d" % i)
+        assert_close(o, r, rtol=1e-4, what="tsplit %s output %d" % (kw, i))
+    return ex, peak, cap
 
 
-def test_tsplit_micro_tensors_are_streamed():
-    batch = 8
-    ctx = ndarray.simgpu(0)
+@pytest.mark.parametrize("pieces", [1, 2, 4, 8])
+def test_tsplit_micro_ops_match_base_for_every_piece_count(pieces):
+    """The lowered graph (every operator as `pieces` micro-ops, batch norm as statistics / finalise /
+    normalise stages, reductions accumulated) computes what the whole-batch graph computes."""
+    ref = reference_run(small_cnn, 8)
+    peak_keep = base_peak_bytes(small_cnn, 8)
+    ex, peak, cap = _tsplit_case(1.0, ref, peak_keep, pieces=pieces)
+    assert ex.plan_result.pieces == pieces
+    assert (ex.stats["micro_ops"] > 0) == (pieces > 1)
+    assert ex.stats["micro_ops"] == ex.plan_result.micro_ops
+
+
+def test_tsplit_plan_fits_half_the_keep_all_peak_and_is_replayed_exactly():
+    ref = reference_run(small_cnn, 8)
+    peak_keep = base_peak_bytes(small_cnn, 8)
+    ex, peak, cap = _tsplit_case(0.5, ref, peak_keep, pieces=4, host_link_gbs=0.5)
+    plan = ex.plan_result
+    assert plan.fits and plan.footprint_bytes <= cap
+    assert ex.stats["micro_ops"] > 0
+    assert ex.stats["recomputed_nodes"] + ex.stats["swap_out_bytes"] > 0
+    assert ex.stats["recomputed_nodes"] == plan.rebuilds
+    assert ex.stats["swap_out_bytes"] == plan.swap_out_bytes and ex.stats["swap_in_bytes"] == plan.swap_in_bytes
+    # the step ran inside the region the planner placed it in, plus the results it returns
+    results = sum(int(np.prod(o.shape)) * 4 for o in ex.run.__self__.orig_eval_node_list and
+                  [np.empty(s) for s in [ex.node_to_shape_map[n] for n in ex.eval_node_list]])
+    assert plan.footprint_bytes <= peak <= plan.footprint_bytes + results + 256 * len(ex.eval_node_list)
+    assert peak <= cap
+
+
+def test_tsplit_swaps_micro_tensors_when_the_link_is_fast():
+    """With a host link that costs nothing the planner evicts by copying out; every copied-out micro-tensor
+    is one transfer with its own event, freed at its planned position and fetched back before its use."""
+    ref = reference_run(small_cnn, 8)
+    peak_keep = base_peak_bytes(small_cnn, 8)
+    ex, peak, cap = _tsplit_case(0.5, ref, peak_keep, pieces=4, host_link_gbs=1e6)
+    st = ex.stats
+    assert st["micro_ops"] > 0 and st["micro_transfers"] > 0 and st["swap_out_bytes"] > 0
+    assert st["planned_frees"] == st["micro_transfers"]
+    assert st["swap_in_bytes"] >= st["swap_out_bytes"]
+    assert ex.plan_result.counts()["swap"] > 0
+
+
+def test_tsplit_without_a_fitting_plan_raises_the_typed_error():
     m = small_cnn()
     grads = ad.gradients(m.loss, m.variables)
-    x, y = m.synthetic_batch(batch, seed=1)
-    peak_keep = base_peak_bytes(small_cnn, batch)
-    ref = reference_run(small_cnn, batch, steps=1)
-    with use_pool(ctx, int(peak_keep * 0.8)):
-        # a slow link makes every swapped tensor worth splitting
-        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, host_link_gbs=0.001, max_split=4)
-        ex.TF32_FLOP_PER_MS = 1e13      # make recompute look expensive so the plan prefers swapping
-        ex.HBM_BYTES_PER_MS = 1e3
-        outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
-    assert ex.stats["swap_out_bytes"] > 0
-    if ex.plan_result.counts()["split_tensors"]:
-        assert ex.stats["micro_transfers"] > 0
+    ctx = ndarray.simgpu(0)
+    x, y = m.synthetic_batch(8, seed=1)
+    with use_pool(ctx, 256 << 10):
+        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, min_split_bytes=1)
+        with pytest.raises(ndarray.OutOfHBMBudget):
+            ex.run({m.X: x, m.y_: y})
+
+
+def test_tsplit_dropout_pieces_draw_the_whole_tensor_mask():
+    """A dropout computed piece by piece (and rebuilt piece by piece in backward) uses the mask of the
+    unsplit tensor: the element index counts from the start of the whole tensor."""
+    def build():
+        X, y_ = ad.Variable(name="X"), ad.Variable(name="y_")
+        rs = np.random.RandomState(4)
+        w1 = ad.Variable(name="w1", value=rs.normal(scale=0.3, size=(16, 3, 3, 3)).astype(np.float32))
+        w2 = ad.Variable(name="w2", value=rs.normal(scale=0.1, size=(16, 16, 3, 3)).astype(np.float32))
+        w3 = ad.Variable(name="w3", value=rs.normal(scale=0.1, size=(16 * 4 * 4, 5)).astype(np.float32))
+        h = ad.relu_op(ad.conv2d_op(X, w1, padding=1, stride=1))
+        h = ad.dropout_op(h, 0.6, seed=77)
+        h = ad.relu_op(ad.conv2d_op(h, w2, padding=1, stride=1))
+        h = ad.dropout_op(h, 0.8, seed=78)
+        h = ad.avg_pool2d_op(h, 4, 4, 0, 4)
+        h = ad.array_reshape_op(h, (-1, 16 * 4 * 4))
+        loss = ad.softmaxcrossentropy_op(ad.matmul_op(h, w3), y_)
+        return X, y_, loss, [w1, w2, w3]
+    rs = np.random.RandomState(0)
+    x = rs.standard_normal((8, 3, 16, 16)).astype(np.float32)
+    y = np.eye(5, dtype=np.float32)[rs.randint(0, 5, 8)]
+    ctx = ndarray.simgpu(0)
+    X, y_, loss, ws = build()
+    base = ad.MemoryExecutor([loss] + ad.gradients(loss, ws), ctx=ctx)
+    with use_pool(ctx, 1 << 20) as pool:
+        ref = base.run({X: x, y_: y}, convert_to_numpy_ret_vals=True)
+        keep_all = pool.stats()["peak"]
+    X, y_, loss, ws = build()
+    with use_pool(ctx, 1 << 20):
+        ex = ad.microopExecutor([loss] + ad.gradients(loss, ws), ctx=ctx, pieces=4, min_split_bytes=1, allow_swap=False,
+                                budget_bytes=int(keep_all * 0.6))
+        outs = ex.run({X: x, y_: y}, convert_to_numpy_ret_vals=True)
+    assert ex.stats["micro_ops"] > 0 and ex.stats["recomputed_nodes"] > 0
     for i, (o, r) in enumerate(zip(outs, ref)):
-        assert_close(o, r, rtol=1e-4, what="tsplit output %d" % i)
+        assert_close(o, r, rtol=1e-5, what="dropout under tsplit, output %d" % i)
 
 
 def test_simulator_and_planner_entry_points():

@@ -91,13 +91,16 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
 
 // step_dev (may be null): index of the training step, kept on the device by the executor so that a
 // step replayed from a CUDA graph still draws a new mask; the seed is mixed exactly as on the host.
+// offset: index of x[0] in the whole tensor when x is a batch piece of it (the mask is a function of the
+// element's index in the WHOLE tensor, so a tensor computed piece by piece gets the same mask).
 __global__ void dropout_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float keep,
-                               unsigned long long seed, const unsigned long long* __restrict__ step_dev) {
+                               unsigned long long seed, const unsigned long long* __restrict__ step_dev,
+                               unsigned long long offset) {
   if (step_dev) seed = (seed + 0x632BE5ABull * *step_dev) & 0x7FFFFFFFFFFFFFFFull;
   const float inv = 1.f / keep;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
-    y[i] = uniform01(seed, (unsigned long long)i) < keep ? x[i] * inv : 0.f;
+    y[i] = uniform01(seed, (unsigned long long)i + offset) < keep ? x[i] * inv : 0.f;
 }
 
 // out[r, :] = sum_j vals[j] * dense[col[j], :]   (one warp per sparse row)
@@ -263,10 +266,10 @@ int tsb_embedding_grad(const float* g, const float* idx, float* dtable, long lon
 }
 
 int tsb_dropout(const float* x, float* y, long long n, float keep, unsigned long long seed,
-                const unsigned long long* step_dev, void* stream) {
+                const unsigned long long* step_dev, unsigned long long offset, void* stream) {
   if (n <= 0) return TSB_OK;
   if (!(keep > 0.f)) return TSB_ERR_ARG;
-  dropout_kernel<<<ew_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n, keep, seed, step_dev);
+  dropout_kernel<<<ew_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n, keep, seed, step_dev, offset);
   return done();
 }
 

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(STAT_THREADS)
 col_partial(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mean,
             const float* __restrict__ invstd, float* __restrict__ part, long long rows, int C,
             long long lda, long long ldb, int chunks, int cw, const float* __restrict__ rscale = nullptr,
-            const float* __restrict__ rbias = nullptr) {
+            const float* __restrict__ rbias = nullptr, long long plane = PLANE_FLOATS) {
   __shared__ float4 s0[STAT_THREADS], s1[STAT_THREADS];
   const int rl = STAT_THREADS / cw;               // row lanes
   const int cx = threadIdx.x % cw, ry = threadIdx.x / cw;
@@ -155,7 +155,7 @@ col_partial(const float* __restrict__ a, const float* __restrict__ b, const floa
       t1.x += u1.x; t1.y += u1.y; t1.z += u1.z; t1.w += u1.w;
     }
     float* p0 = part + (long long)ch * C + c;
-    float* p1 = part + PLANE_FLOATS + (long long)ch * C + c;   // second plane
+    float* p1 = part + plane + (long long)ch * C + c;          // second plane
     *reinterpret_cast<float4*>(p0) = t0;
     *reinterpret_cast<float4*>(p1) = t1;
   }
@@ -217,10 +217,10 @@ __global__ void bn_finalize_fwd(const float* __restrict__ part, int chunks, int 
 }
 
 __global__ void bn_finalize_bwd(const float* __restrict__ part, int chunks, int C, float* __restrict__ dscale,
-                                float* __restrict__ dbias) {
+                                float* __restrict__ dbias, long long plane = PLANE_FLOATS) {
   const int c = blockIdx.x * 32 + threadIdx.x;
   double s, ss;
-  reduce_partials(part, chunks, C, c, s, ss);
+  reduce_partials(part, chunks, C, c, s, ss, plane);
   if (threadIdx.y != 0 || c >= C) return;
   dbias[c] = (float)s;
   dscale[c] = (float)ss;
@@ -305,7 +305,7 @@ struct StatGeom {
   int cw, chunks;
   dim3 grid;
 };
-StatGeom stat_geom(long long rows, int C) {
+StatGeom stat_geom(long long rows, int C, long long chunk_cap = 1 << 30) {
   StatGeom g;
   const int c4 = C / 4;
   g.cw = c4 < 32 ? c4 : 32;
@@ -314,6 +314,7 @@ StatGeom stat_geom(long long rows, int C) {
   long long want = (4ll * sm_count() + col_blocks - 1) / col_blocks;
   const long long cap = PLANE_FLOATS / C;
   if (want > cap) want = cap;
+  if (want > chunk_cap) want = chunk_cap;
   if (want > 4096) want = 4096;
   const long long by_rows = (rows + (long long)rl * STAT_UNROLL - 1) / ((long long)rl * STAT_UNROLL);
   if (want > by_rows) want = by_rows;
@@ -532,6 +533,72 @@ int tsb_bn_relu_backward(const float* dy, const float* x, const float* scale, co
   bn_finalize_bwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, sg.chunks, (int)C, dscale, dbias);
   bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, save_mean, save_invstd, dscale, dbias, dx,
                                                         rows, (int)C, lddy, ldx, lddx, 1.f / (float)rows, bias);
+  return done();
+}
+
+// ---- batch norm over batch pieces (micro-tensors) --------------------------------------------------
+// A batch norm whose input exists only one batch piece at a time takes its column sums piece by piece
+// into a caller-owned partial buffer (two planes of `plane` floats; piece j fills chunk rows
+// [chunk_offset, chunk_offset + *chunks_out)), finalises once over all chunk rows with the row count of
+// the whole batch, and then normalises piece by piece with tsb_bn_apply.  The backward pass does the
+// same with (sum dy, sum dy * xhat).  The arithmetic is the one of the whole-batch entries above: the
+// partial sums are combined in double in a fixed order, so the result does not depend on the split.
+int tsb_bn_stats_partial(const float* x, float* part, long long plane, int chunk_offset, int chunk_cap,
+                         long long rows, long long C, long long ldx, int* chunks_out, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0 || !part || !chunks_out || chunk_cap <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4)) return TSB_ERR_UNSUPPORTED;
+  const StatGeom sg = stat_geom(rows, (int)C, chunk_cap);
+  if ((long long)(chunk_offset + sg.chunks) * C > plane) return TSB_ERR_SCRATCH;
+  col_partial<0><<<sg.grid, STAT_THREADS, 0, st>>>(x, nullptr, nullptr, nullptr, part + (long long)chunk_offset * C,
+                                                   rows, (int)C, ldx, 0, sg.chunks, sg.cw, nullptr, nullptr, plane);
+  *chunks_out = sg.chunks;
+  return done();
+}
+
+int tsb_bn_stats_finalize(const float* part, long long plane, int chunks, double count, long long C, float eps,
+                          float momentum, float* mean, float* invstd, float* run_mean, float* run_var,
+                          void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (chunks <= 0 || C <= 0 || count <= 0 || !part) return TSB_ERR_ARG;
+  bn_finalize_fwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, chunks, (int)C, count, eps, momentum, mean,
+                                                                 invstd, run_mean, run_var, plane);
+  return done();
+}
+
+// rscale / rbias non-null: the forward was the fused batch norm + ReLU (dy is masked by the sign of its output).
+int tsb_bn_bwd_partial(const float* dy, const float* x, const float* mean, const float* invstd,
+                       const float* rscale, const float* rbias, float* part, long long plane, int chunk_offset,
+                       int chunk_cap, long long rows, long long C, long long lddy, long long ldx, int* chunks_out,
+                       void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0 || !part || !chunks_out || chunk_cap <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (lddy % 4)) return TSB_ERR_UNSUPPORTED;
+  const StatGeom sg = stat_geom(rows, (int)C, chunk_cap);
+  if ((long long)(chunk_offset + sg.chunks) * C > plane) return TSB_ERR_SCRATCH;
+  col_partial<1><<<sg.grid, STAT_THREADS, 0, st>>>(dy, x, mean, invstd, part + (long long)chunk_offset * C, rows,
+                                                   (int)C, lddy, ldx, sg.chunks, sg.cw, rscale, rbias, plane);
+  *chunks_out = sg.chunks;
+  return done();
+}
+
+int tsb_bn_bwd_finalize(const float* part, long long plane, int chunks, long long C, float* dscale, float* dbias,
+                        void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (chunks <= 0 || C <= 0 || !part) return TSB_ERR_ARG;
+  bn_finalize_bwd<<<fin_blocks(C), dim3(32, FIN_LANES), 0, st>>>(part, chunks, (int)C, dscale, dbias, plane);
+  return done();
+}
+
+// dx of one batch piece from the whole-batch sums; total_count = rows of the WHOLE batch.
+int tsb_bn_bwd_apply(const float* dy, const float* x, const float* scale, const float* rbias, const float* mean,
+                     const float* invstd, const float* dscale, const float* dbias, float* dx, long long rows,
+                     long long C, long long lddy, long long ldx, long long lddx, double total_count, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows <= 0 || C <= 0 || total_count <= 0) return TSB_ERR_ARG;
+  if ((C % 4) || (ldx % 4) || (lddy % 4) || (lddx % 4)) return TSB_ERR_UNSUPPORTED;
+  bn_apply_bwd<<<ew_grid(rows * (C / 4)), 256, 0, st>>>(dy, x, scale, mean, invstd, dscale, dbias, dx, rows, (int)C,
+                                                        lddy, ldx, lddx, (float)(1.0 / total_count), rbias);
   return done();
 }
 

@@ -1,370 +1,756 @@
-// TSplit planner core: timeline simulation of a training step under an HBM
-// budget and a greedy search over per-tensor decisions.
+// TSplit planner: exact replay of a training step's memory behaviour under an HBM
+// budget, and a greedy search over per-(micro-)tensor decisions.
 //
-// The reference ships only the hooks of its planner (per-op Profiler{time,
-// input, output, workspace} structs, src/common/profiler.h:13-22, and swap-cost
-// constants, python/athena/profiler.py:8-14); the planner modules themselves
-// (microopPlanner / microopOptimizer) are absent.  This is a fresh design:
+// The reference ships only the hooks of its planner (per-op Profiler{time, input,
+// output, workspace} structs, src/common/profiler.h:13-22, swap-cost constants,
+// python/athena/profiler.py:8-14, micro-tensor views and the reuse allocation,
+// src/common/c_runtime_api.cc:164-271); the planner modules themselves
+// (microopPlanner / microopOptimizer) are absent.  This is a fresh design.
 //
-//   simulate():  walks the schedule with three clocks (compute, H2D, D2H).  Swap
-//     class tensors are copied out after their last forward use and freed when
-//     the copy ends; they come back at their prefetch trigger (or on demand,
-//     stalling compute).  Drop class tensors are freed at once and rebuilt from
-//     their inputs when needed (cost = producer time, recursively).  A tensor
-//     moved as k micro-tensors exposes only 1/k of its transfer on the critical
-//     path (the consumer starts on the first piece).  Tracks peak bytes and
-//     reports the first position where the budget is exceeded.
+// Input: the schedule of a step, one entry per node in execution order.  When the
+// executor has lowered the graph to micro-ops, every entry is a micro-op and every
+// tensor a micro-tensor, so all decisions below are per micro-tensor.
 //
-//   plan():  while the simulated peak exceeds the budget, look at the peak
-//     position, score every idle candidate there by memory saved per millisecond
-//     of added step time (swap vs. recompute vs. finer micro-tensor split) and
-//     apply the best; then place prefetch triggers by walking back from each
-//     first backward use until the transfer is hidden.
+// Decision per tensor: KEEP, SWAP (copy to pinned host memory, copy back before
+// it is needed) or DROP (free, rebuild from its inputs when needed).  A tensor that
+// is not KEEP leaves the device in EVERY idle gap between two consecutive uses that
+// is long enough, not only between forward and backward: a swapped tensor is copied
+// out once and fetched once per gap, a dropped one is rebuilt once per gap.
+// Rebuilding a tensor uses its inputs, so each rebuild is a (virtual) use of them.
+//
+// derive():   decisions -> a list of events at schedule positions: evict (release
+//             now / start the copy-out), free (the block of a copied-out tensor, at
+//             the position where the copy is expected to be done; the compute stream
+//             waits for the copy's event there, so the order of pool operations does
+//             not depend on copy timing), prefetch (start the copy-in), plus the
+//             final release position of every tensor.
+// simulate(): replays the events against a REAL instance of the pool allocator
+//             (same best-fit, two-ended placement as the executor's arena), with
+//             three clocks (compute, H2D, D2H).  Because the executor performs the
+//             same pool operations in the same order, "fits" is exact, fragmentation
+//             included, and the predicted peak equals the measured one.
+// search():   while the replay fails at some position, pick among the tensors that
+//             are resident but idle there the one with the most bytes freed per
+//             millisecond of added step time (swap while the host link has spare
+//             time, otherwise rebuild), apply, replay again.  Afterwards hand
+//             tensors back while the plan still fits and turn expensive rebuilds
+//             into swaps where the link has room.
 #include <algorithm>
 #include <cstdint>
 #include <cstring>
+#include <cstdio>
+#include <cstdlib>
 #include <limits>
 #include <utility>
 #include <vector>
 
+extern "C" {
+void* tsb_pool_create(int64_t capacity, int64_t alignment);
+void tsb_pool_destroy(void* h);
+int tsb_pool_alloc(void* h, int64_t bytes, int64_t* offset);
+int tsb_pool_alloc_high(void* h, int64_t bytes, int64_t* offset);
+int tsb_pool_free(void* h, int64_t offset);
+void tsb_pool_stats(void* h, int64_t* out);
+}
+
 namespace {
 
 enum { KEEP = 0, SWAP = 1, DROP = 2 };
+enum { F_EVICTABLE = 1, F_RECOMPUTABLE = 2, F_PINNED = 4, F_EXTERNAL = 8 };
+enum { EV_RELEASE = 0, EV_SWAPOUT = 1, EV_FREE = 2, EV_PREFETCH = 3 };
+
+constexpr int MIN_GAP = 3;          // positions between two uses before a tensor may leave in between
 
 struct Graph {
   int n;
   const int64_t* out_bytes;
   const double* time_ms;
-  const int* phase;
-  const int* managed;
-  const int* recomputable;
-  const int* splittable;
-  const int64_t* ws_bytes;
+  const int* flags;
   const int* in_ptr;
   const int* in_idx;
-  const int* pinned;
-  int64_t budget;
-  double bw;   // bytes per ms, per direction
-  std::vector<int> last_use, last_fwd_use, first_bwd_use;
-  int first_bwd;
+  int64_t capacity;        // bytes of the simulated pool (the planning budget)
+  int64_t small_bytes;     // blocks below this size are carved from the top end, like long-lived ones
+  double bw;               // host link, bytes per ms, per direction
+  std::vector<double> t0;  // prefix sums of time_ms: t0[i] = start of position i on an idle machine
+  std::vector<std::vector<int>> real_uses;
+  bool external(int t) const { return (flags[t] & F_EXTERNAL) != 0 || out_bytes[t] <= 0; }
+  double xfer(int t) const { return (double)out_bytes[t] / bw; }
+};
+
+struct Event { int kind, pos, t; };
+
+struct Fetch { int t, q, nu, free_pos; };
+
+struct Events {
+  std::vector<int> last_use;
+  std::vector<std::vector<int>> uses;                  // per tensor, sorted, virtual uses included
+  std::vector<std::vector<std::pair<int, int>>> gaps;  // per tensor: (evict after q, return at nu)
+  std::vector<std::vector<Event>> after, before;       // per position
+  std::vector<Fetch> fetches;                          // every return of a swapped tensor
+  std::vector<Event> flat;
 };
 
 struct Result {
-  double time_ms = 0;
-  int64_t peak = 0;
-  int peak_pos = -1;
-  int first_over = -1;
-  double stall_ms = 0;
+  double time_ms = 0, stall_ms = 0, rebuild_ms = 0;
+  int64_t peak = 0, fail_need = 0, swap_out = 0, swap_in = 0, fail_free = 0, fail_largest = 0;
+  int fail_pos = -1, rebuilds = 0, on_demand = 0, fail_allocs = 0;
   std::vector<int64_t> mem_at;
+  std::vector<char> resident_at_fail;
+  // one entry per planned allocation, in the order the executor performs them
+  struct Block { int t; int born, died; int64_t size; int64_t offset; };
+  std::vector<Block> blocks;
+  std::vector<Event> prefetched;        // the prefetches that were really started, at their positions
+  int64_t footprint = 0;
 };
 
-void liveness(Graph& g) {
-  g.last_use.assign(g.n, -1);
-  g.last_fwd_use.assign(g.n, -1);
-  g.first_bwd_use.assign(g.n, -1);
-  g.first_bwd = g.n;
+void prepare(Graph& g) {
+  g.t0.assign(g.n + 1, 0.0);
+  for (int i = 0; i < g.n; ++i) g.t0[i + 1] = g.t0[i] + g.time_ms[i];
+  g.real_uses.assign(g.n, {});
   for (int i = 0; i < g.n; ++i)
-    if (g.phase[i] != 0) { g.first_bwd = i; break; }
-  for (int i = 0; i < g.n; ++i) {
-    g.last_use[i] = std::max(g.last_use[i], i);
-    g.last_fwd_use[i] = std::max(g.last_fwd_use[i], i < g.first_bwd ? i : -1);
+    for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) {
+      auto& u = g.real_uses[g.in_idx[e]];
+      if (u.empty() || u.back() != i) u.push_back(i);
+    }
+}
+
+bool gap_ok(const Graph& g, int t, int cls, int q, int nu) {
+  if (nu - q < MIN_GAP) return false;
+  if (cls == SWAP) return g.t0[nu] - g.t0[q + 1] >= 1.5 * g.xfer(t);   // the gap has to hide a round trip's half
+  return true;
+}
+
+// `from[t]`: a tensor that is not KEEP leaves the device only in gaps that start at or after this position
+// (its earlier, usually short, gaps stay resident).
+void derive(const Graph& g, const std::vector<int>& cls, const std::vector<int>& from, Events& ev) {
+  const int n = g.n;
+  ev.last_use.assign(n, 0);
+  ev.uses.assign(n, {});
+  ev.gaps.assign(n, {});
+  ev.after.assign(n, {});
+  ev.before.assign(n, {});
+  ev.fetches.clear();
+  ev.flat.clear();
+  std::vector<std::vector<int>> virt(n);
+  for (int t = n - 1; t >= 0; --t) {
+    std::vector<int>& u = ev.uses[t];
+    u = g.real_uses[t];
+    if (!virt[t].empty()) {
+      u.insert(u.end(), virt[t].begin(), virt[t].end());
+      std::sort(u.begin(), u.end());
+      u.erase(std::unique(u.begin(), u.end()), u.end());
+    }
+    ev.last_use[t] = (g.flags[t] & F_PINNED) ? n : (u.empty() ? t : u.back());
+    if (cls[t] == KEEP || g.external(t) || !(g.flags[t] & F_EVICTABLE)) continue;
+    int q = t;
+    for (int nu : u) {
+      if (q >= from[t] && gap_ok(g, t, cls[t], q, nu)) ev.gaps[t].push_back({q, nu});
+      q = nu;
+    }
+    if (cls[t] == DROP)
+      for (auto& gp : ev.gaps[t])
+        for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) {
+          const int in = g.in_idx[e];
+          if (!g.external(in)) virt[in].push_back(gp.second);
+        }
+  }
+  // evictions and planned frees of copied-out blocks
+  struct Out { int t, q, nu; };
+  std::vector<Out> outs;
+  for (int t = 0; t < n; ++t) {
+    bool first = true;
+    for (auto& gp : ev.gaps[t]) {
+      if (cls[t] == SWAP) {
+        if (first) outs.push_back({t, gp.first, gp.second});
+        else ev.after[gp.first].push_back({EV_RELEASE, gp.first, t});
+        ev.fetches.push_back({t, gp.first, gp.second, first ? -1 : gp.first});
+        first = false;
+      } else {
+        ev.after[gp.first].push_back({EV_RELEASE, gp.first, t});
+      }
+    }
+  }
+  std::sort(outs.begin(), outs.end(), [](const Out& a, const Out& b) { return a.q < b.q; });
+  double td2h = 0;
+  std::vector<int> free_pos(n, -1);
+  for (auto& o : outs) {
+    ev.after[o.q].push_back({EV_SWAPOUT, o.q, o.t});
+    const double start = std::max(td2h, g.t0[o.q + 1]);
+    const double done = start + g.xfer(o.t);
+    td2h = done;
+    int p = o.q;
+    while (p + 1 < o.nu - 1 && g.t0[p + 1] < done) ++p;       // first position that ends after the copy
+    free_pos[o.t] = p;
+    ev.after[p].push_back({EV_FREE, p, o.t});
+  }
+  for (auto& f : ev.fetches)
+    if (f.free_pos < 0) f.free_pos = free_pos[f.t];
+  std::sort(ev.fetches.begin(), ev.fetches.end(), [](const Fetch& a, const Fetch& b) { return a.nu < b.nu; });
+}
+
+// Prefetch triggers: as early as the transfer needs to be hidden, but never so early that the tensor
+// would sit in memory the schedule needs.  `mem` is the pool usage per position of a replay in which
+// every swap-in happens on demand; each placed prefetch adds its bytes to the positions it spans.
+void place_prefetch(const Graph& g, Events& ev, std::vector<int64_t> mem) {
+  for (auto& b : ev.before) b.clear();
+  double th2d = 0;
+  int64_t largest = 0;
+  for (int i = 0; i < g.n; ++i) largest = std::max(largest, g.external(i) ? 0 : g.out_bytes[i]);
+  const int64_t limit = g.capacity - 2 * largest;      // early arrivals must not eat the room the next outputs need
+  for (auto& f : ev.fetches) {
+    const double need = g.xfer(f.t);
+    const int64_t bytes = g.out_bytes[f.t];
+    const int earliest = std::max(f.q, f.free_pos) + 1;
+    int trig = f.nu;
+    while (trig > earliest) {
+      if (g.t0[f.nu] - std::max(th2d, g.t0[trig]) >= need * 1.2) break;
+      if (mem[trig - 1] + bytes > limit) break;
+      --trig;
+    }
+    th2d = std::max(th2d, g.t0[trig]) + need;
+    for (int p = trig; p < f.nu; ++p) mem[p] += bytes;
+    ev.before[trig].push_back({EV_PREFETCH, trig, f.t});
+  }
+}
+
+void flatten(Events& ev) {
+  ev.flat.clear();
+  for (size_t p = 0; p < ev.after.size(); ++p) {
+    for (auto& e : ev.before[p]) ev.flat.push_back(e);
+    for (auto& e : ev.after[p]) ev.flat.push_back(e);
+  }
+}
+
+struct Sim {
+  const Graph& g;
+  const std::vector<int>& cls;
+  const Events& ev;
+  const bool record;
+  Result r;
+  std::vector<int64_t> block;           // index into r.blocks (record mode) or 0, -1 = not resident
+  std::vector<char> on_host, evicting, prefetched;
+  std::vector<double> d2h_done, arrival;
+  std::vector<int> queue, temps;
+  std::vector<std::vector<int>> release_at;
+  std::vector<int> leaving;             // leaving[t] == pos + 1: t is released after position pos
+  double tc = 0, th2d = 0, td2h = 0;
+  int64_t in_use = 0;
+  int ops = 0;                          // allocation / release counter: the time axis of the placement
+  int n_alloc = 0;
+  bool failed = false;
+  const std::vector<std::pair<int, int>>* banned = nullptr;   // (tensor, trigger position) prefetches not to start
+  std::vector<int> pf_pos;              // trigger position of the prefetch that brought a tensor in
+  std::pair<int, int> cancel{-1, -1};   // at a failure: the unused prefetch whose use is farthest away
+
+  Sim(const Graph& g_, const std::vector<int>& c, const Events& e, bool rec) : g(g_), cls(c), ev(e), record(rec) {
+    block.assign(g.n, -1);
+    on_host.assign(g.n, 0);
+    evicting.assign(g.n, 0);
+    prefetched.assign(g.n, 0);
+    d2h_done.assign(g.n, 0.0);
+    arrival.assign(g.n, 0.0);
+    r.mem_at.assign(g.n, 0);
+    release_at.assign(g.n, {});
+    leaving.assign(g.n, 0);
+    pf_pos.assign(g.n, -1);
+    for (int t = 0; t < g.n; ++t)
+      if (!g.external(t) && e.last_use[t] < g.n) release_at[e.last_use[t]].push_back(t);
+  }
+
+  int64_t used() const { return in_use; }
+  static int64_t rounded(int64_t b) { return (b + 255) / 256 * 256; }
+
+  bool alloc(int t, int pos) {
+    const int64_t b = rounded(g.out_bytes[t]);
+    if (in_use + b > g.capacity) {
+      if (!failed) {
+        failed = true;
+        r.fail_pos = pos;
+        r.fail_need = b;
+        r.fail_free = g.capacity - in_use;
+        r.fail_allocs = n_alloc;
+        r.fail_largest = r.fail_free;
+        r.resident_at_fail.assign(g.n, 0);
+        for (int i = 0; i < g.n; ++i) r.resident_at_fail[i] = block[i] >= 0 && !evicting[i];
+        int far = -1;
+        for (int i = 0; i < g.n; ++i) {
+          if (block[i] < 0 || !prefetched[i] || pf_pos[i] < 0) continue;
+          int nu = g.n;
+          for (int u : ev.uses[i]) if (u >= pos) { nu = u; break; }
+          if (nu > pos && nu > far) { far = nu; cancel = {i, pf_pos[i]}; }
+        }
+      }
+      return false;
+    }
+    in_use += b;
+    ++ops;
+    ++n_alloc;
+    block[t] = 0;
+    if (record && !(g.flags[t] & F_PINNED)) {
+      block[t] = (int64_t)r.blocks.size();
+      r.blocks.push_back({t, ops, std::numeric_limits<int>::max(), b, 0});
+    }
+    return true;
+  }
+  void release(int t) {
+    if (block[t] < 0) return;
+    if (on_host[t] && d2h_done[t] > tc) { r.stall_ms += d2h_done[t] - tc; tc = d2h_done[t]; }
+    in_use -= rounded(g.out_bytes[t]);
+    ++ops;
+    if (record && !(g.flags[t] & F_PINNED)) r.blocks[block[t]].died = ops;
+    block[t] = -1;
+    evicting[t] = 0;
+    prefetched[t] = 0;
+  }
+  bool swap_in(int t, int pos, bool prefetch) {
+    if (!alloc(t, pos)) return false;
+    const double start = std::max(std::max(th2d, tc), d2h_done[t]);
+    th2d = start + g.xfer(t);
+    arrival[t] = th2d;
+    prefetched[t] = 1;
+    r.swap_in += g.out_bytes[t];
+    if (!prefetch) ++r.on_demand;
+    return true;
+  }
+  bool ensure(int t, int pos) {
+    if (g.external(t)) return true;
+    if (block[t] >= 0) {
+      evicting[t] = 0;          // needed again before its planned free: the block simply stays
+      return true;
+    }
+    if (cls[t] == SWAP && on_host[t]) return swap_in(t, pos, false);
+    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e)
+      if (!ensure(g.in_idx[e], pos)) return false;
+    if (!alloc(t, pos)) return false;
+    wait_inputs(t);
+    tc += g.time_ms[t];
+    r.rebuild_ms += g.time_ms[t];
+    ++r.rebuilds;
+    temps.push_back(t);
+    // inputs that were only needed for this rebuild (they leave after this position anyway and the node
+    // itself does not read them) go at once, so a rebuild chain holds two links at a time, not all of them
+    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) {
+      const int u = g.in_idx[e];
+      if (g.external(u) || block[u] < 0 || leaving[u] != pos + 1) continue;
+      bool direct = false;
+      for (int k = g.in_ptr[pos]; k < g.in_ptr[pos + 1]; ++k) direct |= (g.in_idx[k] == u);
+      if (!direct) release(u);
+    }
+    return true;
+  }
+  void wait_inputs(int i) {
     for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) {
       const int u = g.in_idx[e];
-      g.last_use[u] = std::max(g.last_use[u], i);
-      if (i < g.first_bwd) g.last_fwd_use[u] = std::max(g.last_fwd_use[u], i);
-      else if (g.first_bwd_use[u] < 0) g.first_bwd_use[u] = i;
-    }
-  }
-  for (int i = 0; i < g.n; ++i)
-    if (g.pinned[i]) g.last_use[i] = g.n;
-}
-
-// dropped tensors are rebuilt from their inputs: keep those recoverable long enough
-void extend_sources(const Graph& g, const std::vector<int>& cls, std::vector<int>& last_use) {
-  last_use = g.last_use;
-  for (int i = g.n - 1; i >= 0; --i)
-    if (cls[i] == DROP)
-      for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) {
-        const int u = g.in_idx[e];
-        if (last_use[u] < last_use[i]) last_use[u] = last_use[i];
-      }
-}
-
-Result simulate(const Graph& g, const std::vector<int>& cls, const std::vector<int>& split,
-                const std::vector<int>& prefetch_at) {
-  Result r;
-  r.mem_at.assign(g.n, 0);
-  std::vector<int> last_use;
-  extend_sources(g, cls, last_use);
-  std::vector<char> resident(g.n, 0), on_host(g.n, 0);
-  std::vector<double> arrival(g.n, 0.0);
-  std::vector<std::vector<int>> fetch_at(g.n + 1), release_at(g.n + 1), fwd_release_at(g.n + 1);
-  for (int t = 0; t < g.n; ++t) {
-    if (cls[t] == SWAP && prefetch_at[t] >= 0 && prefetch_at[t] < g.n) fetch_at[prefetch_at[t]].push_back(t);
-    if (last_use[t] < g.n) release_at[last_use[t]].push_back(t);
-    if (cls[t] != KEEP && g.last_fwd_use[t] >= 0) fwd_release_at[g.last_fwd_use[t]].push_back(t);
-  }
-  struct Pending { double when; int64_t bytes; };
-  std::vector<Pending> pending;      // device bytes waiting for their D2H copy
-  double tc = 0, th2d = 0, td2h = 0;
-  int64_t mem = 0;
-  auto reap = [&](double now) {
-    for (size_t k = 0; k < pending.size();) {
-      if (pending[k].when <= now) { mem -= pending[k].bytes; pending[k] = pending.back(); pending.pop_back(); }
-      else ++k;
-    }
-  };
-  auto make_room = [&](int64_t need) {
-    reap(tc);
-    while (mem + need > g.budget && !pending.empty()) {      // wait for the earliest copy-out to finish
-      size_t best = 0;
-      for (size_t k = 1; k < pending.size(); ++k) if (pending[k].when < pending[best].when) best = k;
-      if (pending[best].when > tc) { r.stall_ms += pending[best].when - tc; tc = pending[best].when; }
-      reap(tc);
-    }
-  };
-  auto exposed = [&](int t) { return (double)g.out_bytes[t] / g.bw; };
-  // recursive rebuild cost / residency
-  std::vector<int> stack;
-  auto ensure = [&](int t, auto&& self) -> void {
-    if (resident[t]) { if (arrival[t] > tc) { r.stall_ms += arrival[t] - tc; tc = arrival[t]; } return; }
-    if (on_host[t]) {                                         // on-demand swap-in
-      make_room(g.out_bytes[t]);
-      const double start = std::max(th2d, tc);
-      const double full = exposed(t);
-      th2d = start + full;
-      const double first_piece = start + full / std::max(1, split[t]);
-      mem += g.out_bytes[t];
-      resident[t] = 1;
-      arrival[t] = th2d;
-      if (first_piece > tc) { r.stall_ms += first_piece - tc; tc = first_piece; }
-      return;
-    }
-    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) self(g.in_idx[e], self);
-    make_room(g.out_bytes[t] + g.ws_bytes[t]);
-    mem += g.out_bytes[t];
-    resident[t] = 1;
-    arrival[t] = 0;
-    tc += g.time_ms[t];
-    stack.push_back(t);
-  };
-  for (int i = 0; i < g.n; ++i) {
-    for (int t : fetch_at[i]) {
-      if (resident[t] || !on_host[t]) continue;
-      reap(tc);
-      // leave head-room for what the schedule allocates before the tensor is used
-      int64_t reserve = 0;
-      for (int j = i; j <= g.first_bwd_use[t] && j < g.n; ++j)
-        reserve = std::max(reserve, g.out_bytes[j] + g.ws_bytes[j]);
-      if (mem + g.out_bytes[t] + 2 * reserve > g.budget) continue;   // no room yet: fetched on demand later
-      const double start = std::max(th2d, tc);
-      th2d = start + exposed(t);
-      mem += g.out_bytes[t];
-      resident[t] = 1;
-      arrival[t] = start + exposed(t) / std::max(1, split[t]);   // consumer can start on the first piece
-    }
-    stack.clear();
-    for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) ensure(g.in_idx[e], ensure);
-    make_room(g.out_bytes[i] + g.ws_bytes[i]);
-    mem += g.out_bytes[i];
-    resident[i] = 1;
-    const int64_t with_ws = mem + g.ws_bytes[i];
-    r.mem_at[i] = with_ws;
-    if (with_ws > r.peak) { r.peak = with_ws; r.peak_pos = i; }
-    if (with_ws > g.budget && r.first_over < 0) r.first_over = i;
-    tc += g.time_ms[i] * (1.0 + 0.01 * (std::max(1, split[i]) - 1));
-    for (int t : fwd_release_at[i]) {
-      if (!resident[t]) continue;
-      if (cls[t] == SWAP) {
-        const double start = std::max(td2h, tc - g.time_ms[i] * (1.0 - 1.0 / std::max(1, split[t])));
-        td2h = start + exposed(t);
-        on_host[t] = 1;
-        resident[t] = 0;
-        pending.push_back({td2h, g.out_bytes[t]});
-      } else {
-        resident[t] = 0;
-        mem -= g.out_bytes[t];
+      if (prefetched[u]) {
+        if (arrival[u] > tc) { r.stall_ms += arrival[u] - tc; tc = arrival[u]; }
+        prefetched[u] = 0;
       }
     }
-    for (int t : stack) {      // rebuilt intermediates that nobody needs later
-      bool is_input = false;
-      for (int e = g.in_ptr[i]; e < g.in_ptr[i + 1]; ++e) is_input |= (g.in_idx[e] == t);
-      if (!is_input && resident[t] && last_use[t] <= i) { resident[t] = 0; mem -= g.out_bytes[t]; }
-    }
-    for (int t : release_at[i])
-      if (resident[t]) { resident[t] = 0; mem -= g.out_bytes[t]; on_host[t] = 0; }
   }
-  r.time_ms = std::max(tc, std::max(th2d, td2h));
+  bool admit(int t, int pos) {
+    int64_t largest = 0;
+    int nu = pos;
+    for (int u : ev.uses[t]) if (u >= pos) { nu = u; break; }
+    for (int j = pos; j <= nu && j < g.n; ++j) largest = std::max(largest, g.external(j) ? 0 : g.out_bytes[j]);
+    return in_use + rounded(g.out_bytes[t]) + 2 * largest <= g.capacity;
+  }
+
+  void run() {
+    const int n = g.n;
+    for (int pos = 0; pos < n && !failed; ++pos) {
+      if (g.flags[pos] & F_EXTERNAL) { r.mem_at[pos] = used(); continue; }
+      for (auto& e : ev.before[pos]) queue.push_back(e.t);
+      if (!queue.empty()) {
+        std::vector<int> waiting;
+        for (int t : queue) {
+          if (!on_host[t] || block[t] >= 0) continue;
+          if (banned && std::find(banned->begin(), banned->end(), std::make_pair(t, pos)) != banned->end()) continue;
+          if (!waiting.empty() || !admit(t, pos)) { waiting.push_back(t); continue; }
+          swap_in(t, pos, true);
+          pf_pos[t] = pos;
+          if (record) r.prefetched.push_back({EV_PREFETCH, pos, t});
+        }
+        queue.swap(waiting);
+      }
+      temps.clear();
+      for (auto& e : ev.after[pos]) if (e.kind == EV_RELEASE) leaving[e.t] = pos + 1;
+      for (int t : release_at[pos]) leaving[t] = pos + 1;
+      bool ok = true;
+      for (int e = g.in_ptr[pos]; e < g.in_ptr[pos + 1] && ok; ++e) ok = ensure(g.in_idx[e], pos);
+      if (!ok) break;
+      if (g.out_bytes[pos] > 0 && !alloc(pos, pos)) break;
+      wait_inputs(pos);
+      tc += g.time_ms[pos];
+      const int64_t u = used();
+      r.mem_at[pos] = u;
+      if (u > r.peak) r.peak = u;
+      for (auto& e : ev.after[pos]) {
+        const int t = e.t;
+        if (block[t] < 0) continue;
+        if (e.kind == EV_SWAPOUT) {
+          if (!on_host[t]) {
+            const double start = std::max(td2h, tc);
+            td2h = start + g.xfer(t);
+            d2h_done[t] = td2h;
+            on_host[t] = 1;
+            r.swap_out += g.out_bytes[t];
+          }
+          evicting[t] = 1;
+        } else if (e.kind == EV_FREE) {
+          if (evicting[t]) release(t);
+        } else if (e.kind == EV_RELEASE) {
+          release(t);
+        }
+      }
+      for (int t : release_at[pos]) {      // last (real or virtual) use was here
+        release(t);
+        on_host[t] = 0;
+      }
+    }
+    r.time_ms = std::max(tc, std::max(th2d, td2h));
+  }
+};
+
+// A prefetch that arrives early holds memory the schedule may need before the tensor is used.  When the
+// replay fails while such a tensor sits unused, that prefetch is struck (the tensor then comes on demand,
+// or by a later trigger) and the replay starts over, so early arrivals never are what makes a plan fail.
+Result simulate(const Graph& g, const std::vector<int>& cls, const Events& ev, bool record = false) {
+  std::vector<std::pair<int, int>> banned;
+  for (int round = 0;; ++round) {
+    Sim s(g, cls, ev, record);
+    s.banned = &banned;
+    s.run();
+    if (s.r.fail_pos < 0 || s.cancel.first < 0 || round >= 64) return std::move(s.r);
+    banned.push_back(s.cancel);
+  }
+}
+
+// Offline placement of the recorded allocations (each lives from its allocation to its release on the
+// executor's operation counter): largest first, each at the lowest offset that is free of the blocks
+// already placed whose lifetimes overlap its own.  Because the executor replays exactly this sequence,
+// every block can be given its address ahead of time: no allocator runs during a step and there is no
+// fragmentation beyond what this packing leaves.  Returns the footprint (highest end offset).
+int64_t place(std::vector<Result::Block>& blocks) {
+  const int n = (int)blocks.size();
+  std::vector<int> order(n);
+  for (int i = 0; i < n; ++i) order[i] = i;
+  std::sort(order.begin(), order.end(), [&](int a, int b) {
+    if (blocks[a].size != blocks[b].size) return blocks[a].size > blocks[b].size;
+    return (blocks[a].died - blocks[a].born) > (blocks[b].died - blocks[b].born);
+  });
+  std::vector<int> placed;
+  placed.reserve(n);
+  int64_t footprint = 0;
+  std::vector<std::pair<int64_t, int64_t>> busy;
+  for (int i : order) {
+    Result::Block& b = blocks[i];
+    busy.clear();
+    for (int j : placed) {
+      const Result::Block& o = blocks[j];
+      if (o.born < b.died && b.born < o.died) busy.push_back({o.offset, o.offset + o.size});
+    }
+    std::sort(busy.begin(), busy.end());
+    int64_t off = 0;
+    for (auto& iv : busy) {
+      if (iv.first - off >= b.size) break;
+      off = std::max(off, iv.second);
+    }
+    b.offset = off;
+    footprint = std::max(footprint, off + b.size);
+    placed.push_back(i);
+  }
+  return footprint;
+}
+
+// decisions -> events -> replay.  Two replays: one with every swap-in on demand (its memory curve tells
+// how early each prefetch may start), then the real one.
+Result evaluate(const Graph& g, const std::vector<int>& cls, const std::vector<int>& from, Events& ev,
+                bool record = false) {
+  derive(g, cls, from, ev);
+  if (!ev.fetches.empty()) {
+    Result jit = simulate(g, cls, ev);
+    place_prefetch(g, ev, jit.mem_at);
+  }
+  flatten(ev);
+  Result r = simulate(g, cls, ev, record);
+  if (record) {
+    // the executor follows the plan literally: keep only the prefetches the replay really started, at the
+    // positions where it started them, and give every allocation its address
+    for (auto& b : ev.before) b.clear();
+    for (auto& e : r.prefetched) ev.before[e.pos].push_back(e);
+    flatten(ev);
+    r.footprint = place(r.blocks);
+  }
   return r;
 }
 
-// min_trigger[t] (when >= 0): a tensor swapped to relieve a backward position must not be fetched
-// back before that position has passed.
-void place_prefetch(const Graph& g, const std::vector<int>& cls, std::vector<int>& prefetch_at,
-                    const std::vector<int>& min_trigger) {
-  // cumulative compute time per position
-  std::vector<double> t0(g.n + 1, 0.0);
-  for (int i = 0; i < g.n; ++i) t0[i + 1] = t0[i] + g.time_ms[i];
-  // process in order of first backward use so transfers queue up realistically
-  std::vector<int> order;
-  for (int t = 0; t < g.n; ++t) if (cls[t] == SWAP && g.first_bwd_use[t] >= 0) order.push_back(t);
-  std::sort(order.begin(), order.end(), [&](int a, int b) { return g.first_bwd_use[a] < g.first_bwd_use[b]; });
-  double link_free = 0.0;
-  for (int t : order) {
-    const double need = (double)g.out_bytes[t] / g.bw;
-    const int use = g.first_bwd_use[t];
-    int trig = use;
-    while (trig > g.first_bwd && t0[use] - t0[trig] < need * 1.25) --trig;
-    if (min_trigger[t] >= 0 && trig < min_trigger[t]) trig = std::min(min_trigger[t], use);
-    const double start = std::max(link_free, t0[trig]);
-    link_free = start + need;
-    prefetch_at[t] = trig;
-  }
-}
-
-double rebuild_ms(const Graph& g, const std::vector<int>& cls, int t, int depth = 0) {
-  // producer time plus the time of dropped inputs that would have to be rebuilt first
+double rebuild_cost(const Graph& g, const std::vector<int>& cls, int t, int depth = 0) {
   double ms = g.time_ms[t];
-  if (depth > 64) return ms;
+  if (depth > 48) return ms;
   for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) {
     const int u = g.in_idx[e];
-    if (cls[u] == DROP) ms += rebuild_ms(g, cls, u, depth + 1);
+    if (g.external(u)) continue;
+    if (cls[u] == DROP) ms += rebuild_cost(g, cls, u, depth + 1);
+    else if (cls[u] == SWAP) ms += 0.5 * g.xfer(u);
   }
   return ms;
+}
+
+void write_out(const Graph& g, const std::vector<int>& cls, const Events& ev, const Result& r, int* cls_out,
+               int* last_use_out, int ev_cap, int* ev_kind, int* ev_pos, int* ev_tensor, int* ev_count,
+               int alloc_cap, int* alloc_tensor, int64_t* alloc_offset, int* alloc_count, double* summary,
+               int64_t* mem_at) {
+  if (cls_out) std::memcpy(cls_out, cls.data(), sizeof(int) * g.n);
+  if (last_use_out) std::memcpy(last_use_out, ev.last_use.data(), sizeof(int) * g.n);
+  int c = 0;
+  for (auto& e : ev.flat) {
+    if (c >= ev_cap) break;
+    ev_kind[c] = e.kind; ev_pos[c] = e.pos; ev_tensor[c] = e.t;
+    ++c;
+  }
+  if (ev_count) *ev_count = (int)ev.flat.size();
+  c = 0;
+  for (auto& b : r.blocks) {
+    if (c >= alloc_cap) break;
+    alloc_tensor[c] = b.t; alloc_offset[c] = b.offset;
+    ++c;
+  }
+  if (alloc_count) *alloc_count = (int)r.blocks.size();
+  summary[0] = r.time_ms; summary[1] = (double)r.peak; summary[2] = r.fail_pos; summary[3] = r.stall_ms;
+  summary[4] = (double)r.fail_need; summary[5] = (double)r.swap_out; summary[6] = (double)r.swap_in;
+  summary[7] = r.rebuild_ms; summary[8] = r.rebuilds; summary[9] = r.on_demand;
+  summary[10] = (double)r.fail_free; summary[11] = (double)r.footprint;
+  if (mem_at) std::memcpy(mem_at, r.mem_at.data(), sizeof(int64_t) * g.n);
+}
+
+int64_t pinned_bytes(const Graph& g) {
+  int64_t b = 0;
+  for (int i = 0; i < g.n; ++i)
+    if ((g.flags[i] & F_PINNED) && !g.external(i)) b += (g.out_bytes[i] + 255) / 256 * 256;
+  return b;
 }
 
 }  // namespace
 
 extern "C" {
 
-// Simulate a given plan.  out[0] = step ms, out[1] = peak bytes, out[2] = first position over budget (-1 = fits),
-// out[3] = stall ms, out[4] = peak position.  mem_at (may be null) receives bytes in use at every position.
-int tsb_plan_simulate(int n, const int64_t* out_bytes, const double* time_ms, const int* phase, const int* managed,
-                      const int* recomputable, const int* splittable, const int64_t* ws_bytes, const int* in_ptr,
-                      const int* in_idx, const int* pinned, int64_t budget, double bw_bytes_per_ms, const int* cls,
-                      const int* split, const int* prefetch_at, double* out, int64_t* mem_at) {
-  if (n <= 0 || !out) return 1;
-  Graph g{n, out_bytes, time_ms, phase, managed, recomputable, splittable, ws_bytes, in_ptr, in_idx, pinned, budget,
-          bw_bytes_per_ms, {}, {}, {}, 0};
-  liveness(g);
-  std::vector<int> c(cls, cls + n), s(split, split + n), p(prefetch_at, prefetch_at + n);
-  Result r = simulate(g, c, s, p);
-  out[0] = r.time_ms; out[1] = (double)r.peak; out[2] = r.first_over; out[3] = r.stall_ms; out[4] = r.peak_pos;
-  if (mem_at) std::memcpy(mem_at, r.mem_at.data(), sizeof(int64_t) * n);
-  return 0;
+// Replay the plan (cls = KEEP/SWAP/DROP per schedule entry, from = first position from which a non-KEEP
+// tensor's gaps are evicted; may be null = from the start) in `capacity` bytes.
+// flags: 1 = may be evicted, 2 = may be rebuilt, 4 = never released (a result; allocated by the caller outside
+// the placed region, but counted against the capacity), 8 = external (feeds, parameters).
+// Outputs: last_use[n]; the event list (kind 0 release / 1 start copy-out / 2 free copied-out block / 3 prefetch,
+// position, tensor) in execution order, events "before" a position first; the allocation list in execution
+// order (tensor, byte offset inside the placed region); summary[12] = step ms, peak bytes in use, first failing
+// position (-1 = fits), stall ms, bytes of the failed request, bytes copied out, bytes copied in, rebuild ms,
+// rebuilt tensors, on-demand swap-ins, free bytes at the failure, footprint of the placed region; mem_at[n]
+// (may be null) = bytes in use at every position.
+// Returns 0, or 6 when an output array is too small (the counts then hold the required sizes).
+int tsb_plan2_simulate(int n, const int64_t* out_bytes, const double* time_ms, const int* flags, const int* in_ptr,
+                       const int* in_idx, int64_t capacity, int64_t small_bytes, double bw_bytes_per_ms,
+                       const int* cls_in, const int* from_in, int* last_use_out, int ev_cap, int* ev_kind,
+                       int* ev_pos, int* ev_tensor, int* ev_count, int alloc_cap, int* alloc_tensor,
+                       int64_t* alloc_offset, int* alloc_count, double* summary, int64_t* mem_at) {
+  if (n <= 0 || !summary) return 1;
+  Graph g{n, out_bytes, time_ms, flags, in_ptr, in_idx, capacity, small_bytes, bw_bytes_per_ms, {}, {}};
+  prepare(g);
+  std::vector<int> cls(cls_in, cls_in + n), from(n, 0);
+  if (from_in) from.assign(from_in, from_in + n);
+  Events ev;
+  Result r = evaluate(g, cls, from, ev, true);
+  write_out(g, cls, ev, r, nullptr, last_use_out, ev_cap, ev_kind, ev_pos, ev_tensor, ev_count, alloc_cap,
+            alloc_tensor, alloc_offset, alloc_count, summary, mem_at);
+  return ((int)ev.flat.size() > ev_cap || (int)r.blocks.size() > alloc_cap) ? 6 : 0;
 }
 
-// Search a plan under `budget`.  Writes cls / split / prefetch_at (length n) and the same `out` summary as
-// tsb_plan_simulate for the chosen plan.  Returns 0 when the plan fits, 5 when no plan was found.
-int tsb_plan_search(int n, const int64_t* out_bytes, const double* time_ms, const int* phase, const int* managed,
-                    const int* recomputable, const int* splittable, const int64_t* ws_bytes, const int* in_ptr,
-                    const int* in_idx, const int* pinned, int64_t budget, double bw_bytes_per_ms, int max_split,
-                    int* cls_out, int* split_out, int* prefetch_out, double* out) {
-  if (n <= 0 || !out) return 1;
-  Graph g{n, out_bytes, time_ms, phase, managed, recomputable, splittable, ws_bytes, in_ptr, in_idx, pinned, budget,
-          bw_bytes_per_ms, {}, {}, {}, 0};
-  liveness(g);
-  std::vector<int> cls(n, KEEP), split(n, 1), prefetch(n, -1);
-  Result r = simulate(g, cls, split, prefetch);
+// Search a plan.  Same outputs as tsb_plan2_simulate plus cls_out[n] and from_out[n].  Returns 0 when the plan
+// fits, 5 when no plan was found (the outputs then describe the best attempt), 6 when the event arrays are too
+// small.
+int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, const int* flags, const int* in_ptr,
+                     const int* in_idx, int64_t capacity, int64_t small_bytes, double bw_bytes_per_ms,
+                     int allow_swap, int* cls_out, int* from_out, int* last_use_out, int ev_cap, int* ev_kind,
+                     int* ev_pos, int* ev_tensor, int* ev_count, int alloc_cap, int* alloc_tensor,
+                     int64_t* alloc_offset, int* alloc_count, double* summary, int64_t* mem_at) {
+  if (n <= 0 || !summary) return 1;
+  Graph g{n, out_bytes, time_ms, flags, in_ptr, in_idx, capacity, small_bytes, bw_bytes_per_ms, {}, {}};
+  prepare(g);
+  const int NEVER = std::numeric_limits<int>::max();
+  std::vector<int> cls(n, KEEP), from(n, NEVER);
+  Events ev;
+  Result r;
+  // The search counts bytes; the placement of the final plan may need a little more than its peak.  When
+  // the footprint overshoots the real capacity, search again with the capacity reduced by the overshoot.
+  for (int round = 0; round < 4; ++round) {
+  r = evaluate(g, cls, from, ev);
+  const double total_ms = g.t0[n];
+  double link_ms = 0.0;                       // copy time (one direction) already committed to swaps
+  std::vector<char> no_drop(n, 0), no_swap(n, 0);
+  const bool debug = getenv("TSB_PLAN_DEBUG") != nullptr;
   int guard = 0;
-  double link_ms = 0.0;     // host-link time already committed to earlier swap decisions
-  std::vector<char> tried_drop(n, 0);
-  std::vector<int> min_trigger(n, -1);
-  while (r.first_over >= 0 && guard++ < 4 * n) {
-    const int pos = r.peak_pos >= 0 ? r.first_over : r.first_over;
-    // candidates: managed KEEP tensors that are alive but idle at `pos`, scored by bytes saved per
-    // millisecond of added step time for their cheaper option
-    struct Cand { double score; int t; int cls; };
+  bool retried = false;
+  while (r.fail_pos >= 0 && guard++ < 16 * n) {
+    const int pos = r.fail_pos;
+    struct Cand { double score; int t; int cls; int q; };
     std::vector<Cand> cands;
     for (int t = 0; t < n; ++t) {
-      if (!g.managed[t] || cls[t] != KEEP || out_bytes[t] <= 0) continue;
-      if (!(t < pos && g.last_fwd_use[t] < pos && g.first_bwd_use[t] > pos)) continue;   // idle across pos
-      double idle = 0.0;
-      for (int i = g.last_fwd_use[t] + 1; i < g.first_bwd_use[t]; ++i) idle += time_ms[i];
-      const double xfer = 2.0 * (double)out_bytes[t] / g.bw;
-      // the link is shared: what earlier decisions already occupy cannot hide this transfer
-      const double swap_cost = std::max(0.0, link_ms + xfer - idle) + 0.05 * xfer;
-      cands.push_back({(double)out_bytes[t] / (swap_cost + 1e-3), t, SWAP});
-      if (g.recomputable[t] && !tried_drop[t]) {
-        int uses_bwd = 0;
-        for (int i = g.first_bwd; i < n; ++i)
-          for (int e = in_ptr[i]; e < in_ptr[i + 1]; ++e) uses_bwd += (in_idx[e] == t);
-        const double rec_cost = rebuild_ms(g, cls, t) * std::max(1, std::min(uses_bwd, 2));
-        cands.push_back({(double)out_bytes[t] / (rec_cost + 1e-3), t, DROP});
+      if (!(g.flags[t] & F_EVICTABLE) || g.external(t) || !r.resident_at_fail[t]) continue;
+      // the gap of t that spans `pos`
+      int q = t, nu = -1;
+      for (int u : ev.uses[t]) {
+        if (u >= pos) { nu = u; break; }
+        q = u;
+      }
+      if (nu < 0 || nu == pos || q >= pos) continue;
+      if (cls[t] != KEEP && from[t] <= q) continue;          // this gap is evicted already (too short to count)
+      bool is_input = false;
+      for (int e = g.in_ptr[pos]; e < g.in_ptr[pos + 1]; ++e) is_input |= (g.in_idx[e] == t);
+      if (is_input) continue;
+      int returns = 0, qq = t;
+      for (int u : ev.uses[t]) { if (qq >= q && u - qq >= MIN_GAP) ++returns; qq = u; }
+      returns = std::max(1, returns);
+      const bool may_swap = cls[t] == KEEP || cls[t] == SWAP, may_drop = cls[t] == KEEP || cls[t] == DROP;
+      // a copy-out only helps here when it can finish between the eviction and the failing position
+      if (allow_swap && may_swap && !no_swap[t] && gap_ok(g, t, SWAP, q, nu) &&
+          (cls[t] == SWAP || g.t0[pos] - g.t0[q + 1] >= g.xfer(t))) {
+        const double x = g.xfer(t);
+        const bool room = link_ms + x * returns <= 0.8 * total_ms;
+        const double cost = room ? 0.03 * x * returns : x * (1 + returns);
+        cands.push_back({(double)g.out_bytes[t] / (cost + 1e-3), t, SWAP, q});
+      }
+      if ((g.flags[t] & F_RECOMPUTABLE) && may_drop && !no_drop[t] && gap_ok(g, t, DROP, q, nu)) {
+        const double cost = rebuild_cost(g, cls, t) * returns;
+        cands.push_back({(double)g.out_bytes[t] / (cost + 1e-3), t, DROP, q});
       }
     }
     std::sort(cands.begin(), cands.end(), [](const Cand& a, const Cand& b) { return a.score > b.score; });
     bool accepted = false;
-    for (size_t ci = 0; ci < cands.size() && ci < 24 && !accepted; ++ci) {
+    auto progress = [&](const Result& trial) {
+      // further along: a later position, or at the same one more of its allocations done / more bytes free
+      return trial.fail_pos < 0 || trial.fail_pos > pos ||
+             (trial.fail_pos == pos && (trial.fail_allocs > r.fail_allocs ||
+                                        (trial.fail_allocs == r.fail_allocs && trial.fail_free > r.fail_free)));
+    };
+    for (size_t ci = 0; ci < cands.size() && ci < 256 && !accepted; ++ci) {
       const int t = cands[ci].t;
-      if (cls[t] != KEEP) continue;
+      std::vector<std::pair<int, std::pair<int, int>>> undo{{t, {cls[t], from[t]}}};
       cls[t] = cands[ci].cls;
-      int k = 1;
-      if (cands[ci].cls == SWAP) {
-        // micro-tensor split: pipeline the transfer when it would otherwise be exposed
-        const double xfer1 = (double)out_bytes[t] / g.bw;
-        while (k < max_split && xfer1 / k > 0.25 && g.splittable[t]) k *= 2;
+      from[t] = std::min(from[t], cands[ci].q);
+      Events tev;
+      Result trial = evaluate(g, cls, from, tev);
+      bool better = progress(trial);
+      if (!better && cands[ci].cls == DROP) {
+        // Dropping t alone only moves the bytes to the inputs its rebuild keeps alive.  Drop the chain:
+        // every input (recursively) that stays resident only for that rebuild, down to tensors that are
+        // small next to t, external or not rebuildable.
+        std::vector<int> frontier{t};
+        for (int depth = 0; depth < 8 && !frontier.empty(); ++depth) {
+          std::vector<int> next;
+          for (int x : frontier)
+            for (int e = g.in_ptr[x]; e < g.in_ptr[x + 1]; ++e) {
+              const int u = g.in_idx[e];
+              if (g.external(u) || cls[u] == SWAP) continue;
+              if (!(g.flags[u] & F_EVICTABLE) || !(g.flags[u] & F_RECOMPUTABLE)) continue;
+              if (g.out_bytes[u] * 3 <= g.out_bytes[t]) continue;
+              int last_before = u;                               // last real use before the failing position
+              bool used_at_or_after = false;
+              for (int w : g.real_uses[u]) {
+                if (w < pos) last_before = w; else used_at_or_after = true;
+              }
+              if (cls[u] == DROP && from[u] <= last_before) continue;      // already evicted over this stretch
+              (void)used_at_or_after;
+              undo.push_back({u, {cls[u], from[u]}});
+              cls[u] = DROP;
+              from[u] = std::min(from[u], last_before);
+              next.push_back(u);
+            }
+          frontier.swap(next);
+        }
+        if (undo.size() > 1) {
+          trial = evaluate(g, cls, from, tev);
+          better = progress(trial);
+        }
       }
-      split[t] = k;
-      const int saved_trigger = min_trigger[t];
-      if (cands[ci].cls == SWAP && pos >= g.first_bwd) min_trigger[t] = pos + 1;
-      place_prefetch(g, cls, prefetch, min_trigger);
-      Result trial = simulate(g, cls, split, prefetch);
-      // keep the decision only when it relieves the position that was over budget
-      // ... and does not raise the peak somewhere else (a long rebuild chain in backward can)
-      const bool better = trial.first_over < 0 ||
-                          ((trial.first_over > pos || trial.mem_at[pos] < r.mem_at[pos]) && trial.peak <= r.peak);
+      if (debug)
+        fprintf(stderr, "pos %d cand t=%d cls=%d q=%d chain %zu score %.3g -> fail %d free %lld (was %lld) %s\n", pos, t,
+                cands[ci].cls, cands[ci].q, undo.size(), cands[ci].score, trial.fail_pos, (long long)trial.fail_free,
+                (long long)r.fail_free, better ? "ACCEPT" : "reject");
       if (better) {
-        if (cands[ci].cls == SWAP) link_ms += 2.0 * (double)out_bytes[t] / g.bw;
-        r = trial;
+        if (cands[ci].cls == SWAP) link_ms += g.xfer(t) * std::max<size_t>(1, tev.gaps[t].size());
+        r = std::move(trial);
+        ev = std::move(tev);
         accepted = true;
       } else {
-        if (cands[ci].cls == DROP) tried_drop[t] = 1;   // rebuilding it only moves the bytes to its inputs
-        cls[t] = KEEP;
-        split[t] = 1;
-        min_trigger[t] = saved_trigger;
+        (cands[ci].cls == DROP ? no_drop : no_swap)[t] = 1;
+        for (auto& u : undo) { cls[u.first] = u.second.first; from[u.first] = u.second.second; }
       }
     }
-    if (!accepted) break;      // the peak is the op's own working set: nothing idle left to evict
+    if (!accepted && !retried) {        // decisions taken since may have made a rejected candidate useful
+      retried = true;
+      std::fill(no_drop.begin(), no_drop.end(), 0);
+      std::fill(no_swap.begin(), no_swap.end(), 0);
+      continue;
+    }
+    if (accepted) retried = false;
+    if (!accepted) break;       // what is resident at the failing position is all in use there
   }
-  place_prefetch(g, cls, prefetch, min_trigger);
-  r = simulate(g, cls, split, prefetch);
-  // The greedy loop takes the biggest savers first and usually overshoots: give tensors back while the
-  // plan still fits, the ones that cost the most step time first.
-  if (r.first_over < 0) {
+  if (r.fail_pos < 0) {
+    // 1. hand tensors back while the plan still fits and does not get slower, most expensive first
     std::vector<std::pair<double, int>> evicted;
     for (int t = 0; t < n; ++t) {
       if (cls[t] == KEEP) continue;
-      const double cost = cls[t] == DROP ? rebuild_ms(g, cls, t) : 2.0 * (double)out_bytes[t] / g.bw;
+      const double cost = cls[t] == DROP ? rebuild_cost(g, cls, t) * std::max<size_t>(1, ev.gaps[t].size())
+                                         : g.xfer(t) * (1 + ev.gaps[t].size()) * 0.25;
       evicted.push_back({cost, t});
     }
-    std::sort(evicted.begin(), evicted.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) {
-      return a.first > b.first;
-    });
+    std::sort(evicted.begin(), evicted.end(),
+              [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
+    int tries = 0;
     for (auto& e : evicted) {
-      const int t = e.second, was = cls[t], was_split = split[t];
+      if (++tries > 192) break;
+      const int t = e.second, was = cls[t], was_from = from[t];
       cls[t] = KEEP;
-      split[t] = 1;
-      place_prefetch(g, cls, prefetch, min_trigger);
-      Result trial = simulate(g, cls, split, prefetch);
-      // leave 12 % of the budget free: measured peaks run about 5 % above the simulated ones (allocation
-      // granularity, fragmentation), and a plan whose peak touches the budget needs an unplanned spill
-      if (trial.first_over < 0 && trial.time_ms <= r.time_ms + 1e-9 &&
-          (double)trial.peak <= 0.88 * (double)budget) {
-        r = trial;
-      } else {
-        cls[t] = was;
-        split[t] = was_split;
+      from[t] = NEVER;
+      Events tev;
+      Result trial = evaluate(g, cls, from, tev);
+      if (trial.fail_pos < 0 && trial.time_ms <= r.time_ms + 1e-9) { r = std::move(trial); ev = std::move(tev); }
+      else { cls[t] = was; from[t] = was_from; }
+    }
+    // 2. expensive rebuilds become swaps where that shortens the step
+    if (allow_swap) {
+      std::vector<std::pair<double, int>> dropped;
+      for (int t = 0; t < n; ++t)
+        if (cls[t] == DROP) dropped.push_back({rebuild_cost(g, cls, t) * std::max<size_t>(1, ev.gaps[t].size()), t});
+      std::sort(dropped.begin(), dropped.end(),
+                [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
+      tries = 0;
+      for (auto& e : dropped) {
+        if (++tries > 96) break;
+        const int t = e.second;
+        cls[t] = SWAP;
+        Events tev;
+        Result trial = evaluate(g, cls, from, tev);
+        if (!tev.gaps[t].empty() && trial.fail_pos < 0 && trial.time_ms < r.time_ms - 1e-6) {
+          r = std::move(trial);
+          ev = std::move(tev);
+        } else {
+          cls[t] = DROP;
+        }
       }
     }
-    place_prefetch(g, cls, prefetch, min_trigger);
-    r = simulate(g, cls, split, prefetch);
   }
-  std::memcpy(cls_out, cls.data(), sizeof(int) * n);
-  std::memcpy(split_out, split.data(), sizeof(int) * n);
-  std::memcpy(prefetch_out, prefetch.data(), sizeof(int) * n);
-  out[0] = r.time_ms; out[1] = (double)r.peak; out[2] = r.first_over; out[3] = r.stall_ms; out[4] = r.peak_pos;
-  return r.first_over < 0 ? 0 : 5;
+  r = evaluate(g, cls, from, ev, true);
+  if (r.fail_pos >= 0) break;
+  const int64_t room = capacity - pinned_bytes(g);
+  if (r.footprint <= room) break;
+  if (round == 3) { r.fail_pos = 0; break; }                 // could not be packed: reported as not fitting
+  g.capacity = (int64_t)((double)g.capacity * (double)room / (double)r.footprint * 0.995);
+  }
+  for (int t = 0; t < n; ++t)
+    if (from[t] == NEVER) from[t] = 0;
+  if (from_out) std::memcpy(from_out, from.data(), sizeof(int) * n);
+  write_out(g, cls, ev, r, cls_out, last_use_out, ev_cap, ev_kind, ev_pos, ev_tensor, ev_count, alloc_cap,
+            alloc_tensor, alloc_offset, alloc_count, summary, mem_at);
+  if ((int)ev.flat.size() > ev_cap || (int)r.blocks.size() > alloc_cap) return 6;
+  return r.fail_pos < 0 ? 0 : 5;
 }
 
 }  // extern "C"

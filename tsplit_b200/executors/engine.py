@@ -134,7 +134,7 @@ class MemoryExecutor(Executor):
         self.swapin_event = {}        # node -> event of an in-flight H2D copy
         self.lru = OrderedDict()      # lazy-evict cache: node -> True (MRU last)
         self._prefetch_queue = []
-        self.locked = set()
+        self.locked = {}              # node -> lock count (an input of the running node and of a nested rebuild)
         self.stats = dict(swap_out_bytes=0, swap_in_bytes=0, recomputed_nodes=0, evictions=0,
                           peak_bytes=0, prefetch_hits=0, on_demand_swapins=0)
 
@@ -199,12 +199,19 @@ class MemoryExecutor(Executor):
         for s in self.streams:
             s.sync()
         self._reap(True)
-        moves = pool.compact()
+        # every live block has to be one this executor can re-bind: results still held by the caller,
+        # another executor's arrays or blocks awaiting a planned free would keep a stale address
+        mine = {a._block for a in self.arr.values()
+                if isinstance(a, ndarray.NDArray) and a._pool is pool and a._block is not None}
+        if pool.live_blocks() - mine:
+            return False
+        moves = pool.compact(stream=self.stream)
         if not moves:
             return False
         for a in self.arr.values():
             if isinstance(a, ndarray.NDArray) and a._pool is pool and a._block in moves:
                 a._rebind(moves[a._block])
+        self.stream.sync()          # the moved bytes have landed before anything is launched on them
         self.stats["compactions"] = self.stats.get("compactions", 0) + 1
         return True
 
@@ -256,6 +263,16 @@ class MemoryExecutor(Executor):
         self._release(best)
         self.stats["evictions"] += 1
         return True
+
+    def _lock(self, node):
+        self.locked[node] = self.locked.get(node, 0) + 1
+
+    def _unlock(self, node):
+        c = self.locked.get(node, 0) - 1
+        if c <= 0:
+            self.locked.pop(node, None)
+        else:
+            self.locked[node] = c
 
     def _host_buffer(self, node):
         h = self.host_bufs.get(node)
@@ -359,7 +376,7 @@ class MemoryExecutor(Executor):
         assert node.inputs, "tensor %s was released and cannot be rebuilt" % node.desc
         for i in node.inputs:
             self._ensure(i, temps)
-            self.locked.add(i)
+            self._lock(i)
         out = self._alloc(node)
         self.arr[node] = out
         state = getattr(node, "state", None)
@@ -371,7 +388,7 @@ class MemoryExecutor(Executor):
             if isinstance(state, dict):
                 state.pop("rematerialise", None)
         for i in node.inputs:
-            self.locked.discard(i)
+            self._unlock(i)
         self.stats["recomputed_nodes"] += 1
         temps.append(node)
         self._log("recompute", node)
@@ -524,14 +541,14 @@ class MemoryExecutor(Executor):
             temps = []
             for i in node.inputs:
                 self._ensure(i, temps)
-                self.locked.add(i)
+                self._lock(i)
             shape = self.node_to_shape_map[node]
             out = self._alloc(node) if shape is not None else None
             if out is not None:
                 self.arr[node] = out
             self._launch(node, out)
             for i in node.inputs:
-                self.locked.discard(i)
+                self._unlock(i)
             self._after_node(idx, node, temps)
 
     def _room_for_prefetch(self, t, idx):
@@ -589,9 +606,7 @@ class MemoryExecutor(Executor):
                 self._release(node, final=True)
 
     # ------------------------------------------------------------------ cost model
-    TF32_FLOP_PER_MS = 7.0e11       # sustained tensor-core rate of the wide-tile convolution / GEMM kernels
-    HBM_BYTES_PER_MS = 5.5e9        # what the batch-norm / pooling / elementwise passes reach
-    LAUNCH_MS = 0.004
+    from ..profiler import FLOPS_PER_MS as TF32_FLOP_PER_MS, HBM_BYTES_PER_MS, LAUNCH_MS
 
     def profile_ops(self):
         """Per-node time in ms.  Static roofline estimate (the reference's
@@ -606,7 +621,8 @@ class MemoryExecutor(Executor):
                 est[n] = measured[n]
                 continue
             out = self.node_to_shape_map.get(n)
-            ins = [self.node_to_shape_map.get(i) for i in n.inputs]
+            # a micro-op states the shapes its operator really sees (batch pieces of whole inputs)
+            ins = n.attrs.get("op_in_shapes") or [self.node_to_shape_map.get(i) for i in n.inputs]
             try:
                 fl = float(n.op.flops(n, ins, out))
             except Exception:

@@ -3,41 +3,48 @@
 The reference imports ``microopExecutor`` / ``microopOptimizer`` /
 ``microopPlanner`` (``gpu_ops/__init__.py:9``, ``examples/imagenet_vgg.py:4-5,
 123-130``) but does not ship them; only their runtime hooks exist (micro-tensor
-views ``src/common/c_runtime_api.cc:212-271``, swap events on every array
-``python/athena/ndarray.py:94-119``, per-op profiler structs).  This module is a
-fresh implementation on top of the plan-driven engine:
+views ``src/common/c_runtime_api.cc:212-271``, the input/output overlap allocation
+``c_runtime_api.cc:164-210``, swap events on every array
+``python/athena/ndarray.py:94-119``, ``SplitOp``, per-op profiler structs).  This
+module is a fresh implementation on top of the plan-driven engine:
 
 * ``microopPlanner``   (policy name ``planner``)   — builds the plan only;
 * ``microopOptimizer`` (policy name ``simulator``) — dry run: predicted step
-  time, peak bytes and feasibility from the native timeline simulator;
+  time, peak bytes and feasibility from the native replay;
 * ``microopExecutor``  (policy name ``tsplit``)    — plans, then runs.
 
-Plan = per forward tensor {keep | swap | recompute}, a micro-tensor count k for
-swapped tensors, and a prefetch trigger.  A tensor with k > 1 moves over the
-host link as k batch slices with one event each; batch-separable consumers
-(convolution forward / data gradient, ReLU and its gradient, pooling, add,
-dropout) then run as k micro-ops, each waiting only for its own slice, so the
-transfer of slice j+1 overlaps the compute on slice j.
+Planning, once per feed shape:
+
+1. the differentiated graph is lowered to micro-ops over k batch pieces
+   (``lowering.py``): operators run piece by piece, every piece of every tensor is
+   a tensor of its own (a micro-tensor);
+2. the native planner (``csrc/planner/planner.cc``) decides keep / swap /
+   recompute per micro-tensor by replaying the step against the real pool
+   allocator, and returns the plan as a list of events at schedule positions
+   (release, start copy-out, free copied-out block, prefetch);
+3. k is chosen among powers of two: the smallest predicted step time among the
+   plans that fit.
+
+Execution follows the event list literally.  A copied-out block is freed at its
+planned position after the compute stream has been made to wait for the copy's
+event, so the sequence of pool operations — and with it the placement of every
+block — is the one the planner replayed, whatever the copy timing.
 """
 from __future__ import annotations
 
-import ctypes
-from ctypes import c_double, c_int, c_int64
+from ctypes import byref, c_double, c_int, c_int64
 
 import numpy as np
 
 from .. import _base, ndarray
+from ..ndarray import OutOfHBMBudget
 from ..ops.misc import PlaceholderOp
 from ..stream import Event
+from . import lowering
 from .engine import MemoryExecutor, KEEP, SWAP, DROP
 
-#: ops whose batch slices can be computed independently (all batch-sized inputs are sliced alike)
-BATCH_SEPARABLE = {"Conv2d", "Conv2dGradData", "Relu", "ReluGradient", "Add", "Mul", "MaxPool2d", "AvgPool2d",
-                   "MaxPool2dGradient", "AvgPool2dGradient", "Dropout", "DropoutGradient", "AddConst", "MulConst"}
-#: ops that are cheap enough to rebuild instead of moving their output over the host link
-RECOMPUTABLE = {"Relu", "BatchNorm", "BatchNormRelu", "MaxPool2d", "AvgPool2d", "Add", "Mul", "AddConst", "MulConst", "Reshape",
-                "Transpose", "Dropout", "Concat", "Slice", "Pad", "Sigmoid", "Tanh", "BroadcastTo",
-                "BroadcastShape", "BroadcastToTF", "AddBroadcast", "Conv2dBroadcastTo", "LayerNorm", "Softmax", "Opposite"}
+F_EVICTABLE, F_RECOMPUTABLE, F_PINNED, F_EXTERNAL = 1, 2, 4, 8
+EV_RELEASE, EV_SWAPOUT, EV_FREE, EV_PREFETCH = 0, 1, 2, 3
 
 
 def _arr(ctype, values):
@@ -45,46 +52,91 @@ def _arr(ctype, values):
 
 
 class Plan(object):
-    """Outcome of planning: decisions per schedule position and the simulator's
-    prediction for them."""
+    """Outcome of planning: per-tensor decisions, the event list and the replay's prediction."""
 
-    def __init__(self, cls, split, prefetch, summary, fits):
-        self.cls, self.split, self.prefetch = cls, split, prefetch
+    def __init__(self, cls, last_use, events, summary, fits, pieces=1, micro_ops=0):
+        self.cls, self.last_use, self.events = cls, last_use, events
         self.predicted_ms, self.predicted_peak_bytes = summary[0], int(summary[1])
-        self.first_over_budget, self.stall_ms, self.peak_position = int(summary[2]), summary[3], int(summary[4])
+        self.first_over_budget, self.stall_ms = int(summary[2]), summary[3]
+        self.fail_need_bytes = int(summary[4])
+        self.swap_out_bytes, self.swap_in_bytes = int(summary[5]), int(summary[6])
+        self.rebuild_ms, self.rebuilds, self.on_demand = summary[7], int(summary[8]), int(summary[9])
         self.fits = fits
+        self.fail_free_bytes = int(summary[10])
+        self.footprint_bytes = int(summary[11])
+        self.allocs = []
+        self.pieces = pieces
+        self.micro_ops = micro_ops
+        self.memory_curve = None
 
     def counts(self):
         return {"keep": self.cls.count(KEEP), "swap": self.cls.count(SWAP), "recompute": self.cls.count(DROP),
-                "split_tensors": sum(1 for k in self.split if k > 1)}
+                "pieces": self.pieces, "micro_ops": self.micro_ops,
+                "split_tensors": self.micro_ops}
 
     def __repr__(self):
-        return "Plan(%s, predicted %.2f ms, peak %.1f MB, fits=%s)" % (
-            self.counts(), self.predicted_ms, self.predicted_peak_bytes / 2**20, self.fits)
+        return ("Plan(%s, predicted %.2f ms, peak %.1f MB in a placed region of %.1f MB, swap out/in %.0f/%.0f MB, "
+                "rebuilds %d, fits=%s)" % (
+                    self.counts(), self.predicted_ms, self.predicted_peak_bytes / 2**20, self.footprint_bytes / 2**20,
+                    self.swap_out_bytes / 2**20, self.swap_in_bytes / 2**20, self.rebuilds, self.fits))
 
 
 class microopExecutor(MemoryExecutor):
     policy_name = "tsplit"
     spill_on_pressure = True
+    recompute_mode = "planned"
 
     def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None,
-                 host_link_gbs=50.0, max_split=8, trace=None, use_graph=False):
+                 host_link_gbs=None, max_split=16, trace=None, use_graph=False, pieces=None,
+                 min_split_bytes=None, allow_swap=True):
         MemoryExecutor.__init__(self, eval_node_list, ctx=ctx, streams=streams, policy=policy,
                                 budget_bytes=budget_bytes, trace=trace, use_graph=use_graph)
-        self.host_link_gbs = float(host_link_gbs)
+        from ..profiler import HOST_LINK_GBS
+        self.host_link_gbs = float(host_link_gbs if host_link_gbs is not None else HOST_LINK_GBS)
         self.max_split = int(max_split)
+        self.fixed_pieces = pieces           # None: chosen by the planner
+        self.min_split_bytes = min_split_bytes
+        self.allow_swap = bool(allow_swap)
         self.plan_result = None
-        self.split = {}
-        #: every forward op may be rebuilt (the planner prices it by the op's time); False restricts
-        #: recomputation to the cheap, memory-bound operators
-        self.recompute_any = True
+        self.lowered = None
+        self.orig_topo_order = list(self.topo_order)
+        self.orig_eval_node_list = list(self.eval_node_list)
+
+    # ------------------------------------------------------------------ shapes / lowering
+    def infer_shape(self, feed_shapes):
+        """Shapes are inferred on the original graph; the plan then installs the lowered schedule."""
+        self.topo_order = self.orig_topo_order
+        self.eval_node_list = self.orig_eval_node_list
+        MemoryExecutor.infer_shape(self, feed_shapes)
+        self.orig_shapes, self.orig_layout = self.node_to_shape_map, self.node_layout
+        self._graph_ok = None
+
+    def _install(self, low):
+        self.lowered = low
+        self.topo_order = low.order
+        self.node_to_shape_map = low.shapes
+        self.node_layout = low.layout
+        self.eval_node_list = low.evals
+        self.index = {n: i for i, n in enumerate(self.topo_order)}
+
+    def _lower(self, k):
+        msb = self.min_split_bytes
+        if msb is None:
+            msb = max(self._budget() // 256, 1 << 20)
+        return lowering.lower(self.orig_topo_order, self.orig_shapes, self.orig_layout, self.orig_eval_node_list,
+                              self.feed_shapes, k, msb)
 
     # ------------------------------------------------------------------ planning
     def _budget(self):
         if self.budget_bytes is not None:
             return int(self.budget_bytes)
         pool = ndarray.get_pool(self.ctx)
-        return int(pool.capacity * 0.9) if pool is not None else 1 << 62
+        return int(pool.capacity) if pool is not None else 1 << 60
+
+    def _small_bytes(self):
+        pool = ndarray.get_pool(self.ctx)
+        cap = pool.capacity if pool is not None else self._budget()
+        return (cap + 255) // 256
 
     def planning_budget(self):
         return self._budget()
@@ -94,180 +146,310 @@ class microopExecutor(MemoryExecutor):
         idx = self.index
         ms = self.profile_ops()
         evals = set(self.eval_node_list)
-        managed = set(self.managed)
-        out_bytes, time_ms, phase, mg, rc, sp, ws, pinned = [], [], [], [], [], [], [], []
+        low = self.lowered
+        out_bytes, time_ms, flags = [], [], []
         in_ptr, in_idx = [0], []
         for n in order:
             external = isinstance(n.op, PlaceholderOp) or n in self.feed_shapes
-            out_bytes.append(0 if external else self.tensor_bytes(n))
+            shp = self.node_to_shape_map.get(n)
+            f = 0
+            if external:
+                f |= F_EXTERNAL
+            elif shp is not None:
+                if n in evals:
+                    f |= F_PINNED
+                elif n not in low.no_evict:
+                    f |= F_EVICTABLE
+                    if n not in low.no_rebuild and n.inputs:
+                        f |= F_RECOMPUTABLE
+            out_bytes.append(0 if external or shp is None else self.tensor_bytes(n))
             time_ms.append(float(ms.get(n, 0.0)))
-            phase.append(0 if self.is_fwd[n] else 1)
-            mg.append(1 if n in managed else 0)
-            rc.append(1 if (n.op.name in RECOMPUTABLE or self.recompute_any) else 0)
-            batch_like = self.node_to_shape_map[n] is not None and len(self.node_to_shape_map[n]) >= 1
-            sp.append(1 if batch_like else 0)
-            try:
-                w = n.op.workspace_bytes(n, [self.node_to_shape_map[i] for i in n.inputs],
-                                         self.node_to_shape_map[n])
-            except Exception:
-                w = 0
-            ws.append(int(w))
-            pinned.append(1 if n in evals else 0)
+            flags.append(f)
             for i in n.inputs:
                 in_idx.append(idx[i])
             in_ptr.append(len(in_idx))
-        return dict(n=len(order), out_bytes=out_bytes, time_ms=time_ms, phase=phase, managed=mg,
-                    recomputable=rc, splittable=sp, ws=ws, in_ptr=in_ptr, in_idx=in_idx or [0], pinned=pinned)
+        return dict(n=len(order), out_bytes=out_bytes, time_ms=time_ms, flags=flags, in_ptr=in_ptr,
+                    in_idx=in_idx or [0])
 
-    def search_plan(self):
+    def _call_planner(self, cls_in=None, budget=None, from_in=None):
         g = self._graph_arrays()
         n = g["n"]
         lib = _base.runtime()
-        cls, split, pre = (c_int * n)(), (c_int * n)(), (c_int * n)()
-        out = (c_double * 5)()
-        rc = lib.tsb_plan_search(
-            c_int(n), _arr(c_int64, g["out_bytes"]), _arr(c_double, g["time_ms"]), _arr(c_int, g["phase"]),
-            _arr(c_int, g["managed"]), _arr(c_int, g["recomputable"]), _arr(c_int, g["splittable"]),
-            _arr(c_int64, g["ws"]), _arr(c_int, g["in_ptr"]), _arr(c_int, g["in_idx"]), _arr(c_int, g["pinned"]),
-            c_int64(self._budget()), c_double(self.host_link_gbs * 1e6), c_int(self.max_split), cls, split, pre,
-            out)
+        cap = 64 * (len(g["in_idx"]) + n) + 64
+        acap = 32 * n + 64
+        while True:
+            cls, last, frm = (c_int * n)(), (c_int * n)(), (c_int * n)()
+            ek, ep, et = (c_int * cap)(), (c_int * cap)(), (c_int * cap)()
+            at, ao = (c_int * acap)(), (c_int64 * acap)()
+            cnt, acnt = c_int(0), c_int(0)
+            summ = (c_double * 12)()
+            mem = (c_int64 * n)()
+            common = (c_int(n), _arr(c_int64, g["out_bytes"]), _arr(c_double, g["time_ms"]), _arr(c_int, g["flags"]),
+                      _arr(c_int, g["in_ptr"]), _arr(c_int, g["in_idx"]),
+                      c_int64(self._budget() if budget is None else int(budget)), c_int64(self._small_bytes()),
+                      c_double(self.host_link_gbs * 1e6))
+            tail = (last, c_int(cap), ek, ep, et, byref(cnt), c_int(acap), at, ao, byref(acnt), summ, mem)
+            if cls_in is None:
+                rc = lib.tsb_plan2_search(*common, c_int(int(self.allow_swap)), cls, frm, *tail)
+            else:
+                cls = _arr(c_int, cls_in)
+                frm = _arr(c_int, from_in if from_in is not None else [0] * n)
+                rc = lib.tsb_plan2_simulate(*common, cls, frm, *tail)
+            if rc == 6:                                  # an output array was too small: the counts say how large
+                cap, acap = max(cap, cnt.value + 64), max(acap, acnt.value + 64)
+                continue
+            break
         assert rc in (0, 5), "planner error %d" % rc
-        return Plan(list(cls), list(split), list(pre), list(out), rc == 0)
+        events = [(ek[i], ep[i], et[i]) for i in range(cnt.value)]
+        plan = Plan(list(cls), list(last), events, list(summ), summ[2] < 0, self.lowered.pieces,
+                    self.lowered.micro_ops)
+        plan.memory_curve = list(mem)
+        plan.active_from = list(frm)
+        plan.allocs = [(at[i], ao[i]) for i in range(acnt.value)]
+        plan.footprint_bytes = int(summ[11])
+        return plan
+
+    def search_plan(self):
+        """Lower for each candidate piece count, plan, keep the fastest plan that fits (or, when none
+        fits, the one that got furthest).  Installs the chosen lowering."""
+        batch = self._batch()
+        if self.fixed_pieces is not None:
+            cand = [int(self.fixed_pieces)]
+        else:
+            cand, k = [1], 2
+            while k <= min(self.max_split, batch):
+                cand.append(k)
+                k *= 2
+        best = None
+        for k in cand:
+            low = self._lower(k)
+            self._install(low)
+            plan = self._call_planner()
+            key = (0, plan.predicted_ms) if plan.fits else (1, -plan.first_over_budget)
+            if best is None or key < best[0]:
+                best = (key, low, plan)
+            if plan.fits and k == 1 and not any(c != KEEP for c in plan.cls):
+                break                                   # everything fits whole: nothing to gain from pieces
+        _, low, plan = best
+        self._install(low)
+        return plan
+
+    def _batch(self):
+        for n in self.orig_topo_order:
+            if n in self.feed_shapes:
+                return int(self.feed_shapes[n][0])
+        return 1
 
     def simulate_plan(self, plan, budget=None):
-        g = self._graph_arrays()
-        n = g["n"]
-        out = (c_double * 5)()
-        mem = (c_int64 * n)()
-        rc = _base.runtime().tsb_plan_simulate(
-            c_int(n), _arr(c_int64, g["out_bytes"]), _arr(c_double, g["time_ms"]), _arr(c_int, g["phase"]),
-            _arr(c_int, g["managed"]), _arr(c_int, g["recomputable"]), _arr(c_int, g["splittable"]),
-            _arr(c_int64, g["ws"]), _arr(c_int, g["in_ptr"]), _arr(c_int, g["in_idx"]), _arr(c_int, g["pinned"]),
-            c_int64(self._budget() if budget is None else int(budget)), c_double(self.host_link_gbs * 1e6),
-            _arr(c_int, plan.cls), _arr(c_int, plan.split), _arr(c_int, plan.prefetch), out, mem)
-        assert rc == 0
-        return list(out), list(mem)
+        p = self._call_planner(cls_in=plan.cls, budget=budget, from_in=getattr(plan, "active_from", None))
+        return [p.predicted_ms, p.predicted_peak_bytes, p.first_over_budget, p.stall_ms], p.memory_curve
 
-    def classify(self):
+    def plan(self):
         self.plan_result = plan = self.search_plan()
-        self.cls, self.prefetch_at, self.split = {}, {}, {}
-        for i, n in enumerate(self.topo_order):
-            if plan.cls[i] != KEEP:
-                self.cls[n] = plan.cls[i]
-            if plan.split[i] > 1:
-                self.split[n] = plan.split[i]
-            if plan.cls[i] == SWAP and plan.prefetch[i] >= 0:
-                self.prefetch_at.setdefault(plan.prefetch[i], []).append(n)
+        self.analyze()
+        order = self.topo_order
+        flags = self._graph_arrays()["flags"]
+        self._managed_set = {n for n, f in zip(order, flags) if f & F_EVICTABLE}      # what an emergency spill may take
+        self.cls = {order[i]: c for i, c in enumerate(plan.cls) if c != KEEP}
+        self.last_use = {order[i]: lu for i, lu in enumerate(plan.last_use)}
+        self.evict_at, self.free_at, self.prefetch_at = {}, {}, {}
+        for kind, pos, t in plan.events:
+            node = order[t]
+            if kind == EV_PREFETCH:
+                self.prefetch_at.setdefault(pos, []).append(node)
+            elif kind == EV_FREE:
+                self.free_at.setdefault(pos, []).append(node)
+            else:
+                self.evict_at.setdefault(pos, []).append((node, kind))
+        self.release_at = {}
+        for n in order:
+            self.release_at.setdefault(self.last_use[n], []).append(n)
+        self.fwd_release_at = {}
+        self._use_pos = {}
+        for i, n in enumerate(order):
+            for u in n.inputs:
+                self._use_pos.setdefault(u, []).append(i)
 
-    # ------------------------------------------------------------------ micro-tensor transfers
+    def _manageable(self, n, evals):
+        return False            # the planner manages every tensor through its own flags
+
+    # ------------------------------------------------------------------ planned execution
     def _reset_state(self):
         MemoryExecutor._reset_state(self)
-        self.micro_events = {}          # node -> [event per batch slice] of an in-flight swap-in
-        self.stats["micro_transfers"] = 0
+        self.evicting = {}              # node -> device array whose copy-out is in flight (freed at its planned position)
         self.stats["micro_ops"] = 0
+        self.stats["micro_transfers"] = 0
+        self.stats["planned_frees"] = 0
+        self._alloc_seq = 0
 
-    def _slices(self, node, k):
-        b = self.node_to_shape_map[node][0]
-        k = max(1, min(k, b))
-        return [ndarray._split_bounds(b, k, j) for j in range(k)]
-
-    def _copy_slice(self, dst, src, lo, hi, batch, stream):
-        """Copy batch rows [lo, hi) of a dense array (the batch is outermost in
-        both layouts, so a slice is one contiguous byte range)."""
-        n = dst.t.numel()
-        per = n // batch
-        if self.on_device:
-            import torch
-            with torch.cuda.stream(stream.torch_stream):
-                d = dst.t.as_strided((n,), (1,)) if dst.is_cuda else dst.t.reshape(-1)
-                s = src.t.as_strided((n,), (1,)) if src.is_cuda else src.t.reshape(-1)
-                d[lo * per:hi * per].copy_(s[lo * per:hi * per], non_blocking=True)
-        else:
-            dst.t.reshape(-1)[lo * per:hi * per] = src.t.reshape(-1)[lo * per:hi * per]
-
-    def _swap_out(self, node):
-        k = self.split.get(node, 1)
-        if k <= 1:
-            return MemoryExecutor._swap_out(self, node)
-        a, h = self.arr[node], self._host_buffer(node)
-        ev = Event(self.ctx)
-        ev.record(self.stream)
-        self.d2h_stream.wait_event(ev)
-        batch = a.shape[0]
-        for lo, hi in self._slices(node, k):
-            self._copy_slice(h, a, lo, hi, batch, self.d2h_stream)
-            self.stats["micro_transfers"] += 1
-        a.gpu2cpu_event.record(self.d2h_stream)
-        self.host[node] = h
-        self.stats["swap_out_bytes"] += a.nbytes
-        self._log("swap_out", node)
-
-    def _swap_in(self, node, prefetch=False):
-        k = self.split.get(node, 1)
-        if k <= 1:
-            return MemoryExecutor._swap_in(self, node, prefetch)
-        if node in self.arr or node in self.swapin_event:
+    # The plan gives every allocation of the step its byte offset inside one region (the planner's
+    # offline placement).  The region is taken from the context's pool as a single block for the
+    # duration of the step (or owned by the executor when no pool is installed), so no allocator
+    # runs while the step executes and the footprint is known before the first launch.
+    def _open_region(self):
+        if self.__dict__.get("_region") is not None:
             return
-        a, h = self._alloc(node), self.host[node]
-        ev = Event(self.ctx)
-        ev.record(self.stream)
-        self.h2d_stream.wait_event(ev)
-        batch, evs = a.shape[0], []
-        for lo, hi in self._slices(node, k):
-            self._copy_slice(a, h, lo, hi, batch, self.h2d_stream)
-            e = Event(self.ctx)
-            e.record(self.h2d_stream)
-            evs.append(e)
-            self.stats["micro_transfers"] += 1
-        a.cpu2gpu_event.record(self.h2d_stream)
-        self.arr[node] = a
-        self.swapin_event[node] = a.cpu2gpu_event
-        self.micro_events[node] = evs
-        self.stats["swap_in_bytes"] += a.nbytes
-        self.stats["prefetch_hits" if prefetch else "on_demand_swapins"] += 1
-        self._log("swap_in", node)
+        nbytes = max(int(self.plan_result.footprint_bytes), 256)
+        pool = ndarray.get_pool(self.ctx)
+        if pool is not None:
+            blk, flat = pool.alloc(nbytes)
+            self._region, self._region_block, self._region_pool = flat, blk, pool
+        else:
+            own = self.__dict__.get("_own_region")
+            if own is None or own.numel() * 4 < nbytes:
+                import torch
+                own = self._own_region = torch.empty((nbytes + 3) // 4, dtype=torch.float32,
+                                                     device=self.ctx.torch_device)
+            self._region, self._region_block, self._region_pool = own, None, None
+        self._region_views = self.__dict__.get("_region_views_cache", {}) if (
+            self.__dict__.get("_region_key") == (self._region.data_ptr(), id(self.plan_result))) else {}
+        self._region_views_cache = self._region_views
+        self._region_key = (self._region.data_ptr(), id(self.plan_result))
+
+    def _close_region(self):
+        if self.__dict__.get("_region") is None:
+            return
+        if self._region_pool is not None and self._region_block is not None:
+            self._region_pool.free(self._region_block)
+        self._region = None
+
+    def _alloc(self, node):
+        shape = self.node_to_shape_map[node]
+        cl = bool(self.node_layout.get(node)) and len(shape) == 4 and ndarray.is_cuda_ctx(self.ctx)
+        if self.last_use.get(node, 0) >= len(self.topo_order):        # a result: outlives the step and its region
+            return ndarray.empty(shape, self.ctx, channels_last=cl, long_lived=True)
+        seq = self._alloc_seq
+        self._alloc_seq += 1
+        allocs = self.plan_result.allocs
+        if seq >= len(allocs) or self.topo_order[allocs[seq][0]] is not node:
+            raise RuntimeError("step diverged from its plan at allocation %d (%s)" % (seq, node.desc))
+        off = allocs[seq][1]
+        key = (off, shape, cl)
+        view = self._region_views.get(key)
+        if view is None:
+            n = ndarray._numel(shape)
+            o = off // 4
+            view = self._region_views[key] = ndarray._make_view(self._region[o:o + max(n, 1)][:n], shape, cl)
+        return ndarray.NDArray(view, self.ctx, owns=False)
 
     def _release(self, node, final=False):
-        self.micro_events.pop(node, None)
-        MemoryExecutor._release(self, node, final)
+        a = self.evicting.pop(node, None)
+        if a is not None:
+            self.stream.wait_event(a.gpu2cpu_event)      # the copy-out has read the block before it is reused
+        a = self.arr.pop(node, None)
+        self.swapin_event.pop(node, None)
+        if a is not None:
+            if node in self.host and a.gpu2cpu_event.recorded:
+                self.stream.wait_event(a.gpu2cpu_event)
+            a._release()
+        if final:
+            self.host.pop(node, None)
 
-    # ------------------------------------------------------------------ micro-ops
-    def _launch(self, node, out):
-        streamed = [i for i in node.inputs if i in self.micro_events]
-        if (not streamed or node.op.name not in BATCH_SEPARABLE or out is None or len(out.shape) < 1):
-            for i in streamed:
-                self.micro_events.pop(i, None)
-            return MemoryExecutor._launch(self, node, out)
-        batch = out.shape[0]
-        k = max(len(self.micro_events[i]) for i in streamed)
-        if any(len(self.micro_events[i]) != k or self.arr[i].shape[0] != batch for i in streamed):
-            for i in streamed:
-                self.micro_events.pop(i, None)
-            return MemoryExecutor._launch(self, node, out)
-        ins = [self.arr[i] for i in node.inputs]
-        for i in node.inputs:                      # whole-tensor events of inputs that are not streamed
-            if i not in streamed:
-                ev = self.swapin_event.pop(i, None)
-                if ev is not None:
-                    self.stream.wait_event(ev)
-        for j in range(k):
-            for i in streamed:
-                self.stream.wait_event(self.micro_events[i][j])
-            lo, hi = ndarray._split_bounds(batch, k, j)
-            sl_in = []
-            for a, i in zip(ins, node.inputs):
-                sliced = isinstance(a, ndarray.NDArray) and len(a.shape) >= 1 and a.shape[0] == batch and \
-                    not isinstance(i.op, PlaceholderOp)
-                sl_in.append(ndarray.NDArray(a.t.narrow(0, lo, hi - lo), a.ctx, owns=False) if sliced else a)
-            sl_out = ndarray.NDArray(out.t.narrow(0, lo, hi - lo), out.ctx, owns=False)
-            if self.on_device:
-                node.op.compute(node, sl_in, sl_out, False, self.stream)
-            else:
-                node.op.compute(node, [a.numpy_view() for a in sl_in], sl_out.numpy_view(), True, self.stream)
-            self.stats["micro_ops"] += 1
-        for i in streamed:
-            self.micro_events.pop(i, None)
-            self.swapin_event.pop(i, None)
+    def _ensure(self, node, temps):
+        if node in self.arr:
+            return
+        if node in self.evicting:
+            self.arr[node] = self.evicting.pop(node)         # needed again before its planned free
+            return
+        if node in self.host:
+            self._swap_in(node)
+            return
+        assert node.inputs, "tensor %s was released and cannot be rebuilt" % node.desc
+        for i in node.inputs:
+            self._ensure(i, temps)
+        out = self._alloc(node)
+        self.arr[node] = out
+        state = getattr(node, "state", None)
+        if isinstance(state, dict):
+            state["rematerialise"] = True      # ops with per-step side results (batch-norm statistics) reuse them
+        try:
+            self._launch(node, out)
+        finally:
+            if isinstance(state, dict):
+                state.pop("rematerialise", None)
+        self.stats["recomputed_nodes"] += 1
+        temps.append(node)
+        # inputs that were only needed for this rebuild leave at once (same rule as the planner's replay)
+        cur = self.topo_order[self._cursor]
+        for i in node.inputs:
+            if i in self._leaving and i in self.arr and i not in cur.inputs and i not in self.feed_shapes \
+                    and not isinstance(i.op, PlaceholderOp):
+                self._release(i, final=self.last_use.get(i, 0) <= self._cursor)
+
+    def _execute(self):
+        if not self.plan_result.fits:
+            p = self.plan_result
+            raise OutOfHBMBudget(
+                "GPU available memory is not enough! no keep / swap / recompute plan over %d batch pieces fits a "
+                "budget of %.1f MB (first position that does not fit: %d of %d, %.1f MB requested, %.1f MB free)" % (
+                    p.pieces, self._budget() / 2**20, p.first_over_budget, len(p.cls), p.fail_need_bytes / 2**20,
+                    p.fail_free_bytes / 2**20))
+        self._open_region()
+        try:
+            self._execute_plan()
+        finally:
+            if not self.use_graph:
+                self.stream.sync() if self.on_device else None
+                self._close_region()
+
+    def _execute_plan(self):
+        self._advance_device_step()
+        order = self.topo_order
+        feeds = self.feed_shapes
+        micro = 0
+        for idx, node in enumerate(order):
+            self._cursor = idx
+            if node in self.arr:
+                continue
+            if isinstance(node.op, PlaceholderOp):
+                self.arr[node] = self._placeholder_value(node)
+                continue
+            for t in self.prefetch_at.get(idx, ()):
+                if t in self.host and t not in self.arr and t not in self.evicting:
+                    self._swap_in(t, prefetch=True)
+            temps = []
+            self._leaving = {t for t, kind in self.evict_at.get(idx, ()) if kind == EV_RELEASE}
+            self._leaving.update(self.release_at.get(idx, ()))
+            for i in node.inputs:
+                if i not in feeds:
+                    self._ensure(i, temps)
+            shape = self.node_to_shape_map[node]
+            out = self._alloc(node) if shape is not None else None
+            if out is not None:
+                self.arr[node] = out
+            self._launch(node, out)
+            if node.attrs.get("piece") is not None:
+                micro += 1
+            for t, kind in self.evict_at.get(idx, ()):
+                if t not in self.arr:
+                    continue
+                if kind == EV_SWAPOUT:
+                    if t not in self.host:
+                        self._swap_out(t)
+                        self.stats["micro_transfers"] += 1
+                    self.evicting[t] = self.arr.pop(t)
+                    self.swapin_event.pop(t, None)
+                else:
+                    self._release(t)
+            for t in self.free_at.get(idx, ()):
+                if t in self.evicting:
+                    self._release(t)
+                    self.stats["planned_frees"] += 1
+            for t in self.release_at.get(idx, ()):
+                if not isinstance(t.op, PlaceholderOp) and t not in feeds:
+                    self._release(t, final=True)
+        for t in list(self.evicting):
+            self._release(t)
+        self.stats["micro_ops"] += micro
+        assert self._alloc_seq == len(self.plan_result.allocs), "step made %d of %d planned allocations" % (
+            self._alloc_seq, len(self.plan_result.allocs))
+
+    def _graph_eligible(self):
+        ok = self.__dict__.get("_graph_ok")
+        if ok is None:
+            ok = MemoryExecutor._graph_eligible(self) and not self.free_at and not self.prefetch_at
+            self._graph_ok = ok
+        return ok
 
 
 class microopPlanner(microopExecutor):
@@ -290,9 +472,9 @@ class microopOptimizer(microopPlanner):
 
     def run(self, feed_dict, convert_to_numpy_ret_vals=False):
         plan = microopPlanner.run(self, feed_dict)
-        summary, mem = self.simulate_plan(plan)
-        return {"predicted_ms": summary[0], "predicted_peak_bytes": int(summary[1]), "fits": summary[2] < 0,
-                "stall_ms": summary[3], "plan": plan, "memory_curve": mem}
+        return {"predicted_ms": plan.predicted_ms, "predicted_peak_bytes": plan.predicted_peak_bytes,
+                "fits": plan.fits, "stall_ms": plan.stall_ms, "plan": plan, "memory_curve": plan.memory_curve,
+                "pieces": plan.pieces, "swap_out_bytes": plan.swap_out_bytes, "swap_in_bytes": plan.swap_in_bytes}
 
 
 def max_batch_search(build_executor, feeds_for_batch, lo=1, hi=4096):

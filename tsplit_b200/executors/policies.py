@@ -110,9 +110,10 @@ class capuchinExecutor(MemoryExecutor):
     lazy_evict = True
     spill_on_pressure = True
 
-    def __init__(self, *a, host_link_gbs=50.0, **kw):
+    def __init__(self, *a, host_link_gbs=None, **kw):
         MemoryExecutor.__init__(self, *a, **kw)
-        self.host_link_gbs = host_link_gbs
+        from ..profiler import HOST_LINK_GBS
+        self.host_link_gbs = HOST_LINK_GBS if host_link_gbs is None else host_link_gbs
         self.measured = None
 
     def classify(self):

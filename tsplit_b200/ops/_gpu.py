@@ -218,10 +218,12 @@ def embedding_grad(g, idx, dtable, stream):
            "embedding_grad")
 
 
-def dropout(x, y, keep_prob, seed, stream, step_dev=0):
-    """``step_dev``: device address of the executor's step counter (0 = ``seed`` is already step-mixed)."""
+def dropout(x, y, keep_prob, seed, stream, step_dev=0, offset=0):
+    """``step_dev``: device address of the executor's step counter (0 = ``seed`` is already step-mixed);
+    ``offset``: index of ``x``'s first element in the whole tensor when ``x`` is a batch piece of it."""
     _check(lib().tsb_dropout(_p(x), _p(y), c_int64(_numel(x.shape)), c_float(keep_prob),
-                             ctypes.c_uint64(seed), c_void_p(step_dev or None), _s(stream)), "dropout")
+                             ctypes.c_uint64(seed), c_void_p(step_dev or None), ctypes.c_uint64(offset),
+                             _s(stream)), "dropout")
 
 
 def step_advance(step_dev, stream):
@@ -275,6 +277,53 @@ def bn_relu_backward(dy, x, scale, bias, save_mean, save_invstd, dx, dscale, dbi
     _check(lib().tsb_bn_relu_backward(_p(dy), _p(x), _p(scale), _p(bias), _p(save_mean), _p(save_invstd), _p(dx),
                                       _p(dscale), _p(dbias), c_int64(rows), c_int64(c), c_int64(ldx),
                                       c_int64(lddy), c_int64(lddx), _s(stream)), "bn_relu_backward")
+
+
+BN_PIECE_CHUNKS = 256      # chunk rows a batch piece may fill in a piece-wise statistics buffer
+
+
+def bn_stats_partial(x, part, plane, chunk_offset, stream):
+    """Column sums / sums of squares of one batch piece into ``part`` (two planes of ``plane`` floats);
+    returns the number of chunk rows written from ``chunk_offset`` on."""
+    rows, c, ldx = _rows_c(x)
+    n = c_int(0)
+    _check(lib().tsb_bn_stats_partial(_p(x), _p(part), c_int64(plane), c_int(chunk_offset), c_int(BN_PIECE_CHUNKS),
+                                      c_int64(rows), c_int64(c), c_int64(ldx), ctypes.byref(n), _s(stream)),
+           "bn_stats_partial")
+    return int(n.value)
+
+
+def bn_stats_finalize(part, plane, chunks, count, c, eps, momentum, mean, invstd, run_mean, run_var, stream):
+    _check(lib().tsb_bn_stats_finalize(_p(part), c_int64(plane), c_int(chunks), ctypes.c_double(count), c_int64(c),
+                                       c_float(eps), c_float(momentum), _p(mean), _p(invstd), _p(run_mean),
+                                       _p(run_var), _s(stream)), "bn_stats_finalize")
+
+
+def bn_bwd_partial(dy, x, mean, invstd, rscale, rbias, part, plane, chunk_offset, stream):
+    rows, c, ldx = _rows_c(x)
+    _, _, lddy = _rows_c(dy)
+    n = c_int(0)
+    _check(lib().tsb_bn_bwd_partial(_p(dy), _p(x), _p(mean), _p(invstd),
+                                    c_void_p(rscale.ptr if rscale is not None else 0),
+                                    c_void_p(rbias.ptr if rbias is not None else 0), _p(part), c_int64(plane),
+                                    c_int(chunk_offset), c_int(BN_PIECE_CHUNKS), c_int64(rows), c_int64(c),
+                                    c_int64(lddy), c_int64(ldx), ctypes.byref(n), _s(stream)), "bn_bwd_partial")
+    return int(n.value)
+
+
+def bn_bwd_finalize(part, plane, chunks, c, dscale, dbias, stream):
+    _check(lib().tsb_bn_bwd_finalize(_p(part), c_int64(plane), c_int(chunks), c_int64(c), _p(dscale), _p(dbias),
+                                     _s(stream)), "bn_bwd_finalize")
+
+
+def bn_bwd_apply(dy, x, scale, rbias, mean, invstd, dscale, dbias, dx, total_rows, stream):
+    rows, c, ldx = _rows_c(x)
+    _, _, lddy = _rows_c(dy)
+    _, _, lddx = _rows_c(dx)
+    _check(lib().tsb_bn_bwd_apply(_p(dy), _p(x), _p(scale), c_void_p(rbias.ptr if rbias is not None else 0),
+                                  _p(mean), _p(invstd), _p(dscale), _p(dbias), _p(dx), c_int64(rows), c_int64(c),
+                                  c_int64(lddy), c_int64(ldx), c_int64(lddx), ctypes.c_double(total_rows),
+                                  _s(stream)), "bn_bwd_apply")
 
 
 def layer_norm(x, scale, bias, y, mean, invstd, eps, stream):

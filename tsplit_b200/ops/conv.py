@@ -132,7 +132,7 @@ class Conv2dGradDataOp(Op):
     def _xshape(self, node, fs, gs):
         like = node.attrs["like"]
         if like is not None and getattr(like, "inferred_shape", None) is not None:
-            return tuple(like.inferred_shape)
+            return (gs[0],) + tuple(like.inferred_shape[1:])      # batch from the gradient (may be a piece)
         ph, pw = _pads(node)
         st = node.attrs["stride"]
         o, c, kh, kw = fs

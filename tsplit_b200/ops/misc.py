@@ -184,12 +184,13 @@ def embedding_lookup_gradient_op(vectors, index, embedding):
 
 
 # -- dropout ---------------------------------------------------------------------------
-def philox_like_mask(shape, keep_prob, seed):
+def philox_like_mask(shape, keep_prob, seed, offset=0):
     """Host twin of the device mask generator: element i is kept when
     ``hash(seed, i)`` maps below ``keep_prob`` (same integer mix as
-    ``csrc/kernels/misc.cu``)."""
+    ``csrc/kernels/misc.cu``).  ``offset``: index of the first element in the whole
+    tensor when ``shape`` is a batch piece of it."""
     n = int(np.prod(shape))
-    i = np.arange(n, dtype=np.uint64)
+    i = np.arange(n, dtype=np.uint64) + np.uint64(offset)
     with np.errstate(over="ignore"):
         x = i + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15)
         x ^= x >> np.uint64(30)
@@ -225,15 +226,17 @@ class DropoutOp(Op):
 
     def np_compute(self, node, iv):
         kp = node.attrs["keep_prob"]
-        m = philox_like_mask(iv[0].shape, kp, step_seed(node))
+        m = philox_like_mask(iv[0].shape, kp, step_seed(node), node.attrs.get("element_offset", 0))
         return (iv[0] * m / kp).astype(np.float32)
 
     def gpu_compute(self, node, iv, out, stream):
         assert iv[0].is_dense() and iv[0].same_layout(out)
+        off = int(node.attrs.get("element_offset", 0))
         if STEP_DEV[0]:
-            G.dropout(iv[0], out, node.attrs["keep_prob"], int(node.attrs["seed"]), stream, step_dev=STEP_DEV[0])
+            G.dropout(iv[0], out, node.attrs["keep_prob"], int(node.attrs["seed"]), stream, step_dev=STEP_DEV[0],
+                      offset=off)
         else:
-            G.dropout(iv[0], out, node.attrs["keep_prob"], step_seed(node), stream)
+            G.dropout(iv[0], out, node.attrs["keep_prob"], step_seed(node), stream, offset=off)
 
     def gradient(self, node, g):
         return [dropout_gradient_op(g, node.attrs["keep_prob"], node)]

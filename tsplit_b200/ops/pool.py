@@ -144,7 +144,8 @@ class AvgPool2dGradientOp(Op):
 
     def np_compute(self, node, iv):
         a = node.attrs
-        return np_avg_pool_grad(iv[0], a["like"].inferred_shape, a["kernel_H"], a["kernel_W"],
+        xs = (iv[0].shape[0],) + tuple(a["like"].inferred_shape[1:])       # batch from the gradient (may be a piece)
+        return np_avg_pool_grad(iv[0], xs, a["kernel_H"], a["kernel_W"],
                                 a["padding"], a["stride"])
 
     def gpu_compute(self, node, iv, out, stream):

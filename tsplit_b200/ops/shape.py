@@ -69,7 +69,10 @@ class ReshapeOp(Op):
         return Op.__call__(self, x, output_shape=tuple(output_shape))
 
     def np_compute(self, node, iv):
-        return iv[0].reshape(_resolve(node.attrs["output_shape"], iv[0].size))
+        shp = tuple(node.attrs["output_shape"])
+        if -1 not in shp and int(np.prod(shp)) != iv[0].size:      # a batch piece of an explicitly shaped reshape
+            shp = (-1,) + shp[1:]
+        return iv[0].reshape(_resolve(shp, iv[0].size))
 
     def gpu_compute(self, node, iv, out, stream):
         _reshape_gpu(iv[0], out, stream)
@@ -88,7 +91,10 @@ class ReshapeGradientOp(Op):
         return Op.__call__(self, g, like=like)
 
     def np_compute(self, node, iv):
-        return iv[0].reshape(node.attrs["like"].inferred_shape)
+        shp = tuple(node.attrs["like"].inferred_shape)
+        if int(np.prod(shp)) != iv[0].size:        # a batch piece: the leading extent follows the input
+            shp = (-1,) + shp[1:]
+        return iv[0].reshape(shp)
 
     def gpu_compute(self, node, iv, out, stream):
         _reshape_gpu(iv[0], out, stream)

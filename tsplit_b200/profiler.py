@@ -10,12 +10,20 @@ from __future__ import annotations
 
 from ._base import get_array_memory
 
-#: host link bandwidth assumed by the static model, MB per ms (= GB/s), per direction
-BandWidth = 45.0 * 1024 / 1000
+#: host link (pinned host memory <-> device), GB/s per direction with both directions busy; measured on a
+#: B200 with ``python -m tsplit_b200.utils.hostlink`` (55.5 / 57.2 GB/s one direction at a time, 49.9 / 50.4
+#: GB/s with both).  The one figure every swap cost model in the package uses.
+HOST_LINK_GBS = 50.0
+#: the same in the reference's unit (MB per ms), ``python/athena/profiler.py:14``
+BandWidth = HOST_LINK_GBS * 1024 / 1000
 PAGEIN_LATENCY = 0.010e-3
 PAGEOUT_LATENCY = 0.010e-3
-#: sustained TF32 tensor-core rate assumed by the static model (FLOP per ms)
-FLOPS_PER_MS = 3.0e11
+#: sustained TF32 tensor-core rate of the wide-tile convolution / GEMM kernels (FLOP per ms), the HBM rate the
+#: batch-norm / pooling / element-wise passes reach (bytes per ms) and the cost of a launch (ms): the static
+#: cost model of every executor (the role of the reference's ``FLOPS_PER_SECOND``, ``profiler.py:8``)
+FLOPS_PER_MS = 7.0e11
+HBM_BYTES_PER_MS = 5.5e9
+LAUNCH_MS = 0.004
 
 
 class Profiler(object):
@@ -49,7 +57,7 @@ def profile_node(node, input_shapes, output_shape, is_static=True, measured_ms=N
     p.workspace_memory = node.op.workspace_bytes(node, input_shapes, output_shape) / 2**20
     if is_static or measured_ms is None:
         flops = node.op.flops(node, input_shapes, output_shape)
-        p.time = max(flops / FLOPS_PER_MS, (p.input_memory + p.output_memory) * 2**20 / 5.0e9) + 0.004
+        p.time = max(flops / FLOPS_PER_MS, (p.input_memory + p.output_memory) * 2**20 / HBM_BYTES_PER_MS) + LAUNCH_MS
     else:
         p.time = measured_ms
     return p

@@ -45,6 +45,7 @@ class MemoryPool(object):
         dev = ctx.torch_device if ctx.device_type == 2 else torch.device("cpu")
         self.arena = torch.empty(n_floats, dtype=torch.float32, device=dev)
         self._views = {}
+        self._live = set()
         self.lib = _lib()
         self.handle = self.lib.tsb_pool_create(self.capacity, _ALIGN)
         assert self.handle, "pool creation failed"
@@ -75,6 +76,7 @@ class MemoryPool(object):
         assert rc == 0, "pool alloc error %d" % rc
         o = off.value // 4
         n = max((int(nbytes) + 3) // 4, 1)
+        self._live.add(off.value)
         return off.value, self.arena[o:o + n]
 
     def alloc_view(self, nbytes, shape, channels_last, long_lived=False):
@@ -93,6 +95,7 @@ class MemoryPool(object):
                     "of a %.1f MB budget" % (nbytes / 2**20, st["free"] / 2**20, st["largest_free"] / 2**20,
                                              st["capacity"] / 2**20))
             raise AssertionError("pool alloc error %d" % rc)
+        self._live.add(off.value)
         key = (off.value, shape, channels_last)
         view = self._views.get(key)
         if view is None:
@@ -108,24 +111,34 @@ class MemoryPool(object):
         if self.handle:
             rc = self.lib.tsb_pool_free(self.handle, int(block))
             assert rc == 0, "pool free of unknown block %r" % (block,)
+            self._live.discard(int(block))
 
-    def compact(self, max_moves=65536):
+    def compact(self, max_moves=65536, stream=None):
         """Defragment: pack all live blocks to the bottom and move their bytes.
         Returns {old_block: new_block}; holders of views into the arena must re-bind
-        (``NDArray._rebind``).  The caller guarantees that no kernel or copy is in flight."""
+        (``NDArray._rebind``).  The caller guarantees that no kernel or copy is in flight.
+        ``stream``: the framework stream the moves are issued on (the caller's compute stream, so
+        that later launches on it are ordered after the moves); default = torch's current stream."""
         old = (c_int64 * max_moves)()
         new = (c_int64 * max_moves)()
         size = (c_int64 * max_moves)()
         n = self.lib.tsb_pool_compact(self.handle, old, new, size, max_moves)
         moves = {}
-        for i in range(n):
-            o, d, b = old[i] // 4, new[i] // 4, size[i] // 4
-            if d + b <= o:
-                self.arena[d:d + b].copy_(self.arena[o:o + b])
-            else:                                   # overlapping ranges: go through a temporary
-                self.arena[d:d + b].copy_(self.arena[o:o + b].clone())
-            moves[int(old[i])] = int(new[i])
+        with ndarray._stream_scope(stream):
+            for i in range(n):
+                o, d, b = old[i] // 4, new[i] // 4, size[i] // 4
+                if d + b <= o:
+                    self.arena[d:d + b].copy_(self.arena[o:o + b])
+                else:                                   # overlapping ranges: go through a temporary
+                    self.arena[d:d + b].copy_(self.arena[o:o + b].clone())
+                moves[int(old[i])] = int(new[i])
+        self._views.clear()
+        self._live = {moves.get(b, b) for b in self._live}
         return moves
+
+    def live_blocks(self):
+        """Offsets of the blocks that are allocated right now."""
+        return set(self._live)
 
     def try_alloc(self, nbytes):
         return bool(self.lib.tsb_pool_try(self.handle, int(nbytes)))
