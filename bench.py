@@ -49,13 +49,14 @@ def parse_args():
                             "superneurons", "capuchin"])
     p.add_argument("--cap-gib", type=float, default=16.0, help="activation pool (HBM cap) per GPU")
     p.add_argument("--batch", type=int, default=0, help="per-GPU batch; 0 = largest batch whose plan fits")
-    p.add_argument("--max-batch", type=int, default=256, help="upper bound of the max-batch search")
-    p.add_argument("--host-link-gbs", type=float, default=45.0)
+    p.add_argument("--max-batch", type=int, default=2048, help="upper bound of the max-batch search")
+    p.add_argument("--host-link-gbs", type=float, default=0.0,
+                   help="host link bandwidth the planner assumes; 0 = measure it (pinned copies, both directions busy)")
+    p.add_argument("--also-batch", type=int, default=256,
+                   help="after the headline run, time this smaller batch with the same policy (0 = skip)")
     p.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     p.add_argument("--graph", type=int, default=0,
                    help="1 = replay the step from a CUDA graph when the plan has no swaps (single GPU)")
-    p.add_argument("--plan-frac", type=float, default=0.9,
-                   help="fraction of the cap the planner may fill (the rest absorbs fragmentation)")
     return p.parse_args()
 
 
@@ -130,8 +131,8 @@ def make_executor(args, model, train_op, ctx):
     if pol == "base":
         return ad.MemoryExecutor(nodes, ctx=ctx, use_graph=graph)
     if pol == "tsplit":
-        return ad.microopExecutor(nodes, ctx=ctx, host_link_gbs=args.host_link_gbs,
-                                  budget_bytes=int(args.cap_gib * 2**30 * args.plan_frac), use_graph=graph)
+        return ad.microopExecutor(nodes, ctx=ctx, host_link_gbs=args.host_link_gbs, use_graph=graph,
+                                  budget_bytes=args.plan_budget, max_split=32)
     if pol in ("vdnnall", "vdnnconv"):
         return ad.vdnnExecutor(nodes, ctx=ctx, policy=pol[4:])
     if pol.startswith("recompute"):
@@ -141,36 +142,48 @@ def make_executor(args, model, train_op, ctx):
     return ad.capuchinExecutor(nodes, ctx=ctx, host_link_gbs=args.host_link_gbs)
 
 
-def find_max_batch(args, model, train_op, ctx, cap_bytes):
-    """Largest batch (multiple of 8, <= --max-batch) whose TSplit plan fits the cap
-    according to the planner's simulator; other policies are probed by running."""
+def batch_ladder(limit):
+    """Candidate batches, largest first: multiples of 256 above 1024, of 128 above 512, of 64 above 256, of 32
+    below."""
+    out, b = [], limit
+    while b >= 8:
+        out.append(b)
+        step = 256 if b > 1024 else 128 if b > 512 else 64 if b > 256 else 32 if b > 32 else 8
+        b = (b - 1) // step * step if b % step else b - step
+    return out
+
+
+def find_max_batch(args, model, train_op, ctx, log):
+    """Largest batch on the ladder (<= --max-batch) for which the TSplit planner finds a plan inside the
+    budget (its replay is byte-exact and every allocation is placed ahead of time, so a plan that fits runs).
+    The ladder is walked downward and the first batch that fits is taken: the result never drops below a
+    batch that was found to fit.  Other policies have no dry run and are probed by running (see main)."""
     from tsplit_b200 import gpu_ops as ad
     nodes = [model.loss, train_op]
-    if args.policy not in ("tsplit",):
-        return args.max_batch
-
-    def fits(b):
-        # 4 % below the executor's own planning budget: a plan whose peak touches the budget tends to
-        # need an unplanned spill at run time (fragmentation), which the warm-up check would then reject
-        sim = ad.microopOptimizer(nodes, ctx=ctx, budget_bytes=int(cap_bytes * args.plan_frac * 0.96),
-                                  host_link_gbs=args.host_link_gbs)
+    for b in batch_ladder(max(8, args.max_batch)):
+        sim = ad.microopOptimizer(nodes, ctx=ctx, budget_bytes=args.plan_budget, host_link_gbs=args.host_link_gbs,
+                                  max_split=32)
         x = np.empty((b,) + model.input_shape, dtype=np.float32)
         y = np.empty((b, model.num_classes), dtype=np.float32)
-        return bool(sim.run({model.X: x, model.y_: y})["fits"])
-    lo, hi = 8, max(8, args.max_batch // 8 * 8)
-    if not fits(lo):
-        return 0
-    while lo < hi:
-        mid = ((lo + hi) // 2 + 7) // 8 * 8
-        if mid > hi:
-            mid = hi
-        if fits(mid):
-            if mid == lo:
-                break
-            lo = mid
-        else:
-            hi = mid - 8
-    return lo
+        r = sim.run({model.X: x, model.y_: y})
+        log.append({"batch": b, "fits": bool(r["fits"]), "pieces": r["pieces"],
+                    "predicted_ms": round(r["predicted_ms"], 1)})
+        if r["fits"]:
+            return b
+    return 0
+
+
+def time_steps(ex, feed, steps, barrier):
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(ex.stream.torch_stream)
+    loss = None
+    for _ in range(steps):
+        loss = ex.run(feed)[0]
+    e1.record(ex.stream.torch_stream)
+    barrier()
+    return e0.elapsed_time(e1), loss
 
 
 def main():
@@ -188,12 +201,25 @@ def main():
 
     from tsplit_b200 import ndarray, optimizer, _base
     from tsplit_b200.runtime.pool import MemoryPool
-    from tsplit_b200.utils import launch_counter
+    from tsplit_b200.utils import launch_counter, hostlink
 
     dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    link = hostlink.measure(local_rank)
+    if not args.host_link_gbs:
+        args.host_link_gbs = min(link["bidir_h2d_gbs"], link["bidir_d2h_gbs"])
+    if dist is not None:                    # every rank plans with the same figure
+        t = torch.tensor([args.host_link_gbs], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        args.host_link_gbs = float(t.item())
 
     ctx = ndarray.gpu(local_rank)
     model = build_model(args.model)
@@ -204,24 +230,23 @@ def main():
         ddp.attach(opt, dist, mode=args.comm)
 
     cap_bytes = int(args.cap_gib * 2**30)
-    batch = args.batch or find_max_batch(args, model, train_op, ctx, cap_bytes)
+    args.plan_budget = cap_bytes - (1 << 20)           # the results of a step (loss) live beside the placed region
+    search_log = []
+    t_plan = time.time()
+    batch = args.batch or (find_max_batch(args, model, train_op, ctx, search_log) if args.policy == "tsplit"
+                           else args.max_batch)
+    plan_seconds = time.time() - t_plan
     if world > 1:                      # every rank must agree
         t = torch.tensor([batch], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         batch = int(t.item())
     assert batch > 0, "no batch fits the cap"
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- warm-up (also builds the plan, tensor maps, side buffers).  A batch chosen by the planner's
-    # simulator is then checked against reality: if the steps needed an unplanned spill, a pool
-    # compaction or an on-demand swap-in (fragmentation the simulator does not model), the batch is
-    # stepped down and the executor rebuilt, so that the timed steps run the plan and nothing else.
-    attempts = 0
-    while True:
+    # ---- build + warm-up at the chosen batch.  Policies without a dry run (and a TSplit plan that meets
+    # something its replay did not see) step down the ladder until the steps run.
+    ladder = [b for b in batch_ladder(max(8, args.max_batch)) if b <= batch] or [batch]
+    pool = ex = None
+    for batch in ladder:
         pool = MemoryPool(ctx, cap_bytes)          # a fresh arena per attempt: an aborted step may leave blocks behind
         ndarray.set_pool(ctx, pool)
         ex = make_executor(args, model, train_op, ctx)
@@ -229,45 +254,41 @@ def main():
         x_dev = ndarray.array(x_np, ctx, use_pool=False)
         y_dev = ndarray.array(y_np, ctx, use_pool=False)
         feed_dev = {model.X: x_dev, model.y_: y_dev}
-        feed_np = {model.X: x_np, model.y_: y_np}
-        unplanned = 0
+        failed = 0
         try:
             for _ in range(max(args.warmup, 3)):
                 loss = ex.run(feed_dev)[0]
-            if args.policy == "tsplit":
-                st_ = ex.stats
-                unplanned = int(st_.get("evictions", 0)) + int(st_.get("on_demand_swapins", 0)) + \
-                    int(st_.get("compactions", 0))
-        except ndarray.OutOfHBMBudget:
+        except (ndarray.OutOfHBMBudget, RuntimeError) as e:
             if args.batch:
                 raise
-            unplanned = 1
+            failed = 1
+            search_log.append({"batch": batch, "ran": False, "why": str(e)[:120]})
         if dist is not None:
-            t = torch.tensor([unplanned], device="cuda")
+            t = torch.tensor([failed], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            unplanned = int(t.item())
-        if not unplanned or args.batch or attempts >= 6 or batch <= 8:
+            failed = int(t.item())
+        if not failed:
             break
-        attempts += 1
-        batch = max(8, (int(batch * 0.94) // 8) * 8)
-        del ex, x_dev, y_dev, feed_dev
+        del ex, x_dev, y_dev, feed_dev, pool
+        ndarray.set_pool(ctx, None)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+    assert not failed, "no batch on the ladder runs under the cap"
     barrier()
 
     # ---- device-timed region
     sampler = ClockSampler(local_rank)
     sampler.start()
     launch_counter.reset()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(ex.stream.torch_stream)
-    for _ in range(args.steps):
-        loss = ex.run(feed_dev)[0]
-    e1.record(ex.stream.torch_stream)
-    barrier()
+    dev_ms, loss = time_steps(ex, feed_dev, args.steps, barrier)
     launches = launch_counter.count()
-    dev_ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
     loss_val = float(loss.asnumpy().reshape(-1)[0])
+    stats = {k: int(v) for k, v in ex.stats.items()}
+    plan = getattr(ex, "plan_result", None)
+    plan_repr, plan_pieces = repr(plan), getattr(plan, "pieces", None)
+    peak_in_pool = pool.stats()["peak"]
+    torch_bytes = int(torch.cuda.max_memory_allocated())
 
     # ---- end-to-end through the public API: every step copies its inputs host -> device from
     # pinned host memory (the caller's own pinned NDArrays) and reads the loss back to the host
@@ -276,14 +297,14 @@ def main():
     y_pin = nd.empty(y_np.shape, nd.cpu(0), pinned=True)
     x_pin.t.copy_(torch.from_numpy(x_np))
     y_pin.t.copy_(torch.from_numpy(y_np))
-    feed_pin = {k: (x_pin if v is x_np else y_pin) for k, v in feed_np.items()}
+    feed_pin = {model.X: x_pin, model.y_: y_pin}
     # two alternating pinned batches, as an input pipeline would hand them over; the copy of the next
     # batch is started before the current step runs (it overlaps the step) and belongs to the timed region
     x_pin2 = nd.empty(x_np.shape, nd.cpu(0), pinned=True)
     y_pin2 = nd.empty(y_np.shape, nd.cpu(0), pinned=True)
     x_pin2.t.copy_(x_pin.t)
     y_pin2.t.copy_(y_pin.t)
-    feeds = [feed_pin, {k: (x_pin2 if v is x_pin else y_pin2) for k, v in feed_pin.items()}]
+    feeds = [feed_pin, {model.X: x_pin2, model.y_: y_pin2}]
     for i in range(2):
         ex.run(feeds[i % 2], convert_to_numpy_ret_vals=True)
     barrier()
@@ -299,6 +320,37 @@ def main():
     torch.cuda.synchronize()
     e2e_ms = s0.elapsed_time(s1)
 
+    # ---- multi-GPU correctness bit: after the same number of steps every rank must hold the same parameters
+    params_equal = None
+    if dist is not None:
+        chk = torch.zeros(2, device="cuda", dtype=torch.float64)
+        for p_ in opt.params:
+            chk[0] += p_.t.double().sum()
+            chk[1] += p_.t.double().abs().sum()
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        params_equal = bool(torch.equal(lo, hi))
+
+    # ---- the same policy at a smaller reference batch (shows what the larger batch costs per image)
+    also = None
+    if args.also_batch and args.also_batch < batch:
+        try:
+            xa, ya = model.synthetic_batch(args.also_batch, seed=rank)
+            fa = {model.X: ndarray.array(xa, ctx, use_pool=False), model.y_: ndarray.array(ya, ctx, use_pool=False)}
+            for _ in range(3):
+                ex.run(fa)
+            ms_a, _ = time_steps(ex, fa, args.steps, barrier)
+            if dist is not None:
+                t = torch.tensor([ms_a], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms_a = float(t.item())
+            also = {"per_gpu_batch": args.also_batch, "ms_per_step": round(ms_a / args.steps, 3),
+                    "img_s": round(args.also_batch * world / (ms_a / args.steps) * 1e3, 1),
+                    "plan": repr(getattr(ex, "plan_result", None))}
+        except Exception as e:                       # the headline stands without it
+            also = {"per_gpu_batch": args.also_batch, "error": str(e)[:160]}
+
     if dist is not None:
         t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -309,6 +361,11 @@ def main():
     value = global_batch / ms_per_step * 1e3
     e2e_value = global_batch / (e2e_ms / args.steps) * 1e3
     h2d = int(x_np.nbytes + y_np.nbytes)
+    swap_bytes = stats.get("swap_out_bytes", 0) + stats.get("swap_in_bytes", 0)
+    # host-link roofline of the swap traffic: the busier direction's bytes over that direction's measured
+    # bandwidth (both directions busy), as a fraction of the step
+    link_ms = max(stats.get("swap_out_bytes", 0) / (link["bidir_d2h_gbs"] * 1e6),
+                  stats.get("swap_in_bytes", 0) / (link["bidir_h2d_gbs"] * 1e6))
     if rank == 0:
         print(json.dumps({
             "metric": "img/s at max batch under HBM cap (VGG-16)" if args.model == "vgg16" else
@@ -319,12 +376,27 @@ def main():
             "data": "synthetic N(0,1) images, uniform labels, random-init weights",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": global_batch, "per_gpu_batch": batch,
+                       "max_batch_found": batch if not args.batch else None,
                        "image": "3x224x224", "parallelism": "dp%d" % world, "optimizer": "momentum-sgd",
                        "hbm_cap_gib_per_gpu": args.cap_gib, "policy": args.policy,
-                       "max_batch_search_limit": args.max_batch,
+                       "max_batch_search_limit": args.max_batch, "max_batch_search": search_log,
+                       "plan_seconds": round(plan_seconds, 1),
                        "l2": "inputs and activations per step exceed the 126 MB L2; no explicit flush",
-                       "plan": repr(getattr(ex, "plan_result", None)), "loss": loss_val,
-                       "executor_stats": {k: int(v) for k, v in ex.stats.items()}},
+                       "plan": plan_repr, "loss": loss_val, "executor_stats": stats,
+                       "pieces": plan_pieces, "micro_ops": stats.get("micro_ops", 0),
+                       "swap_bytes_per_step": swap_bytes,
+                       "swap_link_ms_per_step": round(link_ms, 2),
+                       "swap_roofline_fraction": round(link_ms / ms_per_step, 3),
+                       "host_link_gbs_measured": link,
+                       "peak_bytes_in_pool": int(peak_in_pool),
+                       "bytes_outside_cap": max(0, torch_bytes - cap_bytes),
+                       "bytes_outside_cap_what": "parameters, momentum slots, feed buffers, batch-norm side buffers, "
+                                                 "kernel scratch (torch.cuda.max_memory_allocated minus the pool arena); "
+                                                 "plus library scratch obtained with cudaMalloc, see library_scratch_bytes",
+                       "library_scratch_bytes": int(_base.kernels().tsb_scratch_bytes()) if hasattr(
+                           _base.kernels(), "tsb_scratch_bytes") else None,
+                       "params_equal_across_ranks": params_equal,
+                       "same_policy_at_smaller_batch": also},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "img/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4},

@@ -176,3 +176,42 @@ def test_dropout_draws_a_new_mask_every_step_and_backward_reuses_it():
     assert np.array_equal(y0 != 0, g0 != 0) and np.array_equal(y1 != 0, g1 != 0)    # same mask within a step
     assert not np.array_equal(y0 != 0, y1 != 0)                                     # a new one the next step
     assert 0.3 < (y0 != 0).mean() < 0.7
+
+
+def test_pool_compaction_moves_live_blocks_and_keeps_their_values():
+    """Fragment a simulated-device pool, compact it through an executor that owns every live block and check
+    that the arrays were re-bound to their bytes; a pool with blocks the executor does not own is left alone."""
+    from tsplit_b200.runtime.pool import use_pool
+    from tsplit_b200.models import vgg
+    ctx = ndarray.simgpu(0)
+    m = vgg(16, num_classes=10, image=32, width_div=16, fc_width=32, seed=3)
+    ex = ad.MemoryExecutor([m.loss], ctx=ctx)
+    with use_pool(ctx, 64 << 10) as pool:
+        ex._reset_state()                            # the executor only lends its compaction logic here
+        keep, holes = {}, []
+        for i in range(8):
+            a = ndarray.empty((1024,), ctx)          # 4 KiB each
+            a.numpy_view()[...] = float(i)
+            if i % 2 == 0:
+                keep[i] = a
+            else:
+                holes.append(a)
+        for a in holes:
+            a._release()
+        st = pool.stats()
+        assert st["largest_free"] < st["free"]          # fragmented
+        ex.arr = {("t", i): a for i, a in keep.items()}
+        ex._no_spill = False
+        assert ex._compact(st["largest_free"] + 4096)
+        assert pool.stats()["largest_free"] == pool.stats()["free"]
+        for i, a in keep.items():
+            assert np.all(a.numpy_view() == float(i)), "block %d lost its bytes" % i
+        # a block held by somebody else: the executor must refuse to move anything
+        other = ndarray.empty((1024,), ctx)
+        other.numpy_view()[...] = 99.0
+        hole = ndarray.empty((1024,), ctx)
+        tail = ndarray.empty((1024,), ctx)
+        ex.arr[("t", "tail")] = tail
+        hole._release()
+        assert not ex._compact(pool.stats()["free"])
+        assert np.all(other.numpy_view() == 99.0)

@@ -96,10 +96,14 @@ def test_bounded_wait_reports_a_peer_that_never_signals():
     rc = lib.tsb_fused_allreduce_update(
         c_int(0), c_int(0), c_int(2), PT(*[g.data_ptr() for g in grads]), PT(*[p.data_ptr() for p in params]),
         PT(*[f.data_ptr() for f in flags]), c_void_p(0), c_void_p(0), c_void_p(slot1.data_ptr()),
-        c_void_p(slot2.data_ptr()), c_longlong(n), hv, c_uint(1), c_void_p(0))
+        c_void_p(slot2.data_ptr()), c_longlong(n), hv, c_uint(1), c_int(0), c_void_p(0))
     assert rc & 0xFF in (0, 4), rc          # the launch itself succeeds; a late status may already be visible
     status = lib.tsb_comm_status(c_void_p(0))          # synchronises, reads and clears the status word
     assert (status & 0xF00) == 0x300, hex(status)      # a flag wait of the exchange ran out
+    # the rank that gave up must not have reduced anything: parameters and optimizer state are untouched
+    # (momentum SGD would have written slot1, plain SGD the parameters)
+    assert float(params[0].abs().max()) == 0.0 and float(params[1].abs().max()) == 0.0
+    assert float(slot1.abs().max()) == 0.0 and float(slot2.abs().max()) == 0.0
     # the context is still healthy: the one-GPU emulation of two ranks runs and gives the SGD result
     g2 = [torch.full((n,), 1.0, device=dev), torch.full((n,), 3.0, device=dev)]
     p2 = [torch.zeros(n, device=dev), torch.zeros(n, device=dev)]

@@ -16,8 +16,10 @@
 // (all-gather), and the optimizer state is sharded N ways.  No TMA, no multicast
 // TMA: only ld/st/multimem on generic pointers.
 //
-// Every spin is bounded (about one second); on expiry the kernel records a
-// status word and returns, and the host raises a timeout error.
+// Every spin is bounded (about one second).  When the first exchange runs out, the
+// kernel records a status word and the whole grid returns before the reduction: the
+// parameters and the optimizer state of this rank stay as they were, and the host
+// raises a timeout error.
 //
 // Role in the reference: ncclAllReduce per gradient tensor followed by a stream
 // sync (src/communication/mpi_nccl_communication.cu:101-120) and a separate
@@ -105,6 +107,11 @@ __device__ __forceinline__ void opt_one(float& p, float g, float& s1, float& s2,
   }
 }
 
+// Epoch of the last call on this device whose first exchange ran out of time.  Written by block 0
+// before the grid-wide barrier and read by every block after it, so the whole grid learns that the
+// peers' gradients may be incomplete and leaves without touching parameters or optimizer state.
+__device__ unsigned int g_abort_epoch = 0xFFFFFFFFu;
+
 // flag exchange among ranks, executed by the first `world` threads of block 0
 __device__ bool exchange(const Args& a, int phase) {
   bool ok = true;
@@ -117,6 +124,7 @@ __device__ bool exchange(const Args& a, int phase) {
     while ((int32_t)(ld_acquire_sys(mine) - a.epoch) < 0) {
       if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
         *(volatile int*)a.status = 0x300 + phase;
+        if (phase == 0) atomicExch(&g_abort_epoch, a.epoch);
         __threadfence_system();
         ok = false;
         break;
@@ -220,11 +228,11 @@ __device__ void reduce_update_shard(const Args& a, long long tid, long long nthr
 template <int KIND>
 __global__ void __launch_bounds__(512, 1) fused_allreduce_update(const Args a) {
   cg::grid_group grid = cg::this_grid();
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (!exchange(a, 0)) s_ok = 0;          // gradients of every rank are complete
+  exchange(a, 0);                          // gradients of every rank are complete
   grid.sync();
+  // a peer never signalled: its gradients may be incomplete, so nothing is reduced, no parameter or
+  // optimizer slot is written and no shard is published (every thread of the grid takes this exit)
+  if (*(volatile unsigned int*)&g_abort_epoch == a.epoch) return;
   reduce_update_shard<KIND>(a, blockIdx.x * (long long)blockDim.x + threadIdx.x,
                             (long long)gridDim.x * blockDim.x);
   __threadfence_system();
@@ -322,10 +330,12 @@ long long tsb_fused_shard_begin(long long n, int rank, int world) {
 }
 
 // grad / param / flags: arrays of `world` peer pointers (index = rank).  flags point to 2*16 uint32 words
-// per rank, zero-initialised once; epoch must increase by one per call on every rank.
+// per rank, zero-initialised once; epoch must increase by one per call on every rank (calls that may be in
+// flight together, e.g. one per bucket, need flag words of their own).  max_blocks > 0 caps the grid.
 int tsb_fused_allreduce_update(int kind, int rank, int world, void* const* grad, void* const* param,
                                void* const* flags, const void* grad_mc, void* param_mc, float* slot1,
-                               float* slot2, long long n, const float* hyper, unsigned int epoch, void* stream) {
+                               float* slot2, long long n, const float* hyper, unsigned int epoch, int max_blocks,
+                               void* stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || kind < 0 || kind > 4 || n <= 0 || (n & 3))
     return TSB_ERR_ARG;
   Args a;
@@ -335,6 +345,7 @@ int tsb_fused_allreduce_update(int kind, int rank, int world, void* const* grad,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   long long want = ((a.hi - a.lo) / 4 + 511) / 512;
   int blocks = (int)(want < 1 ? 1 : (want > sm_count() ? sm_count() : want));
+  if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;     // leave SMs to the kernels it overlaps with
   int rc;
   switch (kind) {
     case 0: rc = launch<0>(a, blocks, st); break;

@@ -21,6 +21,7 @@
 #include <tuple>
 
 #include "tc_common.cuh"
+#include "scratch.h"
 
 using namespace tsb;
 
@@ -1206,27 +1207,10 @@ __global__ void flip_transpose_filters(const float* __restrict__ w, float* __res
   }
 }
 
-// Library-owned scratch (split-K partial sums, transposed filters), one buffer per (stream, slot)
-// so that convolutions running concurrently on different streams never share one.  Grows on demand.
-struct Workspace {
-  float* ptr = nullptr;
-  size_t bytes = 0;
-};
+// Library-owned scratch (split-K partial sums, transposed filters, zero-inserted gradients): one buffer
+// per (stream, slot), so that convolutions running concurrently on different streams never share one.
 float* get_ws(cudaStream_t st, int slot, size_t bytes, size_t floor_bytes) {
-  static std::mutex mu;
-  static std::map<std::tuple<int, cudaStream_t, int>, Workspace> table;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  std::lock_guard<std::mutex> g(mu);
-  Workspace& w = table[std::make_tuple(dev, st, slot)];
-  if (w.bytes < bytes) {
-    if (w.ptr) cudaFree(w.ptr);
-    w.ptr = nullptr; w.bytes = 0;
-    const size_t want = bytes < floor_bytes ? floor_bytes : bytes;
-    if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    w.bytes = want;
-  }
-  return w.ptr;
+  return static_cast<float*>(tsb_scratch::get(st, tsb_scratch::CONV_SPLITK + slot, bytes, floor_bytes));
 }
 
 int sm_count() {

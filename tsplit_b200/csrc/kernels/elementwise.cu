@@ -11,6 +11,7 @@
 // Where,Transpose,Slice,Concat,Pad,Broadcast,BroadcastShape,ReduceSum,
 // ReduceSumAxisZero,Conv2dBroadcast,Conv2dReduceSum}.cu
 #include <cuda_runtime.h>
+#include "scratch.h"
 #include <stdint.h>
 
 #define TSB_OK 0
@@ -390,17 +391,8 @@ int done() {
   return e == cudaSuccess ? TSB_OK : (TSB_ERR_LAUNCH | ((int)e << 8));
 }
 
-float* g_colsum_scratch[64] = {nullptr};
 float* colsum_scratch() {   // 64 chunks x up to 64K columns
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!g_colsum_scratch[dev]) {
-    if (cudaMalloc(reinterpret_cast<void**>(&g_colsum_scratch[dev]), 64ll * 65536 * 4) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;
-    }
-  }
-  return g_colsum_scratch[dev];
+  return static_cast<float*>(tsb_scratch::get(nullptr, tsb_scratch::COLSUM_PARTIALS, 64ull * 65536 * 4));
 }
 
 }  // namespace

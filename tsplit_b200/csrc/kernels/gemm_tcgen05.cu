@@ -15,6 +15,7 @@
 // Role in the reference: cublasSgemm / cublasSgemmStridedBatched
 // (src/ops/MatrixMult.cu:4-72, src/ops/BatchMatrixMult.cu:4-43).
 #include "tc_common.cuh"
+#include "scratch.h"
 
 #include <mutex>
 #include <unordered_map>
@@ -666,25 +667,9 @@ int read_status(cudaStream_t stream) {
 
 namespace {
 
-// split-K workspace: grown on demand, per device, owned by the library
-struct Workspace {
-  float* ptr = nullptr;
-  size_t bytes = 0;
-};
-Workspace g_ws[64];
-
-float* get_workspace(size_t bytes) {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  Workspace& w = g_ws[dev];
-  if (w.bytes < bytes) {
-    if (w.ptr) cudaFree(w.ptr);
-    w.ptr = nullptr; w.bytes = 0;
-    size_t want = bytes < (size_t(64) << 20) ? (size_t(64) << 20) : bytes;
-    if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    w.bytes = want;
-  }
-  return w.ptr;
+// split-K partial sums: library scratch keyed by (device, stream)
+float* get_workspace(size_t bytes, cudaStream_t st) {
+  return static_cast<float*>(tsb_scratch::get(st, tsb_scratch::GEMM_SPLITK, bytes, size_t(64) << 20));
 }
 
 int g_sm_count = 0;
@@ -777,18 +762,8 @@ __global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict
   }
 }
 
-Workspace g_pad[64][2];
-float* pad_workspace(int slot, size_t bytes) {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  Workspace& w = g_pad[dev][slot];
-  if (w.bytes < bytes) {
-    if (w.ptr) cudaFree(w.ptr);
-    w.ptr = nullptr; w.bytes = 0;
-    if (cudaMalloc(reinterpret_cast<void**>(&w.ptr), bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    w.bytes = bytes;
-  }
-  return w.ptr;
+float* pad_workspace(int slot, size_t bytes, cudaStream_t st) {
+  return static_cast<float*>(tsb_scratch::get(st, slot ? tsb_scratch::GEMM_PAD_B : tsb_scratch::GEMM_PAD_A, bytes));
 }
 
 int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
@@ -834,7 +809,7 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     if ((lda % 4) || (batch > 1 && (sa % 4))) {
       lda2 = (cols_a + 3) / 4 * 4;
       sa2 = (long long)rows_a * lda2;
-      float* buf = pad_workspace(0, (size_t)batch * sa2 * sizeof(float));
+      float* buf = pad_workspace(0, (size_t)batch * sa2 * sizeof(float), st);
       if (!buf) okpad = false;
       else {
         const long long total = (long long)batch * rows_a * lda2;
@@ -848,7 +823,7 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     if (okpad && ((ldb % 4) || (batch > 1 && (sb % 4)))) {
       ldb2 = (cols_b + 3) / 4 * 4;
       sb2 = (long long)rows_b * ldb2;
-      float* buf = pad_workspace(1, (size_t)batch * sb2 * sizeof(float));
+      float* buf = pad_workspace(1, (size_t)batch * sb2 * sizeof(float), st);
       if (!buf) okpad = false;
       else {
         const long long total = (long long)batch * rows_b * ldb2;
@@ -895,7 +870,7 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     if (ws && ws_bytes >= need) {
       p.ws = ws;
     } else if (may_alloc) {
-      p.ws = get_workspace(need);
+      p.ws = get_workspace(need, st);
       if (!p.ws) return TSB_ERR_OOM;
     } else {
       return TSB_ERR_SCRATCH;

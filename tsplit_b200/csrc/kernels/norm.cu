@@ -15,6 +15,7 @@
 #include <stdint.h>
 
 #include "norm_static.h"
+#include "scratch.h"
 
 #define TSB_OK 0
 #define TSB_ERR_ARG 1
@@ -29,17 +30,8 @@ constexpr int MAX_CHUNKS = 128;
 constexpr long long PLANE_FLOATS = (long long)MAX_CHUNKS * 8192;   // one partial plane: chunks x channels
 constexpr long long SCRATCH_FLOATS = 2 * PLANE_FLOATS;              // two planes (up to 8192 channels at MAX_CHUNKS)
 
-float* g_scratch[64] = {nullptr};
 float* scratch() {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!g_scratch[dev]) {
-    if (cudaMalloc(reinterpret_cast<void**>(&g_scratch[dev]), SCRATCH_FLOATS * sizeof(float)) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;
-    }
-  }
-  return g_scratch[dev];
+  return static_cast<float*>(tsb_scratch::get(nullptr, tsb_scratch::NORM_PARTIALS, SCRATCH_FLOATS * sizeof(float)));
 }
 
 int sm_count() {

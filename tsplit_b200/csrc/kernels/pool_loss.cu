@@ -12,6 +12,7 @@
 // CudnnAvgPool.cu) and the <<<1,1024>>> kernels of src/ops/Softmax.cu:3-22 and
 // src/ops/SoftmaxCrossEntropy.cu:5-104.
 #include <cuda_runtime.h>
+#include "scratch.h"
 #include <float.h>
 #include <stdint.h>
 
@@ -261,19 +262,8 @@ __global__ void pool_bwd_from_argmax(const unsigned char* __restrict__ idx, cons
   }
 }
 
-unsigned char* g_argmax[64] = {nullptr};
-size_t g_argmax_bytes[64] = {0};
 unsigned char* argmax_scratch(size_t bytes) {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (g_argmax_bytes[dev] < bytes) {
-    if (g_argmax[dev]) cudaFree(g_argmax[dev]);
-    g_argmax[dev] = nullptr; g_argmax_bytes[dev] = 0;
-    const size_t want = bytes < (size_t(32) << 20) ? (size_t(32) << 20) : bytes;
-    if (cudaMalloc(reinterpret_cast<void**>(&g_argmax[dev]), want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    g_argmax_bytes[dev] = want;
-  }
-  return g_argmax[dev];
+  return static_cast<unsigned char*>(tsb_scratch::get(nullptr, tsb_scratch::POOL_ARGMAX, bytes, size_t(32) << 20));
 }
 
 // ------------------------------------------------------------------ softmax family
@@ -598,22 +588,9 @@ __global__ void ce_grad_rows(const float* __restrict__ x, const float* __restric
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-float* g_rows[64] = {nullptr};
-long long g_rows_cap[64] = {0};
 float* row_scratch(long long rows) {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (g_rows_cap[dev] < rows) {
-    if (g_rows[dev]) cudaFree(g_rows[dev]);
-    long long want = rows < 65536 ? 65536 : rows;
-    if (cudaMalloc(reinterpret_cast<void**>(&g_rows[dev]), want * sizeof(float)) != cudaSuccess) {
-      cudaGetLastError();
-      g_rows[dev] = nullptr; g_rows_cap[dev] = 0;
-      return nullptr;
-    }
-    g_rows_cap[dev] = want;
-  }
-  return g_rows[dev];
+  return static_cast<float*>(tsb_scratch::get(nullptr, tsb_scratch::LOSS_ROWS, (size_t)rows * sizeof(float),
+                                              size_t(65536) * sizeof(float)));
 }
 
 }  // namespace

@@ -296,9 +296,12 @@ class Executor(object):
 
     # -- CUDA-graph replay ---------------------------------------------------------
     def _run_graph(self, node_to_val):
-        """Capture the whole step once per feed shape; later runs only refresh the
-        feed buffers (their device addresses are stable) and replay."""
+        """Capture the whole step once per feed shape and replay it afterwards.  The captured launches
+        read the feeds from fixed device buffers (not from whatever buffer a feed arrived in: staged
+        feeds alternate between two, and a caller may hand a different device array every step), so
+        every step first copies its feeds into those buffers on the stream."""
         from ..runtime import cudagraph
+        from ..ops import _gpu as G
         if self._graph is None and not getattr(self, "_graph_warm", False):
             # first step with these shapes runs eagerly: it creates the lazily allocated side
             # buffers, tensor maps and workspaces that a capture must not allocate
@@ -306,10 +309,28 @@ class Executor(object):
             self._graph_warm = True
             return
         if self._graph is None:
+            self._graph_feed_arrs = {
+                n: ndarray.empty(v.shape, self.ctx, use_pool=False,
+                                 channels_last=v.is_channels_last() if len(v.shape) == 4 else None)
+                for n, v in node_to_val.items() if isinstance(v, ndarray.NDArray)}
+        fixed = dict(node_to_val)
+        for n, buf in self._graph_feed_arrs.items():
+            G.copy(node_to_val[n], buf, self.stream)
+            fixed[n] = buf
+        captured_now = False
+        if self._graph is None:
             self.stream.sync()
-            self._graph = cudagraph.capture(self.stream, lambda: self._run_eager(dict(node_to_val)))
+            self._graph = cudagraph.capture(self.stream, lambda: self._run_eager(dict(fixed)))
             self._graph_vals = self._last_vals
+            captured_now = True              # the optimizer's host side ran during the capture
         self._graph.launch(self.stream)
+        if not captured_now:
+            # a replay runs no Python: keep the host-side step bookkeeping (checkpoints, Adam's powers) in step
+            for n in self.topo_order:
+                if n.op.name == "Optimizer":
+                    opt = n.attrs["optimizer"]
+                    opt.step_count += 1
+                    opt._begin_step()
         self._last_vals = self._graph_vals
         node_to_val.update(self._graph_vals)
 

@@ -482,9 +482,18 @@ class MemoryExecutor(Executor):
                 return self._run_with_values(node_to_val, convert)
             self._just_captured = True          # this step's Python side (optimizer bookkeeping) ran during capture
             self._graph_outs = [self.arr.get(n) for n in self.eval_node_list]
+            # The captured launches keep the addresses of every intermediate of the step.  Arrays that are
+            # still resident at the end of the capture stay reserved for as long as the graph exists; blocks
+            # that the step itself freed and re-used belong to the pool again, which is safe only while this
+            # executor is the pool's sole user during a replay (a second executor on the same pool must not
+            # run between a replay's launch and its completion).
+            self._graph_keep = [a for n, a in self.arr.items()
+                                if n not in self.eval_node_list and not isinstance(n.op, PlaceholderOp)
+                                and n not in fixed]
             for n in list(self.arr.keys()):
                 if n not in self.eval_node_list and not isinstance(n.op, PlaceholderOp) and n not in fixed:
-                    self._release(n, final=True)
+                    self.arr.pop(n)
+                    self.host.pop(n, None)
         captured_now = self.__dict__.pop("_just_captured", False)
         self._step_graph.launch(self.stream)
         self.stream.sync()
