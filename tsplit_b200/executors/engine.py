@@ -67,6 +67,7 @@ class MemoryExecutor(Executor):
         self.index = {n: i for i, n in enumerate(self.topo_order)}
         self.stats = {}
         self._planned_for = None
+        self._direct, self._bucket_ready_at, self._comm, self._comm_opt = {}, {}, None, None
 
     # ------------------------------------------------------------------ analysis
     def analyze(self):
@@ -115,6 +116,7 @@ class MemoryExecutor(Executor):
                         self.last_use[u] = self.last_use[n]
 
     def plan(self):
+        self._setup_comm()
         self.analyze()
         self.classify()
         self._extend_sources()
@@ -125,6 +127,50 @@ class MemoryExecutor(Executor):
         for n, c in self.cls.items():
             if c != KEEP:
                 self.fwd_release_at.setdefault(self.last_fwd_use[n], []).append(n)
+
+    # ------------------------------------------------------------------ gradient exchange hooks
+    def _setup_comm(self):
+        """When the optimizer has a bucketed communicator (``parallel/fused_allreduce.py``): allocate each
+        parameter gradient inside the communicator's symmetric gradient array (no staging copy), and note
+        after which schedule position each bucket is complete, so that its fused all-reduce + update can be
+        launched there and overlap the rest of the backward pass."""
+        self._direct, self._bucket_ready_at, self._comm, self._comm_opt = {}, {}, None, None
+        if not self.on_device:
+            return
+        for pos, n in enumerate(self.topo_order):
+            if n.op.name != "Optimizer":
+                continue
+            opt = n.attrs.get("optimizer") or n.attrs.get("orig").attrs.get("optimizer")
+            comm = getattr(opt, "communicator", None)
+            if comm is None or not hasattr(comm, "launch_bucket"):
+                return
+            self._comm, self._comm_opt = comm, opt
+            index = {m: i for i, m in enumerate(self.topo_order)}
+            users = {}
+            for m in self.topo_order:
+                for i in m.inputs:
+                    users.setdefault(i, []).append(m)
+            ready = {}
+            for i, g in enumerate(n.inputs):
+                arr = comm.grad_array(i)
+                shp = self.node_to_shape_map.get(g)
+                want = ndarray._make_view(arr.t.as_strided((arr.t.numel(),), (1,)), shp,
+                                          bool(self.node_layout.get(g)) and len(shp) == 4)
+                if tuple(arr.shape) == tuple(shp) and arr.strides == tuple(want.stride()) and g not in self.feed_shapes \
+                        and not isinstance(g.op, PlaceholderOp) and g not in self.eval_node_list:
+                    self._direct[g] = arr
+                # complete after its producer and after every micro-op that accumulates into it
+                last = max([index[g]] + [index[u] for u in users.get(g, ()) if index[u] < pos])
+                k = comm.bucket_of[i]
+                ready[k] = max(ready.get(k, -1), last)
+            for k, p in ready.items():
+                self._bucket_ready_at.setdefault(p, []).append(k)
+            return
+
+    def _after_launch(self, idx):
+        """Launch the gradient buckets that are complete once position ``idx`` has been issued."""
+        for k in self._bucket_ready_at.get(idx, ()):
+            self._comm.launch_bucket(k, self._comm_opt, self.stream)
 
     # ------------------------------------------------------------------ memory state
     def _reset_state(self):
@@ -166,6 +212,9 @@ class MemoryExecutor(Executor):
         return False
 
     def _alloc(self, node):
+        direct = self._direct.get(node)
+        if direct is not None:
+            return direct
         shape = self.node_to_shape_map[node]
         cl = self.node_layout.get(node)
         self._reap(False)
@@ -329,6 +378,9 @@ class MemoryExecutor(Executor):
         self._log("swap_in", node)
 
     def _release(self, node, final=False):
+        if node in self._direct:                 # lives in the communicator's array, not in the pool
+            self.arr.pop(node, None)
+            return
         a = self.arr.pop(node, None)
         self.lru.pop(node, None)
         self.swapin_event.pop(node, None)
@@ -519,6 +571,8 @@ class MemoryExecutor(Executor):
 
     def _execute(self):
         self._advance_device_step()
+        if self._comm is not None:
+            self._comm.open_step()
         order = self.topo_order
         self._cursor = 0
         for idx, node in enumerate(order):
@@ -556,6 +610,8 @@ class MemoryExecutor(Executor):
             if out is not None:
                 self.arr[node] = out
             self._launch(node, out)
+            if self._bucket_ready_at:
+                self._after_launch(idx)
             for i in node.inputs:
                 self._unlock(i)
             self._after_node(idx, node, temps)

@@ -118,6 +118,7 @@ class microopExecutor(MemoryExecutor):
         self.node_layout = low.layout
         self.eval_node_list = low.evals
         self.index = {n: i for i, n in enumerate(self.topo_order)}
+        self._setup_comm()
 
     def _lower(self, k):
         msb = self.min_split_bytes
@@ -162,7 +163,8 @@ class microopExecutor(MemoryExecutor):
                     f |= F_EVICTABLE
                     if n not in low.no_rebuild and n.inputs:
                         f |= F_RECOMPUTABLE
-            out_bytes.append(0 if external or shp is None else self.tensor_bytes(n))
+            # a gradient that is produced inside the communicator's symmetric array takes no bytes of the region
+            out_bytes.append(0 if external or shp is None or n in self._direct else self.tensor_bytes(n))
             time_ms.append(float(ms.get(n, 0.0)))
             flags.append(f)
             for i in n.inputs:
@@ -314,6 +316,9 @@ class microopExecutor(MemoryExecutor):
         self._region = None
 
     def _alloc(self, node):
+        direct = self._direct.get(node)
+        if direct is not None:
+            return direct
         shape = self.node_to_shape_map[node]
         cl = bool(self.node_layout.get(node)) and len(shape) == 4 and ndarray.is_cuda_ctx(self.ctx)
         if self.last_use.get(node, 0) >= len(self.topo_order):        # a result: outlives the step and its region
@@ -333,6 +338,9 @@ class microopExecutor(MemoryExecutor):
         return ndarray.NDArray(view, self.ctx, owns=False)
 
     def _release(self, node, final=False):
+        if node in self._direct:                 # lives in the communicator's array, not in the region
+            self.arr.pop(node, None)
+            return
         a = self.evicting.pop(node, None)
         if a is not None:
             self.stream.wait_event(a.gpu2cpu_event)      # the copy-out has read the block before it is reused
@@ -394,6 +402,8 @@ class microopExecutor(MemoryExecutor):
 
     def _execute_plan(self):
         self._advance_device_step()
+        if self._comm is not None:
+            self._comm.open_step()
         order = self.topo_order
         feeds = self.feed_shapes
         micro = 0
@@ -418,6 +428,8 @@ class microopExecutor(MemoryExecutor):
             if out is not None:
                 self.arr[node] = out
             self._launch(node, out)
+            if self._bucket_ready_at:
+                self._after_launch(idx)
             if node.attrs.get("piece") is not None:
                 micro += 1
             for t, kind in self.evict_at.get(idx, ()):

@@ -112,6 +112,7 @@ class FusedCommunicator(object):
             self.slot2.append(torch.zeros(max(shard, 4), dtype=torch.float32, device=dev))
         self.epoch = 0
         self._launched = set()
+        self._step_open = False
         self._grad_views = {}
         self.comm_stream = create_stream_handle(self.ctx)
         #: thread blocks of a bucket kernel that runs beside the backward pass (the last bucket of a step
@@ -153,9 +154,14 @@ class FusedCommunicator(object):
                 G.copy_raw(g.ptr, [1], base + 4 * self.offsets[i], [1], [g.t.numel()], stream)
 
     # -- launches ----------------------------------------------------------------------
-    def begin_step(self):
+    def open_step(self):
+        """Start a step: no bucket launched yet, next epoch of the flag words.  Executors that launch buckets
+        during backward call it before the first launch; otherwise the optimizer node does."""
         self._launched = set()
         self.epoch += 1
+        self._step_open = True
+
+    begin_step = open_step
 
     def launch_bucket(self, k, optimizer, compute_stream, overlapped=True):
         """Run the fused kernel for bucket ``k`` on the communication stream, after everything issued so far
@@ -185,8 +191,8 @@ class FusedCommunicator(object):
         """Called by the optimizer node: launch the buckets the executor has not launched during backward
         (all of them for an executor that does not know about buckets) and order the compute stream after
         the communication stream."""
-        if not self._launched and self.epoch_open is False:
-            self.begin_step()
+        if not self._step_open:
+            self.open_step()
         pending = [k for k in range(len(self.buckets)) if k not in self._launched]
         for k in pending:
             first, last, _, _ = self.buckets[k]
@@ -196,14 +202,7 @@ class FusedCommunicator(object):
         ev = Event(self.ctx)
         ev.record(self.comm_stream)
         stream.wait_event(ev)
-        self.epoch_open = False
-
-    epoch_open = False
-
-    def open_step(self):
-        """Executors that launch buckets themselves call this once at the start of a step."""
-        self.begin_step()
-        self.epoch_open = True
+        self._step_open = False
 
     def check(self, stream):
         st = self.lib.tsb_comm_status(c_void_p(stream.handle if stream is not None else 0))
