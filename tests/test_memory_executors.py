@@ -165,6 +165,30 @@ def test_tsplit_swaps_micro_tensors_when_the_link_is_fast():
     assert ex.plan_result.counts()["swap"] > 0
 
 
+@pytest.mark.parametrize("pieces,frac,swap", [(8, 0.3, True), (16, 0.15, True), (16, 0.15, False)])
+def test_tsplit_deep_rebuild_chains_replay_the_plan_exactly(pieces, frac, swap):
+    """Budgets far below the keep-all peak force rebuild chains that nest several levels deep (a rebuilt
+    tensor's inputs are themselves rebuilt, shared inputs are released early and fetched again).  The executor
+    must perform exactly the allocations the planner replayed (it raises when it diverges) and compute the
+    keep-all results."""
+    batch = 16
+    ref = reference_run(small_cnn, batch)
+    peak_keep = base_peak_bytes(small_cnn, batch)
+    ctx = ndarray.simgpu(0)
+    m = small_cnn()
+    grads = ad.gradients(m.loss, m.variables)
+    x, y = m.synthetic_batch(batch, seed=1)
+    with use_pool(ctx, int(peak_keep * frac)) as pool:
+        ex = ad.microopExecutor([m.loss] + grads, ctx=ctx, pieces=pieces, min_split_bytes=1, allow_swap=swap,
+                                host_link_gbs=0.05)
+        for _ in range(2):
+            outs = ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)
+        assert pool.stats()["peak"] <= int(peak_keep * frac)
+    assert ex.stats["recomputed_nodes"] == ex.plan_result.rebuilds > len(ex.topo_order) // 8
+    for i, (o, r) in enumerate(zip(outs, ref)):
+        assert_close(o, r, rtol=1e-4, what="pieces=%d frac=%s output %d" % (pieces, frac, i))
+
+
 def test_tsplit_without_a_fitting_plan_raises_the_typed_error():
     m = small_cnn()
     grads = ad.gradients(m.loss, m.variables)

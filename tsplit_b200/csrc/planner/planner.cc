@@ -233,6 +233,7 @@ struct Sim {
   std::vector<int> queue, temps;
   std::vector<std::vector<int>> release_at;
   std::vector<int> leaving;             // leaving[t] == pos + 1: t is released after position pos
+  std::vector<int> pinned_by_rebuild;   // inputs of rebuilds that are under way
   double tc = 0, th2d = 0, td2h = 0;
   int64_t in_use = 0;
   int ops = 0;                          // allocation / release counter: the time axis of the placement
@@ -252,6 +253,7 @@ struct Sim {
     r.mem_at.assign(g.n, 0);
     release_at.assign(g.n, {});
     leaving.assign(g.n, 0);
+    pinned_by_rebuild.assign(g.n, 0);
     pf_pos.assign(g.n, -1);
     for (int t = 0; t < g.n; ++t)
       if (!g.external(t) && e.last_use[t] < g.n) release_at[e.last_use[t]].push_back(t);
@@ -319,8 +321,11 @@ struct Sim {
       return true;
     }
     if (cls[t] == SWAP && on_host[t]) return swap_in(t, pos, false);
-    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e)
+    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) {
       if (!ensure(g.in_idx[e], pos)) return false;
+      ++pinned_by_rebuild[g.in_idx[e]];              // a nested rebuild must not send it away again
+    }
+    for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) --pinned_by_rebuild[g.in_idx[e]];
     if (!alloc(t, pos)) return false;
     wait_inputs(t);
     tc += g.time_ms[t];
@@ -331,7 +336,7 @@ struct Sim {
     // itself does not read them) go at once, so a rebuild chain holds two links at a time, not all of them
     for (int e = g.in_ptr[t]; e < g.in_ptr[t + 1]; ++e) {
       const int u = g.in_idx[e];
-      if (g.external(u) || block[u] < 0 || leaving[u] != pos + 1) continue;
+      if (g.external(u) || block[u] < 0 || leaving[u] != pos + 1 || pinned_by_rebuild[u] > 0) continue;
       bool direct = false;
       for (int k = g.in_ptr[pos]; k < g.in_ptr[pos + 1]; ++k) direct |= (g.in_idx[k] == u);
       if (!direct) release(u);

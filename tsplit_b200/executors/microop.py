@@ -365,6 +365,9 @@ class microopExecutor(MemoryExecutor):
         assert node.inputs, "tensor %s was released and cannot be rebuilt" % node.desc
         for i in node.inputs:
             self._ensure(i, temps)
+            self._lock(i)                      # a nested rebuild must not send it away again
+        for i in node.inputs:
+            self._unlock(i)
         out = self._alloc(node)
         self.arr[node] = out
         state = getattr(node, "state", None)
@@ -380,9 +383,10 @@ class microopExecutor(MemoryExecutor):
         # inputs that were only needed for this rebuild leave at once (same rule as the planner's replay)
         cur = self.topo_order[self._cursor]
         for i in node.inputs:
-            if i in self._leaving and i in self.arr and i not in cur.inputs and i not in self.feed_shapes \
+            if i in self._leaving and i in self.arr and i not in cur.inputs and i not in self.locked \
+                    and i not in self.feed_shapes \
                     and not isinstance(i.op, PlaceholderOp):
-                self._release(i, final=self.last_use.get(i, 0) <= self._cursor)
+                self._release(i)               # its host copy (if any) stays valid until the position's final releases
 
     def _execute(self):
         if not self.plan_result.fits:
