@@ -44,14 +44,6 @@
 #include <utility>
 #include <vector>
 
-extern "C" {
-void* tsb_pool_create(int64_t capacity, int64_t alignment);
-void tsb_pool_destroy(void* h);
-int tsb_pool_alloc(void* h, int64_t bytes, int64_t* offset);
-int tsb_pool_alloc_high(void* h, int64_t bytes, int64_t* offset);
-int tsb_pool_free(void* h, int64_t offset);
-void tsb_pool_stats(void* h, int64_t* out);
-}
 
 namespace {
 
@@ -59,7 +51,6 @@ enum { KEEP = 0, SWAP = 1, DROP = 2 };
 enum { F_EVICTABLE = 1, F_RECOMPUTABLE = 2, F_PINNED = 4, F_EXTERNAL = 8 };
 enum { EV_RELEASE = 0, EV_SWAPOUT = 1, EV_FREE = 2, EV_PREFETCH = 3 };
 
-constexpr int MIN_GAP = 3;          // positions between two uses before a tensor may leave in between
 
 struct Graph {
   int n;
@@ -69,8 +60,8 @@ struct Graph {
   const int* in_ptr;
   const int* in_idx;
   int64_t capacity;        // bytes of the simulated pool (the planning budget)
-  int64_t small_bytes;     // blocks below this size are carved from the top end, like long-lived ones
   double bw;               // host link, bytes per ms, per direction
+  int min_gap = 3;         // positions between two uses before a tensor may leave in between
   std::vector<double> t0;  // prefix sums of time_ms: t0[i] = start of position i on an idle machine
   std::vector<std::vector<int>> real_uses;
   bool external(int t) const { return (flags[t] & F_EXTERNAL) != 0 || out_bytes[t] <= 0; }
@@ -100,6 +91,7 @@ struct Result {
   struct Block { int t; int born, died; int64_t size; int64_t offset; };
   std::vector<Block> blocks;
   std::vector<Event> prefetched;        // the prefetches that were really started, at their positions
+  std::vector<int> rebuild_count;       // per tensor
   int64_t footprint = 0;
 };
 
@@ -115,7 +107,7 @@ void prepare(Graph& g) {
 }
 
 bool gap_ok(const Graph& g, int t, int cls, int q, int nu) {
-  if (nu - q < MIN_GAP) return false;
+  if (nu - q < g.min_gap) return false;
   if (cls == SWAP) return g.t0[nu] - g.t0[q + 1] >= 1.5 * g.xfer(t);   // the gap has to hide a round trip's half
   return true;
 }
@@ -251,6 +243,7 @@ struct Sim {
     d2h_done.assign(g.n, 0.0);
     arrival.assign(g.n, 0.0);
     r.mem_at.assign(g.n, 0);
+    r.rebuild_count.assign(g.n, 0);
     release_at.assign(g.n, {});
     leaving.assign(g.n, 0);
     pinned_by_rebuild.assign(g.n, 0);
@@ -331,6 +324,7 @@ struct Sim {
     tc += g.time_ms[t];
     r.rebuild_ms += g.time_ms[t];
     ++r.rebuilds;
+    ++r.rebuild_count[t];
     temps.push_back(t);
     // inputs that were only needed for this rebuild (they leave after this position anyway and the node
     // itself does not read them) go at once, so a rebuild chain holds two links at a time, not all of them
@@ -435,14 +429,8 @@ Result simulate(const Graph& g, const std::vector<int>& cls, const Events& ev, b
 // already placed whose lifetimes overlap its own.  Because the executor replays exactly this sequence,
 // every block can be given its address ahead of time: no allocator runs during a step and there is no
 // fragmentation beyond what this packing leaves.  Returns the footprint (highest end offset).
-int64_t place(std::vector<Result::Block>& blocks) {
+int64_t place_in_order(std::vector<Result::Block>& blocks, const std::vector<int>& order) {
   const int n = (int)blocks.size();
-  std::vector<int> order(n);
-  for (int i = 0; i < n; ++i) order[i] = i;
-  std::sort(order.begin(), order.end(), [&](int a, int b) {
-    if (blocks[a].size != blocks[b].size) return blocks[a].size > blocks[b].size;
-    return (blocks[a].died - blocks[a].born) > (blocks[b].died - blocks[b].born);
-  });
   std::vector<int> placed;
   placed.reserve(n);
   int64_t footprint = 0;
@@ -465,6 +453,39 @@ int64_t place(std::vector<Result::Block>& blocks) {
     placed.push_back(i);
   }
   return footprint;
+}
+
+// Three placement orders are tried (largest block first; largest size x lifetime first; longest lifetime
+// first) and the tightest packing is kept.
+int64_t place(std::vector<Result::Block>& blocks) {
+  const int n = (int)blocks.size();
+  std::vector<int> order(n);
+  auto life = [&](int i) { return (int64_t)blocks[i].died - blocks[i].born; };
+  int64_t best = std::numeric_limits<int64_t>::max();
+  std::vector<int64_t> best_off(n, 0);
+  for (int variant = 0; variant < 3; ++variant) {
+    for (int i = 0; i < n; ++i) order[i] = i;
+    std::sort(order.begin(), order.end(), [&](int a, int b) {
+      if (variant == 0) {
+        if (blocks[a].size != blocks[b].size) return blocks[a].size > blocks[b].size;
+        return life(a) > life(b);
+      }
+      if (variant == 1) {
+        const double aa = (double)blocks[a].size * (double)life(a), bb = (double)blocks[b].size * (double)life(b);
+        if (aa != bb) return aa > bb;
+        return a < b;
+      }
+      if (life(a) != life(b)) return life(a) > life(b);
+      return blocks[a].size > blocks[b].size;
+    });
+    const int64_t fp = place_in_order(blocks, order);
+    if (fp < best) {
+      best = fp;
+      for (int i = 0; i < n; ++i) best_off[i] = blocks[i].offset;
+    }
+  }
+  for (int i = 0; i < n; ++i) blocks[i].offset = best_off[i];
+  return best;
 }
 
 // decisions -> events -> replay.  Two replays: one with every swap-in on demand (its memory curve tells
@@ -504,7 +525,7 @@ double rebuild_cost(const Graph& g, const std::vector<int>& cls, int t, int dept
 void write_out(const Graph& g, const std::vector<int>& cls, const Events& ev, const Result& r, int* cls_out,
                int* last_use_out, int ev_cap, int* ev_kind, int* ev_pos, int* ev_tensor, int* ev_count,
                int alloc_cap, int* alloc_tensor, int64_t* alloc_offset, int* alloc_count, double* summary,
-               int64_t* mem_at) {
+               int64_t* mem_at, int* rebuild_count = nullptr) {
   if (cls_out) std::memcpy(cls_out, cls.data(), sizeof(int) * g.n);
   if (last_use_out) std::memcpy(last_use_out, ev.last_use.data(), sizeof(int) * g.n);
   int c = 0;
@@ -526,6 +547,7 @@ void write_out(const Graph& g, const std::vector<int>& cls, const Events& ev, co
   summary[7] = r.rebuild_ms; summary[8] = r.rebuilds; summary[9] = r.on_demand;
   summary[10] = (double)r.fail_free; summary[11] = (double)r.footprint;
   if (mem_at) std::memcpy(mem_at, r.mem_at.data(), sizeof(int64_t) * g.n);
+  if (rebuild_count) std::memcpy(rebuild_count, r.rebuild_count.data(), sizeof(int) * g.n);
 }
 
 int64_t pinned_bytes(const Graph& g) {
@@ -548,22 +570,24 @@ extern "C" {
 // order (tensor, byte offset inside the placed region); summary[12] = step ms, peak bytes in use, first failing
 // position (-1 = fits), stall ms, bytes of the failed request, bytes copied out, bytes copied in, rebuild ms,
 // rebuilt tensors, on-demand swap-ins, free bytes at the failure, footprint of the placed region; mem_at[n]
-// (may be null) = bytes in use at every position.
+// (may be null) = bytes in use at every position; rebuild_count[n] (may be null) = times each tensor is rebuilt.
 // Returns 0, or 6 when an output array is too small (the counts then hold the required sizes).
 int tsb_plan2_simulate(int n, const int64_t* out_bytes, const double* time_ms, const int* flags, const int* in_ptr,
-                       const int* in_idx, int64_t capacity, int64_t small_bytes, double bw_bytes_per_ms,
+                       const int* in_idx, int64_t capacity, int64_t min_gap, double bw_bytes_per_ms,
                        const int* cls_in, const int* from_in, int* last_use_out, int ev_cap, int* ev_kind,
                        int* ev_pos, int* ev_tensor, int* ev_count, int alloc_cap, int* alloc_tensor,
-                       int64_t* alloc_offset, int* alloc_count, double* summary, int64_t* mem_at) {
+                       int64_t* alloc_offset, int* alloc_count, double* summary, int64_t* mem_at,
+                       int* rebuild_count) {
   if (n <= 0 || !summary) return 1;
-  Graph g{n, out_bytes, time_ms, flags, in_ptr, in_idx, capacity, small_bytes, bw_bytes_per_ms, {}, {}};
+  Graph g{n, out_bytes, time_ms, flags, in_ptr, in_idx, capacity, bw_bytes_per_ms};
+  g.min_gap = min_gap > 0 ? (int)min_gap : 3;
   prepare(g);
   std::vector<int> cls(cls_in, cls_in + n), from(n, 0);
   if (from_in) from.assign(from_in, from_in + n);
   Events ev;
   Result r = evaluate(g, cls, from, ev, true);
   write_out(g, cls, ev, r, nullptr, last_use_out, ev_cap, ev_kind, ev_pos, ev_tensor, ev_count, alloc_cap,
-            alloc_tensor, alloc_offset, alloc_count, summary, mem_at);
+            alloc_tensor, alloc_offset, alloc_count, summary, mem_at, rebuild_count);
   return ((int)ev.flat.size() > ev_cap || (int)r.blocks.size() > alloc_cap) ? 6 : 0;
 }
 
@@ -571,12 +595,14 @@ int tsb_plan2_simulate(int n, const int64_t* out_bytes, const double* time_ms, c
 // fits, 5 when no plan was found (the outputs then describe the best attempt), 6 when the event arrays are too
 // small.
 int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, const int* flags, const int* in_ptr,
-                     const int* in_idx, int64_t capacity, int64_t small_bytes, double bw_bytes_per_ms,
+                     const int* in_idx, int64_t capacity, int64_t min_gap, double bw_bytes_per_ms,
                      int allow_swap, int* cls_out, int* from_out, int* last_use_out, int ev_cap, int* ev_kind,
                      int* ev_pos, int* ev_tensor, int* ev_count, int alloc_cap, int* alloc_tensor,
-                     int64_t* alloc_offset, int* alloc_count, double* summary, int64_t* mem_at) {
+                     int64_t* alloc_offset, int* alloc_count, double* summary, int64_t* mem_at,
+                     int* rebuild_count) {
   if (n <= 0 || !summary) return 1;
-  Graph g{n, out_bytes, time_ms, flags, in_ptr, in_idx, capacity, small_bytes, bw_bytes_per_ms, {}, {}};
+  Graph g{n, out_bytes, time_ms, flags, in_ptr, in_idx, capacity, bw_bytes_per_ms};
+  g.min_gap = min_gap > 0 ? (int)min_gap : 3;
   prepare(g);
   const int NEVER = std::numeric_limits<int>::max();
   std::vector<int> cls(n, KEEP), from(n, NEVER);
@@ -610,7 +636,7 @@ int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, con
       for (int e = g.in_ptr[pos]; e < g.in_ptr[pos + 1]; ++e) is_input |= (g.in_idx[e] == t);
       if (is_input) continue;
       int returns = 0, qq = t;
-      for (int u : ev.uses[t]) { if (qq >= q && u - qq >= MIN_GAP) ++returns; qq = u; }
+      for (int u : ev.uses[t]) { if (qq >= q && u - qq >= g.min_gap) ++returns; qq = u; }
       returns = std::max(1, returns);
       const bool may_swap = cls[t] == KEEP || cls[t] == SWAP, may_drop = cls[t] == KEEP || cls[t] == DROP;
       // a copy-out only helps here when it can finish between the eviction and the failing position
@@ -753,7 +779,7 @@ int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, con
     if (from[t] == NEVER) from[t] = 0;
   if (from_out) std::memcpy(from_out, from.data(), sizeof(int) * n);
   write_out(g, cls, ev, r, cls_out, last_use_out, ev_cap, ev_kind, ev_pos, ev_tensor, ev_count, alloc_cap,
-            alloc_tensor, alloc_offset, alloc_count, summary, mem_at);
+            alloc_tensor, alloc_offset, alloc_count, summary, mem_at, rebuild_count);
   if ((int)ev.flat.size() > ev_cap || (int)r.blocks.size() > alloc_cap) return 6;
   return r.fail_pos < 0 ? 0 : 5;
 }

@@ -558,5 +558,7 @@ def lower(topo_order, shapes, layout, eval_nodes, feed_nodes, pieces, min_split_
     for n in out.order:
         if isinstance(n.op, _MicroBase) and not n.op.recomputable:
             out.no_rebuild.add(n)
+        if n.op.name == "Optimizer":
+            out.no_rebuild.update(n.inputs)     # a finished parameter gradient may be copied out, never recomputed
     out.evals = [whole_input(n) if kind[n] != "ext" else n for n in eval_nodes]
     return out

@@ -88,7 +88,7 @@ class microopExecutor(MemoryExecutor):
 
     def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None,
                  host_link_gbs=None, max_split=16, trace=None, use_graph=False, pieces=None,
-                 min_split_bytes=None, allow_swap=True):
+                 min_split_bytes=None, allow_swap=True, min_gap=None):
         MemoryExecutor.__init__(self, eval_node_list, ctx=ctx, streams=streams, policy=policy,
                                 budget_bytes=budget_bytes, trace=trace, use_graph=use_graph)
         from ..profiler import HOST_LINK_GBS
@@ -97,6 +97,9 @@ class microopExecutor(MemoryExecutor):
         self.fixed_pieces = pieces           # None: chosen by the planner
         self.min_split_bytes = min_split_bytes
         self.allow_swap = bool(allow_swap)
+        #: uses closer than this many schedule positions keep a tensor resident (None: chosen by the planner)
+        self.fixed_gap = min_gap is not None
+        self.min_gap = int(min_gap) if min_gap is not None else 3
         self.plan_result = None
         self.lowered = None
         self.orig_topo_order = list(self.topo_order)
@@ -133,11 +136,6 @@ class microopExecutor(MemoryExecutor):
             return int(self.budget_bytes)
         pool = ndarray.get_pool(self.ctx)
         return int(pool.capacity) if pool is not None else 1 << 60
-
-    def _small_bytes(self):
-        pool = ndarray.get_pool(self.ctx)
-        cap = pool.capacity if pool is not None else self._budget()
-        return (cap + 255) // 256
 
     def planning_budget(self):
         return self._budget()
@@ -186,11 +184,12 @@ class microopExecutor(MemoryExecutor):
             cnt, acnt = c_int(0), c_int(0)
             summ = (c_double * 12)()
             mem = (c_int64 * n)()
+            rbc = (c_int * n)()
             common = (c_int(n), _arr(c_int64, g["out_bytes"]), _arr(c_double, g["time_ms"]), _arr(c_int, g["flags"]),
                       _arr(c_int, g["in_ptr"]), _arr(c_int, g["in_idx"]),
-                      c_int64(self._budget() if budget is None else int(budget)), c_int64(self._small_bytes()),
+                      c_int64(self._budget() if budget is None else int(budget)), c_int64(int(self.min_gap)),
                       c_double(self.host_link_gbs * 1e6))
-            tail = (last, c_int(cap), ek, ep, et, byref(cnt), c_int(acap), at, ao, byref(acnt), summ, mem)
+            tail = (last, c_int(cap), ek, ep, et, byref(cnt), c_int(acap), at, ao, byref(acnt), summ, mem, rbc)
             if cls_in is None:
                 rc = lib.tsb_plan2_search(*common, c_int(int(self.allow_swap)), cls, frm, *tail)
             else:
@@ -207,13 +206,14 @@ class microopExecutor(MemoryExecutor):
                     self.lowered.micro_ops)
         plan.memory_curve = list(mem)
         plan.active_from = list(frm)
+        plan.rebuild_count = list(rbc)
         plan.allocs = [(at[i], ao[i]) for i in range(acnt.value)]
         plan.footprint_bytes = int(summ[11])
         return plan
 
     def search_plan(self):
-        """Lower for each candidate piece count, plan, keep the fastest plan that fits (or, when none
-        fits, the one that got furthest).  Installs the chosen lowering."""
+        """Lower for each candidate piece count, plan with each candidate residency gap, keep the fastest plan
+        that fits (or, when none fits, the one that got furthest).  Installs the chosen lowering."""
         batch = self._batch()
         if self.fixed_pieces is not None:
             cand = [int(self.fixed_pieces)]
@@ -222,17 +222,22 @@ class microopExecutor(MemoryExecutor):
             while k <= min(self.max_split, batch):
                 cand.append(k)
                 k *= 2
+        gaps = [self.min_gap] if self.fixed_gap else [3, 6, 12]
         best = None
         for k in cand:
             low = self._lower(k)
             self._install(low)
-            plan = self._call_planner()
-            key = (0, plan.predicted_ms) if plan.fits else (1, -plan.first_over_budget)
-            if best is None or key < best[0]:
-                best = (key, low, plan)
+            for gap in (gaps if k > 1 else gaps[:1]):
+                self.min_gap = gap
+                plan = self._call_planner()
+                plan.min_gap = gap
+                key = (0, plan.predicted_ms) if plan.fits else (1, -plan.first_over_budget)
+                if best is None or key < best[0]:
+                    best = (key, low, plan)
             if plan.fits and k == 1 and not any(c != KEEP for c in plan.cls):
                 break                                   # everything fits whole: nothing to gain from pieces
         _, low, plan = best
+        self.min_gap = plan.min_gap
         self._install(low)
         return plan
 
