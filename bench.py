@@ -173,6 +173,18 @@ def find_max_batch(args, model, train_op, ctx, log):
     return 0
 
 
+def library_scratch_bytes():
+    """Bytes the kernel library holds as scratch obtained with cudaMalloc (split-K partial sums, padded and
+    transposed operand copies, column partial sums): outside the pool and outside torch's allocator."""
+    import ctypes
+    from tsplit_b200 import _base
+    lib = _base.kernels()
+    raw = object.__getattribute__(lib, "_lib") if not isinstance(lib, ctypes.CDLL) else lib
+    fn = raw.tsb_scratch_bytes
+    fn.restype = ctypes.c_longlong
+    return int(fn())
+
+
 def time_steps(ex, feed, steps, barrier):
     import torch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -393,8 +405,7 @@ def main():
                        "bytes_outside_cap_what": "parameters, momentum slots, feed buffers, batch-norm side buffers, "
                                                  "kernel scratch (torch.cuda.max_memory_allocated minus the pool arena); "
                                                  "plus library scratch obtained with cudaMalloc, see library_scratch_bytes",
-                       "library_scratch_bytes": int(_base.kernels().tsb_scratch_bytes()) if hasattr(
-                           _base.kernels(), "tsb_scratch_bytes") else None,
+                       "library_scratch_bytes": library_scratch_bytes(),
                        "params_equal_across_ranks": params_equal,
                        "same_policy_at_smaller_batch": also},
             "clocks": clocks,

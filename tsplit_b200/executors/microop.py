@@ -222,20 +222,36 @@ class microopExecutor(MemoryExecutor):
             while k <= min(self.max_split, batch):
                 cand.append(k)
                 k *= 2
-        gaps = [self.min_gap] if self.fixed_gap else [3, 6, 12]
         best = None
+
+        def consider(low, gap):
+            nonlocal best
+            self.min_gap = gap
+            plan = self._call_planner()
+            plan.min_gap = gap
+            key = (0, plan.predicted_ms) if plan.fits else (1, -plan.first_over_budget)
+            if best is None or key < best[0]:
+                best = (key, low, plan)
+            return plan, key
+
+        first_gap = self.min_gap if self.fixed_gap else 6
+        worse = 0
         for k in cand:
             low = self._lower(k)
             self._install(low)
-            for gap in (gaps if k > 1 else gaps[:1]):
-                self.min_gap = gap
-                plan = self._call_planner()
-                plan.min_gap = gap
-                key = (0, plan.predicted_ms) if plan.fits else (1, -plan.first_over_budget)
-                if best is None or key < best[0]:
-                    best = (key, low, plan)
+            plan, key = consider(low, first_gap)
             if plan.fits and k == 1 and not any(c != KEEP for c in plan.cls):
                 break                                   # everything fits whole: nothing to gain from pieces
+            # more pieces cost launches: once a plan fits and finer splits come out slower, stop refining
+            if best[0][0] == 0:
+                worse = worse + 1 if key > best[0] else 0
+                if worse >= 2:
+                    break
+        if not self.fixed_gap and best[1].pieces > 1:
+            low = best[1]
+            self._install(low)
+            for gap in (3, 12):
+                consider(low, gap)
         _, low, plan = best
         self.min_gap = plan.min_gap
         self._install(low)
