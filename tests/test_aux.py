@@ -215,3 +215,27 @@ def test_pool_compaction_moves_live_blocks_and_keeps_their_values():
         hole._release()
         assert not ex._compact(pool.stats()["free"])
         assert np.all(other.numpy_view() == 99.0)
+
+
+def test_pool_guard_zones_catch_a_write_past_the_end():
+    """Debug mode of the pool (the stand-in for a memory checker): a write that runs past a tensor's end
+    lands in the guard zone behind its block and is reported when the block is freed."""
+    from tsplit_b200.runtime.pool import MemoryPool, PoolCorruption
+    ctx = ndarray.simgpu(0)
+    pool = MemoryPool(ctx, 1 << 20, canary=True)
+    ndarray.set_pool(ctx, pool)
+    try:
+        a = ndarray.empty((100,), ctx)
+        b = ndarray.empty((100,), ctx)
+        a.numpy_view()[...] = 1.0
+        pool.check_canaries()                      # clean
+        a._release()                               # clean free
+        flat = pool.arena.numpy()
+        start = b._block // 4
+        flat[start:start + 104] = 7.0              # 4 floats too many
+        with pytest.raises(PoolCorruption):
+            pool.check_canaries()
+        with pytest.raises(PoolCorruption):
+            b._release()
+    finally:
+        ndarray.set_pool(ctx, None)

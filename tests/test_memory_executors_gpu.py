@@ -231,3 +231,46 @@ def test_base_executor_graph_replay_reads_each_steps_feeds():
         assert opt.step_count == 6
     np.testing.assert_allclose(outs[1], outs[0], rtol=1e-4)
     assert abs(outs[0][0] - outs[0][1]) > 1e-6
+
+
+def test_tsplit_step_with_swaps_replays_from_one_cuda_graph(keep_all):
+    """A planned step is static (fixed offsets, fixed pinned buffers, planned events), so the whole step with
+    its copy-outs, planned frees and prefetches on the copy streams is captured into one CUDA graph; the
+    replayed steps train exactly like the eager ones."""
+    ctx = ndarray.gpu(0)
+    _, peak_keep = keep_all
+    runs = []
+    for use_graph in (False, True):
+        m = net()
+        opt = optimizer.MomentumOptimizer(0.01, 0.9, ctx=ctx)
+        train = opt.minimize(m.loss)
+        x, y = m.synthetic_batch(16, seed=2)
+        with use_pool(ctx, int(peak_keep * 0.5)):
+            ex = ad.microopExecutor([m.loss, train], ctx=ctx, pieces=4, min_split_bytes=1, host_link_gbs=1e5,
+                                    use_graph=use_graph)
+            losses = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0][0]) for _ in range(7)]
+        assert ex.stats["swap_out_bytes"] > 0 and ex.stats["micro_ops"] > 0
+        if use_graph:
+            assert ex._step_graph is not None, "the step was not captured"
+        assert opt.step_count == 7
+        runs.append(losses)
+    np.testing.assert_allclose(runs[1], runs[0], rtol=1e-5)
+    assert runs[0][-1] < runs[0][0]
+
+
+def test_device_timeline_of_a_swap_plan(tmp_path):
+    """Tracing brackets every launch and copy with timing events on its own stream: the device records carry
+    kernel / copy durations and show copies on streams other than the compute stream."""
+    from tsplit_b200.utils import trace
+    recs = []
+    outs, peak, ex = run(ad.vdnnExecutor, "conv", 4 << 30, steps=1, trace=recs)
+    dev = ex.device_trace()
+    kinds = {r[0] for r in dev}
+    assert {"op", "swap_out", "swap_in"} <= kinds
+    assert all(r[5] >= r[4] >= 0.0 for r in dev)
+    op_streams = {r[3] for r in dev if r[0] == "op"}
+    copy_streams = {r[3] for r in dev if r[0] in ("swap_out", "swap_in")}
+    assert len(op_streams) == 1 and not (op_streams & copy_streams)
+    assert sum(r[5] - r[4] for r in dev if r[0] == "op") > 0.0
+    doc = trace.to_chrome_trace(recs, str(tmp_path / "t.json"), device_records=dev)
+    assert any(e["pid"] == 1 and e["cat"].startswith("device:") for e in doc["traceEvents"])

@@ -355,11 +355,13 @@ class MemoryExecutor(Executor):
         ev = Event(self.ctx)
         ev.record(self.stream)                       # data is complete at this point of compute
         self.d2h_stream.wait_event(ev)
+        mark = self._device_mark(self.d2h_stream) if self.trace is not None else None
         self._raw_copy(h, a, self.d2h_stream)
         a.gpu2cpu_event.record(self.d2h_stream)
         self.host[node] = h
         self.stats["swap_out_bytes"] += a.nbytes
         self._log("swap_out", node)
+        self._device_span("swap_out", node, mark, self.d2h_stream)
 
     def _swap_in(self, node, prefetch=False):
         if node in self.arr or node in self.swapin_event:
@@ -369,6 +371,7 @@ class MemoryExecutor(Executor):
         ev = Event(self.ctx)
         ev.record(self.stream)                       # the block's previous owner is done here
         self.h2d_stream.wait_event(ev)
+        mark = self._device_mark(self.h2d_stream) if self.trace is not None else None
         self._raw_copy(a, h, self.h2d_stream)
         a.cpu2gpu_event.record(self.h2d_stream)
         self.arr[node] = a
@@ -376,6 +379,7 @@ class MemoryExecutor(Executor):
         self.stats["swap_in_bytes"] += a.nbytes
         self.stats["prefetch_hits" if prefetch else "on_demand_swapins"] += 1
         self._log("swap_in", node)
+        self._device_span("swap_in", node, mark, self.h2d_stream)
 
     def _release(self, node, final=False):
         if node in self._direct:                 # lives in the communicator's array, not in the pool
@@ -403,18 +407,58 @@ class MemoryExecutor(Executor):
             ev = self.swapin_event.pop(i, None)
             if ev is not None:
                 self.stream.wait_event(ev)
-        t0 = time.perf_counter() if self.trace is not None else 0
+        tracing = self.trace is not None
+        t0 = time.perf_counter() if tracing else 0
+        dev = self._device_mark(self.stream) if tracing else None
         if self.on_device:
-            node.op.compute(node, ins, out, False, self.stream)
+            if tracing:
+                from ..utils.trace import nvtx_range
+                with nvtx_range("%s:%s" % (node.op.name, node.desc)):
+                    node.op.compute(node, ins, out, False, self.stream)
+            else:
+                node.op.compute(node, ins, out, False, self.stream)
         else:
             node.op.compute(node, [a.numpy_view() if isinstance(a, ndarray.NDArray) else a for a in ins],
                             out.numpy_view() if out is not None else None, True, self.stream)
-        if self.trace is not None:
+        if tracing:
             self.trace.append(("op", node.desc, node.op.name, t0, time.perf_counter()))
+            self._device_span("op", node, dev, self.stream)
 
     def _log(self, kind, node):
         if self.trace is not None:
             self.trace.append((kind, node.desc, node.op.name, time.perf_counter(), time.perf_counter()))
+
+    # -- device timeline: a timing event before and after every action on the stream it runs on ----------
+    def _device_mark(self, stream):
+        if not self.on_device:
+            return None
+        ev = Event(self.ctx, timing=True)
+        ev.record(stream)
+        return ev
+
+    def _device_span(self, kind, node, start, stream):
+        """Close a span opened by ``_device_mark``: the pair of events gives the action's time ON THE DEVICE
+        (kernel or copy duration and its position relative to the other streams), which the host clock of the
+        launch cannot.  Resolved by ``device_trace`` after the step."""
+        if start is None:
+            return
+        end = Event(self.ctx, timing=True)
+        end.record(stream)
+        self.__dict__.setdefault("_device_spans", []).append((kind, node.desc, node.op.name, stream.id, start, end))
+
+    def device_trace(self):
+        """Device-time records of the traced steps: ``(kind, node, op, stream id, start ms, end ms)`` relative
+        to the first recorded event.  Synchronises."""
+        spans = self.__dict__.get("_device_spans", [])
+        if not spans:
+            return []
+        for s in self.streams:
+            s.sync()
+        origin = spans[0][4]
+        out = []
+        for kind, desc, op, sid, a, b in spans:
+            out.append((kind, desc, op, sid, origin.elapsed_ms(a), origin.elapsed_ms(b)))
+        return out
 
     def _ensure(self, node, temps):
         """Make ``node`` resident: cache hit, swap-in, or recompute from its inputs."""
@@ -524,8 +568,11 @@ class MemoryExecutor(Executor):
             for n, v in fixed.items():
                 self.arr[n] = v
             self.stream.sync()
+            from ..utils import launch_counter
+            before = launch_counter.count()
             try:
                 self._step_graph = cudagraph.capture(self.stream, self._execute)
+                self._graph_launches = launch_counter.count() - before      # kernels one replay launches
             except Exception:
                 # something in this step cannot be captured (an allocation path that synchronises, a
                 # library buffer that had to grow): stay on the eager path for good
@@ -548,13 +595,15 @@ class MemoryExecutor(Executor):
                     self.host.pop(n, None)
         captured_now = self.__dict__.pop("_just_captured", False)
         self._step_graph.launch(self.stream)
+        from ..utils import launch_counter
+        launch_counter.add(self.__dict__.get("_graph_launches", 0))
         self.stream.sync()
         if not captured_now:
             # the optimizer's Python side did not run: keep its host-side step bookkeeping (checkpoints) in step.
             # Hyper-parameters are kernel arguments of the captured launch: a changed learning rate needs a new capture.
             for n in self.topo_order:
                 if n.op.name == "Optimizer":
-                    opt = n.attrs["optimizer"]
+                    opt = n.attrs.get("optimizer") or n.attrs["orig"].attrs["optimizer"]
                     opt.step_count += 1
                     opt._begin_step()
         outs = self._graph_outs

@@ -477,16 +477,31 @@ class microopExecutor(MemoryExecutor):
                     self._release(t, final=True)
         for t in list(self.evicting):
             self._release(t)
+        # the copy streams end the step joined to the compute stream (nothing of this step is left in flight on
+        # them when the compute stream's work is done; a capture needs that to close)
+        for side in (self.d2h_stream, self.h2d_stream):
+            ev = Event(self.ctx)
+            ev.record(side)
+            self.stream.wait_event(ev)
         self.stats["micro_ops"] += micro
         assert self._alloc_seq == len(self.plan_result.allocs), "step made %d of %d planned allocations" % (
             self._alloc_seq, len(self.plan_result.allocs))
 
     def _graph_eligible(self):
+        """A planned step is a fixed sequence of launches, copies and event waits at fixed addresses (every
+        allocation has its offset in the region, every copy its pinned host buffer), so the whole step, swaps
+        included, is captured into one CUDA graph across the three streams and replayed.  Not with a
+        communicator (its epoch is a kernel argument) and not while tracing."""
         ok = self.__dict__.get("_graph_ok")
         if ok is None:
-            ok = MemoryExecutor._graph_eligible(self) and not self.free_at and not self.prefetch_at
-            self._graph_ok = ok
-        return ok
+            ok = self.trace is None
+            for n in self.topo_order:
+                if n.op.name == "Optimizer":
+                    opt = n.attrs.get("optimizer") or n.attrs["orig"].attrs.get("optimizer")
+                    if opt is None or getattr(opt, "communicator", None) is not None:
+                        ok = False
+            self._graph_ok = bool(ok)
+        return self._graph_ok
 
 
 class microopPlanner(microopExecutor):

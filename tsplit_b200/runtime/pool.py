@@ -37,8 +37,24 @@ def _lib():
     return lib
 
 
+class PoolCorruption(RuntimeError):
+    """A guard zone behind a pool block was overwritten (a kernel or copy ran past the end of its tensor)."""
+
+
+CANARY_BYTES = 256
+_CANARY_VALUE = -6.259853398707798e18        # 0xDEADBEEF as an fp32 bit pattern
+
+
 class MemoryPool(object):
-    def __init__(self, ctx, capacity_bytes):
+    """``canary=True`` (or ``TSPLIT_POOL_CANARY=1``) is the debug mode that stands in for a memory checker:
+    every block gets a 256-byte guard zone behind it, filled with a pattern at allocation and verified when the
+    block is freed and by ``check_canaries()``; a damaged zone raises :class:`PoolCorruption` naming the block.
+    The check reads device memory back, so it synchronises: not for timed runs."""
+
+    def __init__(self, ctx, capacity_bytes, canary=None):
+        import os
+        self.canary = bool(int(os.environ.get("TSPLIT_POOL_CANARY", "0"))) if canary is None else bool(canary)
+        self._guards = {}            # block offset -> (first float of the guard zone, floats)
         self.ctx = ctx
         self.capacity = int(capacity_bytes) // _ALIGN * _ALIGN
         n_floats = self.capacity // 4
@@ -66,7 +82,10 @@ class MemoryPool(object):
         off = c_int64()
         high = long_lived or nbytes * 256 < self.capacity
         fn = self.lib.tsb_pool_alloc_high if high else self.lib.tsb_pool_alloc
-        rc = fn(self.handle, int(nbytes), ctypes.byref(off))
+        want = int(nbytes) + (CANARY_BYTES + 3 if self.canary else 0)
+        rc = fn(self.handle, want, ctypes.byref(off))
+        if rc == 0 and self.canary:
+            self._arm(off.value, int(nbytes))
         if rc == 5:
             st = self.stats()
             raise ndarray.OutOfHBMBudget(
@@ -86,7 +105,10 @@ class MemoryPool(object):
         off = c_int64()
         high = long_lived or nbytes * 256 < self.capacity
         fn = self.lib.tsb_pool_alloc_high if high else self.lib.tsb_pool_alloc
-        rc = fn(self.handle, int(nbytes), ctypes.byref(off))
+        want = int(nbytes) + (CANARY_BYTES + 3 if self.canary else 0)
+        rc = fn(self.handle, want, ctypes.byref(off))
+        if rc == 0 and self.canary:
+            self._arm(off.value, int(nbytes))
         if rc != 0:
             if rc == 5:
                 st = self.stats()
@@ -107,7 +129,33 @@ class MemoryPool(object):
                                                          channels_last)
         return off.value, view
 
+    def _arm(self, offset, nbytes):
+        first = (offset + nbytes + 3) // 4
+        n = CANARY_BYTES // 4
+        self.arena[first:first + n].fill_(_CANARY_VALUE)
+        self._guards[offset] = (first, n)
+
+    def _verify(self, offset):
+        g = self._guards.get(offset)
+        if g is None:
+            return
+        zone = self.arena[g[0]:g[0] + g[1]]
+        bad = int((zone != _CANARY_VALUE).sum().item())
+        if bad:
+            raise PoolCorruption("guard zone behind pool block at offset %d damaged (%d of %d words): something wrote "
+                                 "past the end of that tensor" % (offset, bad, g[1]))
+
+    def check_canaries(self):
+        """Verify the guard zone of every live block (debug mode only)."""
+        for off in list(self._guards):
+            self._verify(off)
+
     def free(self, block):
+        if self.canary and int(block) in self._guards:
+            try:
+                self._verify(int(block))
+            finally:
+                self._guards.pop(int(block), None)
         if self.handle:
             rc = self.lib.tsb_pool_free(self.handle, int(block))
             assert rc == 0, "pool free of unknown block %r" % (block,)
