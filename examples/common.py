@@ -52,18 +52,70 @@ def make_executor(policy, nodes, ctx):
 
 def default_ctx():
     import torch
-    return ndarray.gpu(0) if torch.cuda.is_available() else ndarray.simgpu(0)
+    if torch.cuda.is_available():
+        return ndarray.gpu(int(os.environ.get("LOCAL_RANK", "0")))
+    return ndarray.simgpu(0)
+
+
+# -- data-parallel runs: `python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 examples/X.py ...`
+_DIST = [None]
+
+
+def dist_setup():
+    """Join the process group when launched by torchrun (one process per GPU); returns (rank, world)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1:
+        return 0, 1
+    import torch
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _DIST[0] = dist
+    return dist.get_rank(), world
+
+
+def attach(opt, mode="fused"):
+    """Data-parallel gradient exchange for ``opt`` (the fused NVLink all-reduce + update kernel by default)."""
+    if _DIST[0] is not None:
+        from tsplit_b200.parallel import ddp
+        ddp.attach(opt, _DIST[0], mode=mode)
+    return opt
+
+
+def max_over_ranks(value):
+    if _DIST[0] is None:
+        return value
+    import torch
+    t = torch.tensor([float(value)], device="cuda", dtype=torch.float64)
+    _DIST[0].all_reduce(t, op=_DIST[0].ReduceOp.MAX)
+    return float(t.item())
 
 
 def timed_run(executor, feed, iters=3):
     """Warm-up (one run; three with ``--graph``, whose capture happens on the third), then ``iters``
-    timed runs; seconds per iteration."""
+    timed runs; seconds per iteration.  On a CUDA context the time is taken on the device with events on the
+    executor's stream, and with several ranks it is the maximum over the ranks."""
     out = executor.run(feed)
     if not isinstance(out, list):
         return out
     if USE_GRAPH[0]:
         executor.run(feed)
         executor.run(feed)
+    on_device = getattr(executor, "on_device", False)
+    if on_device:
+        import torch
+        if _DIST[0] is not None:
+            _DIST[0].barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(executor.stream.torch_stream)
+        for _ in range(iters):
+            executor.run(feed)
+        e1.record(executor.stream.torch_stream)
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / 1e3 / iters)
     t0 = time.time()
     for _ in range(iters):
         executor.run(feed)
@@ -71,14 +123,21 @@ def timed_run(executor, feed, iters=3):
 
 
 def sweep(run_at_batch, batches, out_path=None):
-    """Call ``run_at_batch(b)`` for growing b until the budget is exceeded."""
+    """Call ``run_at_batch(b)`` for growing b until the budget is exceeded (on any rank)."""
     results = []
     for b in batches:
+        failed = 0
         try:
             t = run_at_batch(b)
         except ndarray.OutOfHBMBudget as e:
             print("Batch size: %d does not fit: %s" % (b, e))
+            failed, t = 1, None
+        if _DIST[0] is None and failed:
             break
+        if _DIST[0] is not None and max_over_ranks(failed):
+            break
+        if int(os.environ.get("RANK", "0")) != 0:
+            continue
         print("Batch size: {} , time: {} s".format(b, t))
         results.append((b, t))
         if out_path:
@@ -94,7 +153,9 @@ def parse(description, extra=None):
     p.add_argument("-b", "--batch", type=int, default=0, help="single batch size (0 = sweep)")
     p.add_argument("--cap-gib", type=float, default=16.0, help="HBM budget of the activation pool")
     p.add_argument("--out", default=None, help="append results to this file")
-    p.add_argument("--graph", type=int, default=0, help="1 = replay swap-free steps from a CUDA graph")
+    p.add_argument("--graph", type=int, default=0, help="1 = replay fixed steps from a CUDA graph")
+    p.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                   help="gradient exchange when launched with several ranks")
     if extra:
         extra(p)
     args = p.parse_args()

@@ -213,3 +213,21 @@ def test_cpu_operator_library_against_numpy():
     cpu_links.optimizer_update(4, p, g, m_, v_, [0.01, 0.9, 0.999, 0.9, 0.999, 1e-7])
     m_ref, v_ref = 0.1 * g, 0.001 * g * g
     np.testing.assert_allclose(p, p0 - 0.01 * (m_ref / 0.1) / (np.sqrt(v_ref / 0.001) + 1e-7), rtol=1e-4)
+
+
+def test_cpu_context_executor_runs_on_the_native_host_kernels():
+    """``Executor(ctx=ndarray.cpu(0))`` sends matmul / conv / pool / element-wise / cross-entropy through the
+    OpenMP library and gives what the NumPy oracle (``ctx=None``) gives."""
+    from tsplit_b200.models import vgg
+    outs = []
+    for ctx in (None, ndarray.cpu(0)):
+        m = vgg(16, num_classes=10, image=32, width_div=16, fc_width=32, seed=3)
+        grads = ad.gradients(m.loss, m.variables)
+        ex = ad.Executor([m.loss] + grads, ctx=ctx)
+        x, y = m.synthetic_batch(4, seed=1)
+        before = cpu_links.CALLS[0]
+        outs.append([np.asarray(o) for o in ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)])
+        used = cpu_links.CALLS[0] - before
+        assert (used > 20) == (ctx is not None), "native kernel calls: %d" % used
+    for a, b in zip(outs[1], outs[0]):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)

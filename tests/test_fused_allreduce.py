@@ -77,6 +77,18 @@ def test_two_gpu_training_matches_nccl_baseline():
 
 
 @pytest.mark.gpu
+def test_two_gpu_parameter_server_with_gpu_resident_shards():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSPLIT_NVLS="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29617", os.path.join(HERE, "ps_gpu_worker.py")]
+    res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-4000:]
+    assert "PS_GPU_OK" in res.stdout, res.stdout[-4000:]
+
+
+@pytest.mark.gpu
 def test_bounded_wait_reports_a_peer_that_never_signals():
     """Failure detection on the device: rank 0 of a 2-rank exchange whose peer never writes its flag.
     The kernel's flag wait gives up after about a second, leaves a status code that the host turns

@@ -247,6 +247,15 @@ class Executor(object):
             G.step_advance(self._step_dev.data_ptr(), self.stream)
 
     def run(self, feed_dict, convert_to_numpy_ret_vals=False):
+        from .. import graph
+        native = self.ctx is not None and self.ctx.device_type == 1       # CPU context: native host kernels
+        prev, graph.CPU_NATIVE[0] = graph.CPU_NATIVE[0], native
+        try:
+            return self._run(feed_dict, convert_to_numpy_ret_vals)
+        finally:
+            graph.CPU_NATIVE[0] = prev
+
+    def _run(self, feed_dict, convert_to_numpy_ret_vals=False):
         self._begin_step()
         node_to_val = self._ingest(feed_dict)
         feed_shapes = {n: _shape_of(v) for n, v in node_to_val.items()}

@@ -14,6 +14,8 @@ from collections import deque
 
 _node_ids = itertools.count()
 _PHASE = ["forward"]
+#: set by executors that run on a CPU context: operators use their native host kernels
+CPU_NATIVE = [False]
 
 
 class phase_scope(object):
@@ -101,6 +103,10 @@ class Op(object):
     # -- execution ---------------------------------------------------------
     def compute(self, node, input_vals, output_val, use_numpy=True, stream_handle=None):
         if use_numpy:
+            # executors on a CPU context (ndarray.cpu) route the operators that have one through the native
+            # host library (cpu_links -> csrc/runtime/cpu_ops.cc); ctx=None stays pure NumPy, the oracle
+            if CPU_NATIVE[0] and output_val is not None and self.cpu_compute(node, input_vals, output_val):
+                return output_val
             res = self.np_compute(node, input_vals)
             if output_val is not None and res is not None:
                 output_val[...] = res
@@ -109,6 +115,11 @@ class Op(object):
 
     def np_compute(self, node, input_vals):
         raise NotImplementedError(self.name)
+
+    def cpu_compute(self, node, input_vals, output_val):
+        """Native host kernel (OpenMP) writing ``output_val``; returns False when the op has none or the
+        operands do not qualify (then the NumPy path runs)."""
+        return False
 
     def gpu_compute(self, node, input_vals, output_val, stream_handle):
         raise NotImplementedError("%s has no GPU kernel" % self.name)

@@ -76,6 +76,14 @@ class Conv2dOp(Op):
         ph, pw = _pads(node)
         return np_conv2d(iv[0], iv[1], ph, pw, node.attrs["stride"])
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], out):
+            return False
+        ph, pw = _pads(node)
+        cpu_links.conv2d(iv[0], iv[1], out, ph, pw, node.attrs["stride"])
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         ph, pw = _pads(node)
         bn = node.attrs.get("bn_consumer")

@@ -33,6 +33,14 @@ class _Binary(Op):
     def np_compute(self, node, iv):
         return self._np(iv[0], iv[1])
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        code = cpu_links.BINARY.get(self.name)
+        if code is None or not cpu_links.ok(iv[0], iv[1], out) or iv[0].shape != out.shape or iv[1].shape != out.shape:
+            return False
+        cpu_links.binary(code, iv[0], iv[1], out)
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         a, b = iv
         if _is_scalar_shape(a.shape) and not _is_scalar_shape(b.shape):
@@ -133,6 +141,14 @@ class _Unary(Op):
 
     def np_compute(self, node, iv):
         return self._np(iv[0], node.const_attr)
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        code = cpu_links.UNARY.get(self.name)
+        if code is None or not cpu_links.ok(iv[0], out) or iv[0].shape != out.shape:
+            return False
+        cpu_links.unary(code, iv[0], out, 0.0 if node.const_attr is None else float(node.const_attr))
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         G.unary(self.gpu_code, iv[0], out, stream,

@@ -35,6 +35,14 @@ class MatMulOp(Op):
         b = b.T if node.attrs["trans_B"] else b
         return np.matmul(a, b)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        a, b = iv
+        if not (cpu_links.ok(a, b, out) and a.ndim == 2 and b.ndim == 2):
+            return False
+        cpu_links.matrix_multiply(a, b, out, node.attrs["trans_A"], node.attrs["trans_B"])
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         a, b = iv
         ta, tb = node.attrs["trans_A"], node.attrs["trans_B"]

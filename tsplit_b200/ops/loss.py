@@ -85,6 +85,13 @@ class SoftmaxCrossEntropyOp(Op):
     def gpu_compute(self, node, iv, out, stream):
         G.softmax_ce(iv[0], iv[1], out, stream)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], out):
+            return False
+        cpu_links.softmax_crossentropy(iv[0], iv[1], out)
+        return True
+
     def gradient(self, node, g):
         from .misc import zeroslike_op
         return [softmaxcrossentropy_gradient_op(node.inputs[0], node.inputs[1], g),

@@ -79,6 +79,14 @@ class _PoolOp(Op):
     def gpu_compute(self, node, iv, out, stream):
         G.pool(self.kind, iv[0], out, *self._a(node), stream=stream)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], out):
+            return False
+        kh, kw, pad, st = self._a(node)
+        cpu_links.pool2d(self.kind, iv[0], out, kh, kw, pad, st)
+        return True
+
     def infer_shape(self, node, s):
         n, c, h, w = s[0]
         kh, kw, pad, st = self._a(node)

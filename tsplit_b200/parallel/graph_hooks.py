@@ -61,6 +61,13 @@ class PsCommunicateOp(Op):
     def compute(self, node, input_vals, output_val, use_numpy=True, stream_handle=None):
         ps, var = node.attrs["ps"], node.attrs["var"]
         g = input_vals[0]
+        if hasattr(ps, "push_pull_device") and not use_numpy and isinstance(g, ndarray.NDArray) and g.is_cuda:
+            # GPU-resident shards: the push and the pull are one kernel over NVLink, nothing visits the host
+            from ..ops import _gpu as G
+            arr = ps.push_pull_device(var.name, g, node.attrs["lr"], node.attrs["mode"], stream_handle)
+            G.copy(arr, output_val, stream_handle)
+            var.tensor_value = arr               # the next forward pass reads the served value in place
+            return
         g_np = g if isinstance(g, np.ndarray) else g.asnumpy()
         delta = (-node.attrs["lr"] / ps.num_workers) * g_np
         new_w = ps.push_pull(var.name, delta, mode=node.attrs["mode"])
@@ -103,9 +110,17 @@ def ps_gradients(output_node, node_list, ps, lr=0.01, mode="BSP"):
     """Gradients pushed to the parameter servers; each returned node evaluates
     to the freshly pulled weight of its variable."""
     grads = gradients(output_node, node_list)
-    for v in node_list:
-        if v.tensor_value is not None:
-            tv = v.tensor_value
-            ps.init(v.name, tv.asnumpy() if isinstance(tv, ndarray.NDArray) else np.asarray(tv))
+    if hasattr(ps, "push_pull_device"):          # GPU-resident shards: register the device values, then exchange handles
+        for v in node_list:
+            ps.init(v.name, v.tensor_value)
+        ps.finalize()
+        asp = mode == "ASP"
+        for v in node_list:
+            v.tensor_value = ps.value_array(v.name, asp=asp)
+    else:
+        for v in node_list:
+            if v.tensor_value is not None:
+                tv = v.tensor_value
+                ps.init(v.name, tv.asnumpy() if isinstance(tv, ndarray.NDArray) else np.asarray(tv))
     with phase_scope("update"):
         return [ps_communicate_op(g, v, ps, lr, mode) for g, v in zip(grads, node_list)]
