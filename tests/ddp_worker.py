@@ -73,9 +73,30 @@ def main():
     other = flat.clone()
     dist.broadcast(other, src=0)
     assert torch.equal(flat, other), "ranks diverged"
+    # the NVSwitch path: multimem.ld_reduce of the gradients and multimem.st of the new parameters through the
+    # switch instead of one load / store per peer.  The switch adds in its own order, so equality is to rounding.
+    nvls_used = False
+    if os.environ.get("TSPLIT_TEST_NVLS", "1") == "1":
+        os.environ["TSPLIT_NVLS"] = "1"
+        m = vgg(16, num_classes=16, image=32, width_div=8, fc_width=64, seed=11)
+        opt = optimizer.MomentumOptimizer(0.05, 0.9, ctx=ctx)
+        train_op = opt.minimize(m.loss)
+        comm = ddp.attach(opt, dist, mode="fused")
+        nvls_used = bool(comm.grad_mc)
+        if nvls_used:
+            ex = ad.Executor([m.loss, train_op], ctx=ctx)
+            x, y = m.synthetic_batch(8, seed=100 + rank)
+            for _ in range(4):
+                ex.run({m.X: x, m.y_: y})
+            comm.check(ex.stream)
+            torch.cuda.synchronize()
+            for a, b in zip([p.asnumpy() for p in opt.params], p_fused):
+                np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-4, err_msg="multimem path vs peer loads")
+        os.environ["TSPLIT_NVLS"] = "0"
     dist.barrier()
     if rank == 0:
         print("losses nccl", l_ref, "fused", l_fused)
+        print("NVLS path exercised:", nvls_used)
         print("DDP_OK")
     dist.destroy_process_group()
 

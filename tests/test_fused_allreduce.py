@@ -68,7 +68,8 @@ def test_all_ranks_emulated_on_one_gpu(kind, hyper, world, n):
 def test_two_gpu_training_matches_nccl_baseline():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSPLIT_NVLS="0")
+    # no rank leaves this test early, so the NVSwitch (multimem) path may be exercised next to the peer-load path
+    env = dict(os.environ, TSPLIT_NVLS="0", TSPLIT_TEST_NVLS="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29613", os.path.join(HERE, "ddp_worker.py")]
     res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
