@@ -16,8 +16,9 @@ def run(batch_size, args, ctx):
     m = inception_v4()
     if world > 1:
         # data parallel: every rank trains on its own batch, gradients are reduced and applied by the fused kernel
-        opt = attach(optimizer.MomentumOptimizer(0.01, 0.9, ctx=ctx), args.comm)
+        opt = optimizer.MomentumOptimizer(0.01, 0.9, ctx=ctx)
         nodes = [m.loss, opt.minimize(m.loss)]
+        attach(opt, args.comm)
     else:
         grads = ad.gradients(m.loss, m.variables)
         nodes = [m.loss] + grads + [m.y]

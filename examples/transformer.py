@@ -25,8 +25,9 @@ def run(batch_size, args, ctx):
     t = transformer(vocab_size=args.vocab_size, d_model=args.d_model, d_ff=args.d_ff, num_blocks=args.num_blocks,
                     num_heads=args.num_heads, maxlen1=args.maxlen1, maxlen2=args.maxlen2,
                     dropout_rate=args.dropout_rate, batch_size=batch_size)
-    opt = attach(optimizer.AdamOptimizer(args.lr, ctx=ctx), args.comm)
+    opt = optimizer.AdamOptimizer(args.lr, ctx=ctx)
     train = opt.minimize(t.loss)
+    attach(opt, args.comm)
     ex = make_executor(args.policy, [t.loss, train], ctx)
     return timed_run(ex, t.synthetic_batch())
 

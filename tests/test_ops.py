@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from tsplit_b200 import ndarray, gpu_ops as ad
-from helpers import run_graph, assert_close
+from helpers import run_graph, assert_close, assert_close_per_channel
 
 
 
@@ -171,7 +171,14 @@ def test_conv_then_batch_norm_takes_statistics_from_the_conv_epilogue(n, c, hw, 
         loss = ad.reduce_sum_op(ad.mul_op(z, z), [0, 1, 2, 3])
         gx, gf, gs, gb = ad.gradients(loss, [x, f, s, b])
         return {"x": x, "w": f, "s": s, "b": b}, [z, gx, gf, gs, gb]
-    both(build, {"x": xv, "w": wv, "s": sv, "b": bv}, ctx, rtol=2e-2)
+    feeds = {"x": xv, "w": wv, "s": sv, "b": bv}
+    both(build, feeds, ctx, rtol=2e-2)
+    # and channel by channel: activations and their gradient per channel, the filter gradient per output channel,
+    # the scale / bias gradients element by element
+    ref = run_graph(build, feeds, None)
+    got = run_graph(build, feeds, ctx)
+    for i, axis in ((0, 1), (1, 1), (2, 0), (3, 1), (4, 1)):
+        assert_close_per_channel(got[i], ref[i], axis, rtol=5e-2, what="output %d per channel" % i)
 
 
 def test_conv_bias_helpers(ctx):

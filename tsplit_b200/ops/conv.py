@@ -7,10 +7,13 @@ gradient), ``:367-405`` (filter gradient), ``Conv2dBroadcast.py``,
 (``src/ops/CudnnConv2d.cu:127-602``).
 
 GPU path: implicit GEMM on the 5th-generation tensor cores
-(``csrc/kernels/conv_tcgen05.cu``) — activation patches are gathered straight
-into 128-byte-swizzled shared memory by ``cp.async`` producers, filter tiles
-arrive by TMA, ``tcgen05.mma.kind::tf32`` accumulates in TMEM.  Operands are
-channels-last.  The NumPy path (im2col + matmul) is the oracle.
+(``csrc/kernels/conv_tcgen05.cu``) — both operands arrive by TMA (the activation
+patches through an im2col-mode tensor map that does padding, stride and image wrap
+in the copy unit; channel counts that are no multiple of 32 fall back to ``cp.async``
+gather warps), ``tcgen05.mma.kind::tf32`` accumulates in TMEM, CTA pairs
+(``cta_group::2``) for 256-column tiles, output tiles leave by TMA store.  Operands are
+channels-last.  The NumPy path (patch view + einsum) is the oracle; on a CPU context
+the forward runs on the native host kernel (``cpu_links.conv2d``).
 """
 from __future__ import annotations
 

@@ -65,7 +65,9 @@ def main():
     args = ap.parse_args()
     rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    own_group = not dist.is_initialized()
+    if own_group:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     world = dist.get_world_size()
     ctx = ndarray.gpu(local)
     st = current_stream(ctx)
@@ -120,7 +122,8 @@ def main():
                                   floor_ms * LINK_GBS_MEASURED / LINK_GBS_NOMINAL / results["fused"], 3),
                               "bus_gbs": round(bus, 1)}))
         del comm, opt
-    dist.destroy_process_group()
+    if own_group:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
