@@ -616,6 +616,8 @@ int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, con
   double link_ms = 0.0;                       // copy time (one direction) already committed to swaps
   std::vector<char> no_drop(n, 0), no_swap(n, 0);
   const bool debug = getenv("TSB_PLAN_DEBUG") != nullptr;
+  // refinement trials after a plan fits (each is a full replay); TSB_PLAN_REFINE overrides
+  const int refine_tries = getenv("TSB_PLAN_REFINE") ? atoi(getenv("TSB_PLAN_REFINE")) : 600;
   int guard = 0;
   bool retried = false;
   while (r.fail_pos >= 0 && guard++ < 16 * n) {
@@ -736,7 +738,7 @@ int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, con
               [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
     int tries = 0;
     for (auto& e : evicted) {
-      if (++tries > 192) break;
+      if (++tries > refine_tries) break;
       const int t = e.second, was = cls[t], was_from = from[t];
       cls[t] = KEEP;
       from[t] = NEVER;
@@ -754,7 +756,7 @@ int tsb_plan2_search(int n, const int64_t* out_bytes, const double* time_ms, con
                 [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
       tries = 0;
       for (auto& e : dropped) {
-        if (++tries > 96) break;
+        if (++tries > refine_tries / 2) break;
         const int t = e.second;
         cls[t] = SWAP;
         Events tev;

@@ -111,6 +111,42 @@ def single(op, batch, channel, hw, iters):
             fn = lambda: G.softmax_ce_grad(x, y, g, z, st)
             work = 3.0 * x.nbytes / 1e6
         unit = "GB/s"
+    elif op in ("allreduce_emulate", "optimizer"):
+        # elements = batch * channel * hw * hw
+        elems = n * c * hw * hw // 4 * 4
+        if op == "allreduce_emulate":
+            # every rank's gradient / parameter array on ONE device, the shards processed one after the other by
+            # one launch: the reduce + momentum update + parameter store code of the fused all-reduce without
+            # links (what a single-GPU profiler capture can see of it).  Two ranks.
+            from .parallel import fused_allreduce as fa
+            grads = [torch.randn(elems, device="cuda") for _ in range(2)]
+            params = [torch.zeros(elems, device="cuda") for _ in range(2)]
+            s1, s2 = torch.zeros(elems, device="cuda"), torch.zeros(elems, device="cuda")
+            fn = lambda: fa.emulate(1, grads, params, s1, s2, [0.01, 0.9], st.handle)
+            work, unit = (2 + 1 + 2 + 2) * elems * 4 / 1e6, "GB/s"   # read 2 grads + param + slot, write slot + 2 params
+        else:
+            from . import optimizer as O
+            ps = [ndarray.empty((elems // 8,), ctx) for _ in range(8)]
+            gs = [ndarray.empty((elems // 8,), ctx) for _ in range(8)]
+            ss = [ndarray.empty((elems // 8,), ctx) for _ in range(8)]
+            for t in ps + gs + ss:
+                t.t.normal_()
+            fn = lambda: G.optimizer_step(1, ps, gs, ss, None, [0.01, 0.9], st)
+            work, unit = 5.0 * elems * 4 / 1e6, "GB/s"               # read p, g, slot; write p, slot
+    elif op in ("maxpool_fwd", "maxpool_bwd"):
+        x = ndarray.empty((n, c, hw, hw), ctx)
+        yo = ndarray.empty((n, c, hw // 2, hw // 2), ctx)
+        x.t.normal_()
+        G.pool(0, x, yo, 2, 2, 0, 2, st)
+        if op == "maxpool_fwd":
+            fn = lambda: G.pool(0, x, yo, 2, 2, 0, 2, st)
+            work, unit = 1.25 * x.nbytes / 1e6, "GB/s"
+        else:
+            dy = ndarray.empty((n, c, hw // 2, hw // 2), ctx)
+            dy.t.normal_()
+            dx = ndarray.empty((n, c, hw, hw), ctx)
+            fn = lambda: G.pool_grad(0, x, yo, dy, dx, 2, 2, 0, 2, st)
+            work, unit = 2.5 * x.nbytes / 1e6, "GB/s"                # read x, y, dy; write dx
     else:
         x = ndarray.empty((n, c, hw, hw), ctx)
         y = ndarray.empty((n, c, hw, hw), ctx)
@@ -144,7 +180,8 @@ def single(op, batch, channel, hw, iters):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu", "conv_fwd", "conv_dgrad",
-                                  "conv_wgrad", "bnrelu_bwd", "softmax", "softmax_grad", "ce_grad"])
+                                  "conv_wgrad", "bnrelu_bwd", "softmax", "softmax_grad", "ce_grad",
+                                  "allreduce_emulate", "optimizer", "maxpool_fwd", "maxpool_bwd"])
     p.add_argument("--sweep", default="batch", choices=["batch", "channel", "hw"])
     p.add_argument("--single", action="store_true", help="one configuration (for profiler captures)")
     p.add_argument("--batch", type=int, default=32)
