@@ -266,3 +266,40 @@ def test_max_batch_search_finds_the_boundary():
     with use_pool(ctx, peak8 + 4096):
         best = ad.max_batch_search(build, feeds, lo=1, hi=32)
     assert 8 <= best < 16
+
+
+def test_tsplit_region_reuse_is_ordered_by_events_not_by_timing():
+    """Every planned block lies on bytes other blocks held before it.  With stream logging on, the executor
+    records which stream touched which block when; the happens-before checker then proves that each reuse is
+    ordered after the last access to the previous holder by a record -> wait chain (the copy-out of a swapped
+    micro-tensor before the planned free, the compute stream's event before a prefetch writes).  Dropping the
+    wait in front of a planned free must be caught."""
+    from tsplit_b200.runtime import hbcheck
+    from tsplit_b200.executors.microop import microopExecutor
+    peak_keep = base_peak_bytes(small_cnn, 8)
+
+    def run_logged(ex_cls):
+        ctx = ndarray.simgpu(0)
+        m = small_cnn()
+        grads = ad.gradients(m.loss, m.variables)
+        x, y = m.synthetic_batch(8, seed=1)
+        with use_pool(ctx, int(peak_keep * 0.5)):
+            ex = ex_cls([m.loss] + grads, ctx=ctx, pieces=4, min_split_bytes=1, host_link_gbs=1e6)
+            with hbcheck.logging_streams() as log:
+                ex.run({m.X: x, m.y_: y})
+                log = list(log)
+        assert ex.stats["micro_transfers"] > 0 and ex.stats["planned_frees"] > 0
+        assert len(ex.hb_accesses) > 1000
+        return hbcheck.check(log, ex.hb_accesses)
+
+    assert run_logged(microopExecutor) == []
+
+    class Careless(microopExecutor):
+        def _release(self, node, final=False):               # frees a copied-out block without waiting for its copy
+            a = self.evicting.pop(node, None)
+            if a is not None:
+                self.arr.pop(node, None)
+                return
+            microopExecutor._release(self, node, final)
+    violations = run_logged(Careless)
+    assert violations and any(v[0] == "write unordered after read" for v in violations)

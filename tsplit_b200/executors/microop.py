@@ -40,6 +40,7 @@ from .. import _base, ndarray
 from ..ndarray import OutOfHBMBudget
 from ..ops.misc import PlaceholderOp
 from ..stream import Event
+from .. import stream as _stream
 from . import lowering
 from .engine import MemoryExecutor, KEEP, SWAP, DROP
 
@@ -304,6 +305,7 @@ class microopExecutor(MemoryExecutor):
         self.stats["micro_transfers"] = 0
         self.stats["planned_frees"] = 0
         self._alloc_seq = 0
+        self.hb_accesses, self._hb_blocks, self._hb_overlaps = [], [], {}
 
     # The plan gives every allocation of the step its byte offset inside one region (the planner's
     # offline placement).  The region is taken from the context's pool as a single block for the
@@ -356,7 +358,54 @@ class microopExecutor(MemoryExecutor):
             n = ndarray._numel(shape)
             o = off // 4
             view = self._region_views[key] = ndarray._make_view(self._region[o:o + max(n, 1)][:n], shape, cl)
-        return ndarray.NDArray(view, self.ctx, owns=False)
+        arr = ndarray.NDArray(view, self.ctx, owns=False)
+        if _stream.LOGGING[0]:
+            self._hb_new_block(arr, seq, off, ndarray._numel(shape) * 4)
+        return arr
+
+    # -- happens-before evidence (simulated device, stream logging on): which stream touched which planned
+    # block when, and which earlier blocks a new block lies on top of.  `runtime/hbcheck.check(log,
+    # executor.hb_accesses)` then proves that every reuse of region bytes is ordered after the last access to
+    # the block that held them before (by a record -> wait chain), whatever the copies' timing.
+    def _hb_new_block(self, arr, seq, off, size):
+        arr._hb_id = seq
+        earlier = [i for (i, o, sz) in self._hb_blocks if o < off + size and off < o + sz]
+        self._hb_blocks.append((seq, off, size))
+        self._hb_overlaps[seq] = earlier
+
+    def _hb_access(self, arr, stream, write):
+        if not _stream.LOGGING[0]:
+            return
+        bid = getattr(arr, "_hb_id", None)
+        if bid is None:
+            return
+        pos = len(_stream.ORDER_LOG)
+        for prev in self._hb_overlaps.pop(bid, ()):          # first touch of the block: it overwrites what lay there
+            self.hb_accesses.append((pos, stream.id, prev, True))
+        self.hb_accesses.append((pos, stream.id, bid, bool(write)))
+
+    def _launch(self, node, out):
+        MemoryExecutor._launch(self, node, out)
+        if _stream.LOGGING[0]:
+            # the launch is submitted after the waits on its inputs' prefetches: its accesses take the place
+            # behind them in the ordering log, and the launch an entry of its own
+            for i in node.inputs:
+                a = self.arr.get(i)
+                if a is not None:
+                    # an accumulating micro-op writes into its last input
+                    mutates = node.attrs.get("first") is False and i is node.inputs[-1]
+                    self._hb_access(a, self.stream, mutates)
+            if out is not None:
+                self._hb_access(out, self.stream, True)
+            _stream.ORDER_LOG.append(("launch", self.stream.id, -1))
+
+    def _raw_copy(self, dst, src, stream):
+        if _stream.LOGGING[0]:
+            self._hb_access(src, stream, False)
+            self._hb_access(dst, stream, True)
+        MemoryExecutor._raw_copy(self, dst, src, stream)
+        if _stream.LOGGING[0]:
+            _stream.ORDER_LOG.append(("copy", stream.id, -1))
 
     def _release(self, node, final=False):
         if node in self._direct:                 # lives in the communicator's array, not in the region
