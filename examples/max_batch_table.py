@@ -40,7 +40,8 @@ def main():
         res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         line = next((ln for ln in reversed(res.stdout.splitlines()) if ln.startswith("{")), None)
         if res.returncode != 0 or line is None:
-            rows.append((pol, None, None, None, (res.stderr.strip().splitlines() or ["failed"])[-1][:80]))
+            why = (res.stderr.strip().splitlines() or ["no output"])[-1][:80]
+            rows.append((pol, None, None, None, "did not finish (exit code %d): %s" % (res.returncode, why)))
             continue
         j = json.loads(line)
         raw.append(j)

@@ -303,3 +303,22 @@ def test_tsplit_region_reuse_is_ordered_by_events_not_by_timing():
             microopExecutor._release(self, node, final)
     violations = run_logged(Careless)
     assert violations and any(v[0] == "write unordered after read" for v in violations)
+
+
+def test_host_swap_space_is_bounded_with_a_typed_error(monkeypatch):
+    """A swap-everything policy whose host copies exceed the host swap budget fails with an error the batch
+    sweep catches (a subclass of OutOfHBMBudget), not by exhausting page-locked host memory."""
+    from tsplit_b200.ndarray import OutOfHostSwapSpace, OutOfHBMBudget
+    monkeypatch.setenv("TSPLIT_HOST_SWAP_GIB", "0.00001")          # ~10 KB
+    ctx = ndarray.simgpu(0)
+    m = small_cnn()
+    grads = ad.gradients(m.loss, m.variables)
+    x, y = m.synthetic_batch(8, seed=1)
+    ex = ad.vdnnExecutor([m.loss] + grads, ctx=ctx, policy="all")
+    with pytest.raises(OutOfHostSwapSpace) as e:
+        ex.run({m.X: x, m.y_: y})
+    assert isinstance(e.value, OutOfHBMBudget) and "host swap space" in str(e.value)
+    monkeypatch.delenv("TSPLIT_HOST_SWAP_GIB")
+    ex2 = ad.vdnnExecutor([m.loss] + grads, ctx=ctx, policy="all")
+    ex2.run({m.X: x, m.y_: y})
+    assert ex2.host_bytes > 0

@@ -326,6 +326,12 @@ class MemoryExecutor(Executor):
     def _host_buffer(self, node):
         h = self.host_bufs.get(node)
         if h is None:
+            need = 4 * ndarray._numel(self.node_to_shape_map[node])
+            if self.host_bytes + need > self.host_budget_bytes:
+                raise ndarray.OutOfHostSwapSpace(
+                    "host swap space is not enough! need %.1f MB more on top of %.1f MB pinned, budget %.1f MB" % (
+                        need / 2**20, self.host_bytes / 2**20, self.host_budget_bytes / 2**20))
+            self.host_bytes += need
             h = self.host_bufs[node] = ndarray.empty(self.node_to_shape_map[node], ndarray.cpu(0),
                                                      pinned=self.on_device)
         return h
@@ -492,7 +498,15 @@ class MemoryExecutor(Executor):
     # ------------------------------------------------------------------ run
     def memory_plan(self, feed_shapes):
         self.node_to_arr_map = {}
+        had = bool(getattr(self, "host_bufs", None))
         self.host_bufs = {}
+        self.host_bytes = 0
+        if had and self.on_device:
+            # page-locked buffers of the previous feed shape go back to the OS, not to torch's host cache:
+            # a batch sweep would otherwise pin the sum over its trials
+            import torch
+            getattr(torch._C, "_host_emptyCache", lambda: None)()
+        self.host_budget_bytes = ndarray.host_swap_budget_bytes()
         self.plan()
 
     def run(self, feed_dict, convert_to_numpy_ret_vals=False):

@@ -37,6 +37,25 @@ class OutOfHBMBudget(MemoryError):
     batch-size sweep terminate cleanly."""
 
 
+class OutOfHostSwapSpace(OutOfHBMBudget):
+    """Raised when the pinned host buffers that hold swapped-out tensors would exceed the host swap budget
+    (``TSPLIT_HOST_SWAP_GIB``, default: half of the host memory available when the executor plans).  Page-locked
+    memory cannot be paged out, so an unbounded swap-everything policy at a very large batch would otherwise end
+    with the process killed by the host's out-of-memory handler instead of an error a batch sweep can catch."""
+
+
+def host_swap_budget_bytes():
+    import os
+    v = os.environ.get("TSPLIT_HOST_SWAP_GIB")
+    if v:
+        return int(float(v) * 2**30)
+    try:
+        import psutil
+        return int(psutil.virtual_memory().available // 2)
+    except Exception:
+        return 64 << 30
+
+
 class DLContext(object):
     MASK2STR = {1: "cpu", 2: "gpu", 3: "simgpu"}
 
