@@ -114,6 +114,24 @@ class WholeOp(_MicroBase):
         return orig.op.compute(orig, ins, out, use_numpy, stream)
 
 
+class FillOp(_MicroBase):
+    """``OnesLike`` / ``ZerosLike`` of a whole tensor.  The result depends on the operand's SHAPE only, which is
+    known when the graph is lowered, so the micro-op takes no input: the ones that seed the backward pass do not
+    wait for the loss to be accumulated over all pieces, and a network without whole-batch statistics lowers to a
+    single level in which every piece runs forward AND backward before the next one starts."""
+
+    def compute(self, node, ins, out, use_numpy=True, stream=None):
+        value = node.attrs["orig"].op.value
+        if use_numpy:
+            out[...] = value
+        else:
+            G.fill(out, value, stream)
+        return None
+
+    def flops(self, node, input_shapes, output_shape):
+        return float(np.prod(output_shape)) if output_shape else 1.0
+
+
 class PieceOp(_MicroBase):
     """Piece j of k of a batch-separable operator."""
 
@@ -408,6 +426,9 @@ def lower(topo_order, shapes, layout, eval_nodes, feed_nodes, pieces, min_split_
         return "whole"
 
     kind = {n: kind_of(n) for n in topo_order}
+    for n in topo_order:
+        if kind[n] == "whole" and k > 1 and n.op.name in ("OnesLike", "ZerosLike") and shapes.get(n) is not None:
+            kind[n] = "fill"
     # a split batch-norm backward needs its forward split too (the statistics live in the forward's state either way),
     # and the pick node that only renames dx follows its producer
     for n in topo_order:
@@ -423,13 +444,13 @@ def lower(topo_order, shapes, layout, eval_nodes, feed_nodes, pieces, min_split_
             level[n], avail[n] = 0, 0
             continue
         lv = 0
-        for i in n.inputs:
+        for i in (n.inputs if kd != "fill" else ()):
             a = avail[i]
             if split_out[i] and kd in ("whole",):
                 a += 1                      # merge of all pieces
             lv = max(lv, a)
         level[n] = lv
-        if kd in ("sep", "whole", "alias"):
+        if kd in ("sep", "whole", "alias", "fill"):
             avail[n] = lv
         elif kd == "red":
             avail[n] = lv + 1               # all pieces accumulated
@@ -489,7 +510,9 @@ def lower(topo_order, shapes, layout, eval_nodes, feed_nodes, pieces, min_split_
         # 1. whole operators and finalise stages of this level
         for n in here:
             kd = kind[n]
-            if kd == "whole" and level[n] == lv:
+            if kd == "fill" and level[n] == lv:
+                whole_of[n] = emit(_mk(FillOp(n.op.name), [], n), shapes[n], n)
+            elif kd == "whole" and level[n] == lv:
                 if n.op.name in ("BatchNormGradScale", "BatchNormGradBias") and kind.get(n.inputs[0]) == "bnb":
                     ins = [whole_of[n.inputs[1]]]       # the sums are read from the gradient node's state
                 else:
