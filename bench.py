@@ -56,7 +56,8 @@ def parse_args():
                    help="after the headline run, time this smaller batch with the same policy (0 = skip)")
     p.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     p.add_argument("--graph", type=int, default=0,
-                   help="1 = replay the step from a CUDA graph when the plan has no swaps (single GPU)")
+                   help="1 = replay the step from a CUDA graph (single GPU); 2 = replay it from the native tape "
+                        "of recorded calls (any number of GPUs)")
     return p.parse_args()
 
 
@@ -127,7 +128,7 @@ def make_executor(args, model, train_op, ctx):
     from tsplit_b200 import gpu_ops as ad
     nodes = [model.loss, train_op]
     pol = args.policy
-    graph = bool(getattr(args, "graph", 0))
+    graph = {0: False, 1: True, 2: "tape"}[int(getattr(args, "graph", 0))]
     if pol == "base":
         return ad.MemoryExecutor(nodes, ctx=ctx, use_graph=graph)
     if pol == "tsplit":
@@ -395,6 +396,9 @@ def main():
                        "plan_seconds": round(plan_seconds, 1),
                        "l2": "inputs and activations per step exceed the 126 MB L2; no explicit flush",
                        "plan": plan_repr, "loss": loss_val, "executor_stats": stats,
+                       "step_replay": {0: "python loop", 1: "cuda graph", 2: "native tape"}[int(args.graph)],
+                       "native_replay_host_us_and_actions": (ex.replay_host_us() if hasattr(ex, "replay_host_us")
+                                                             else None),
                        "pieces": plan_pieces, "micro_ops": stats.get("micro_ops", 0),
                        "swap_bytes_per_step": swap_bytes,
                        "swap_link_ms_per_step": round(link_ms, 2),

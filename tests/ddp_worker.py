@@ -33,14 +33,19 @@ def train(mode, rank, ctx, steps=4, executor="plain"):
         # on the communication stream as soon as its last gradient exists
         from tsplit_b200.runtime.pool import use_pool
         with use_pool(ctx, 256 << 20):
-            ex = ad.microopExecutor([m.loss, train_op], ctx=ctx, pieces=2 if executor == "tsplit" else 1,
-                                    min_split_bytes=1)
+            ex = ad.microopExecutor([m.loss, train_op], ctx=ctx, pieces=1 if executor == "engine" else 2,
+                                    min_split_bytes=1,
+                                    use_graph="tape" if executor == "tape" and mode == "fused" else False)
             for _ in range(steps):
                 losses.append(float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0][0]))
             if mode == "fused":
                 assert len(comm.buckets) > 1, "the test is meant to exercise several buckets"
                 assert ex._direct, "no gradient was produced in place"
                 assert ex._bucket_ready_at, "no bucket was scheduled inside the backward pass"
+            if executor == "tape" and mode == "fused":
+                # two eager steps, one recorded, the rest replayed by the C++ loop, cooperative launches included
+                assert ex._step_graph is not None, getattr(ex, "replay_failure", "")
+                assert "tsb_fused_allreduce_update" in ex._step_graph.tape.names
     if hasattr(comm, "check"):
         comm.check(ex.stream)
     torch.cuda.synchronize()
@@ -57,11 +62,12 @@ def main():
     l_fused, p_fused = train("fused", rank, ctx)
     for a, b in zip(p_fused, p_ref):
         np.testing.assert_allclose(a, b, rtol=5e-3, atol=5e-4)
-    for kind in ("engine", "tsplit"):
+    for kind in ("engine", "tsplit", "tape"):
         # same executor, NCCL all-reduce + local update as the yardstick (a different executor may legitimately
         # differ by a switched ReLU, see tests/test_memory_executors_gpu.py)
-        _, p_base = train("nccl", rank, ctx, executor=kind)
-        l_e, p_e = train("fused", rank, ctx, executor=kind)
+        steps = 7 if kind == "tape" else 4
+        _, p_base = train("nccl", rank, ctx, steps=steps, executor=kind)
+        l_e, p_e = train("fused", rank, ctx, steps=steps, executor=kind)
         for a, b in zip(p_e, p_base):
             np.testing.assert_allclose(a, b, rtol=5e-3, atol=5e-4, err_msg="overlapped buckets, executor " + kind)
         flat_e = torch.cat([torch.from_numpy(p).reshape(-1) for p in p_e]).cuda()

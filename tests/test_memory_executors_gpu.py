@@ -153,7 +153,7 @@ def test_graph_replay_of_a_swap_free_step_matches_eager():
                     for _ in range(6)]
         outs.append(vals)
         if use_graph:
-            assert ex._step_graph is not None, "the step was not captured"
+            assert ex._step_graph is not None, "the step was not captured: %s" % getattr(ex, "replay_failure", "")
     np.testing.assert_allclose(outs[1], outs[0], rtol=1e-5)
     assert outs[0][-1] < outs[0][0]
 
@@ -173,7 +173,7 @@ def test_graph_replay_with_adam_keeps_the_bias_correction_in_step():
         outs.append(vals)
         assert opt.step_count == 6
         if use_graph:
-            assert ex._step_graph is not None, "the step was not captured"
+            assert ex._step_graph is not None, "the step was not captured: %s" % getattr(ex, "replay_failure", "")
     np.testing.assert_allclose(outs[1], outs[0], rtol=1e-4)
 
 
@@ -251,11 +251,62 @@ def test_tsplit_step_with_swaps_replays_from_one_cuda_graph(keep_all):
             losses = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0][0]) for _ in range(7)]
         assert ex.stats["swap_out_bytes"] > 0 and ex.stats["micro_ops"] > 0
         if use_graph:
-            assert ex._step_graph is not None, "the step was not captured"
+            assert ex._step_graph is not None, "the step was not captured: %s" % getattr(ex, "replay_failure", "")
         assert opt.step_count == 7
         runs.append(losses)
     np.testing.assert_allclose(runs[1], runs[0], rtol=1e-5)
     assert runs[0][-1] < runs[0][0]
+
+
+def test_tsplit_step_with_swaps_replays_from_the_native_tape(keep_all):
+    """The same planned step recorded as a list of native calls (kernel entries, event records, stream waits,
+    copies) and replayed by the C++ loop: steps train exactly like the eager ones, and the replay's host time per
+    action is reported."""
+    from tsplit_b200.runtime import tape
+    assert tape.available()
+    ctx = ndarray.gpu(0)
+    _, peak_keep = keep_all
+    runs = []
+    for use_graph in (False, "tape"):
+        m = net()
+        opt = optimizer.MomentumOptimizer(0.01, 0.9, ctx=ctx)
+        train = opt.minimize(m.loss)
+        x, y = m.synthetic_batch(16, seed=2)
+        with use_pool(ctx, int(peak_keep * 0.5)):
+            ex = ad.microopExecutor([m.loss, train], ctx=ctx, pieces=4, min_split_bytes=1, host_link_gbs=1e5,
+                                    use_graph=use_graph)
+            losses = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0][0]) for _ in range(7)]
+        assert ex.stats["swap_out_bytes"] > 0 and ex.stats["micro_ops"] > 0
+        if use_graph:
+            assert ex._step_graph is not None, "the step was not recorded: %s" % getattr(ex, "replay_failure", "")
+            us, actions = ex.replay_host_us()
+            names = set(ex._step_graph.tape.names)
+            assert {"tsb_memcpy_async", "tsb_event_record", "tsb_stream_wait_event"} <= names
+            assert actions > 100 and 0 < us / actions < 50.0
+            print("native replay: %d actions, %.1f us host time, %.2f us per action" % (actions, us, us / actions))
+        assert opt.step_count == 7
+        runs.append(losses)
+    np.testing.assert_allclose(runs[1], runs[0], rtol=1e-5)
+    assert runs[0][-1] < runs[0][0]
+
+
+def test_native_tape_replay_with_adam_matches_eager():
+    ctx = ndarray.gpu(0)
+    outs = []
+    for use_graph in (False, "tape"):
+        m = net()
+        opt = optimizer.AdamOptimizer(learning_rate=0.001, ctx=ctx)
+        train = opt.minimize(m.loss)
+        x, y = m.synthetic_batch(16, seed=2)
+        with use_pool(ctx, 4 << 30):
+            ex = ad.MemoryExecutor([m.loss, train], ctx=ctx, use_graph=use_graph)
+            vals = [float(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0].reshape(-1)[0])
+                    for _ in range(6)]
+        outs.append(vals)
+        assert opt.step_count == 6
+        if use_graph:
+            assert ex._step_graph is not None, "the step was not recorded: %s" % getattr(ex, "replay_failure", "")
+    np.testing.assert_allclose(outs[1], outs[0], rtol=1e-4)
 
 
 def test_device_timeline_of_a_swap_plan(tmp_path):

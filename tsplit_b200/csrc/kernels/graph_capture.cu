@@ -24,7 +24,10 @@ int tsb_graph_end(void* stream, void** exec_out) {
   if (!exec_out) return TSB_ERR_ARG;
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph);
-  if (e != cudaSuccess) return rc(e);
+  if (e != cudaSuccess) {
+    cudaGetLastError();   // an invalidated capture is over now; the next launch's error check must not see it
+    return rc(e);
+  }
   cudaGraphExec_t exec = nullptr;
   e = cudaGraphInstantiate(&exec, graph, 0);
   cudaGraphDestroy(graph);
@@ -38,6 +41,25 @@ int tsb_graph_launch(void* exec, void* stream) {
 }
 
 int tsb_graph_destroy(void* exec) { return rc(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(exec))); }
+
+// Stream-ordering and copy actions as entries of their own, so that a recorded step (csrc/runtime/step_tape.cc)
+// replays them like any kernel entry.  `event` is a cudaEvent_t the caller owns.
+int tsb_event_record(void* event, void* stream) {
+  if (!event) return TSB_ERR_ARG;
+  return rc(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+}
+
+int tsb_stream_wait_event(void* stream, void* event) {
+  if (!event) return TSB_ERR_ARG;
+  return rc(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+}
+
+// Byte copy between device memory and page-locked host memory (either direction) on `stream`.
+int tsb_memcpy_async(void* dst, const void* src, long long bytes, void* stream) {
+  if (!dst || !src || bytes < 0) return TSB_ERR_ARG;
+  if (bytes == 0) return TSB_OK;
+  return rc(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+}
 
 // free / total device memory in bytes
 int tsb_mem_info(long long* free_b, long long* total_b) {

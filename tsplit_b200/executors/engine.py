@@ -43,6 +43,27 @@ def nbytes(shape):
     return n
 
 
+class _TapedStep(object):
+    """A step recorded by ``runtime/tape.py``; same ``launch`` face as a captured CUDA graph."""
+
+    def __init__(self, tape, executor):
+        self.tape, self.executor = tape, executor
+
+    def launch(self, stream):
+        from ..runtime.tape import TapeError
+        values = {}
+        comm = self.executor._comm
+        if comm is not None:
+            values["comm_epoch"] = comm.replay_epoch()
+        try:
+            self.tape.replay(values)
+        except TapeError as e:
+            if e.entry == "tsb_fused_allreduce_update" and e.status & 0xFF == 4:
+                from ..parallel.fused_allreduce import CollectiveTimeout
+                raise CollectiveTimeout("fused all-reduce: a peer did not signal in time (code %x)" % (e.status >> 8))
+            raise
+
+
 class MemoryExecutor(Executor):
     """Base of all memory-saving executors."""
 
@@ -53,8 +74,11 @@ class MemoryExecutor(Executor):
     def __init__(self, eval_node_list, ctx=None, streams=None, policy=None, budget_bytes=None, trace=None,
                  use_graph=False):
         Executor.__init__(self, eval_node_list, ctx=ctx, policy=policy)
-        # CUDA-graph replay of the whole step (plans without swaps only, see _graph_eligible)
+        # replay of the whole step without the interpreter (see _graph_eligible): use_graph=True / "graph" captures
+        # a CUDA graph; use_graph="tape" records the native calls and replays them from a C++ loop
+        # (csrc/runtime/step_tape.cc), which also covers steps with a gradient exchange between GPUs
         self.use_graph = bool(use_graph) and self.on_device
+        self.replay_mode = "tape" if use_graph == "tape" else "graph"
         self._step_graph = None
         self._graph_steps_seen = 0
         assert ctx is not None and ndarray.is_gpu_ctx(ctx), "memory executors need a (simulated) GPU context"
@@ -181,6 +205,7 @@ class MemoryExecutor(Executor):
         self.lru = OrderedDict()      # lazy-evict cache: node -> True (MRU last)
         self._prefetch_queue = []
         self.locked = {}              # node -> lock count (an input of the running node and of a nested rebuild)
+        self._side_used = set()       # copy streams this step has put work on
         self.stats = dict(swap_out_bytes=0, swap_in_bytes=0, recomputed_nodes=0, evictions=0,
                           peak_bytes=0, prefetch_hits=0, on_demand_swapins=0)
 
@@ -339,19 +364,12 @@ class MemoryExecutor(Executor):
     def _raw_copy(self, dst, src, stream):
         """Byte copy of a dense array between device and pinned host (same element order)."""
         if self.on_device:
-            import torch
-            with torch.cuda.stream(stream.torch_stream):
-                # both sides are dense with the same logical shape; physical order may differ
-                # (channels-last on device, row-major on host), so copy through flat storage views
-                flat_dev = src.t if src.is_cuda else dst.t
-                n = flat_dev.numel()
-                dev_flat = flat_dev.as_strided((n,), (1,))
-                host = dst.t if src.is_cuda else src.t
-                host_flat = host.reshape(-1)
-                if src.is_cuda:
-                    host_flat.copy_(dev_flat, non_blocking=True)
-                else:
-                    dev_flat.copy_(host_flat, non_blocking=True)
+            # both sides are dense with the same logical shape; physical order may differ (channels-last on
+            # the device, row-major on the host), so the copy is one run of bytes between the two storages.
+            # It is an entry of the kernel library (cudaMemcpyAsync) so that a recorded step replays it.
+            dev = src if src.is_cuda else dst
+            nbytes = 4 * dev.t.numel()
+            G.memcpy_async(dst.t.data_ptr(), src.t.data_ptr(), nbytes, stream)
         else:
             dst.t.reshape(-1)[...] = src.t.reshape(-1)
 
@@ -363,6 +381,7 @@ class MemoryExecutor(Executor):
         self.d2h_stream.wait_event(ev)
         mark = self._device_mark(self.d2h_stream) if self.trace is not None else None
         self._raw_copy(h, a, self.d2h_stream)
+        self._side_used.add(self.d2h_stream)
         a.gpu2cpu_event.record(self.d2h_stream)
         self.host[node] = h
         self.stats["swap_out_bytes"] += a.nbytes
@@ -379,6 +398,7 @@ class MemoryExecutor(Executor):
         self.h2d_stream.wait_event(ev)
         mark = self._device_mark(self.h2d_stream) if self.trace is not None else None
         self._raw_copy(a, h, self.h2d_stream)
+        self._side_used.add(self.h2d_stream)
         a.cpu2gpu_event.record(self.h2d_stream)
         self.arr[node] = a
         self.swapin_event[node] = a.cpu2gpu_event
@@ -556,10 +576,25 @@ class MemoryExecutor(Executor):
             for n in self.topo_order:
                 if n.op.name == "Optimizer":
                     opt = n.attrs.get("optimizer")
-                    if opt is None or getattr(opt, "communicator", None) is not None:
+                    if opt is None or (getattr(opt, "communicator", None) is not None and self.replay_mode != "tape"):
                         ok = False
-            self._graph_ok = bool(ok)
+            self._graph_ok = bool(ok) and self._replay_backend_ok()
         return self._graph_ok
+
+    def _replay_backend_ok(self):
+        if self.replay_mode != "tape":
+            return True
+        from ..runtime import tape
+        return tape.available()
+
+    def _record_tape(self):
+        """Run the step once the ordinary way while every native call is recorded; returns the replayable step."""
+        from ..runtime import tape
+        with tape.recording() as rec:
+            self._execute()
+        if rec.invalid is not None:
+            raise RuntimeError("step cannot be replayed natively: " + rec.invalid)
+        return _TapedStep(tape.Tape(rec), self), rec.kernels
 
     def _run_graphed(self, node_to_val, convert):
         """Two eager steps (they size every library scratch buffer, tensor map and side buffer and let
@@ -585,11 +620,16 @@ class MemoryExecutor(Executor):
             from ..utils import launch_counter
             before = launch_counter.count()
             try:
-                self._step_graph = cudagraph.capture(self.stream, self._execute)
-                self._graph_launches = launch_counter.count() - before      # kernels one replay launches
-            except Exception:
+                if self.replay_mode == "tape":
+                    self._step_graph, self._graph_launches = self._record_tape()
+                    self._just_recorded = True      # the recording ran the step: nothing to launch this time
+                else:
+                    self._step_graph = cudagraph.capture(self.stream, self._execute)
+                    self._graph_launches = launch_counter.count() - before      # kernels one replay launches
+            except Exception as e:
                 # something in this step cannot be captured (an allocation path that synchronises, a
                 # library buffer that had to grow): stay on the eager path for good
+                self.replay_failure = "%s: %s" % (type(e).__name__, e)
                 self.use_graph = False
                 self._step_graph = None
                 return self._run_with_values(node_to_val, convert)
@@ -608,9 +648,10 @@ class MemoryExecutor(Executor):
                     self.arr.pop(n)
                     self.host.pop(n, None)
         captured_now = self.__dict__.pop("_just_captured", False)
-        self._step_graph.launch(self.stream)
-        from ..utils import launch_counter
-        launch_counter.add(self.__dict__.get("_graph_launches", 0))
+        if not self.__dict__.pop("_just_recorded", False):
+            self._step_graph.launch(self.stream)
+            from ..utils import launch_counter
+            launch_counter.add(self.__dict__.get("_graph_launches", 0))
         self.stream.sync()
         if not captured_now:
             # the optimizer's Python side did not run: keep its host-side step bookkeeping (checkpoints) in step.
@@ -624,6 +665,13 @@ class MemoryExecutor(Executor):
         if convert:
             outs = [o.asnumpy() if isinstance(o, ndarray.NDArray) else o for o in outs]
         return outs
+
+    def replay_host_us(self):
+        """Host time of the last native replay in microseconds and its number of actions (``use_graph="tape"``)."""
+        g = self._step_graph
+        if isinstance(g, _TapedStep):
+            return g.tape.last_host_ns / 1e3, len(g.tape)
+        return None
 
     def _run_eager_step(self, node_to_val, convert):
         saved, self.use_graph = self.use_graph, False

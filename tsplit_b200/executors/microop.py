@@ -529,6 +529,8 @@ class microopExecutor(MemoryExecutor):
         # the copy streams end the step joined to the compute stream (nothing of this step is left in flight on
         # them when the compute stream's work is done; a capture needs that to close)
         for side in (self.d2h_stream, self.h2d_stream):
+            if side not in self._side_used:     # (a stream without work of this step is not part of a capture)
+                continue
             ev = Event(self.ctx)
             ev.record(side)
             self.stream.wait_event(ev)
@@ -539,17 +541,18 @@ class microopExecutor(MemoryExecutor):
     def _graph_eligible(self):
         """A planned step is a fixed sequence of launches, copies and event waits at fixed addresses (every
         allocation has its offset in the region, every copy its pinned host buffer), so the whole step, swaps
-        included, is captured into one CUDA graph across the three streams and replayed.  Not with a
-        communicator (its epoch is a kernel argument) and not while tracing."""
+        included, is captured into one CUDA graph across the three streams and replayed.  Not while tracing; with a
+        communicator only as a native tape (``use_graph="tape"``): the fused exchange is a cooperative launch whose
+        epoch argument changes every step, which a captured graph cannot hold and the tape supplies at replay."""
         ok = self.__dict__.get("_graph_ok")
         if ok is None:
             ok = self.trace is None
             for n in self.topo_order:
                 if n.op.name == "Optimizer":
                     opt = n.attrs.get("optimizer") or n.attrs["orig"].attrs.get("optimizer")
-                    if opt is None or getattr(opt, "communicator", None) is not None:
+                    if opt is None or (getattr(opt, "communicator", None) is not None and self.replay_mode != "tape"):
                         ok = False
-            self._graph_ok = bool(ok)
+            self._graph_ok = bool(ok) and self._replay_backend_ok()
         return self._graph_ok
 
 

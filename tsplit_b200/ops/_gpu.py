@@ -109,6 +109,12 @@ def copy(x, y, stream):
     unary(UN_COPY, x, y, stream)
 
 
+def memcpy_async(dst_ptr, src_ptr, nbytes, stream):
+    """Byte copy between device memory and pinned host memory on ``stream`` (the swap path)."""
+    rc = lib().tsb_memcpy_async(c_void_p(dst_ptr), c_void_p(src_ptr), ctypes.c_longlong(nbytes), _s(stream))
+    _check(rc, "memcpy_async")
+
+
 def copy_raw(x_ptr, x_strides, y_ptr, y_strides, shape, stream):
     shape, (xs, ys) = _collapse(list(shape), list(x_strides), list(y_strides))
     rc = lib().tsb_strided_unary(c_int(UN_COPY), c_void_p(x_ptr), c_void_p(y_ptr), c_int(len(shape)),

@@ -28,6 +28,7 @@ import torch
 
 from .. import _base, ndarray
 from ..ops import _gpu as G
+from ..runtime import tape as _tape
 
 
 class CollectiveTimeout(RuntimeError):
@@ -163,6 +164,12 @@ class FusedCommunicator(object):
 
     begin_step = open_step
 
+    def replay_epoch(self):
+        """Next epoch of the flag words for a step that is replayed from a recording instead of issued here."""
+        self.epoch += 1
+        self._step_open = False
+        return c_uint(self.epoch)
+
     def launch_bucket(self, k, optimizer, compute_stream, overlapped=True):
         """Run the fused kernel for bucket ``k`` on the communication stream, after everything issued so far
         on ``compute_stream`` (which must include the producers of the bucket's gradients)."""
@@ -180,7 +187,7 @@ class FusedCommunicator(object):
             c_int(optimizer.kind), c_int(self.rank), c_int(self.world), gp, pp, fp,
             c_void_p(self.grad_mc + 4 * lo if self.grad_mc else 0),
             c_void_p(self.param_mc + 4 * lo if self.param_mc else 0), c_void_p(self.slot1[k].data_ptr()),
-            c_void_p(self.slot2[k].data_ptr()), c_longlong(hi - lo), hv, c_uint(self.epoch),
+            c_void_p(self.slot2[k].data_ptr()), c_longlong(hi - lo), hv, _tape.dyn("comm_epoch", c_uint(self.epoch)),
             c_int(self.overlap_blocks if overlapped else 0), c_void_p(self.comm_stream.handle))
         if rc & 0xFF == 4:
             raise CollectiveTimeout("fused all-reduce: a peer did not signal in time (code %x)" % (rc >> 8))

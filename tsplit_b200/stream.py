@@ -9,12 +9,21 @@ inspects, so stream discipline is testable without a GPU.
 from __future__ import annotations
 
 import itertools
+from ctypes import c_void_p
 
 import torch
+
+from . import _base
+from .runtime import tape as _tape
 
 _ids = itertools.count()
 ORDER_LOG = []          # (kind, stream_id, event_id) tuples, host contexts only
 LOGGING = [False]
+
+
+def _native(name):
+    """The raw library entry (not the counting proxy): the call is only recorded here, torch has made it."""
+    return getattr(_base.kernels()._lib, name)
 
 
 def _is_cuda(ctx):
@@ -45,6 +54,11 @@ class Stream(object):
         if self.torch_stream is not None:
             if event.recorded:
                 self.torch_stream.wait_event(event.torch_event)
+                rec = _tape.ACTIVE[0]
+                if rec is not None:              # a step is being recorded: the same wait as a native action
+                    rec.record("tsb_stream_wait_event", _native("tsb_stream_wait_event"),
+                               (c_void_p(self.handle), c_void_p(event.torch_event.cuda_event)), 0)
+                    rec.hold(event)
         elif LOGGING[0]:
             ORDER_LOG.append(("wait", self.id, event.id))
 
@@ -76,7 +90,13 @@ class Event(object):
         self.recorded = True
         if self.torch_event is not None:
             ts = getattr(stream_handle, "torch_stream", None)
-            self.torch_event.record(ts if ts is not None else torch.cuda.current_stream())
+            ts = ts if ts is not None else torch.cuda.current_stream()
+            self.torch_event.record(ts)
+            rec = _tape.ACTIVE[0]
+            if rec is not None:
+                rec.record("tsb_event_record", _native("tsb_event_record"),
+                           (c_void_p(self.torch_event.cuda_event), c_void_p(ts.cuda_stream)), 0)
+                rec.hold(self)
         elif LOGGING[0]:
             ORDER_LOG.append(("record", getattr(stream_handle, "id", -1), self.id))
 

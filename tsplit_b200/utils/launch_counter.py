@@ -5,6 +5,8 @@ number of kernels that entry launches (a lower bound: conditional extra kernels
 such as a split-K reduction are not counted)."""
 from __future__ import annotations
 
+from ..runtime import tape as _tape
+
 _count = [0]
 
 #: kernels launched per entry point (entries not listed launch one)
@@ -12,6 +14,7 @@ KERNELS_PER_ENTRY = {
     "tsb_bn_forward": 3, "tsb_bn_backward": 3, "tsb_softmax_ce": 2, "tsb_layer_norm_grad": 3,
     "tsb_graph_begin": 0, "tsb_graph_end": 0, "tsb_graph_destroy": 0, "tsb_device_status": 0,
     "tsb_mem_info": 0, "tsb_scratch_bytes": 0, "tsb_scratch_trim": 0, "tsb_graph_launch": 0,
+    "tsb_event_record": 0, "tsb_stream_wait_event": 0, "tsb_memcpy_async": 0,
 }
 
 
@@ -41,11 +44,14 @@ class CountingLib(object):
             return w
         fn = getattr(self._lib, name)
         k = KERNELS_PER_ENTRY.get(name, 1)
-        if not name.startswith("tsb_") or k == 0:
+        if not name.startswith("tsb_") or name in _tape.NOT_ACTIONS:
             return fn
 
-        def call(*a, _fn=fn, _k=k):
+        def call(*a, _fn=fn, _k=k, _name=name, _active=_tape.ACTIVE):
             _count[0] += _k
-            return _fn(*a)
+            rc = _fn(*a)
+            if _active[0] is not None:
+                _active[0].record(_name, _fn, a, _k)      # a step is being recorded for native replay
+            return rc
         self._wrapped[name] = call
         return call
