@@ -216,7 +216,7 @@ def main():
     from tsplit_b200.runtime.pool import MemoryPool
     from tsplit_b200.utils import launch_counter, hostlink
 
-    dist = None
+    dist = comm = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -240,7 +240,9 @@ def main():
     train_op = opt.minimize(model.loss)
     if world > 1:
         from tsplit_b200.parallel import ddp
-        ddp.attach(opt, dist, mode=args.comm)
+        comm = ddp.attach(opt, dist, mode=args.comm)
+        if hasattr(comm, "exposed_ms"):
+            comm.timing = True
 
     cap_bytes = int(args.cap_gib * 2**30)
     args.plan_budget = cap_bytes - (1 << 20)           # the results of a step (loss) live beside the placed region
@@ -294,6 +296,10 @@ def main():
     sampler.start()
     launch_counter.reset()
     dev_ms, loss = time_steps(ex, feed_dev, args.steps, barrier)
+    exposed_comm_ms = None
+    if comm is not None and hasattr(comm, "exposed_ms"):
+        v = comm.exposed_ms(last=args.steps)
+        exposed_comm_ms = round(sum(v) / max(len(v), 1), 3) if v else None
     launches = launch_counter.count()
     clocks = sampler.stop()
     loss_val = float(loss.asnumpy().reshape(-1)[0])
@@ -396,6 +402,7 @@ def main():
                        "plan_seconds": round(plan_seconds, 1),
                        "l2": "inputs and activations per step exceed the 126 MB L2; no explicit flush",
                        "plan": plan_repr, "loss": loss_val, "executor_stats": stats,
+                       "exposed_comm_ms_per_step": exposed_comm_ms,
                        "step_replay": {0: "python loop", 1: "cuda graph", 2: "native tape"}[int(args.graph)],
                        "native_replay_host_us_and_actions": (ex.replay_host_us() if hasattr(ex, "replay_host_us")
                                                              else None),

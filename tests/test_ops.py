@@ -125,6 +125,10 @@ CONVS = [
     (12, 64, 56, 56, 320, 3, 1, 2),    # strided, ragged channel tile
     (4, 64, 14, 14, 128, 1, 0, 2),     # 1x1 stride-2 projection (strided dgrad through zero insertion)
     (2, 32, 15, 17, 64, 3, 1, 3),      # stride 3, sizes that leave a remainder
+    (2, 64, 35, 35, 96, 3, 0, 2),      # stride 2 without padding on an odd image (parity classes of unequal size)
+    (2, 32, 28, 28, 64, 5, 2, 2),      # stride 2, 5x5: three and two taps per parity
+    (2, 32, 16, 12, 64, 2, 0, 2),      # stride 2, 2x2: one tap per parity, no padding taps
+    (3, 32, 9, 9, 32, 1, 0, 2),        # 1x1 stride 2 on an odd image: three of the four parities are zero
 ]
 
 

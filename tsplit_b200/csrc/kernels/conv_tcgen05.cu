@@ -14,6 +14,7 @@
 //
 // Role in the reference: cudnnConvolutionForward / BackwardData / BackwardFilter
 // (src/ops/CudnnConv2d.cu:127-602).
+#include <climits>
 #include <cstdio>
 #include <cstdlib>
 #include <map>
@@ -1177,6 +1178,78 @@ __global__ void upsample_zero_insert(const float* __restrict__ dy, float* __rest
   }
 }
 
+// Stride-2 dgrad without inserted zeros.  dx[2i + a] (a = 0, 1 per axis) only receives the filter taps
+// kh = 2t + r with r = (a + pad) & 1, and with q = (a + pad - r) / 2
+//     dx_a[i] = sum_t dy[i + q - t] * w[2t + r]
+// which is the data gradient of a STRIDE-1 convolution with the sub-filter w[2t + r] (T taps) and padding q.  So
+// each of the four (row parity, column parity) classes is one stride-1 forward launch over dy with the class's
+// flipped, transposed sub-filter; the four dense results are then interleaved into dx by one kernel.  The launch
+// pads dy by T - 1 - q at the leading edge and by R - OH + q at the trailing edge (R = ceil((H - a) / 2) rows of
+// the class; the two differ, and the trailing one may be negative), so it produces exactly R rows.
+// 3x3 / pad 1: 1 + 2 taps per axis, 9 tap-positions per 2x2 block of dx against 36 on the zero-inserted
+// gradient; 1x1 / pad 0: 1 against 4.
+struct ParityAxis {
+  int r, T, q, R, pad_lead, pad_trail;
+  bool empty;            // no tap falls on this parity: the class is zero
+};
+
+bool parity_axis(int H, int OH, int K, int pad, int a, ParityAxis* d) {
+  d->r = (a + pad) & 1;
+  d->T = K > d->r ? (K - d->r + 1) / 2 : 0;
+  d->q = (a + pad - d->r) / 2;
+  d->R = H > a ? (H - a + 1) / 2 : 0;
+  d->empty = d->T == 0;
+  d->pad_lead = d->T - 1 - d->q;
+  d->pad_trail = d->R - OH + d->q;
+  return d->empty || d->R == 0 || (d->pad_lead >= 0 && OH + d->pad_lead + d->pad_trail >= d->T);
+}
+
+// out[c][Ta-1-ta][Tb-1-tb][o] = w[o][2ta + ra][2tb + rb][c]: the class's sub-filter, flipped and transposed.
+__global__ void parity_filters(const float* __restrict__ w, float* __restrict__ out, int O, int C, int KH, int KW,
+                               int ra, int Ta, int rb, int Tb) {
+  __shared__ float tile[32][33];
+  const int ta = blockIdx.z / Tb, tb = blockIdx.z - ta * Tb;
+  const int ftap = (Ta - 1 - ta) * Tb + (Tb - 1 - tb);
+  const int tap = (2 * ta + ra) * KW + (2 * tb + rb);
+  const int taps = KH * KW, subtaps = Ta * Tb;
+  const int c0 = blockIdx.x * 32, o0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int o = o0 + r, c = c0 + threadIdx.x;
+    tile[r][threadIdx.x] = (o < O && c < C) ? w[((long long)o * taps + tap) * C + c] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r, o = o0 + threadIdx.x;
+    if (c < C && o < O) out[((long long)c * subtaps + ftap) * O + o] = tile[threadIdx.x][r];
+  }
+}
+
+// dx[n][y][x][:] = part[(y & 1) * 2 + (x & 1)][n][y >> 1][x >> 1][:] (a null part is a class of zeros).  One pass
+// over dx with contiguous 16-byte stores; C % 4 == 0.
+struct ParityParts {
+  const float* part[4];
+  int R[4][2];           // rows, columns of each class
+};
+
+__global__ void parity_interleave(const ParityParts pp, float* __restrict__ dx, int N, int H, int W, int C) {
+  const int C4 = C >> 2;
+  const long long total = (long long)N * H * W * C4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C4) * 4;
+    long long r = i / C4;
+    const int x = (int)(r % W); r /= W;
+    const int y = (int)(r % H);
+    const int n = (int)(r / H);
+    const int k = (y & 1) * 2 + (x & 1);
+    const float* src = pp.part[k];
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (src)
+      v = *reinterpret_cast<const float4*>(src + (((long long)n * pp.R[k][0] + (y >> 1)) * pp.R[k][1] + (x >> 1)) * C + c);
+    *reinterpret_cast<float4*>(dx + i * 4) = v;
+  }
+}
+
 __global__ void conv_splitk_reduce(const float* __restrict__ ws, float* __restrict__ out, int splits,
                                    long long per_split, int accumulate) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_split;
@@ -1211,6 +1284,16 @@ __global__ void flip_transpose_filters(const float* __restrict__ w, float* __res
 // per (stream, slot), so that convolutions running concurrently on different streams never share one.
 float* get_ws(cudaStream_t st, int slot, size_t bytes, size_t floor_bytes) {
   return static_cast<float*>(tsb_scratch::get(st, tsb_scratch::CONV_SPLITK + slot, bytes, floor_bytes));
+}
+
+// TSB_CONV_DGRAD_PARITY=0 selects the zero-insertion path for stride-2 data gradients (for comparison).
+bool dgrad_parity_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TSB_CONV_DGRAD_PARITY");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
 }
 
 int sm_count() {
@@ -1353,14 +1436,17 @@ ConvParams base_params(int N, int C, int H, int W, int O, int KH, int KW, int OH
 // im2col-mode map of the activation `a`[N,H,W,C] for a KHxKW window with this padding and stride.
 // Returns TSB_ERR_UNSUPPORTED when the shape is outside what the TMA path handles (the caller
 // then gathers with cp.async instead).
+// ph / pw pad the top / left edge, ph_end / pw_end the bottom / right edge (they may differ, and the end padding
+// may be negative: trailing rows of `a` that no window reaches).
 int im2col_map(CUtensorMap* out, const float* a, int N, int C, int H, int W, int KH, int KW, int OH, int OW, int ph,
-               int pw, int stride, int pixels, bool atom32) {
+               int pw, int stride, int pixels, bool atom32, int ph_end, int pw_end) {
   if (C % 32) return TSB_ERR_UNSUPPORTED;
   if (KH > 255 || KW > 255) return TSB_ERR_UNSUPPORTED;
-  if (H + 2 * ph < KH || W + 2 * pw < KW) return TSB_ERR_UNSUPPORTED;
-  if ((H + 2 * ph - KH) / stride + 1 != OH || (W + 2 * pw - KW) / stride + 1 != OW) return TSB_ERR_UNSUPPORTED;
+  if (H + ph + ph_end < KH || W + pw + pw_end < KW) return TSB_ERR_UNSUPPORTED;
+  if ((H + ph + ph_end - KH) / stride + 1 != OH || (W + pw + pw_end - KW) / stride + 1 != OW)
+    return TSB_ERR_UNSUPPORTED;
   const int lower[2] = {-pw, -ph};
-  const int upper[2] = {pw - (KW - 1), ph - (KH - 1)};
+  const int upper[2] = {pw_end - (KW - 1), ph_end - (KH - 1)};
   return tsb_host::make_tmap_im2col_f32(out, a, C, W, H, N, lower, upper, 32, pixels, stride, stride, atom32);
 }
 
@@ -1371,8 +1457,11 @@ int im2col_map(CUtensorMap* out, const float* a, int N, int C, int H, int W, int
 // report the number of chunks; 0 chunks = statistics not produced (the caller computes them itself).
 int run_forward(const float* src, const float* wts, float* out, int N, int C, int H, int W, int O, int KH, int KW,
                 int OH, int OW, int ph, int pw, int stride, cudaStream_t st, float* stats = nullptr,
-                long long stats_plane = 0, int max_chunks = 0, int* chunks_out = nullptr) {
+                long long stats_plane = 0, int max_chunks = 0, int* chunks_out = nullptr, int ph_end = INT_MIN,
+                int pw_end = INT_MIN) {
   if (chunks_out) *chunks_out = 0;
+  if (ph_end == INT_MIN) ph_end = ph;      // symmetric padding unless the caller says otherwise
+  if (pw_end == INT_MIN) pw_end = pw;
   ConvParams p = base_params(N, C, H, W, O, KH, KW, OH, OW, ph, pw, stride);
   p.status = tsb_host::status_word(st);
   if (!p.status) return TSB_ERR_LAUNCH;
@@ -1395,7 +1484,7 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
     if (rc) return rc;
     p.tma_store = 1;
   }
-  rc = im2col_map(&tmi, src, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BM, false);
+  rc = im2col_map(&tmi, src, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BM, false, ph_end, pw_end);
   if (rc == TSB_OK) {
     const char* e = getenv("TSB_CONV_PAIR");              // "0" selects the one-CTA tiles everywhere
     const int ptn = (p.NC + bn - 1) / bn;
@@ -1436,9 +1525,74 @@ int run_forward(const float* src, const float* wts, float* out, int N, int C, in
   return launch_bn<0, false>(bn, tm, tm, tmo, p, st);
 }
 
+// dx[N,H,W,C] = stride-2 dgrad(dy[N,OH,OW,O], w[O,KH,KW,C]) by parity classes (see parity_filters).
+// Returns TSB_ERR_UNSUPPORTED when a class cannot be written as a stride-1 launch.
+int run_dgrad_parity(float* dx, const float* w, const float* dy, int N, int C, int H, int W, int O, int KH, int KW,
+                     int OH, int OW, int ph, int pw, cudaStream_t st) {
+  ParityAxis ax[2], bx[2];
+  for (int a = 0; a < 2; ++a) {
+    if (!parity_axis(H, OH, KH, ph, a, &ax[a]) || !parity_axis(W, OW, KW, pw, a, &bx[a])) return TSB_ERR_UNSUPPORTED;
+  }
+  size_t wmax = 0, ptotal = 0, poff[4] = {0, 0, 0, 0};
+  bool live[4];
+  for (int a = 0; a < 2; ++a)
+    for (int b = 0; b < 2; ++b) {
+      const int k = a * 2 + b;
+      live[k] = !(ax[a].empty || bx[b].empty || ax[a].R == 0 || bx[b].R == 0);
+      if (!live[k]) continue;
+      const size_t wb = (size_t)C * ax[a].T * bx[b].T * O * sizeof(float);
+      if (wb > wmax) wmax = wb;
+      poff[k] = ptotal;
+      ptotal += ((size_t)N * ax[a].R * bx[b].R * C * sizeof(float) + 255) & ~size_t(255);
+    }
+  if (ptotal > (size_t(4) << 30)) return TSB_ERR_UNSUPPORTED;
+  // every class has its own filter buffer: the four launches are queued back to back
+  float* wt = wmax ? get_ws(st, 1, 4 * wmax, size_t(16) << 20) : nullptr;
+  float* parts = ptotal ? get_ws(st, 2, ptotal, size_t(64) << 20) : nullptr;
+  if ((wmax && !wt) || (ptotal && !parts)) return TSB_ERR_OOM;
+  ParityParts pp;
+  for (int a = 0; a < 2; ++a)
+    for (int b = 0; b < 2; ++b) {
+      const int k = a * 2 + b;
+      const ParityAxis &A = ax[a], &B = bx[b];
+      pp.part[k] = nullptr;
+      pp.R[k][0] = A.R; pp.R[k][1] = B.R;
+      if (!live[k]) continue;
+      float* wk = wt + (size_t)k * (wmax / sizeof(float));
+      float* part = reinterpret_cast<float*>(reinterpret_cast<char*>(parts) + poff[k]);
+      dim3 grid((C + 31) / 32, (O + 31) / 32, A.T * B.T);
+      parity_filters<<<grid, dim3(32, 8), 0, st>>>(w, wk, O, C, KH, KW, A.r, A.T, B.r, B.T);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+      const int rc = run_forward(dy, wk, part, N, O, OH, OW, C, A.T, B.T, A.R, B.R, A.pad_lead, B.pad_lead, 1, st,
+                                 nullptr, 0, 0, nullptr, A.pad_trail, B.pad_trail);
+      if (rc) return rc;
+      pp.part[k] = part;
+    }
+  const long long work = (long long)N * H * W * (C / 4);
+  long long blocks = (work + 255) / 256;
+  if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+  parity_interleave<<<(unsigned)blocks, 256, 0, st>>>(pp, dx, N, H, W, C);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
+  return TSB_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+// Geometry of one parity class of a stride-2 data gradient along one axis (host arithmetic only; see
+// parity_filters).  out = {r, T, q, R, leading pad, trailing pad, empty}; returns 1 if the class can run as a stride-1 launch.
+int tsb_conv_parity_axis(int H, int OH, int K, int pad, int a, int* out) {
+  ParityAxis d;
+  const bool ok = parity_axis(H, OH, K, pad, a, &d);
+  if (out) {
+    out[0] = d.r; out[1] = d.T; out[2] = d.q; out[3] = d.R; out[4] = d.pad_lead; out[5] = d.pad_trail;
+    out[6] = d.empty ? 1 : 0;
+  }
+  return ok ? 1 : 0;
+}
 
 // kind 0: y = conv(x, w);  1: x(dx) = dgrad(y(dy), w);  2: w(dw) = wgrad(x, y(dy)).
 // x[N,H,W,C], w[O,KH,KW,C], y[N,OH,OW,O] dense channels-last fp32; C % 4 == 0 and O % 4 == 0.
@@ -1463,6 +1617,9 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return TSB_ERR_LAUNCH | ((int)e << 8);
     rc = run_forward(y, wt, x, N, O, OH, OW, C, KH, KW, H, W, KH - 1 - ph, KW - 1 - pw, 1, st);
+  } else if (kind == 1 && stride == 2 && (O % 32) == 0 && ph <= KH - 1 && pw <= KW - 1 && dgrad_parity_enabled() &&
+             (rc = run_dgrad_parity(x, w, y, N, C, H, W, O, KH, KW, OH, OW, ph, pw, st)) != TSB_ERR_UNSUPPORTED) {
+    // stride-2 dgrad as four stride-1 launches over dy, one per output-pixel parity (rc holds the outcome)
   } else if (kind == 1 && stride > 1 && (O % 32) == 0 && ph <= KH - 1 && pw <= KW - 1 &&
              (long long)N * (H - KH + 1 + 2 * ph) * (W - KW + 1 + 2 * pw) * O * 4 <= (4ll << 30)) {
     // strided dgrad = stride-1 forward convolution of the zero-inserted dy with the flipped, transposed filters
@@ -1550,7 +1707,7 @@ int tsb_conv2d(int kind, float* x, float* w, float* y, int N, int C, int H, int 
       p.ws = get_ws(st, 0, need, size_t(128) << 20);
       if (!p.ws) return TSB_ERR_OOM;
     }
-    rc = im2col_map(&tmi, x, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BK, true);
+    rc = im2col_map(&tmi, x, N, C, H, W, KH, KW, OH, OW, ph, pw, stride, BK, true, ph, pw);
     if (rc == TSB_OK) {
       rc = use_pair ? launch_wgrad_pair(tm, tmi, p, st) : launch_bn<2, true>(bn, tm, tmi, tm, p, st);
     } else if (rc == TSB_ERR_UNSUPPORTED) {

@@ -151,7 +151,17 @@ def single(op, batch, channel, hw, iters):
         x = ndarray.empty((n, c, hw, hw), ctx)
         y = ndarray.empty((n, c, hw, hw), ctx)
         x.t.normal_(), y.t.normal_()
-        if op.startswith("conv"):
+        if op in ("conv_dgrad_s2", "conv_dgrad_s2_1x1"):
+            # data gradient of a stride-2 layer (3x3 / pad 1, or the 1x1 projection): dx is hw x hw, dy half that;
+            # the rate counts the layer's useful FLOPs only
+            k = 3 if op == "conv_dgrad_s2" else 1
+            w = ndarray.empty((c, c, k, k), ctx)
+            w.t.normal_()
+            dy = ndarray.empty((n, c, hw // 2, hw // 2), ctx)
+            dy.t.normal_()
+            fn = lambda: G.conv2d(1, x, w, dy, k // 2, k // 2, 2, st)
+            work, unit = 2.0 * n * (hw // 2) ** 2 * c * c * k * k / 1e9, "TFLOP/s"
+        elif op.startswith("conv"):
             w = ndarray.empty((c, c, 3, 3), ctx)
             w.t.normal_()
             kind = {"conv_fwd": 0, "conv_dgrad": 1, "conv_wgrad": 2}[op]
@@ -181,7 +191,8 @@ def main():
     p = argparse.ArgumentParser()
     p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu", "conv_fwd", "conv_dgrad",
                                   "conv_wgrad", "bnrelu_bwd", "softmax", "softmax_grad", "ce_grad",
-                                  "allreduce_emulate", "optimizer", "maxpool_fwd", "maxpool_bwd"])
+                                  "allreduce_emulate", "optimizer", "maxpool_fwd", "maxpool_bwd",
+                                  "conv_dgrad_s2", "conv_dgrad_s2_1x1"])
     p.add_argument("--sweep", default="batch", choices=["batch", "channel", "hw"])
     p.add_argument("--single", action="store_true", help="one configuration (for profiler captures)")
     p.add_argument("--batch", type=int, default=32)
@@ -189,7 +200,7 @@ def main():
     p.add_argument("--hw", type=int, default=56)
     p.add_argument("--iters", type=int, default=3)
     a = p.parse_args()
-    if a.single or a.op in ("conv_fwd", "conv_dgrad", "conv_wgrad", "bnrelu_bwd"):
+    if a.single or a.op in ("conv_fwd", "conv_dgrad", "conv_wgrad", "bnrelu_bwd", "conv_dgrad_s2", "conv_dgrad_s2_1x1"):
         single(a.op if a.op != "conv2d" else "conv_fwd", a.batch, a.channel, a.hw, a.iters)
         return
     for v, ms, rate, unit in sweep(a.op, a.sweep):

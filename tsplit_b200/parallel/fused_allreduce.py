@@ -116,6 +116,8 @@ class FusedCommunicator(object):
         self._step_open = False
         self._grad_views = {}
         self.comm_stream = create_stream_handle(self.ctx)
+        self.timing = False           # True: time the compute stream's wait for the exchange (exposed_ms)
+        self._exposed = []
         #: thread blocks of a bucket kernel that runs beside the backward pass (the last bucket of a step
         #: has nothing left to overlap with and takes the whole GPU)
         self.overlap_blocks = int(os.environ.get("TSPLIT_OVERLAP_BLOCKS", "48")) if overlap_blocks is None \
@@ -206,10 +208,26 @@ class FusedCommunicator(object):
             self._stage(grads, range(first, last), stream)
             self.launch_bucket(k, optimizer, stream, overlapped=(k != pending[-1]))
         from ..stream import Event
+        if self.timing:
+            t0 = Event(self.ctx, timing=True)
+            t0.record(stream)
         ev = Event(self.ctx)
         ev.record(self.comm_stream)
         stream.wait_event(ev)
+        if self.timing:
+            t1 = Event(self.ctx, timing=True)
+            t1.record(stream)
+            self._exposed.append((t0, t1))
+            del self._exposed[:-64]
         self._step_open = False
+
+    def exposed_ms(self, last=None):
+        """Time the compute stream spent waiting for the communication stream at the optimizer node in each of
+        the ``last`` most recent steps (all recorded ones if None): the part of the gradient exchange that backward
+        did not hide.  Needs ``self.timing = True`` before those steps; synchronises."""
+        torch.cuda.synchronize()
+        pairs = self._exposed if last is None else self._exposed[-int(last):]
+        return [a.elapsed_ms(b) for a, b in pairs]
 
     def check(self, stream):
         st = self.lib.tsb_comm_status(c_void_p(stream.handle if stream is not None else 0))
