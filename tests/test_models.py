@@ -42,6 +42,18 @@ def test_transformer_trains_on_cpu():
     assert np.all(np.isfinite(losses)) and losses[-1] < losses[0]
 
 
+def test_transformer_head_layout_and_fused_softmax_match_the_operator_chain():
+    outs = []
+    for hl in (True, False):
+        t = transformer(vocab_size=50, d_model=16, num_heads=2, d_ff=32, num_blocks=1, maxlen1=6, maxlen2=6,
+                        batch_size=3, head_layout=hl, fused_softmax=hl, seed=5)
+        grads = ad.gradients(t.loss, t.variables)
+        outs.append(ad.Executor([t.loss] + grads, ctx=None).run(t.synthetic_batch(), convert_to_numpy_ret_vals=True))
+    assert len(outs[0]) == len(outs[1])
+    for a, b in zip(*outs):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
 def _one_step_grads(build_loss_vars_feed, ctx):
     loss, variables, feed = build_loss_vars_feed()
     grads = ad.gradients(loss, variables)

@@ -96,6 +96,87 @@ def test_matmul_and_grads(ta, tb, ctx):
     both(build, {"a": a, "b": b}, ctx, rtol=5e-3)
 
 
+@pytest.mark.parametrize("n,h,tq,tk,d", [(2, 4, 40, 40, 32), (3, 2, 37, 45, 64), (2, 8, 255, 255, 64), (1, 2, 8, 130, 20)])
+def test_batch_matmul_in_head_layout_with_gradients(n, h, tq, tk, d, ctx):
+    """The attention products on operands stored [N, T, H, d]: scores = Q K^T (both operands in head layout),
+    context = P V (V and the result in head layout), and through ``ad.gradients`` the four products of the backward
+    pass (dQ, dK: result in head layout; dV: MN-major operand in head layout; dP: both operands in head layout)."""
+    q, k, v = f32(n, tq, h, d), f32(n, tk, h, d), f32(n, tk, h, d)
+
+    def build():
+        Q, K, V = ad.Variable("q"), ad.Variable("k"), ad.Variable("v")
+        scores = ad.batch_matmul_op(Q, K, trans_B=True, heads_A=True, heads_B=True)
+        probs = ad.softmax_op(scores * 0.2)
+        ctxv = ad.batch_matmul_op(probs, V, heads_B=True, heads_out=True)
+        loss = ad.reduce_sum_op(ad.mul_op(ctxv, ctxv), [0, 1, 2, 3])
+        gq, gk, gv = ad.gradients(loss, [Q, K, V])
+        return {"q": Q, "k": K, "v": V}, [scores, ctxv, gq, gk, gv]
+    both(build, {"q": q, "k": k, "v": v}, ctx, rtol=6e-3)
+
+
+@pytest.mark.parametrize("n,h,tq,tk,causal,masked", [(2, 3, 16, 16, True, True), (2, 2, 37, 45, False, True),
+                                                     (1, 4, 255, 255, True, False), (2, 2, 8, 600, False, True)])
+def test_masked_softmax_and_gradient(n, h, tq, tk, causal, masked, ctx):
+    scores = f32(n, h, tq, tk, scale=3.0)
+    tokens = (np.random.RandomState(3).rand(n, tk) > 0.3).astype(np.float32) * 7.0
+    tokens[:, 0] = 5.0                       # at least one real key per row
+    g = f32(n, h, tq, tk)
+
+    def build():
+        S, T, Gv = ad.Variable("s"), ad.Variable("t"), ad.Variable("g")
+        p = ad.masked_softmax_op(S, T if masked else None, scale=0.125, causal=causal)
+        loss = ad.reduce_sum_op(ad.mul_op(p, Gv), [0, 1, 2, 3])
+        ds, = ad.gradients(loss, [S])
+        return {"s": S, "t": T, "g": Gv}, [p, ds]
+    both(build, {"s": scores, "t": tokens, "g": g}, ctx, rtol=2e-3)
+
+
+def test_masked_softmax_equals_the_operator_chain():
+    n, h, tq, tk = 2, 3, 6, 6
+    scores, tokens = f32(n, h, tq, tk), np.array([[3, 1, 0, 2, 0, 0], [4, 4, 4, 0, 1, 2]], np.float32)
+
+    def chain(S, T):
+        s = S * 0.5
+        zeros = ad.zeroslike_op(T)
+        mask = ad.array_reshape_op(ad.where_op(T, zeros, ad.addbyconst_op(zeros, -1e9)), (n, 1, 1, tk))
+        s = s + ad.broadcasttoTF_op(mask, s)
+        tril = ad.Variable("tril", value=np.tril(np.ones((tq, tk), np.float32)), trainable=False)
+        s = ad.where_op(ad.broadcast_shape_op(tril, (n, h, tq, tk)), s, ad.addbyconst_op(ad.zeroslike_op(s), -1e9))
+        return ad.softmax_op(s)
+    outs = []
+    for fused in (True, False):
+        S, T = ad.Variable("s"), ad.Variable("t")
+        p = ad.masked_softmax_op(S, T, scale=0.5, causal=True) if fused else chain(S, T)
+        loss = ad.reduce_sum_op(ad.mul_op(p, p), [0, 1, 2, 3])
+        outs.append(ad.Executor([p] + ad.gradients(loss, [S]), ctx=None).run({S: scores, T: tokens},
+                                                                              convert_to_numpy_ret_vals=True))
+    for a, b in zip(*outs):
+        np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-7)
+
+
+def test_head_layout_equals_transposed_heads():
+    """NumPy oracle: the head-layout products equal the transpose -> batched product -> transpose chain."""
+    q, k, v = f32(2, 5, 3, 4), f32(2, 7, 3, 4), f32(2, 7, 3, 4)
+
+    def build(head_layout):
+        Q, K, V = ad.Variable("q"), ad.Variable("k"), ad.Variable("v")
+        if head_layout:
+            s = ad.batch_matmul_op(Q, K, trans_B=True, heads_A=True, heads_B=True)
+            c = ad.batch_matmul_op(ad.softmax_op(s), V, heads_B=True, heads_out=True)
+        else:
+            tq, tk, tv = (ad.transpose_op(x, (0, 2, 1, 3)) for x in (Q, K, V))
+            s = ad.batch_matmul_op(tq, tk, trans_B=True)
+            c = ad.transpose_op(ad.batch_matmul_op(ad.softmax_op(s), tv), (0, 2, 1, 3))
+        loss = ad.reduce_sum_op(ad.mul_op(c, c), [0, 1, 2, 3])
+        return [s, c] + ad.gradients(loss, [Q, K, V]), {Q: q, K: k, V: v}
+    outs = []
+    for hl in (True, False):
+        nodes, feed = build(hl)
+        outs.append(ad.Executor(nodes, ctx=None).run(feed, convert_to_numpy_ret_vals=True))
+    for a, b in zip(*outs):
+        np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-6)
+
+
 def test_batch_matmul(ctx):
     def build():
         A, B = ad.Variable("a"), ad.Variable("b")

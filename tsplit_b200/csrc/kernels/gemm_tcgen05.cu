@@ -45,7 +45,32 @@ struct GemmParams {
   int kblocks;        // ceil(K / BK)
   int a_chunked, b_chunked;   // MN-major operand mapped (32 cols, k, chunk of 32 cols, batch): one box per stage
   int* status;
+  // Head layout (attention): the batch is (outer, head) with `heads` heads, and an operand flagged here is stored
+  // [outer][row][head][col] instead of [outer][head][row][col].  Its tensor map then has the head as batch
+  // dimension and the rows of all outer batches in one row dimension; batch (o, h) starts `o * shift` rows in.
+  int heads;                  // 0: plain batched GEMM
+  int a_heads, b_heads, c_heads;
+  int a_shift, b_shift;       // rows per outer batch of A / B in memory (M or K rows, N or K rows)
+  long long sc2;              // C stride of the outer batch when c_heads (sc is then the head stride)
 };
+
+// Tensor-map batch coordinate and row offset of A and B, and the offset of C, for batch index b.
+struct BatchAt {
+  int ab, ar, bb, br;
+  long long c_off;
+};
+__device__ __forceinline__ BatchAt batch_at(const GemmParams& p, int b) {
+  BatchAt t;
+  t.ab = t.bb = b; t.ar = t.br = 0;
+  t.c_off = (long long)b * p.sc;
+  if (p.heads > 0) {
+    const int o = b / p.heads, h = b - o * p.heads;
+    if (p.a_heads) { t.ab = h; t.ar = o * p.a_shift; }
+    if (p.b_heads) { t.bb = h; t.br = o * p.b_shift; }
+    if (p.c_heads) t.c_off = (long long)o * p.sc2 + (long long)h * p.sc;
+  }
+  return t;
+}
 
 template <int BN>
 struct Cfg {
@@ -115,6 +140,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int n0 = (tile % p.tiles_n) * BN;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(p.kblocks, kb0 + kb_per_split);
+        const BatchAt at = batch_at(p, b);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
@@ -123,21 +149,24 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem_a + s * A_STAGE_BYTES;
           uint8_t* sb = smem_b + s * C::B_STAGE_BYTES;
           const int k0 = kb * BK;
+          // (the row dimension in memory is M / N for a K-major operand and K for an MN-major one)
           if (!A_MN) {
-            tma_load_3d(sa, &tmA, &full[s], k0, m0, b);
+            tma_load_3d(sa, &tmA, &full[s], k0, m0 + at.ar, at.ab);
           } else if (p.a_chunked) {
-            tma_load_4d(sa, &tmA, &full[s], 0, k0, m0 >> 5, b);
+            tma_load_4d(sa, &tmA, &full[s], 0, k0 + at.ar, m0 >> 5, at.ab);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 32; ++c) tma_load_3d(sa + c * (BK * 128), &tmA, &full[s], m0 + c * 32, k0, b);
+            for (int c = 0; c < BM / 32; ++c)
+              tma_load_3d(sa + c * (BK * 128), &tmA, &full[s], m0 + c * 32, k0 + at.ar, at.ab);
           }
           if (!B_MN) {
-            tma_load_3d(sb, &tmB, &full[s], k0, n0, b);
+            tma_load_3d(sb, &tmB, &full[s], k0, n0 + at.br, at.bb);
           } else if (p.b_chunked) {
-            tma_load_4d(sb, &tmB, &full[s], 0, k0, n0 >> 5, b);
+            tma_load_4d(sb, &tmB, &full[s], 0, k0 + at.br, n0 >> 5, at.bb);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) tma_load_3d(sb + c * (BK * 128), &tmB, &full[s], n0 + c * 32, k0, b);
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_3d(sb + c * (BK * 128), &tmB, &full[s], n0 + c * 32, k0 + at.br, at.bb);
           }
         }
       }
@@ -213,7 +242,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         crow = p.ws + ((long long)(split * p.batch + b) * p.m + row) * p.n;
         accumulate = false;
       } else {
-        crow = p.c + (long long)b * p.sc + (long long)row * p.ldc;
+        crow = p.c + batch_at(p, b).c_off + (long long)row * p.ldc;
         accumulate = p.accumulate != 0;
       }
 #pragma unroll 1
@@ -336,6 +365,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int b = (int)(item / tiles);
         const int m0 = (tile / ptn) * 256 + (int)rank * 128;     // this CTA's rows of A
         const int n0 = (tile % ptn) * P2_BN + (int)rank * P2_BNH;   // this CTA's columns of B
+        const BatchAt at = batch_at(p, b);
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = it % P2_STAGES;
           const uint32_t ph = (it / P2_STAGES) & 1;
@@ -344,10 +374,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           uint8_t* sa = smem_a + s * A_STAGE_BYTES;
           uint8_t* sb = smem_b + s * P2_B_STAGE_BYTES;
           const int k0 = kb * BK;
-          if (!A_MN) tma_load_3d_2sm(sa, &tmA, &full[s], k0, m0, b);
-          else tma_load_4d_2sm(sa, &tmA, &full[s], 0, k0, m0 >> 5, b);
-          if (!B_MN) tma_load_3d_2sm(sb, &tmB, &full[s], k0, n0, b);
-          else tma_load_4d_2sm(sb, &tmB, &full[s], 0, k0, n0 >> 5, b);
+          if (!A_MN) tma_load_3d_2sm(sa, &tmA, &full[s], k0, m0 + at.ar, at.ab);
+          else tma_load_4d_2sm(sa, &tmA, &full[s], 0, k0 + at.ar, m0 >> 5, at.ab);
+          if (!B_MN) tma_load_3d_2sm(sb, &tmB, &full[s], k0, n0 + at.br, at.bb);
+          else tma_load_4d_2sm(sb, &tmB, &full[s], 0, k0 + at.br, n0 >> 5, at.bb);
         }
       }
       if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -400,7 +430,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x114)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      float* crow = p.c + (long long)b * p.sc + (long long)row * p.ldc;
+      float* crow = p.c + batch_at(p, b).c_off + (long long)row * p.ldc;
       const bool accumulate = p.accumulate != 0;
 #pragma unroll 1
       for (int c0 = 0; c0 < P2_BN; c0 += 32) {
@@ -793,8 +823,12 @@ static int choose_splits(long long tiles, int kblocks, int forced) {
 int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, int k, long long lda,
                        long long ldb, long long ldc, int trans_a, int trans_b, int batch, long long sa,
                        long long sb, long long sc, int accumulate, int forced_splits, float* ws,
-                       size_t ws_bytes, bool may_alloc, cudaStream_t st) {
+                       size_t ws_bytes, bool may_alloc, cudaStream_t st, int heads = 0, int head_mask = 0) {
   if (m <= 0 || n <= 0 || k <= 0 || batch <= 0) return TSB_ERR_ARG;
+  if (heads < 0 || (heads > 0 && (batch % heads) != 0)) return TSB_ERR_ARG;
+  if (heads == 0) head_mask = 0;
+  const bool a_heads = (head_mask & 1) != 0, b_heads = (head_mask & 2) != 0, c_heads = (head_mask & 4) != 0;
+  if (head_mask) forced_splits = 1;       // the split-K scratch and its reduction address C by one batch stride
   const bool aligned = (lda % 4 == 0) && (ldb % 4 == 0) && (sa % 4 == 0) && (sb % 4 == 0) &&
                        ((reinterpret_cast<uintptr_t>(a) & 15) == 0) && ((reinterpret_cast<uintptr_t>(b) & 15) == 0);
   // Only the row strides are off (e.g. 255-wide attention matrices): pad the operand rows into scratch
@@ -806,6 +840,7 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     const int rows_a = trans_a ? k : m, cols_a = trans_a ? m : k;
     const int rows_b = trans_b ? n : k, cols_b = trans_b ? k : n;
     bool okpad = true;
+    if (((lda % 4) && a_heads) || ((ldb % 4) && b_heads)) return TSB_ERR_UNSUPPORTED;
     if ((lda % 4) || (batch > 1 && (sa % 4))) {
       lda2 = (cols_a + 3) / 4 * 4;
       sa2 = (long long)rows_a * lda2;
@@ -836,8 +871,10 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
     }
     if (okpad)
       return tsb_gemm_tf32_impl(ap, bp, c, m, n, k, lda2, ldb2, ldc, trans_a, trans_b, batch, sa2, sb2, sc, accumulate,
-                                forced_splits, ws, ws_bytes, may_alloc, st);
+                                forced_splits, ws, ws_bytes, may_alloc, st, heads,
+                                head_mask & ~((ap != a ? 1 : 0) | (bp != b ? 2 : 0)));   // a padded copy is plain
   }
+  if (!aligned && head_mask) return TSB_ERR_UNSUPPORTED;
   if (!aligned) {
     if (getenv("TSB_GEMM_TRACE"))
       fprintf(stderr, "[gemm] SIMT fallback m %d n %d k %d lda %lld ldb %lld ta %d tb %d batch %d sa %lld sb %lld a%%16 %d b%%16 %d\n",
@@ -853,6 +890,11 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
   GemmParams p;
   p.c = c; p.m = m; p.n = n; p.k = k; p.batch = batch; p.ldc = ldc; p.sc = sc;
   p.accumulate = accumulate;
+  p.heads = head_mask ? heads : 0;
+  p.a_heads = a_heads; p.b_heads = b_heads; p.c_heads = c_heads;
+  p.a_shift = trans_a ? k : m;
+  p.b_shift = trans_b ? n : k;
+  p.sc2 = (long long)m * ldc;
   p.tiles_m = (m + BM - 1) / BM;
   p.tiles_n = (n + bn - 1) / bn;
   p.kblocks = (k + BK - 1) / BK;
@@ -892,32 +934,36 @@ int tsb_gemm_tf32_impl(const float* a, const float* b, float* c, int m, int n, i
   const uint64_t sab = (uint64_t)(batch > 1 ? sa : (long long)(trans_a ? k : m) * lda) * 4;
   const uint64_t sbb = (uint64_t)(batch > 1 ? sb : (long long)(trans_b ? n : k) * ldb) * 4;
   int rc;
+  // an operand in head layout: rows of all outer batches in the row dimension, the head as batch dimension
+  const uint64_t outer = head_mask ? (uint64_t)(batch / heads) : 1;
+  const uint64_t a_rows = a_heads ? outer : 1, a_bat = a_heads ? (uint64_t)heads : (uint64_t)batch;
+  const uint64_t b_rows = b_heads ? outer : 1, b_bat = b_heads ? (uint64_t)heads : (uint64_t)batch;
   if (!trans_a) {   // A[m][k], K contiguous -> K-major
-    uint64_t d[3] = {(uint64_t)k, (uint64_t)m, (uint64_t)batch}, s[2] = {(uint64_t)lda * 4, sab};
+    uint64_t d[3] = {(uint64_t)k, (uint64_t)m * a_rows, a_bat}, s[2] = {(uint64_t)lda * 4, sab};
     uint32_t bx[3] = {BK, BM, 1};
     rc = tsb_host::make_tmap_f32(&ta, a, 3, d, s, bx);
   } else if (m % 32 == 0) {   // A stored [k][m], M contiguous -> MN-major; all chunks of a stage in one box
-    uint64_t d[4] = {32, (uint64_t)k, (uint64_t)m / 32, (uint64_t)batch}, s[3] = {(uint64_t)lda * 4, 128, sab};
+    uint64_t d[4] = {32, (uint64_t)k * a_rows, (uint64_t)m / 32, a_bat}, s[3] = {(uint64_t)lda * 4, 128, sab};
     uint32_t bx[4] = {32, BK, BM / 32, 1};
     rc = tsb_host::make_tmap_f32(&ta, a, 4, d, s, bx, true);
     p.a_chunked = 1;
   } else {
-    uint64_t d[3] = {(uint64_t)m, (uint64_t)k, (uint64_t)batch}, s[2] = {(uint64_t)lda * 4, sab};
+    uint64_t d[3] = {(uint64_t)m, (uint64_t)k * a_rows, a_bat}, s[2] = {(uint64_t)lda * 4, sab};
     uint32_t bx[3] = {32, BK, 1};
     rc = tsb_host::make_tmap_f32(&ta, a, 3, d, s, bx, true);
   }
   if (rc) return rc;
   if (trans_b) {    // B stored [n][k], K contiguous -> K-major
-    uint64_t d[3] = {(uint64_t)k, (uint64_t)n, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
+    uint64_t d[3] = {(uint64_t)k, (uint64_t)n * b_rows, b_bat}, s[2] = {(uint64_t)ldb * 4, sbb};
     uint32_t bx[3] = {BK, bbox, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx);
   } else if (n % 32 == 0) {   // B[k][n], N contiguous -> MN-major; all chunks of a stage in one box
-    uint64_t d[4] = {32, (uint64_t)k, (uint64_t)n / 32, (uint64_t)batch}, s[3] = {(uint64_t)ldb * 4, 128, sbb};
+    uint64_t d[4] = {32, (uint64_t)k * b_rows, (uint64_t)n / 32, b_bat}, s[3] = {(uint64_t)ldb * 4, 128, sbb};
     uint32_t bx[4] = {32, BK, bbox / 32, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 4, d, s, bx, true);
     p.b_chunked = 1;
   } else {
-    uint64_t d[3] = {(uint64_t)n, (uint64_t)k, (uint64_t)batch}, s[2] = {(uint64_t)ldb * 4, sbb};
+    uint64_t d[3] = {(uint64_t)n, (uint64_t)k * b_rows, b_bat}, s[2] = {(uint64_t)ldb * 4, sbb};
     uint32_t bx[3] = {32, BK, 1};
     rc = tsb_host::make_tmap_f32(&tb, b, 3, d, s, bx, true);
   }
@@ -947,6 +993,21 @@ int tsb_gemm_tf32(const float* a, const float* b, float* c, int m, int n, int k,
                   int accumulate, void* stream) {
   return tsb_gemm_tf32_impl(a, b, c, m, n, k, lda, ldb, ldc, trans_a, trans_b, batch, sa, sb, sc, accumulate, 0,
                             nullptr, 0, true, static_cast<cudaStream_t>(stream));
+}
+
+// Batched GEMM over (outer, head) with operands in head layout.  batch = outer * heads; bit 0 / 1 / 2 of
+// head_mask says that A / B / C is stored [outer][row][head][col] (what a [N, T, heads * d] projection output is,
+// read in place) instead of [outer][head][row][col]: such an operand is given with its row stride (heads * d), its
+// HEAD stride as batch stride (d), and rows-per-outer-batch equal to its full row extent.  An operand in head layout
+// whose row dimension is K (an MN-major operand) is read past the end of its K rows into the next outer batch when
+// K is not a multiple of 32; the other operand is zero there, so finite data there contributes nothing.
+int tsb_gemm_tf32_heads(const float* a, const float* b, float* c, int m, int n, int k, long long lda, long long ldb,
+                        long long ldc, int trans_a, int trans_b, int batch, long long sa, long long sb, long long sc,
+                        int accumulate, int heads, int head_mask, void* stream) {
+  if (heads <= 0 || (head_mask & ~7)) return TSB_ERR_ARG;
+  if ((head_mask & 1) && (head_mask & 2) && trans_a && !trans_b) return TSB_ERR_UNSUPPORTED;   // both K dimensions folded
+  return tsb_gemm_tf32_impl(a, b, c, m, n, k, lda, ldb, ldc, trans_a, trans_b, batch, sa, sb, sc, accumulate, 1,
+                            nullptr, 0, true, static_cast<cudaStream_t>(stream), heads, head_mask);
 }
 
 // Same with an explicit split-K factor (tests, tuning).

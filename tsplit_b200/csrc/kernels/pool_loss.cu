@@ -443,6 +443,91 @@ __global__ void __launch_bounds__(256) softmax_grad_warp_rows(const float4* __re
   }
 }
 
+// Attention soft-max: y = softmax(scale * x + mask) over rows of `cols` scores, one warp per row, the row held in
+// registers, so the scaling, the key-padding mask and the causal mask cost no pass of their own.
+//   key_tokens (optional) [batch][cols]: a key whose token is 0 is padding and gets -1e9 added
+//   causal: column j of query row q (row % tq) is replaced by -1e9 when j > q
+// Rows are [batch][rows_per_batch] with rows_per_batch = heads * tq.
+template <int NE>
+__global__ void __launch_bounds__(256) masked_softmax_warp_rows(const float* __restrict__ x,
+                                                                const float* __restrict__ key_tokens,
+                                                                float* __restrict__ y, long long rows, int cols,
+                                                                long long rows_per_batch, int tq, float scale,
+                                                                int causal) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float* xr = x + row * cols;
+    const float* kt = key_tokens ? key_tokens + (row / rows_per_batch) * cols : nullptr;
+    const int q = (int)(row % tq);
+    float v[NE];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      float t = -FLT_MAX;
+      if (i < cols) {
+        t = __ldg(xr + i) * scale;
+        if (kt && __ldg(kt + i) == 0.f) t += -1e9f;
+        if (causal && i > q) t = -1e9f;
+      }
+      v[j] = t;
+      m = fmaxf(m, t);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      v[j] = i < cols ? __expf(v[j] - m) : 0.f;
+      s += v[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.f / s;
+    float* yr = y + row * cols;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      if (i < cols) yr[i] = v[j] * inv;
+    }
+  }
+}
+
+// Its backward: dx = scale * y * (dy - sum(dy * y)) (masked positions have y = 0).
+template <int NE>
+__global__ void __launch_bounds__(256) scaled_softmax_grad_warp_rows(const float* __restrict__ y,
+                                                                     const float* __restrict__ dy,
+                                                                     float* __restrict__ dx, long long rows, int cols,
+                                                                     float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float* yr = y + row * cols;
+    const float* gr = dy + row * cols;
+    float a[NE], g[NE];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      a[j] = i < cols ? __ldg(yr + i) : 0.f;
+      g[j] = i < cols ? __ldg(gr + i) : 0.f;
+      s += a[j] * g[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    float* dr = dx + row * cols;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      const int i = lane + 32 * j;
+      if (i < cols) dr[i] = scale * a[j] * (g[j] - s);
+    }
+  }
+}
+
 // Any row length: one CTA per row, the second pass finds the row in L2.
 __global__ void softmax_grad_rows(const float* __restrict__ y, const float* __restrict__ dy, float* __restrict__ dx,
                                   long long rows, long long cols) {
@@ -700,6 +785,44 @@ int tsb_softmax_grad(const float* y, const float* dy, float* dx, long long rows,
   }
   const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
   softmax_grad_rows<<<grid, cols >= 1024 ? 256 : 128, 0, st>>>(y, dy, dx, rows, cols);
+  return done();
+}
+
+// y = softmax(scale * x + key-padding mask [+ causal mask]) row-wise; rows = batch * rows_per_batch, query index
+// of a row = row % tq.  cols <= 1024 (TSB_ERR_UNSUPPORTED beyond: the caller composes the operators instead).
+int tsb_masked_softmax(const float* x, const float* key_tokens, float* y, long long rows, long long cols,
+                       long long rows_per_batch, int tq, float scale, int causal, void* stream) {
+  if (rows <= 0 || cols <= 0 || rows_per_batch <= 0 || tq <= 0) return TSB_ERR_ARG;
+  if (cols > 1024) return TSB_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long blocks = (rows + 7) / 8;
+  const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+  const int c = (int)cols;
+#define TSB_MSM(NE) masked_softmax_warp_rows<NE><<<wgrid, 256, 0, st>>>(x, key_tokens, y, rows, c, rows_per_batch, tq, scale, causal)
+  if (c <= 64) TSB_MSM(2);
+  else if (c <= 128) TSB_MSM(4);
+  else if (c <= 256) TSB_MSM(8);
+  else if (c <= 512) TSB_MSM(16);
+  else TSB_MSM(32);
+#undef TSB_MSM
+  return done();
+}
+
+int tsb_scaled_softmax_grad(const float* y, const float* dy, float* dx, long long rows, long long cols, float scale,
+                            void* stream) {
+  if (rows <= 0 || cols <= 0) return TSB_ERR_ARG;
+  if (cols > 1024) return TSB_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long blocks = (rows + 7) / 8;
+  const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+  const int c = (int)cols;
+#define TSB_SSG(NE) scaled_softmax_grad_warp_rows<NE><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c, scale)
+  if (c <= 64) TSB_SSG(2);
+  else if (c <= 128) TSB_SSG(4);
+  else if (c <= 256) TSB_SSG(8);
+  else if (c <= 512) TSB_SSG(16);
+  else TSB_SSG(32);
+#undef TSB_SSG
   return done();
 }
 

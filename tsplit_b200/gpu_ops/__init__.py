@@ -20,7 +20,7 @@ from ..ops.shape import (array_reshape_op, array_reshape_gradient_op, transpose_
                          broadcastto_op, broadcast_shape_op, broadcasttoTF_op, add_broadcast_op, reduce_sum_op,
                          reducesumaxiszero_op)
 from ..ops.loss import (softmax_func, softmax_op, softmax_gradient_op, softmaxcrossentropy_op,
-                        softmaxcrossentropy_gradient_op)
+                        softmaxcrossentropy_gradient_op, masked_softmax_op, masked_softmax_gradient_op)
 from ..ops.misc import (Variable, placeholder_op, oneslike_op, zeroslike_op, one_hot_op,
                         embedding_lookup_op, embedding_lookup_gradient_op, dropout_op, dropout_gradient_op,
                         swap_out_op, swap_in_op, split_op)

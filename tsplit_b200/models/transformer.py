@@ -5,6 +5,8 @@ and causal masks, label smoothing — the model of the reference's
 commented out (``transformer.py:156-158``) restored and optional layer norm."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
 
 from .. import gpu_ops as ad
@@ -13,10 +15,15 @@ from .common import Params
 
 class TransformerConfig(object):
     def __init__(self, vocab_size=32000, d_model=512, num_heads=8, d_ff=2048, num_blocks=6, maxlen1=256,
-                 maxlen2=256, dropout_rate=0.0, layer_norm=True, batch_size=8):
+                 maxlen2=256, dropout_rate=0.0, layer_norm=True, batch_size=8, head_layout=True,
+                 fused_softmax=True):
         self.vocab_size, self.d_model, self.num_heads, self.d_ff = vocab_size, d_model, num_heads, d_ff
         self.num_blocks, self.maxlen1, self.maxlen2 = num_blocks, maxlen1, maxlen2
         self.dropout_rate, self.layer_norm, self.batch_size = dropout_rate, layer_norm, batch_size
+        #: attention products read / write the [N, T, heads, d] projection layout in place (no head transposes)
+        self.head_layout = bool(head_layout) and os.environ.get("TSPLIT_HEAD_LAYOUT", "1") != "0"
+        #: scale + padding mask + causal mask + soft-max as one operator (``ad.masked_softmax_op``)
+        self.fused_softmax = bool(fused_softmax) and os.environ.get("TSPLIT_FUSED_SOFTMAX", "1") != "0"
 
 
 class TransformerModel(object):
@@ -63,28 +70,42 @@ class TransformerModel(object):
         N, H, d = hp.batch_size, hp.num_heads, hp.d_model
         dh = d // H
 
+        head_layout = getattr(hp, "head_layout", True)
+
         def heads(x2d, T):
-            return ad.transpose_op(ad.array_reshape_op(x2d, (N, T, H, dh)), (0, 2, 1, 3))
+            x = ad.array_reshape_op(x2d, (N, T, H, dh))
+            # head layout: the batched products read the projection output [N, T, H, dh] in place; otherwise the
+            # heads are transposed to the front as in the reference's example
+            return x if head_layout else ad.transpose_op(x, (0, 2, 1, 3))
         q2 = ad.array_reshape_op(q_in, (-1, d))
         k2 = ad.array_reshape_op(kv_in, (-1, d))
         q = heads(self.dense(q2, d, d, name + "_q"), Tq)
         k = heads(self.dense(k2, d, d, name + "_k"), Tk)
         v = heads(self.dense(k2, d, d, name + "_v"), Tk)
-        scores = ad.batch_matmul_op(q, k, trans_B=True) * (1.0 / np.sqrt(float(dh)))      # (N, H, Tq, Tk)
-        if key_tokens is not None:            # padding mask: token id 0 is padding
-            zeros = ad.zeroslike_op(key_tokens)
-            neg = ad.addbyconst_op(zeros, -1e9)
-            mask = ad.array_reshape_op(ad.where_op(key_tokens, zeros, neg), (N, 1, 1, Tk))
-            scores = scores + ad.broadcasttoTF_op(mask, scores)
-        if causal:
-            tril = self.const(name + "_tril", np.tril(np.ones((Tq, Tk))))
-            future = ad.broadcast_shape_op(tril, (N, H, Tq, Tk))
-            neg = ad.addbyconst_op(ad.zeroslike_op(scores), -1e9)
-            scores = ad.where_op(future, scores, neg)
-        probs = ad.softmax_op(scores)
+        scores = ad.batch_matmul_op(q, k, trans_B=True, heads_A=head_layout, heads_B=head_layout)   # (N, H, Tq, Tk)
+        scale = 1.0 / np.sqrt(float(dh))
+        if getattr(hp, "fused_softmax", True):
+            # scale, key-padding mask (token id 0), causal mask and soft-max in one pass over the scores
+            probs = ad.masked_softmax_op(scores, key_tokens, scale=scale, causal=causal)
+        else:
+            scores = scores * scale
+            if key_tokens is not None:            # padding mask: token id 0 is padding
+                zeros = ad.zeroslike_op(key_tokens)
+                neg = ad.addbyconst_op(zeros, -1e9)
+                mask = ad.array_reshape_op(ad.where_op(key_tokens, zeros, neg), (N, 1, 1, Tk))
+                scores = scores + ad.broadcasttoTF_op(mask, scores)
+            if causal:
+                tril = self.const(name + "_tril", np.tril(np.ones((Tq, Tk))))
+                future = ad.broadcast_shape_op(tril, (N, H, Tq, Tk))
+                neg = ad.addbyconst_op(ad.zeroslike_op(scores), -1e9)
+                scores = ad.where_op(future, scores, neg)
+            probs = ad.softmax_op(scores)
         if hp.dropout_rate:
             probs = ad.dropout_op(probs, 1.0 - hp.dropout_rate)
-        ctx = ad.transpose_op(ad.batch_matmul_op(probs, v), (0, 2, 1, 3))
+        if head_layout:
+            ctx = ad.batch_matmul_op(probs, v, heads_B=True, heads_out=True)                # (N, Tq, H, dh)
+        else:
+            ctx = ad.transpose_op(ad.batch_matmul_op(probs, v), (0, 2, 1, 3))
         out = ad.array_reshape_op(ctx, (N, Tq, d))
         out = ad.array_reshape_op(self.dense(ad.array_reshape_op(out, (-1, d)), d, d, name + "_o"), (N, Tq, d))
         return self.norm(out + q_in, name)

@@ -196,6 +196,21 @@ def softmax_grad(y, dy, dx, stream):
            "softmax_grad")
 
 
+def masked_softmax(x, key_tokens, y, scale, causal, stream):
+    """y = softmax(scale * x + padding mask [+ causal mask]) over the last axis of x [N, H, Tq, Tk]."""
+    n, h, tq, tk = x.shape
+    rc = lib().tsb_masked_softmax(_p(x), c_void_p(key_tokens.ptr if key_tokens is not None else 0), _p(y),
+                                  c_int64(n * h * tq), c_int64(tk), c_int64(h * tq), c_int(tq), c_float(scale),
+                                  c_int(int(causal)), _s(stream))
+    _check(rc, "masked_softmax")
+
+
+def scaled_softmax_grad(y, dy, dx, scale, stream):
+    rows, cols = _numel(y.shape[:-1]), y.shape[-1]
+    _check(lib().tsb_scaled_softmax_grad(_p(y), _p(dy), _p(dx), c_int64(rows), c_int64(cols), c_float(scale),
+                                         _s(stream)), "scaled_softmax_grad")
+
+
 def softmax_ce(logits, labels, loss, stream):
     rows, cols = logits.shape
     _check(lib().tsb_softmax_ce(_p(logits), _p(labels), _p(loss), c_int64(rows), c_int64(cols),
@@ -376,9 +391,17 @@ def pool_grad(kind, x, y, dy, dx, kh, kw, pad, stride, stream):
 
 # -- tensor-core contractions -------------------------------------------------------
 def gemm(a, b, c, trans_a, trans_b, stream, batch=1, sa=0, sb=0, sc=0, m=None, n=None, k=None,
-         lda=None, ldb=None, ldc=None, accumulate=False):
+         lda=None, ldb=None, ldc=None, accumulate=False, heads=0, head_mask=0):
     """C[m,n] (+)= op(A)·op(B), row-major operands, TF32 tensor cores
-    (tcgen05, fp32 accumulate in TMEM)."""
+    (tcgen05, fp32 accumulate in TMEM).  ``heads`` / ``head_mask`` (bit 0 A, 1 B, 2 C): that operand is in head
+    layout ``[outer][row][head][col]`` and is given with its head stride as batch stride."""
+    if head_mask:
+        rc = lib().tsb_gemm_tf32_heads(_p(a), _p(b), _p(c), c_int(m), c_int(n), c_int(k), c_int64(lda),
+                                       c_int64(ldb), c_int64(ldc), c_int(int(trans_a)), c_int(int(trans_b)),
+                                       c_int(batch), c_int64(sa), c_int64(sb), c_int64(sc),
+                                       c_int(int(accumulate)), c_int(heads), c_int(head_mask), _s(stream))
+        _check(rc, "gemm_tf32_heads")
+        return
     rc = lib().tsb_gemm_tf32(_p(a), _p(b), _p(c), c_int(m), c_int(n), c_int(k), c_int64(lda),
                              c_int64(ldb), c_int64(ldc), c_int(int(trans_a)), c_int(int(trans_b)),
                              c_int(batch), c_int64(sa), c_int64(sb), c_int64(sc),
