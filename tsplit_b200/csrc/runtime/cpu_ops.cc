@@ -185,4 +185,256 @@ int tsb_cpu_optimizer(int kind, float* p, const float* g, float* s1, float* s2, 
   return 0;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Backward and data-movement operators (the rest of the reference's host backend: src/dnnl_ops/Conv2d.cpp
+// gradients, MaxPool / AvgPool gradients, BatchNorm gradient, Relu gradient, Softmax, Concat, Pad, Dropout,
+// broadcast_to, ReduceSumAxisZero, Transpose, ArraySet).
+// ---------------------------------------------------------------------------------------------------------
+
+// dx[N,C,H,W] = data gradient of the NCHW x OIHW cross-correlation; dy[N,O,OH,OW].
+int tsb_cpu_conv2d_dgrad(const float* dy, const float* w, float* dx, int N, int C, int H, int W, int O, int KH, int KW,
+                         int OH, int OW, int ph, int pw, int stride) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int c = 0; c < C; ++c) {
+      float* xc = dx + ((int64_t)n * C + c) * H * W;
+      std::fill(xc, xc + (int64_t)H * W, 0.f);
+      for (int o = 0; o < O; ++o) {
+        const float* yo = dy + ((int64_t)n * O + o) * OH * OW;
+        const float* wc = w + ((int64_t)o * C + c) * KH * KW;
+        for (int kh = 0; kh < KH; ++kh)
+          for (int kw = 0; kw < KW; ++kw) {
+            const float wv = wc[kh * KW + kw];
+            for (int oh = 0; oh < OH; ++oh) {
+              const int ih = oh * stride - ph + kh;
+              if (ih < 0 || ih >= H) continue;
+              for (int ow = 0; ow < OW; ++ow) {
+                const int iw = ow * stride - pw + kw;
+                if (iw < 0 || iw >= W) continue;
+                xc[ih * W + iw] += wv * yo[oh * OW + ow];
+              }
+            }
+          }
+      }
+    }
+  return 0;
+}
+
+// dw[O,C,KH,KW] = filter gradient.
+int tsb_cpu_conv2d_wgrad(const float* x, const float* dy, float* dw, int N, int C, int H, int W, int O, int KH, int KW,
+                         int OH, int OW, int ph, int pw, int stride) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int o = 0; o < O; ++o)
+    for (int c = 0; c < C; ++c) {
+      float* wc = dw + ((int64_t)o * C + c) * KH * KW;
+      for (int kh = 0; kh < KH; ++kh)
+        for (int kw = 0; kw < KW; ++kw) {
+          double acc = 0;
+          for (int n = 0; n < N; ++n) {
+            const float* xc = x + ((int64_t)n * C + c) * H * W;
+            const float* yo = dy + ((int64_t)n * O + o) * OH * OW;
+            for (int oh = 0; oh < OH; ++oh) {
+              const int ih = oh * stride - ph + kh;
+              if (ih < 0 || ih >= H) continue;
+              for (int ow = 0; ow < OW; ++ow) {
+                const int iw = ow * stride - pw + kw;
+                if (iw < 0 || iw >= W) continue;
+                acc += (double)xc[ih * W + iw] * yo[oh * OW + ow];
+              }
+            }
+          }
+          wc[kh * KW + kw] = (float)acc;
+        }
+    }
+  return 0;
+}
+
+// kind 0: max (the gradient goes to the first row-major maximum of each window; needs x), 1: average.
+int tsb_cpu_pool2d_grad(int kind, const float* x, const float* dy, float* dx, int N, int C, int H, int W, int KH, int KW,
+                        int OH, int OW, int pad, int stride) {
+#pragma omp parallel for schedule(static)
+  for (int64_t nc = 0; nc < (int64_t)N * C; ++nc) {
+    const float* xc = x ? x + nc * H * W : nullptr;
+    const float* gc = dy + nc * OH * OW;
+    float* dc = dx + nc * H * W;
+    std::fill(dc, dc + (int64_t)H * W, 0.f);
+    for (int oh = 0; oh < OH; ++oh)
+      for (int ow = 0; ow < OW; ++ow) {
+        const float g = gc[oh * OW + ow];
+        if (kind == 0) {
+          // padding counts as -inf; the first maximum in row-major window order wins.  A window that lies
+          // entirely in the padding has no element to give its gradient to.
+          float best = -INFINITY;
+          int bi = -1;
+          for (int kh = 0; kh < KH; ++kh)
+            for (int kw = 0; kw < KW; ++kw) {
+              const int ih = oh * stride - pad + kh, iw = ow * stride - pad + kw;
+              if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+              const float v = xc[ih * W + iw];
+              if (bi < 0 || v > best) { best = v; bi = ih * W + iw; }
+            }
+          if (bi >= 0) dc[bi] += g;
+        } else {
+          const float share = g / (float)(KH * KW);
+          for (int kh = 0; kh < KH; ++kh)
+            for (int kw = 0; kw < KW; ++kw) {
+              const int ih = oh * stride - pad + kh, iw = ow * stride - pad + kw;
+              if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+              dc[ih * W + iw] += share;
+            }
+        }
+      }
+  }
+  return 0;
+}
+
+// Spatial batch-norm backward, NCHW, from the saved mean / invstd.  relu != 0: dy is first masked by the sign of
+// the forward output (scale * xhat + bias > 0), the fused BN+ReLU form.
+int tsb_cpu_batchnorm_grad(const float* dy, const float* x, const float* scale, const float* bias, const float* mean,
+                           const float* invstd, float* dx, float* dscale, float* dbias, int N, int C, int HW, int relu) {
+#pragma omp parallel for schedule(static)
+  for (int c = 0; c < C; ++c) {
+    const float m = mean[c], is = invstd[c], sc = scale[c], bi = bias ? bias[c] : 0.f;
+    double sg = 0, sgx = 0;
+    for (int n = 0; n < N; ++n) {
+      const float* g = dy + ((int64_t)n * C + c) * HW;
+      const float* p = x + ((int64_t)n * C + c) * HW;
+      for (int i = 0; i < HW; ++i) {
+        const float xh = (p[i] - m) * is;
+        const float gv = (relu && !(sc * xh + bi > 0.f)) ? 0.f : g[i];
+        sg += gv; sgx += (double)gv * xh;
+      }
+    }
+    const double cnt = (double)N * HW;
+    if (dscale) dscale[c] = (float)sgx;
+    if (dbias) dbias[c] = (float)sg;
+    for (int n = 0; n < N; ++n) {
+      const float* g = dy + ((int64_t)n * C + c) * HW;
+      const float* p = x + ((int64_t)n * C + c) * HW;
+      float* d = dx + ((int64_t)n * C + c) * HW;
+      for (int i = 0; i < HW; ++i) {
+        const float xh = (p[i] - m) * is;
+        const float gv = (relu && !(sc * xh + bi > 0.f)) ? 0.f : g[i];
+        d[i] = sc * is * (float)(gv - sg / cnt - xh * sgx / cnt);
+      }
+    }
+  }
+  return 0;
+}
+
+int tsb_cpu_softmax(const float* x, float* y, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * cols;
+    float* yr = y + r * cols;
+    float m = xr[0];
+    for (int64_t i = 1; i < cols; ++i) m = std::max(m, xr[i]);
+    double s = 0;
+    for (int64_t i = 0; i < cols; ++i) { yr[i] = std::exp(xr[i] - m); s += yr[i]; }
+    const float inv = (float)(1.0 / s);
+    for (int64_t i = 0; i < cols; ++i) yr[i] *= inv;
+  }
+  return 0;
+}
+
+// dx = y * (dy - sum(dy * y)) row-wise
+int tsb_cpu_softmax_grad(const float* y, const float* dy, float* dx, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* yr = y + r * cols;
+    const float* gr = dy + r * cols;
+    double s = 0;
+    for (int64_t i = 0; i < cols; ++i) s += (double)yr[i] * gr[i];
+    for (int64_t i = 0; i < cols; ++i) dx[r * cols + i] = yr[i] * (gr[i] - (float)s);
+  }
+  return 0;
+}
+
+// y[cols] = sum over rows of x[rows][cols]
+int tsb_cpu_reduce_sum_axis0(const float* x, float* y, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t j = 0; j < cols; ++j) {
+    double s = 0;
+    for (int64_t r = 0; r < rows; ++r) s += x[r * cols + j];
+    y[j] = (float)s;
+  }
+  return 0;
+}
+
+// y[rows][cols] = x[cols] for every row
+int tsb_cpu_broadcast_rows(const float* x, float* y, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) std::memcpy(y + r * cols, x, (size_t)cols * sizeof(float));
+  return 0;
+}
+
+// y = transpose(x, perm): y's dimension d is x's dimension perm[d]; ndim <= 8.
+int tsb_cpu_transpose(const float* x, float* y, int ndim, const int64_t* xshape, const int* perm) {
+  if (ndim < 1 || ndim > 8) return 1;
+  int64_t xstride[8], yshape[8], ystep[8], total = 1;
+  xstride[ndim - 1] = 1;
+  for (int d = ndim - 2; d >= 0; --d) xstride[d] = xstride[d + 1] * xshape[d + 1];
+  for (int d = 0; d < ndim; ++d) { yshape[d] = xshape[perm[d]]; ystep[d] = xstride[perm[d]]; total *= yshape[d]; }
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < total; ++i) {
+    int64_t rem = i, off = 0;
+    for (int d = ndim - 1; d >= 0; --d) { off += (rem % yshape[d]) * ystep[d]; rem /= yshape[d]; }
+    y[i] = x[off];
+  }
+  return 0;
+}
+
+// Copy a dense block: y[outer][ycols] columns [yoff, yoff + xcols) <- x[outer][xcols] (grad = 0), or the reverse
+// direction x <- y (grad != 0).  Serves concat / concat gradient along any axis (outer = product of the leading
+// dimensions, cols = product of the axis and the trailing ones) and pad / pad gradient of the last axes row by row.
+int tsb_cpu_copy_block(float* x, float* y, int64_t outer, int64_t xcols, int64_t ycols, int64_t yoff, int grad) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < outer; ++r) {
+    if (grad) std::memcpy(x + r * xcols, y + r * ycols + yoff, (size_t)xcols * sizeof(float));
+    else std::memcpy(y + r * ycols + yoff, x + r * xcols, (size_t)xcols * sizeof(float));
+  }
+  return 0;
+}
+
+// Constant padding of the two trailing axes of x[outer][H][W] into y[outer][H + pt + pb][W + pl + pr] (grad = 0:
+// y is written completely), or the gradient x <- interior of y (grad != 0).
+int tsb_cpu_pad2d(float* x, float* y, int64_t outer, int H, int W, int pt, int pb, int pl, int pr, float value, int grad) {
+  const int YH = H + pt + pb, YW = W + pl + pr;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < outer; ++r) {
+    float* yr = y + r * YH * YW;
+    float* xr = x + r * (int64_t)H * W;
+    if (!grad) std::fill(yr, yr + (int64_t)YH * YW, value);
+    for (int h = 0; h < H; ++h) {
+      if (grad) std::memcpy(xr + (int64_t)h * W, yr + (int64_t)(h + pt) * YW + pl, (size_t)W * sizeof(float));
+      else std::memcpy(yr + (int64_t)(h + pt) * YW + pl, xr + (int64_t)h * W, (size_t)W * sizeof(float));
+    }
+  }
+  return 0;
+}
+
+int tsb_cpu_array_set(float* y, int64_t n, float value) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) y[i] = value;
+  return 0;
+}
+
+// y = x * mask / keep; element i is kept when the 64-bit mix of (seed, i + offset) maps below `keep` — the same
+// integer mix as the device kernel (csrc/kernels/misc_optim.cu: uniform01) and the NumPy path, so forward,
+// recompute and backward of one step agree without storing the mask.
+int tsb_cpu_dropout(const float* x, float* y, int64_t n, float keep, uint64_t seed, int64_t offset) {
+  const float inv = 1.f / keep;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    uint64_t h = (uint64_t)(i + offset) + seed * 0x9E3779B97F4A7C15ull;
+    h ^= h >> 30; h *= 0xBF58476D1CE4E5B9ull;
+    h ^= h >> 27; h *= 0x94D049BB133111EBull;
+    h ^= h >> 31;
+    const float u = (float)(h >> 40) * (1.0f / 16777216.0f);
+    y[i] = u < keep ? x[i] * inv : 0.f;
+  }
+  return 0;
+}
+
 }  // extern "C"

@@ -159,6 +159,14 @@ class Conv2dGradDataOp(Op):
         xs = self._xshape(node, iv[0].shape, iv[1].shape)
         return np_conv2d_grad_data(iv[0], iv[1], xs, ph, pw, node.attrs["stride"])
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], out):
+            return False
+        ph, pw = _pads(node)
+        cpu_links.conv2d_grad_data(iv[1], iv[0], out, ph, pw, node.attrs["stride"])
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         ph, pw = _pads(node)
         G.conv2d(1, out, iv[0], iv[1], ph, pw, node.attrs["stride"], stream)
@@ -198,6 +206,14 @@ class Conv2dGradFilterOp(Op):
         ph, pw = _pads(node)
         fs = self._fshape(node, iv[0].shape, iv[1].shape)
         return np_conv2d_grad_filter(iv[0], iv[1], fs, ph, pw, node.attrs["stride"])
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], out):
+            return False
+        ph, pw = _pads(node)
+        cpu_links.conv2d_grad_filter(iv[0], iv[1], out, ph, pw, node.attrs["stride"])
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         ph, pw = _pads(node)

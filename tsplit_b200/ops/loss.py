@@ -30,6 +30,13 @@ class SoftmaxOp(Op):
     def np_compute(self, node, iv):
         return softmax_func(iv[0]).astype(np.float32)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], out):
+            return False
+        cpu_links.softmax(iv[0], out)
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         G.softmax(iv[0], out, stream)
 
@@ -54,6 +61,13 @@ class SoftmaxGradientOp(Op):
     def np_compute(self, node, iv):
         y, dy = iv
         return (y * (dy - np.sum(dy * y, axis=-1, keepdims=True))).astype(np.float32)
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], out):
+            return False
+        cpu_links.softmax_grad(iv[0], iv[1], out)
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         G.softmax_grad(iv[0], iv[1], out, stream)

@@ -71,6 +71,13 @@ class _FillLike(Op):
     def np_compute(self, node, iv):
         return np.full(iv[0].shape, self.value, dtype=np.float32)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(out):
+            return False
+        cpu_links.array_set(out, self.value)
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         G.fill(out, self.value, stream)
 
@@ -229,6 +236,13 @@ class DropoutOp(Op):
         m = philox_like_mask(iv[0].shape, kp, step_seed(node), node.attrs.get("element_offset", 0))
         return (iv[0] * m / kp).astype(np.float32)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], out):
+            return False
+        cpu_links.dropout(iv[0], out, node.attrs["keep_prob"], step_seed(node), int(node.attrs.get("element_offset", 0)))
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         assert iv[0].is_dense() and iv[0].same_layout(out)
         off = int(node.attrs.get("element_offset", 0))
@@ -252,6 +266,7 @@ class DropoutGradientOp(Op):
         return Op.__call__(self, g, keep_prob=float(keep_prob), seed=forward_node.attrs["seed"])
 
     np_compute = DropoutOp.np_compute
+    cpu_compute = DropoutOp.cpu_compute
     gpu_compute = DropoutOp.gpu_compute
 
     def gradient(self, node, g):

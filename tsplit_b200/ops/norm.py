@@ -91,6 +91,23 @@ class BatchNormOp(Op):
         st["np_run_var"] = mom * st.get("np_run_var", np.ones_like(var)) + (1 - mom) * var
         return y
 
+    def cpu_compute(self, node, iv, out, relu=False):
+        from .. import cpu_links
+        x, scale, bias = iv
+        if x.ndim != 4 or not cpu_links.ok(x, scale, bias, out):
+            return False
+        c = x.shape[1]
+        mean, invstd = np.empty(c, np.float32), np.empty(c, np.float32)
+        cpu_links.batch_norm(x, scale, bias, out, mean, invstd, node.attrs["eps"])
+        if relu:
+            cpu_links.unary(cpu_links.UNARY["Relu"], out, out)
+        st, mom = node.state, node.attrs["momentum"]
+        var = 1.0 / (invstd.astype(np.float64) ** 2) - node.attrs["eps"]
+        st["np_mean"], st["np_invstd"] = mean, invstd
+        st["np_run_mean"] = mom * st.get("np_run_mean", np.zeros_like(mean)) + (1 - mom) * mean
+        st["np_run_var"] = mom * st.get("np_run_var", np.ones_like(mean)) + (1 - mom) * var.astype(np.float32)
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         self._forward(node, iv, out, stream, False)
 
@@ -120,6 +137,9 @@ class BatchNormReluOp(BatchNormOp):
     def np_compute(self, node, iv):
         return np.maximum(BatchNormOp.np_compute(self, node, iv), 0)
 
+    def cpu_compute(self, node, iv, out):
+        return BatchNormOp.cpu_compute(self, node, iv, out, relu=True)
+
     def gpu_compute(self, node, iv, out, stream):
         self._forward(node, iv, out, stream, True)
 
@@ -147,6 +167,18 @@ class BatchNormReluGradientOp(Op):
         dx, ds, db = np_bn_backward(g * (y > 0), x, scale, mean, invstd)
         node.state["np_dscale"], node.state["np_dbias"] = ds.reshape(scale.shape), db.reshape(scale.shape)
         return dx
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        g, x, scale, bias = iv
+        fwd = node.attrs["fwd"]
+        if x.ndim != 4 or fwd is None or "np_mean" not in fwd.state or not cpu_links.ok(g, x, scale, bias, out):
+            return False
+        ds, db = np.empty(scale.shape, np.float32), np.empty(scale.shape, np.float32)
+        cpu_links.batch_norm_grad(g, x, scale, bias, np.ascontiguousarray(fwd.state["np_mean"], np.float32),
+                                  np.ascontiguousarray(fwd.state["np_invstd"], np.float32), out, ds, db, relu=True)
+        node.state["np_dscale"], node.state["np_dbias"] = ds, db
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         g, x, scale, bias = iv
@@ -189,6 +221,18 @@ class BatchNormGradientOp(Op):
         dx, ds, db = np_bn_backward(g, x, scale, mean, invstd)
         node.state["np_dscale"], node.state["np_dbias"] = ds.reshape(scale.shape), db.reshape(scale.shape)
         return dx
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        g, x, scale = iv
+        fwd = node.attrs["fwd"]
+        if x.ndim != 4 or fwd is None or "np_mean" not in fwd.state or not cpu_links.ok(g, x, scale, out):
+            return False
+        ds, db = np.empty(scale.shape, np.float32), np.empty(scale.shape, np.float32)
+        cpu_links.batch_norm_grad(g, x, scale, None, np.ascontiguousarray(fwd.state["np_mean"], np.float32),
+                                  np.ascontiguousarray(fwd.state["np_invstd"], np.float32), out, ds, db, relu=False)
+        node.state["np_dscale"], node.state["np_dbias"] = ds, db
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         g, x, scale = iv

@@ -129,6 +129,14 @@ class MaxPool2dGradientOp(Op):
         a = node.attrs
         return np_max_pool_grad(iv[2], iv[0], iv[1], a["kernel_H"], a["kernel_W"], a["padding"], a["stride"])
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[1], iv[2], out):
+            return False
+        a = node.attrs
+        cpu_links.pool2d_grad(0, iv[2], iv[1], out, a["kernel_H"], a["kernel_W"], a["padding"], a["stride"])
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         a = node.attrs
         G.pool_grad(0, iv[2], iv[0], iv[1], out, a["kernel_H"], a["kernel_W"], a["padding"], a["stride"], stream)
@@ -155,6 +163,14 @@ class AvgPool2dGradientOp(Op):
         xs = (iv[0].shape[0],) + tuple(a["like"].inferred_shape[1:])       # batch from the gradient (may be a piece)
         return np_avg_pool_grad(iv[0], xs, a["kernel_H"], a["kernel_W"],
                                 a["padding"], a["stride"])
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], out):
+            return False
+        a = node.attrs
+        cpu_links.pool2d_grad(1, None, iv[0], out, a["kernel_H"], a["kernel_W"], a["padding"], a["stride"])
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         a = node.attrs

@@ -120,6 +120,13 @@ class TransposeOp(Op):
     def np_compute(self, node, iv):
         return np.transpose(iv[0], self._perm(node, iv[0].ndim))
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], out) or iv[0].ndim > 8:
+            return False
+        cpu_links.transpose(iv[0], out, self._perm(node, iv[0].ndim))
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         x = iv[0]
         perm = self._perm(node, len(x.shape))
@@ -213,6 +220,19 @@ class ConcatOp(Op):
     def np_compute(self, node, iv):
         return np.concatenate(iv, axis=node.attrs["axis"])
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], out):
+            return False
+        ax = node.attrs["axis"]
+        outer = int(np.prod(out.shape[:ax], dtype=np.int64))
+        ycols, off = out.size // max(outer, 1), 0
+        for x in iv:
+            xcols = x.size // max(outer, 1)
+            cpu_links.copy_block(x, out, outer, xcols, ycols, off)
+            off += xcols
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         ax = node.attrs["axis"]
         off = 0
@@ -254,6 +274,17 @@ class ConcatGradientOp(Op):
         sl[ax] = slice(b, b + n)
         return iv[0][tuple(sl)]
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        g = iv[0]
+        if not cpu_links.ok(g, out):
+            return False
+        ax, b, n = self._range(node, g.shape)
+        outer = int(np.prod(g.shape[:ax], dtype=np.int64))
+        inner = int(np.prod(g.shape[ax + 1:], dtype=np.int64))
+        cpu_links.copy_block(out, g, outer, n * inner, g.shape[ax] * inner, b * inner, grad=True)
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         g = iv[0]
         ax, b, n = self._range(node, g.shape)
@@ -283,6 +314,14 @@ class PadOp(Op):
         return np.pad(iv[0], self._full(node, iv[0].ndim), mode="constant",
                       constant_values=node.attrs["constant_values"])
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        pads = self._full(node, iv[0].ndim)
+        if not cpu_links.ok(iv[0], out) or iv[0].ndim < 2 or any(p != (0, 0) for p in pads[:-2]):
+            return False                       # the native kernel pads the two trailing axes
+        cpu_links.pad2d(iv[0], out, pads[-2], pads[-1], float(node.attrs["constant_values"]))
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         x = iv[0]
         pads = self._full(node, len(x.shape))
@@ -311,6 +350,14 @@ class PadGradientOp(Op):
     def np_compute(self, node, iv):
         pads = self._full(node, iv[0].ndim)
         return iv[0][tuple(slice(p[0], d - p[1]) for p, d in zip(pads, iv[0].shape))]
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        pads = self._full(node, iv[0].ndim)
+        if not cpu_links.ok(iv[0], out) or iv[0].ndim < 2 or any(p != (0, 0) for p in pads[:-2]):
+            return False
+        cpu_links.pad2d(out, iv[0], pads[-2], pads[-1], grad=True)
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         g = iv[0]
@@ -355,6 +402,15 @@ class BroadcastToOp(Op):
 
     def np_compute(self, node, iv):
         return np.broadcast_to(iv[0], iv[1].shape)
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        x = iv[0]
+        # the native kernel tiles the whole input along new leading dimensions (the reference's form)
+        if not cpu_links.ok(x, out) or x.size == 0 or tuple(out.shape[out.ndim - x.ndim:]) != tuple(x.shape):
+            return False
+        cpu_links.broadcast_rows(x, out)
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         x = iv[0]
@@ -546,6 +602,13 @@ class ReduceSumAxisZeroOp(Op):
     def np_compute(self, node, iv):
         r = iv[0].sum(axis=0)
         return r.reshape((1,)) if r.ndim == 0 else r
+
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], out) or iv[0].ndim < 1:
+            return False
+        cpu_links.reduce_sum_axis_zero(iv[0], out)
+        return True
 
     def gpu_compute(self, node, iv, out, stream):
         x = iv[0]
