@@ -4,6 +4,7 @@ eventual), at-least-once delivery under message loss, heartbeats, the TCP ring
 all-reduce (including a neighbour that never joins), communicator classes, the
 in-graph gradient exchange nodes and the CPU operator library."""
 import os
+import sys
 import socket
 import threading
 import time
@@ -231,3 +232,47 @@ def test_cpu_context_executor_runs_on_the_native_host_kernels():
         assert (used > 20) == (ctx is not None), "native kernel calls: %d" % used
     for a, b in zip(outs[1], outs[0]):
         np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+
+
+def _run_ps_workers(port, workers, mode, env=None):
+    import subprocess
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ps_net_worker.py")
+    e = dict(os.environ, **(env or {}))
+    procs = [subprocess.Popen([sys.executable, worker, str(port), str(r), str(workers), mode], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, env=e) for r in range(workers)]
+    return [(p.wait(timeout=120), p.stdout.read()) for p in procs]
+
+
+def test_parameter_server_across_processes_over_tcp():
+    """Server in this process (listening on the loopback interface), two workers in child processes: BSP push-pull
+    sums every worker's delta each step, sparse rows arrive, and both workers say goodbye."""
+    from tsplit_b200.parallel import ps_net
+    srv = ps_net.serve(num_servers=2, num_workers=2)
+    try:
+        res = _run_ps_workers(srv.port, 2, "train")
+        for rc, out in res:
+            assert rc == 0 and "WORKER_OK" in out, out
+        assert srv.wait_for_workers(timeout=10) and srv.gone() == 0
+        w = np.empty(1000, np.float32)
+        srv.store.wait(srv.store.pull("w", w))
+        np.testing.assert_allclose(w, (1 + 2) * (1 + 2 + 3))
+    finally:
+        srv.stop()
+
+
+def test_a_worker_that_leaves_is_seen_by_the_server_and_times_out_the_others():
+    """Rank 1 exits between steps without a goodbye: the server counts it as gone and releases (or refuses) the
+    barrier rank 0 waits in, so rank 0's BSP step ends with PSConnectionError (at the latest after its own request
+    timeout) instead of hanging."""
+    from tsplit_b200.parallel import ps_net
+    srv = ps_net.serve(num_servers=1, num_workers=2)
+    try:
+        res = _run_ps_workers(srv.port, 2, "leave_early", env={"PS_TIMEOUT": "2"})
+        assert res[1][0] == 0
+        assert res[0][0] == 3 and "TIMEOUT" in res[0][1], res[0]
+        t0 = time.time()
+        while srv.gone() < 1 and time.time() - t0 < 5:
+            time.sleep(0.05)
+        assert srv.gone() >= 1
+    finally:
+        srv.stop()

@@ -59,6 +59,7 @@ struct PS {
   std::condition_variable bar_cv;
   int bar_count = 0;
   int64_t bar_gen = 0;
+  int64_t bar_broken = 0;      // bumped by tsb_ps_release_barrier
 
   // heartbeats
   std::mutex hb_mu;
@@ -234,18 +235,32 @@ int tsb_ps_wait(void* h, int64_t ts) {
   return 0;
 }
 
-// Blocks until num_workers callers have arrived (Postoffice::Barrier among workers).
+// Blocks until num_workers callers have arrived (Postoffice::Barrier among workers).  Returns 0, or 5 when the
+// barrier was released by tsb_ps_release_barrier instead (a worker is known to be gone, or the server shuts down).
 int tsb_ps_barrier(void* h) {
   PS* p = static_cast<PS*>(h);
   std::unique_lock<std::mutex> lk(p->bar_mu);
   const int64_t gen = p->bar_gen;
+  const int64_t broken = p->bar_broken;
   if (++p->bar_count == p->num_workers) {
     p->bar_count = 0;
     ++p->bar_gen;
     p->bar_cv.notify_all();
   } else {
-    p->bar_cv.wait(lk, [&] { return p->bar_gen != gen; });
+    p->bar_cv.wait(lk, [&] { return p->bar_gen != gen || p->bar_broken != broken; });
+    if (p->bar_gen == gen) return 5;           // released without everybody
   }
+  return 0;
+}
+
+// Release every caller that waits in the barrier now, with status 5, and forget their arrivals.
+int tsb_ps_release_barrier(void* h) {
+  PS* p = static_cast<PS*>(h);
+  if (!p) return 1;
+  std::lock_guard<std::mutex> lk(p->bar_mu);
+  p->bar_count = 0;
+  ++p->bar_broken;
+  p->bar_cv.notify_all();
   return 0;
 }
 

@@ -68,7 +68,8 @@ void* tsb_ring_connect(int n, int id, const char* host, int base_port, int timeo
   ::setsockopt(r->listen_fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
   sockaddr_in addr{};
   addr.sin_family = AF_INET;
-  addr.sin_addr.s_addr = htonl(INADDR_ANY);
+  // every rank of this ring lives at `host` (default: the loopback interface), so that is where this rank listens
+  ::inet_pton(AF_INET, host && *host ? host : "127.0.0.1", &addr.sin_addr);
   addr.sin_port = htons((uint16_t)(base_port + id));
   if (::bind(r->listen_fd, reinterpret_cast<sockaddr*>(&addr), sizeof(addr)) != 0 || ::listen(r->listen_fd, 4) != 0) {
     ::close(r->listen_fd);
