@@ -211,6 +211,10 @@ def main():
     if world != args.gpus and world > 1:
         args.gpus = world
     torch.cuda.set_device(local_rank)
+    cpus = None
+    if world > 1:      # pinned swap buffers on the NUMA node of this rank's GPU
+        from tsplit_b200.utils.affinity import bind_to_gpu
+        cpus = bind_to_gpu(local_rank)
 
     from tsplit_b200 import ndarray, optimizer, _base
     from tsplit_b200.runtime.pool import MemoryPool
@@ -226,7 +230,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    link = hostlink.measure(local_rank)
+    barrier()          # all ranks measure at the same time: they share the host's memory bandwidth during training too
+    link = hostlink.measure(local_rank, repeats=8 if world > 1 else 4, shared=world > 1)
     if not args.host_link_gbs:
         args.host_link_gbs = min(link["bidir_h2d_gbs"], link["bidir_d2h_gbs"])
     if dist is not None:                    # every rank plans with the same figure
@@ -403,6 +408,7 @@ def main():
                        "l2": "inputs and activations per step exceed the 126 MB L2; no explicit flush",
                        "plan": plan_repr, "loss": loss_val, "executor_stats": stats,
                        "exposed_comm_ms_per_step": exposed_comm_ms,
+                       "cpus_bound_to_gpu": len(cpus) if cpus else 0,
                        "step_replay": {0: "python loop", 1: "cuda graph", 2: "native tape"}[int(args.graph)],
                        "native_replay_host_us_and_actions": (ex.replay_host_us() if hasattr(ex, "replay_host_us")
                                                              else None),

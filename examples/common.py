@@ -70,6 +70,8 @@ def dist_setup():
     import torch.distributed as dist
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    from tsplit_b200.utils.affinity import bind_to_gpu
+    bind_to_gpu(local)                 # pinned swap buffers on the NUMA node of this rank's GPU
     if not dist.is_initialized():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _DIST[0] = dist

@@ -239,3 +239,38 @@ def test_pool_guard_zones_catch_a_write_past_the_end():
             b._release()
     finally:
         ndarray.set_pool(ctx, None)
+
+
+def test_rank_binds_its_threads_to_the_cpus_next_to_its_gpu(monkeypatch):
+    """``bind_to_gpu`` applies NVML's CPU set of the GPU to the calling thread (a fake NVML here: no GPU setting is
+    read or changed), leaves the thread alone when NVML is missing or the set is not usable, and honours the switch."""
+    import os
+    import sys
+    import types
+    from tsplit_b200.utils.affinity import bind_to_gpu
+    if not hasattr(os, "sched_setaffinity"):
+        pytest.skip("no sched_setaffinity on this platform")
+    before = os.sched_getaffinity(0)
+    want = set(sorted(before)[:max(1, len(before) // 2)])
+    if want == before:
+        pytest.skip("only one CPU available")
+    asked = []
+    fake = types.ModuleType("pynvml")
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: asked.append(i) or ("gpu", i)
+    fake.nvmlDeviceGetHandleByUUID = lambda u: ("gpu", u)
+    mask = [sum(1 << (c - 64 * w) for c in want if 64 * w <= c < 64 * (w + 1)) for w in range((max(before) // 64) + 1)]
+    fake.nvmlDeviceGetCpuAffinity = lambda h, n: (mask + [0] * n)[:n]
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    try:
+        assert bind_to_gpu(3) == sorted(want) and asked == [3]
+        assert os.sched_getaffinity(0) == want
+        os.sched_setaffinity(0, before)
+        monkeypatch.setenv("TSPLIT_BIND_CPUS", "0")
+        assert bind_to_gpu(3) is None and os.sched_getaffinity(0) == before
+        monkeypatch.delenv("TSPLIT_BIND_CPUS")
+        fake.nvmlDeviceGetCpuAffinity = lambda h, n: [0] * n          # a CPU set outside this process's cpuset
+        assert bind_to_gpu(0) is None and os.sched_getaffinity(0) == before
+    finally:
+        os.sched_setaffinity(0, before)

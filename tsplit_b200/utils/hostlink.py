@@ -16,12 +16,13 @@ import json
 _CACHE = {}
 
 
-def measure(device=0, mbytes=256, repeats=4):
+def measure(device=0, mbytes=256, repeats=4, shared=False):
     """Returns {"h2d_gbs", "d2h_gbs", "bidir_h2d_gbs", "bidir_d2h_gbs"} for pinned copies of
     ``mbytes`` MiB (best of ``repeats``); the bidirectional figures are per direction while
-    both run on their own streams."""
+    both run on their own streams.  ``shared``: other processes of the box copy at the same time (one rank per
+    GPU measuring together); then the MEDIAN repeat counts, because the best one is the moment the others paused."""
     import torch
-    key = (device, mbytes)
+    key = (device, mbytes, bool(shared))
     if key in _CACHE:
         return _CACHE[key]
     n = mbytes * 2**20 // 4
@@ -35,6 +36,7 @@ def measure(device=0, mbytes=256, repeats=4):
 
     def timed(fn_in, fn_out):
         best_in = best_out = None
+        all_in, all_out = [], []
         for _ in range(repeats + 1):
             torch.cuda.synchronize(dev)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -52,9 +54,14 @@ def measure(device=0, mbytes=256, repeats=4):
             if fn_in:
                 t = ev[0].elapsed_time(ev[1])
                 best_in = t if best_in is None else min(best_in, t)
+                all_in.append(t)
             if fn_out:
                 t = ev[2].elapsed_time(ev[3])
                 best_out = t if best_out is None else min(best_out, t)
+                all_out.append(t)
+        if shared:
+            return (sorted(all_in)[len(all_in) // 2] if all_in else None,
+                    sorted(all_out)[len(all_out) // 2] if all_out else None)
         return best_in, best_out
 
     h2d = lambda: d_a.copy_(h_a, non_blocking=True)
