@@ -111,6 +111,27 @@ def single(op, batch, channel, hw, iters):
             fn = lambda: G.softmax_ce_grad(x, y, g, z, st)
             work = 3.0 * x.nbytes / 1e6
         unit = "GB/s"
+    elif op in ("masked_softmax", "attention_scores", "attention_context"):
+        # batch = N, channel = heads, hw = sequence length; head size 64
+        heads, t, d = c, hw, 64
+        q, k, v = (ndarray.empty((n, t, heads, d), ctx) for _ in range(3))
+        sc, pr = ndarray.empty((n, heads, t, t), ctx), ndarray.empty((n, heads, t, t), ctx)
+        ctxv = ndarray.empty((n, t, heads, d), ctx)
+        tok = ndarray.empty((n, t), ctx)
+        for a in (q, k, v, sc):
+            a.t.normal_()
+        tok.t.fill_(1.0)
+        if op == "masked_softmax":
+            fn = lambda: G.masked_softmax(sc, tok, pr, 0.125, True, st)
+            work, unit = 2.0 * sc.nbytes / 1e6, "GB/s"                  # read the scores, write the probabilities
+        elif op == "attention_scores":     # Q K^T, both operands read in the [N, T, heads, d] projection layout
+            fn = lambda: G.gemm(q, k, sc, False, True, st, batch=n * heads, m=t, n=t, k=d, sa=d, sb=d, sc=t * t,
+                                lda=heads * d, ldb=heads * d, ldc=t, heads=heads, head_mask=3)
+            work, unit = (q.nbytes + k.nbytes + sc.nbytes) / 1e6, "GB/s"
+        else:                              # P V, V and the result in the projection layout
+            fn = lambda: G.gemm(sc, v, ctxv, False, False, st, batch=n * heads, m=t, n=d, k=t, sa=t * t, sb=d, sc=d,
+                                lda=t, ldb=heads * d, ldc=heads * d, heads=heads, head_mask=6)
+            work, unit = (sc.nbytes + v.nbytes + ctxv.nbytes) / 1e6, "GB/s"
     elif op in ("allreduce_emulate", "optimizer"):
         # elements = batch * channel * hw * hw
         elems = n * c * hw * hw // 4 * 4
@@ -192,7 +213,8 @@ def main():
     p.add_argument("op", choices=["conv2d", "matmul", "bn", "maxpool", "relu", "conv_fwd", "conv_dgrad",
                                   "conv_wgrad", "bnrelu_bwd", "softmax", "softmax_grad", "ce_grad",
                                   "allreduce_emulate", "optimizer", "maxpool_fwd", "maxpool_bwd",
-                                  "conv_dgrad_s2", "conv_dgrad_s2_1x1"])
+                                  "conv_dgrad_s2", "conv_dgrad_s2_1x1", "masked_softmax", "attention_scores",
+                                  "attention_context"])
     p.add_argument("--sweep", default="batch", choices=["batch", "channel", "hw"])
     p.add_argument("--single", action="store_true", help="one configuration (for profiler captures)")
     p.add_argument("--batch", type=int, default=32)
