@@ -496,6 +496,73 @@ __global__ void __launch_bounds__(256) masked_softmax_warp_rows(const float* __r
   }
 }
 
+// The same with 16-byte lanes (cols % 4 == 0, 16-byte aligned rows): NV float4 per lane.
+template <int NV>
+__global__ void __launch_bounds__(256) masked_softmax_warp_rows_v4(const float4* __restrict__ x,
+                                                                   const float4* __restrict__ key_tokens,
+                                                                   float4* __restrict__ y, long long rows, int nvec,
+                                                                   long long rows_per_batch, int tq, float scale,
+                                                                   int causal) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float4* xr = x + row * nvec;
+    const float4* kt = key_tokens ? key_tokens + (row / rows_per_batch) * nvec : nullptr;
+    const int q = (int)(row % tq);
+    float4 v[NV];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      float4 t = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+      if (i < nvec) {
+        t = __ldg(xr + i);
+        t.x *= scale; t.y *= scale; t.z *= scale; t.w *= scale;
+        if (kt) {
+          const float4 k = __ldg(kt + i);
+          if (k.x == 0.f) t.x += -1e9f;
+          if (k.y == 0.f) t.y += -1e9f;
+          if (k.z == 0.f) t.z += -1e9f;
+          if (k.w == 0.f) t.w += -1e9f;
+        }
+        if (causal) {
+          const int c = 4 * i;
+          if (c > q) t.x = -1e9f;
+          if (c + 1 > q) t.y = -1e9f;
+          if (c + 2 > q) t.z = -1e9f;
+          if (c + 3 > q) t.w = -1e9f;
+        }
+      }
+      v[j] = t;
+      m = fmaxf(m, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec) {
+        v[j].x = __expf(v[j].x - m); v[j].y = __expf(v[j].y - m);
+        v[j].z = __expf(v[j].z - m); v[j].w = __expf(v[j].w - m);
+      } else {
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.f / s;
+    float4* yr = y + row * nvec;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec) yr[i] = make_float4(v[j].x * inv, v[j].y * inv, v[j].z * inv, v[j].w * inv);
+    }
+  }
+}
+
 // Its backward: dx = scale * y * (dy - sum(dy * y)) (masked positions have y = 0).
 template <int NE>
 __global__ void __launch_bounds__(256) scaled_softmax_grad_warp_rows(const float* __restrict__ y,
@@ -524,6 +591,39 @@ __global__ void __launch_bounds__(256) scaled_softmax_grad_warp_rows(const float
     for (int j = 0; j < NE; ++j) {
       const int i = lane + 32 * j;
       if (i < cols) dr[i] = scale * a[j] * (g[j] - s);
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) scaled_softmax_grad_warp_rows_v4(const float4* __restrict__ y,
+                                                                        const float4* __restrict__ dy,
+                                                                        float4* __restrict__ dx, long long rows,
+                                                                        int nvec, float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarp) {
+    const float4* yr = y + row * nvec;
+    const float4* gr = dy + row * nvec;
+    float4 a[NV], g[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      a[j] = i < nvec ? __ldg(yr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      g[j] = i < nvec ? __ldg(gr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s += (a[j].x * g[j].x + a[j].y * g[j].y) + (a[j].z * g[j].z + a[j].w * g[j].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    float4* dr = dx + row * nvec;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec)
+        dr[i] = make_float4(scale * a[j].x * (g[j].x - s), scale * a[j].y * (g[j].y - s),
+                            scale * a[j].z * (g[j].z - s), scale * a[j].w * (g[j].w - s));
     }
   }
 }
@@ -798,6 +898,19 @@ int tsb_masked_softmax(const float* x, const float* key_tokens, float* y, long l
   const long long blocks = (rows + 7) / 8;
   const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
   const int c = (int)cols;
+  if (c % 4 == 0 && aligned16(x) && aligned16(y) && (!key_tokens || aligned16(key_tokens))) {
+    const int nvec = c / 4;
+    const float4* xv = reinterpret_cast<const float4*>(x);
+    const float4* kv = reinterpret_cast<const float4*>(key_tokens);
+    float4* yv = reinterpret_cast<float4*>(y);
+#define TSB_MSV(NV) masked_softmax_warp_rows_v4<NV><<<wgrid, 256, 0, st>>>(xv, kv, yv, rows, nvec, rows_per_batch, tq, scale, causal)
+    if (nvec <= 32) TSB_MSV(1);
+    else if (nvec <= 64) TSB_MSV(2);
+    else if (nvec <= 128) TSB_MSV(4);
+    else TSB_MSV(8);
+#undef TSB_MSV
+    return done();
+  }
 #define TSB_MSM(NE) masked_softmax_warp_rows<NE><<<wgrid, 256, 0, st>>>(x, key_tokens, y, rows, c, rows_per_batch, tq, scale, causal)
   if (c <= 64) TSB_MSM(2);
   else if (c <= 128) TSB_MSM(4);
@@ -816,6 +929,19 @@ int tsb_scaled_softmax_grad(const float* y, const float* dy, float* dx, long lon
   const long long blocks = (rows + 7) / 8;
   const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
   const int c = (int)cols;
+  if (c % 4 == 0 && aligned16(y) && aligned16(dy) && aligned16(dx)) {
+    const int nvec = c / 4;
+    const float4* yv = reinterpret_cast<const float4*>(y);
+    const float4* gv = reinterpret_cast<const float4*>(dy);
+    float4* dv = reinterpret_cast<float4*>(dx);
+#define TSB_SSV(NV) scaled_softmax_grad_warp_rows_v4<NV><<<wgrid, 256, 0, st>>>(yv, gv, dv, rows, nvec, scale)
+    if (nvec <= 32) TSB_SSV(1);
+    else if (nvec <= 64) TSB_SSV(2);
+    else if (nvec <= 128) TSB_SSV(4);
+    else TSB_SSV(8);
+#undef TSB_SSV
+    return done();
+  }
 #define TSB_SSG(NE) scaled_softmax_grad_warp_rows<NE><<<wgrid, 256, 0, st>>>(y, dy, dx, rows, c, scale)
   if (c <= 64) TSB_SSG(2);
   else if (c <= 128) TSB_SSG(4);
