@@ -54,6 +54,20 @@ struct GemmParams {
   long long sc2;              // C stride of the outer batch when c_heads (sc is then the head stride)
 };
 
+// Order in which the persistent CTAs walk the output tiles: groups of TILE_GROUP_M tile rows, column by column
+// inside a group.  The CTAs that run at the same time (consecutive tile indices) then share TILE_GROUP_M row
+// panels of A and a handful of column panels of B, which together stay in L2, instead of one or two rows of A
+// and every panel of B.
+constexpr int TILE_GROUP_M = 8;
+__device__ __forceinline__ void tile_mn(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = TILE_GROUP_M * tiles_n;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int m_first = g * TILE_GROUP_M;
+  const int rows = min(TILE_GROUP_M, tiles_m - m_first);
+  tn = r / rows;
+  tm = m_first + (r - tn * rows);
+}
+
 // Tensor-map batch coordinate and row offset of A and B, and the offset of C, for batch index b.
 struct BatchAt {
   int ab, ar, bb, br;
@@ -136,8 +150,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const long long rest = item / tiles;
         const int b = (int)(rest % p.batch);
         const int split = (int)(rest / p.batch);
-        const int m0 = (tile / p.tiles_n) * BM;
-        const int n0 = (tile % p.tiles_n) * BN;
+        int tm, tn;
+        tile_mn(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(p.kblocks, kb0 + kb_per_split);
         const BatchAt at = batch_at(p, b);
@@ -227,8 +242,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const long long rest = item / tiles;
       const int b = (int)(rest % p.batch);
       const int split = (int)(rest / p.batch);
-      const int m0 = (tile / p.tiles_n) * BM;
-      const int n0 = (tile % p.tiles_n) * BN;
+      int tm, tn;
+      tile_mn(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
       const int acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
       const int kb0 = split * kb_per_split;
@@ -363,8 +379,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (long long item = pair; item < items && ok; item += npairs) {
         const int tile = (int)(item % tiles);
         const int b = (int)(item / tiles);
-        const int m0 = (tile / ptn) * 256 + (int)rank * 128;     // this CTA's rows of A
-        const int n0 = (tile % ptn) * P2_BN + (int)rank * P2_BNH;   // this CTA's columns of B
+        int tm, tn;
+        tile_mn(tile, ptm, ptn, tm, tn);
+        const int m0 = tm * 256 + (int)rank * 128;           // this CTA's rows of A
+        const int n0 = tn * P2_BN + (int)rank * P2_BNH;      // this CTA's columns of B
         const BatchAt at = batch_at(p, b);
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = it % P2_STAGES;
@@ -423,8 +441,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (long long item = pair; item < items && ok; item += npairs, ++acc_it) {
       const int tile = (int)(item % tiles);
       const int b = (int)(item / tiles);
-      const int m0 = (tile / ptn) * 256 + (int)rank * 128;
-      const int n0 = (tile % ptn) * P2_BN;
+      int tm, tn;
+      tile_mn(tile, ptm, ptn, tm, tn);
+      const int m0 = tm * 256 + (int)rank * 128;
+      const int n0 = tn * P2_BN;
       const int acc = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, p.status, 0x114)) { ok = false; break; }

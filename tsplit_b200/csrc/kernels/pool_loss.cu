@@ -459,8 +459,10 @@ __global__ void __launch_bounds__(256) masked_softmax_warp_rows(const float* __r
   const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long row = warp0; row < rows; row += nwarp) {
     const float* xr = x + row * cols;
-    const float* kt = key_tokens ? key_tokens + (row / rows_per_batch) * cols : nullptr;
-    const int q = (int)(row % tq);
+    // 32-bit index arithmetic (rows < 2^31, checked by the launcher): two 64-bit divisions per row would cost as much
+    // as the row's loads
+    const float* kt = key_tokens ? key_tokens + (long long)((unsigned)row / (unsigned)rows_per_batch) * cols : nullptr;
+    const int q = (int)((unsigned)row % (unsigned)tq);
     float v[NE];
     float m = -FLT_MAX;
 #pragma unroll
@@ -508,8 +510,8 @@ __global__ void __launch_bounds__(256) masked_softmax_warp_rows_v4(const float4*
   const long long nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long row = warp0; row < rows; row += nwarp) {
     const float4* xr = x + row * nvec;
-    const float4* kt = key_tokens ? key_tokens + (row / rows_per_batch) * nvec : nullptr;
-    const int q = (int)(row % tq);
+    const float4* kt = key_tokens ? key_tokens + (long long)((unsigned)row / (unsigned)rows_per_batch) * nvec : nullptr;
+    const int q = (int)((unsigned)row % (unsigned)tq);
     float4 v[NV];
     float m = -FLT_MAX;
 #pragma unroll
@@ -893,7 +895,7 @@ int tsb_softmax_grad(const float* y, const float* dy, float* dx, long long rows,
 int tsb_masked_softmax(const float* x, const float* key_tokens, float* y, long long rows, long long cols,
                        long long rows_per_batch, int tq, float scale, int causal, void* stream) {
   if (rows <= 0 || cols <= 0 || rows_per_batch <= 0 || tq <= 0) return TSB_ERR_ARG;
-  if (cols > 1024) return TSB_ERR_UNSUPPORTED;
+  if (cols > 1024 || rows >= (1ll << 31) || rows_per_batch >= (1ll << 31)) return TSB_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long blocks = (rows + 7) / 8;
   const int wgrid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
