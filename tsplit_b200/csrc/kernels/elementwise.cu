@@ -256,7 +256,9 @@ __global__ void binary_rows(const float* __restrict__ p, const float* __restrict
        r += (long long)gridDim.x * blockDim.y) {
     long long oa, ob, oy;
     offsets3(o, r, oa, ob, oy);
-    for (int c = threadIdx.x; c < inner; c += 32) y[oy + c * sy] = bin<OP>(p[oa + c * sa], q[ob + c * sb]);
+    // gridDim.y column slices per row: few long rows would otherwise leave most SMs idle
+    for (int c = threadIdx.x + 32 * blockIdx.y; c < inner; c += 32 * gridDim.y)
+      y[oy + c * sy] = bin<OP>(p[oa + c * sa], q[ob + c * sb]);
   }
 }
 template <int OP>
@@ -266,7 +268,8 @@ __global__ void unary_rows(const float* __restrict__ x, float* __restrict__ y, c
        r += (long long)gridDim.x * blockDim.y) {
     long long ox, oy;
     offsets2(o, r, ox, oy);
-    for (int c = threadIdx.x; c < inner; c += 32) y[oy + c * sy] = un<OP>(OP == UN_FILL ? 0.f : x[ox + c * sx], a);
+    for (int c = threadIdx.x + 32 * blockIdx.y; c < inner; c += 32 * gridDim.y)
+      y[oy + c * sy] = un<OP>(OP == UN_FILL ? 0.f : x[ox + c * sx], a);
   }
 }
 
@@ -397,6 +400,22 @@ float* colsum_scratch() {   // 64 chunks x up to 64K columns
 
 }  // namespace
 
+// Grid of the row-form kernels: eight rows per block along x; when that leaves SMs idle (few long rows, e.g. an
+// NCHW image batch seen as N * C rows of H * W), the columns of a row are cut into gridDim.y slices of >= 256.
+dim3 rows_grid(long long outer, int inner) {
+  const int gx = grid_for(outer * 32, 256);
+  int gy = 1;
+  const int want = 148 * 4;
+  if (gx < want) {
+    gy = (want + gx - 1) / gx;
+    const int most = (inner + 255) / 256;
+    if (gy > most) gy = most;
+    if (gy < 1) gy = 1;
+    if (gy > 65535) gy = 65535;
+  }
+  return dim3((unsigned)gx, (unsigned)gy, 1);
+}
+
 #define UN_CASE(OPC) \
   case OPC: unary_flat<OPC><<<grid, 256, 0, st>>>(x, y, n, alpha); break;
 #define UNR_CASE(OPC) \
@@ -507,7 +526,7 @@ int tsb_strided_unary(int op, const float* x, float* y, int nd, const long long*
   if (nd >= 2 && shape[nd - 1] >= 64 && shape[nd - 1] < (1ll << 31)) {
     const long long outer = n / shape[nd - 1];
     const int inner = (int)shape[nd - 1];
-    const int rgrid = grid_for(outer * 32, 256);
+    const dim3 rgrid = rows_grid(outer, inner);
     Dims dr = d;
     dr.nd = nd - 1;
     switch (op) {
@@ -551,7 +570,7 @@ int tsb_strided_binary(int op, const float* a, const float* b, float* y, int nd,
   if (nd >= 2 && shape[nd - 1] >= 64 && shape[nd - 1] < (1ll << 31)) {
     const long long outer = n / shape[nd - 1];
     const int inner = (int)shape[nd - 1];
-    const int rgrid = grid_for(outer * 32, 256);
+    const dim3 rgrid = rows_grid(outer, inner);
     Dims dr = d;
     dr.nd = nd - 1;
     switch (op) {

@@ -230,6 +230,7 @@ class Executor(object):
         """Publish this executor's step index to the ops that draw per-step random numbers."""
         from ..ops import misc
         misc.STEP[0] = self.__dict__.get("_run_index", 0)
+        misc.RUN_ID[0] += 1
         self._run_index = misc.STEP[0] + 1
         if self.on_device:
             # the same index on the device, advanced by a one-thread kernel at the start of every step

@@ -146,7 +146,50 @@ class PieceOp(_MicroBase):
                 return orig.op.compute(orig, ins, out, use_numpy, stream)
             finally:
                 orig.attrs.pop("element_offset", None)
+        bn = node.attrs.get("stat_for")
+        if bn is not None and not use_numpy and self._conv_with_stats(node, orig, bn, ins, out, stream):
+            return None
         return orig.op.compute(orig, ins, out, use_numpy, stream)
+
+    @staticmethod
+    def _open_stats(st, first):
+        """Start the piece-wise sums of a new step (the first piece that arrives in a run does it)."""
+        from ..ops import misc
+        if first and st.get("opened_run") != misc.RUN_ID[0]:
+            st["opened_run"] = misc.RUN_ID[0]
+            st["micro_chunks"], st["micro_rows"] = 0, 0
+            st["stats_open"] = True
+            st["conv_stat_pieces"] = set()
+        return st.get("stats_open") and st.get("opened_run") == misc.RUN_ID[0]
+
+    def _conv_with_stats(self, node, orig, bn, ins, out, stream):
+        """Piece j of a convolution whose output feeds a batch norm that is computed piece by piece: the
+        epilogue leaves the piece's column sums in the batch norm's piece-wise buffer, so the separate
+        statistics pass over this piece (``BnStatOp``) has nothing left to do.  Only in the forward pass of the
+        step: a rebuild of the piece after the statistics were finalised is a plain convolution."""
+        from ..ops.conv import _pads
+        x, w = ins
+        j, k = node.attrs["piece"], node.attrs["pieces"]
+        st = _bn_state(bn)
+        if not self._open_stats(st, node.attrs.get("stat_first", False)) or j in st["conv_stat_pieces"]:
+            return False
+        o = out.shape[1]
+        if o % 4 or x.shape[1] % 4 or not (x.is_channels_last() and w.is_channels_last() and out.is_channels_last()):
+            return False
+        plane = k * G.BN_PIECE_CHUNKS * o
+        part = st.get("micro_part")
+        if part is None or part.shape != (2 * plane,):
+            part = st["micro_part"] = _side((2 * plane,), out.ctx)
+        ph, pw = _pads(orig)
+        room = k * G.BN_PIECE_CHUNKS - st["micro_chunks"]
+        chunks = G.conv2d_fwd_stats(x, w, out, ph, pw, orig.attrs["stride"], part, stream,
+                                    chunk_offset=st["micro_chunks"], plane=plane,
+                                    max_chunks=min(G.BN_PIECE_CHUNKS, room))
+        if chunks:
+            st["micro_chunks"] += chunks
+            st["micro_rows"] += out.shape[0] * out.shape[2] * out.shape[3]
+            st["conv_stat_pieces"].add(j)
+        return True
 
 
 class AccumulateOp(_MicroBase):
@@ -225,11 +268,12 @@ class BnStatOp(_MicroBase):
             return None
         c = x.shape[1]
         plane = k * G.BN_PIECE_CHUNKS * c
+        PieceOp._open_stats(st, node.attrs["first"])
+        if j in st.get("conv_stat_pieces", ()):
+            return None                 # the convolution that produced this piece left its sums in the epilogue
         part = st.get("micro_part")
         if part is None or part.shape != (2 * plane,):
             part = st["micro_part"] = _side((2 * plane,), x.ctx)
-        if node.attrs["first"]:
-            st["micro_chunks"], st["micro_rows"] = 0, 0
         st["micro_chunks"] += G.bn_stats_partial(x, part, plane, st["micro_chunks"], stream)
         st["micro_rows"] += x.shape[0] * x.shape[2] * x.shape[3]
         return None
@@ -258,6 +302,7 @@ class BnFinalizeOp(_MicroBase):
             st["run_mean"], st["run_var"] = _side((c,), scale.ctx, 0.0), _side((c,), scale.ctx, 1.0)
         G.bn_stats_finalize(st["micro_part"], st["micro_part"].shape[0] // 2, st["micro_chunks"], st["micro_rows"], c,
                             eps, mom, st["mean"], st["invstd"], st["run_mean"], st["run_var"], stream)
+        st["stats_open"] = False        # pieces rebuilt from here on are plain convolutions
         return None
 
 
@@ -561,6 +606,12 @@ def lower(topo_order, shapes, layout, eval_nodes, feed_nodes, pieces, min_split_
                     out.micro_ops += 1
                 elif kd == "bnf":
                     if level[n] == lv:          # statistics stage
+                        src = n.inputs[0]
+                        if kind.get(src) == "sep" and src.op.name == "Conv2d" and (src, j) in piece_of and \
+                                src.attrs.get("bn_consumer") is n:
+                            # the convolution piece right before this stage takes the sums in its epilogue
+                            piece_of[(src, j)].attrs["stat_for"] = n
+                            piece_of[(src, j)].attrs["stat_first"] = n not in stat_started
                         node = _mk(BnStatOp(n.op.name + "Stats"), ins[:1], n, first=n not in stat_started,
                                    **dict(common, cut=cut[:1], op_in_shapes=seen[:1]))
                         stat_started.add(n)

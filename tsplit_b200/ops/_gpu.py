@@ -435,10 +435,13 @@ def conv2d(kind, x, w, y, ph, pw, stride, stream):
 CONV_STAT_MAX_CHUNKS = 304      # upper bound of per-CTA partial-sum slots a forward convolution may fill
 
 
-def conv2d_fwd_stats(x, w, y, ph, pw, stride, part, stream):
+def conv2d_fwd_stats(x, w, y, ph, pw, stride, part, stream, chunk_offset=0, plane=None, max_chunks=None):
     """Forward convolution that also leaves per-CTA column sums / sums of squares of ``y`` in
     ``part`` (flat array of 2 * CONV_STAT_MAX_CHUNKS * O floats) for the batch norm that follows.
-    Returns the number of chunks written; 0 = no statistics (the plain kernel ran)."""
+    Returns the number of chunks written; 0 = no statistics (the plain kernel ran).
+    ``chunk_offset`` / ``plane`` / ``max_chunks``: write the chunk rows from that row on into a buffer whose two
+    planes are ``plane`` floats apart and that has room for ``max_chunks`` more rows (the piece-wise statistics
+    buffer of a batch norm whose input is computed piece by piece)."""
     n, c, h, wd = x.shape
     o, _, kh, kw = w.shape
     _, _, oh, ow = y.shape
@@ -448,8 +451,10 @@ def conv2d_fwd_stats(x, w, y, ph, pw, stride, part, stream):
     chunks = c_int(0)
     rc = lib().tsb_conv2d_fwd_stats(_p(x), _p(w), _p(y), c_int(n), c_int(c), c_int(h), c_int(wd), c_int(o),
                                     c_int(kh), c_int(kw), c_int(oh), c_int(ow), c_int(ph), c_int(pw),
-                                    c_int(stride), _p(part), c_int64(CONV_STAT_MAX_CHUNKS * o),
-                                    c_int(CONV_STAT_MAX_CHUNKS), ctypes.byref(chunks), _s(stream))
+                                    c_int(stride), c_void_p(part.ptr + 4 * int(chunk_offset) * o),
+                                    c_int64(CONV_STAT_MAX_CHUNKS * o if plane is None else plane),
+                                    c_int(CONV_STAT_MAX_CHUNKS if max_chunks is None else max_chunks),
+                                    ctypes.byref(chunks), _s(stream))
     _check(rc, "conv2d_fwd_stats")
     return int(chunks.value)
 

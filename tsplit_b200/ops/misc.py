@@ -214,6 +214,9 @@ def philox_like_mask(shape, keep_prob, seed, offset=0):
 STEP = [0]
 #: device address of the running executor's step counter (0 = none: the host index above is used)
 STEP_DEV = [0]
+#: bumped at the start of every ``run`` of every executor: per-step side state of an operator (batch-norm sums
+#: collected piece by piece) tells a new step from a rebuild inside the same step by it
+RUN_ID = [0]
 
 
 def step_seed(node):
