@@ -48,6 +48,10 @@ F_EVICTABLE, F_RECOMPUTABLE, F_PINNED, F_EXTERNAL = 1, 2, 4, 8
 EV_RELEASE, EV_SWAPOUT, EV_FREE, EV_PREFETCH = 0, 1, 2, 3
 
 
+#: (graph, feed shapes, budget, link, ...) -> (piece count, gap) chosen by an earlier search in this process
+_CHOICES = {}
+
+
 def _arr(ctype, values):
     return (ctype * len(values))(*values)
 
@@ -172,8 +176,13 @@ class microopExecutor(MemoryExecutor):
         return dict(n=len(order), out_bytes=out_bytes, time_ms=time_ms, flags=flags, in_ptr=in_ptr,
                     in_idx=in_idx or [0])
 
-    def _call_planner(self, cls_in=None, budget=None, from_in=None):
-        g = self._graph_arrays()
+    def _call_planner(self, cls_in=None, budget=None, from_in=None, arrays=None, gap=None, low=None):
+        """One native planning call.  ``arrays`` / ``gap`` / ``low``: graph arrays, residency gap and lowering to
+        plan for instead of the installed ones (then nothing of ``self`` that a lowering changes is read, so calls
+        for different lowerings may run in parallel threads; the native planner keeps no global state)."""
+        g = self._graph_arrays() if arrays is None else arrays
+        gap = self.min_gap if gap is None else gap
+        low = self.lowered if low is None else low
         n = g["n"]
         lib = _base.runtime()
         cap = 64 * (len(g["in_idx"]) + n) + 64
@@ -188,7 +197,7 @@ class microopExecutor(MemoryExecutor):
             rbc = (c_int * n)()
             common = (c_int(n), _arr(c_int64, g["out_bytes"]), _arr(c_double, g["time_ms"]), _arr(c_int, g["flags"]),
                       _arr(c_int, g["in_ptr"]), _arr(c_int, g["in_idx"]),
-                      c_int64(self._budget() if budget is None else int(budget)), c_int64(int(self.min_gap)),
+                      c_int64(self._budget() if budget is None else int(budget)), c_int64(int(gap)),
                       c_double(self.host_link_gbs * 1e6))
             tail = (last, c_int(cap), ek, ep, et, byref(cnt), c_int(acap), at, ao, byref(acnt), summ, mem, rbc)
             if cls_in is None:
@@ -203,8 +212,7 @@ class microopExecutor(MemoryExecutor):
             break
         assert rc in (0, 5), "planner error %d" % rc
         events = [(ek[i], ep[i], et[i]) for i in range(cnt.value)]
-        plan = Plan(list(cls), list(last), events, list(summ), summ[2] < 0, self.lowered.pieces,
-                    self.lowered.micro_ops)
+        plan = Plan(list(cls), list(last), events, list(summ), summ[2] < 0, low.pieces, low.micro_ops)
         plan.memory_curve = list(mem)
         plan.active_from = list(frm)
         plan.rebuild_count = list(rbc)
@@ -212,9 +220,35 @@ class microopExecutor(MemoryExecutor):
         plan.footprint_bytes = int(summ[11])
         return plan
 
+    def _choice_key(self):
+        return (tuple(id(n) for n in self.orig_eval_node_list), tuple(sorted((id(n), tuple(s)) for n, s in
+                                                                              self.feed_shapes.items())),
+                self._budget(), round(self.host_link_gbs, 3), self.allow_swap, self.max_split, self.min_split_bytes,
+                self.fixed_pieces, self.min_gap if self.fixed_gap else None, self._comm is not None)
+
     def search_plan(self):
         """Lower for each candidate piece count, plan with each candidate residency gap, keep the fastest plan
-        that fits (or, when none fits, the one that got furthest).  Installs the chosen lowering."""
+        that fits (or, when none fits, the one that got furthest).  Installs the chosen lowering.  The chosen
+        (piece count, gap) is remembered per graph, feed shape and budget, so that an executor built after a dry
+        run (``microopOptimizer``) of the same configuration plans once instead of searching again."""
+        key = self._choice_key()
+        known = _CHOICES.get(key)
+        if known is not None:
+            k, gap = known
+            low = self._lower(k)
+            self._install(low)
+            self.min_gap = gap
+            plan = self._call_planner()
+            plan.min_gap = gap
+            if plan.fits:
+                return plan
+            _CHOICES.pop(key, None)             # not this configuration after all: search
+        plan = self._search_plan()
+        if plan.fits:
+            _CHOICES[key] = (plan.pieces, plan.min_gap)
+        return plan
+
+    def _search_plan(self):
         batch = self._batch()
         if self.fixed_pieces is not None:
             cand = [int(self.fixed_pieces)]
@@ -248,11 +282,29 @@ class microopExecutor(MemoryExecutor):
                 worse = worse + 1 if key > best[0] else 0
                 if worse >= 2:
                     break
-        if not self.fixed_gap and best[1].pieces > 1:
-            low = best[1]
-            self._install(low)
-            for gap in (3, 12):
-                consider(low, gap)
+        if best[1].pieces > 1 and (self.fixed_pieces is None or not self.fixed_gap) and \
+                (best[0][0] != 0 or any(c != KEEP for c in best[2].cls)):
+            # The predicted time is not smooth in the piece count and the gap (the greedy search lands in different
+            # plans): plan a small grid around the best piece count, the planner calls in parallel threads.
+            k0 = best[1].pieces
+            ks = [k0] if self.fixed_pieces is not None else sorted(
+                {k for k in (k0 * 3 // 4, k0, k0 * 5 // 4, k0 * 3 // 2) if 2 <= k <= min(self.max_split, batch)})
+            gaps = [first_gap] if self.fixed_gap else [3, 6, 12]
+            jobs = []
+            for k in ks:
+                low = best[1] if k == k0 else self._lower(k)
+                self._install(low)
+                arrays = self._graph_arrays()
+                jobs += [(low, arrays, gap) for gap in gaps if not (k == k0 and gap == first_gap)]
+            import os
+            from concurrent.futures import ThreadPoolExecutor
+            with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1, 12))) as pool:
+                plans = list(pool.map(lambda j: self._call_planner(arrays=j[1], gap=j[2], low=j[0]), jobs))
+            for (low, _, gap), plan in zip(jobs, plans):
+                plan.min_gap = gap
+                key = (0, plan.predicted_ms) if plan.fits else (1, -plan.first_over_budget)
+                if key < best[0]:
+                    best = (key, low, plan)
         _, low, plan = best
         self.min_gap = plan.min_gap
         self._install(low)
