@@ -284,11 +284,12 @@ class microopExecutor(MemoryExecutor):
                     break
         if best[1].pieces > 1 and (self.fixed_pieces is None or not self.fixed_gap) and \
                 (best[0][0] != 0 or any(c != KEEP for c in best[2].cls)):
-            # The predicted time is not smooth in the piece count and the gap (the greedy search lands in different
-            # plans): plan a small grid around the best piece count, the planner calls in parallel threads.
+            # The predicted time is not smooth in the residency gap (the greedy search lands in different plans):
+            # plan the best piece count with the other gaps too, the planner calls in parallel threads.  (Piece
+            # counts between the powers of two were tried as well: VGG-16 at 2048 predicted 7 % faster with 24
+            # pieces than with 16 and measured 1 % slower, with a third more swap traffic; they are not searched.)
             k0 = best[1].pieces
-            ks = [k0] if self.fixed_pieces is not None else sorted(
-                {k for k in (k0 * 3 // 4, k0, k0 * 5 // 4, k0 * 3 // 2) if 2 <= k <= min(self.max_split, batch)})
+            ks = [k0]
             gaps = [first_gap] if self.fixed_gap else [3, 6, 12]
             jobs = []
             for k in ks:
