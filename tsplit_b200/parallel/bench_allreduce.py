@@ -77,6 +77,24 @@ def main():
         comm = FusedCommunicator(opt, dist, use_multimem=bool(args.nvls), bucket_mb=1 << 20)   # one bucket
         grad = ndarray.empty((n,), ctx, use_pool=False)
         grad.t.normal_()
+        # one checked step first: rank-dependent gradients, zero velocity; the fused kernel must leave
+        # p - lr * mean(g) on every rank (first momentum step), compared with an NCCL all-reduce of the same data
+        g_chk = torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(100 + rank))
+        dist.broadcast(comm.param_bucket, src=0)       # as data-parallel training starts: the same parameters everywhere
+        p_before = comm.param_bucket.clone()
+        comm.grad_bucket.copy_(g_chk)
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.begin_step()
+        comm.launch_bucket(0, opt, st, overlapped=False)
+        st.wait_event(_recorded(comm.comm_stream, ctx))
+        torch.cuda.synchronize()
+        dist.all_reduce(g_chk)
+        want = p_before - 0.01 * g_chk / world
+        err = (comm.param_bucket - want).abs().max()
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        max_err = float(err.item())
+        dist.barrier()
         # the kernel proper (gradients already in the symmetric array): time launches back to back
         comm.grad_bucket.copy_(grad.t)
 
@@ -120,7 +138,7 @@ def main():
                               "fraction_of_link_roofline_of_measured": round(floor_ms / results["fused"], 3),
                               "fraction_of_link_roofline_of_nominal": round(
                                   floor_ms * LINK_GBS_MEASURED / LINK_GBS_NOMINAL / results["fused"], 3),
-                              "bus_gbs": round(bus, 1)}))
+                              "bus_gbs": round(bus, 1), "checked_step_max_abs_err": max_err}))
         del comm, opt
     if own_group:
         dist.destroy_process_group()
