@@ -1,3 +1,11 @@
+"""Communicator classes with the reference's names and call signatures (``MPI_Communicator``,
+``NCCL_Communicator``, the ``ncclDataType_t`` / ``ncclRedOp_t`` enums; reference:
+``python/athena/communicator/mpi_comm.py:33-85``, ``mpi_nccl_comm.py:47-142``, ``nccl_comm.py:16-89``) on top of
+``torch.distributed``: user scripts written against the reference's communicators (``dlarrayNcclAllReduce``,
+``dlarrayBroadcast``, ``all_reduce`` of a host array) run unchanged.  The training path does not go through them:
+the gradient exchange is ``parallel/fused_allreduce.py`` (one kernel per bucket over NVLink), these classes are the
+explicit collectives an example or a test calls by hand (exercised with gloo ranks in
+``tests/test_distributed_cpu.py``)."""
 from __future__ import annotations
 
 import os
