@@ -408,6 +408,8 @@ def main():
                        "l2": "inputs and activations per step exceed the 126 MB L2; no explicit flush",
                        "plan": plan_repr, "loss": loss_val, "executor_stats": stats,
                        "exposed_comm_ms_per_step": exposed_comm_ms,
+                       "exchange_path": (None if comm is None else "multimem (NVSwitch)" if getattr(comm, "grad_mc", 0)
+                                         else "peer loads / stores" if hasattr(comm, "grad_bucket") else "nccl"),
                        "cpus_bound_to_gpu": len(cpus) if cpus else 0,
                        "step_replay": {0: "python loop", 1: "cuda graph", 2: "native tape"}[int(args.graph)],
                        "native_replay_host_us_and_actions": (ex.replay_host_us() if hasattr(ex, "replay_host_us")
