@@ -20,13 +20,15 @@ POLICIES = ["None", "base", "vdnnconv", "vdnnall", "superneurons", "recompute_me
             "capuchin", "simulator", "profiler", "planner", "tsplit"]
 
 
-USE_GRAPH = [False]       # set by ``--graph 1``: replay fixed (swap-free) steps from a CUDA graph
+#: set by ``--graph``: 1 = replay fixed steps from a CUDA graph, 2 = from the native tape of recorded calls
+#: (``"tape"``; the memory executors only: it also covers steps with the multi-GPU gradient exchange)
+USE_GRAPH = [False]
 
 
 def make_executor(policy, nodes, ctx):
     g = USE_GRAPH[0]
     if policy in ("None", "base"):
-        return ad.Executor(nodes, ctx=ctx, use_graph=g)
+        return ad.Executor(nodes, ctx=ctx, use_graph=g is True)
     if policy == "vdnnconv":
         return ad.vdnnExecutor(nodes, ctx=ctx, policy="conv")
     if policy == "vdnnall":
@@ -155,13 +157,13 @@ def parse(description, extra=None):
     p.add_argument("-b", "--batch", type=int, default=0, help="single batch size (0 = sweep)")
     p.add_argument("--cap-gib", type=float, default=16.0, help="HBM budget of the activation pool")
     p.add_argument("--out", default=None, help="append results to this file")
-    p.add_argument("--graph", type=int, default=0, help="1 = replay fixed steps from a CUDA graph")
+    p.add_argument("--graph", type=int, default=0, help="1 = replay fixed steps from a CUDA graph, 2 = from the native tape of recorded calls")
     p.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                    help="gradient exchange when launched with several ranks")
     if extra:
         extra(p)
     args = p.parse_args()
-    USE_GRAPH[0] = bool(args.graph)
+    USE_GRAPH[0] = {0: False, 1: True, 2: "tape"}[int(args.graph)]
     return args
 
 
