@@ -518,6 +518,14 @@ class MemoryExecutor(Executor):
     # ------------------------------------------------------------------ run
     def memory_plan(self, feed_shapes):
         self.node_to_arr_map = {}
+        if self.__dict__.get("_step_graph") is not None or self.__dict__.get("_graph_steps_seen"):
+            # a new feed shape: the captured graph / recorded tape holds the old shapes and addresses
+            if self.on_device:
+                self.stream.sync()
+            self._step_graph, self._graph_steps_seen, self._graph_ok = None, 0, None
+            self._graph_keep, self._graph_feeds = [], None
+            if hasattr(self, "_close_region"):
+                self._close_region()
         had = bool(getattr(self, "host_bufs", None))
         self.host_bufs = {}
         self.host_bytes = 0
