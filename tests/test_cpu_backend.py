@@ -137,3 +137,33 @@ def test_training_step_runs_forward_and_backward_natively(family):
         assert ("MaxPool2dGradient" in native) or ("AvgPool2dGradient" in native), native
     for a, b in zip(outs[1], outs[0]):       # fp32 sums in another order through 10-26 layers: compare to the tensor's scale
         assert np.abs(a - b).max() <= 2e-3 * max(np.abs(b).max(), 1e-3)
+
+
+@pytest.mark.parametrize("make", [
+    lambda ctx: __import__("tsplit_b200").optimizer.SGDOptimizer(0.05, ctx=ctx),
+    lambda ctx: __import__("tsplit_b200").optimizer.MomentumOptimizer(0.05, 0.9, ctx=ctx),
+    lambda ctx: __import__("tsplit_b200").optimizer.MomentumOptimizer(0.05, 0.9, nesterov=True, ctx=ctx),
+    lambda ctx: __import__("tsplit_b200").optimizer.AdaGradOptimizer(0.005, ctx=ctx),
+    lambda ctx: __import__("tsplit_b200").optimizer.AdamOptimizer(0.01, ctx=ctx),
+], ids=["sgd", "momentum", "nesterov", "adagrad", "adam"])
+def test_optimizers_update_natively_on_a_cpu_context(make):
+    """Four training steps of an MLP on ``ndarray.cpu(0)`` (update kernels of the host library) give the losses and
+    parameters of the NumPy oracle."""
+    from tsplit_b200.models import mlp
+    runs = []
+    for ctx in (None, ndarray.cpu(0)):
+        m = mlp(seed=11)
+        opt = make(ctx)
+        train = opt.minimize(m.loss)
+        ex = ad.Executor([m.loss, train], ctx=ctx)
+        x, y = m.synthetic_batch(32, seed=4)
+        before = cpu_links.CALLS[0]
+        losses = [float(np.asarray(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0]).reshape(-1)[0])
+                  for _ in range(4)]
+        calls = cpu_links.CALLS[0] - before
+        assert (calls > 0) == (ctx is not None)
+        runs.append((losses, [np.asarray(p.asnumpy() if hasattr(p, "asnumpy") else p).copy() for p in opt.params]))
+    np.testing.assert_allclose(runs[1][0], runs[0][0], rtol=5e-4)
+    for a, b in zip(runs[1][1], runs[0][1]):       # (AdaGrad divides by the root of a tiny accumulator: absolute floor)
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=1e-4)
+    assert runs[0][0][-1] < runs[0][0][0]

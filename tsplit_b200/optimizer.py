@@ -109,10 +109,19 @@ class Optimizer(object):
                                  s1[lo:hi] if s1 else None, s2[lo:hi] if s2 else None,
                                  self.hyper(), stream_handle, hyper_dev=hdev)
             return
+        from . import graph, cpu_links
+        native = graph.CPU_NATIVE[0]          # an executor on ndarray.cpu: the OpenMP update kernels
+        s1, s2 = self.slots() if native else (None, None)
         for i, g in enumerate(grads):
             p = params[i]
             pv = p.numpy_view() if isinstance(p, ndarray.NDArray) else p
             gv = g.numpy_view() if isinstance(g, ndarray.NDArray) else g
+            if native:
+                a = self._np(s1[i]) if s1 else None
+                b = self._np(s2[i]) if s2 else None
+                if cpu_links.ok(pv, gv, *[x for x in (a, b) if x is not None]) and pv.shape == gv.shape:
+                    cpu_links.optimizer_update(self.kind, pv, gv, a, b, self.hyper())
+                    continue
             self._np_update(i, pv, gv)
 
     def _begin_step(self):
