@@ -164,6 +164,8 @@ def test_optimizers_update_natively_on_a_cpu_context(make):
         assert (calls > 0) == (ctx is not None)
         runs.append((losses, [np.asarray(p.asnumpy() if hasattr(p, "asnumpy") else p).copy() for p in opt.params]))
     np.testing.assert_allclose(runs[1][0], runs[0][0], rtol=5e-4)
-    for a, b in zip(runs[1][1], runs[0][1]):       # (AdaGrad divides by the root of a tiny accumulator: absolute floor)
-        np.testing.assert_allclose(a, b, rtol=2e-4, atol=1e-4)
+    # AdaGrad and Adam divide by the root of an accumulator that is tiny where the gradient is: there the update
+    # is lr * sign-ish and a last-bit difference of the gradient moves it by a fraction of lr: absolute floor
+    for a, b in zip(runs[1][1], runs[0][1]):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=5e-4)
     assert runs[0][0][-1] < runs[0][0][0]

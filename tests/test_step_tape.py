@@ -84,3 +84,44 @@ def test_result_pointers_replay_into_the_tapes_own_storage_and_objects_make_a_re
     assert rec.invalid is not None and "cannot be stored" in rec.invalid
     with pytest.raises(AssertionError):
         tape.Tape(rec)
+
+
+def test_cpu_context_training_step_replays_from_the_tape():
+    """``Executor(ctx=ndarray.cpu(0), use_graph="tape")``: one eager step, one recorded step, then the C++ loop.
+    An MLP with momentum SGD runs entirely on host kernels, so its step is recorded; losses and parameters equal
+    those of the Python loop.  A different batch is read every step (the feeds go through fixed buffers)."""
+    from tsplit_b200 import ndarray, gpu_ops as ad, optimizer
+    from tsplit_b200.models import mlp
+    runs = []
+    for mode in (False, "tape"):
+        m = mlp(seed=11)
+        opt = optimizer.MomentumOptimizer(0.05, 0.9, ctx=ndarray.cpu(0))
+        train = opt.minimize(m.loss)
+        ex = ad.Executor([m.loss, train], ctx=ndarray.cpu(0), use_graph=mode)
+        losses = []
+        for step in range(6):
+            x, y = m.synthetic_batch(32, seed=step % 2)
+            losses.append(float(np.asarray(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0]).reshape(-1)[0]))
+        if mode:
+            assert ex._cpu_tape is not None, getattr(ex, "replay_failure", "")
+            assert len(ex._cpu_tape) > 8 and "tsb_cpu_optimizer" in ex._cpu_tape.names
+        assert opt.step_count == 6
+        runs.append((losses, [np.asarray(p.asnumpy() if hasattr(p, "asnumpy") else p).copy() for p in opt.params]))
+    np.testing.assert_allclose(runs[1][0], runs[0][0], rtol=1e-6)
+    for a, b in zip(runs[1][1], runs[0][1]):
+        np.testing.assert_allclose(a, b, rtol=1e-6, atol=1e-7)
+    assert abs(runs[0][0][2] - runs[0][0][3]) > 1e-6          # the two batches really differ
+
+
+def test_cpu_step_with_an_operator_without_host_kernel_keeps_the_python_loop():
+    from tsplit_b200 import ndarray, gpu_ops as ad, optimizer
+    from tsplit_b200.models import mlp
+    m = mlp(seed=11)
+    opt = optimizer.AdamOptimizer(0.01, ctx=ndarray.cpu(0))          # hyper-parameters change every step
+    train = opt.minimize(m.loss)
+    ex = ad.Executor([m.loss, train], ctx=ndarray.cpu(0), use_graph="tape")
+    x, y = m.synthetic_batch(16, seed=0)
+    losses = [float(np.asarray(ex.run({m.X: x, m.y_: y}, convert_to_numpy_ret_vals=True)[0]).reshape(-1)[0])
+              for _ in range(4)]
+    assert ex._cpu_tape is None and "Adam" in ex.replay_failure
+    assert losses[-1] < losses[0] and opt.step_count == 4

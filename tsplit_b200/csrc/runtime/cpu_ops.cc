@@ -323,6 +323,25 @@ int tsb_cpu_batchnorm_grad(const float* dy, const float* x, const float* scale, 
   return 0;
 }
 
+// dx = (softmax(logits) - labels) * g[0] / rows: the gradient of the mean cross-entropy, scaled by the incoming
+// gradient of the loss (a one-element array).
+int tsb_cpu_softmax_ce_grad(const float* logits, const float* labels, const float* g, float* dx, int64_t rows,
+                            int64_t cols) {
+  const double scale = (double)g[0] / (double)rows;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* xr = logits + r * cols;
+    const float* lr = labels + r * cols;
+    float m = xr[0];
+    for (int64_t i = 1; i < cols; ++i) m = std::max(m, xr[i]);
+    double s = 0;
+    for (int64_t i = 0; i < cols; ++i) s += std::exp((double)xr[i] - m);
+    const double lse = m + std::log(s);
+    for (int64_t i = 0; i < cols; ++i) dx[r * cols + i] = (float)((std::exp(xr[i] - lse) - lr[i]) * scale);
+  }
+  return 0;
+}
+
 int tsb_cpu_softmax(const float* x, float* y, int64_t rows, int64_t cols) {
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < rows; ++r) {

@@ -140,6 +140,10 @@ class Executor(object):
         self.use_graph = bool(use_graph) and self.on_device
         self._graph = None
         self._graph_feed_arrs = None
+        # a CPU-context executor can replay its step from the native tape too (use_graph="tape"): every operator
+        # of the step must have a host kernel (csrc/runtime/cpu_ops.cc), else it keeps its Python loop
+        self.cpu_tape = use_graph == "tape" and ctx is not None and ctx.device_type == 1
+        self._cpu_tape, self._cpu_tape_state = None, "warm"
 
     # -- shapes ---------------------------------------------------------------
     def infer_shape(self, feed_shapes):
@@ -267,9 +271,12 @@ class Executor(object):
                 self.memory_plan(feed_shapes)
             self._graph = None
             self._graph_warm = False
+            self._cpu_tape, self._cpu_tape_state = None, "warm"
 
         if self.use_graph:
             self._run_graph(node_to_val)
+        elif self.cpu_tape and self._cpu_tape_state != "off":
+            self._run_cpu_tape(node_to_val)
         else:
             self._run_eager(node_to_val)
 
@@ -303,6 +310,48 @@ class Executor(object):
                 node.op.compute(node, ins, out, False, self.stream)
             node_to_val[node] = out
         self._last_vals = node_to_val
+
+    # -- native replay of a CPU-context step ------------------------------------------
+    def _run_cpu_tape(self, node_to_val):
+        """First step eager, second step recorded (it runs the ordinary way while every host-library call is
+        appended to a tape), later steps one call of the C++ replay loop.  Feeds are copied into fixed host
+        arrays first, because the recorded calls hold addresses."""
+        from .. import graph
+        from ..runtime import tape
+        if self._cpu_tape_state == "warm" or not tape.available():
+            self._cpu_tape_state = "record" if tape.available() else "off"
+            return self._run_eager(node_to_val)
+        if self._cpu_tape is None:
+            self._cpu_feed_arrs = {n: ndarray.empty(_shape_of(v), self.ctx) for n, v in node_to_val.items()
+                                   if not isinstance(v, ndarray.ND_Sparse_Array)}
+        fixed = dict(node_to_val)
+        for n, buf in self._cpu_feed_arrs.items():
+            v = node_to_val[n]
+            buf.numpy_view()[...] = v.numpy_view() if isinstance(v, ndarray.NDArray) else v
+            fixed[n] = buf
+        if self._cpu_tape is None:
+            before = graph.NUMPY_FALLBACKS[0]
+            with tape.recording() as rec:
+                self._run_eager(fixed)
+            if rec.invalid is None and graph.NUMPY_FALLBACKS[0] != before:
+                rec.invalid = "%d operators of the step have no host kernel" % (graph.NUMPY_FALLBACKS[0] - before)
+            if rec.invalid is not None or not rec.fns:
+                self.replay_failure = rec.invalid or "nothing was recorded"
+                self._cpu_tape_state = "off"
+                node_to_val.update(self._last_vals)
+                return
+            self._cpu_tape = tape.Tape(rec)
+            self._cpu_tape_vals = self._last_vals
+            node_to_val.update(self._last_vals)
+            return
+        self._cpu_tape.replay()
+        for n in self.topo_order:            # the optimizer's Python side did not run: keep its step count in step
+            if n.op.name == "Optimizer":
+                opt = n.attrs["optimizer"]
+                opt.step_count += 1
+                opt._begin_step()
+        self._last_vals = self._cpu_tape_vals
+        node_to_val.update(self._cpu_tape_vals)
 
     # -- CUDA-graph replay ---------------------------------------------------------
     def _run_graph(self, node_to_val):

@@ -16,6 +16,8 @@ _node_ids = itertools.count()
 _PHASE = ["forward"]
 #: set by executors that run on a CPU context: operators use their native host kernels
 CPU_NATIVE = [False]
+#: operators of CPU-context executors that ran on NumPy because they have no native host kernel
+NUMPY_FALLBACKS = [0]
 
 
 class phase_scope(object):
@@ -107,6 +109,8 @@ class Op(object):
             # host library (cpu_links -> csrc/runtime/cpu_ops.cc); ctx=None stays pure NumPy, the oracle
             if CPU_NATIVE[0] and output_val is not None and self.cpu_compute(node, input_vals, output_val):
                 return output_val
+            if CPU_NATIVE[0]:
+                NUMPY_FALLBACKS[0] += 1          # a CPU-context step with one of these cannot be replayed natively
             res = self.np_compute(node, input_vals)
             if output_val is not None and res is not None:
                 output_val[...] = res

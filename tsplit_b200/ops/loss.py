@@ -201,6 +201,13 @@ class SoftmaxCrossEntropyGradientOp(Op):
         y, y_, g = iv
         return ((softmax_func(y) - y_) * g.reshape(-1)[0] / y.shape[0]).astype(np.float32)
 
+    def cpu_compute(self, node, iv, out):
+        from .. import cpu_links
+        if not cpu_links.ok(iv[0], iv[1], iv[2], out) or iv[0].ndim != 2 or iv[2].size != 1:
+            return False
+        cpu_links.softmax_crossentropy_grad(iv[0], iv[1], iv[2], out)
+        return True
+
     def gpu_compute(self, node, iv, out, stream):
         G.softmax_ce_grad(iv[0], iv[1], iv[2], out, stream)
 

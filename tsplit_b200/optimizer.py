@@ -121,7 +121,12 @@ class Optimizer(object):
                 b = self._np(s2[i]) if s2 else None
                 if cpu_links.ok(pv, gv, *[x for x in (a, b) if x is not None]) and pv.shape == gv.shape:
                     cpu_links.optimizer_update(self.kind, pv, gv, a, b, self.hyper())
+                    if self.kind == 4:
+                        from .runtime import tape
+                        if tape.ACTIVE[0] is not None:      # the bias-correction powers are part of the recorded bytes
+                            tape.ACTIVE[0].invalid = "Adam's hyper-parameters change every step"
                     continue
+                graph.NUMPY_FALLBACKS[0] += 1
             self._np_update(i, pv, gv)
 
     def _begin_step(self):

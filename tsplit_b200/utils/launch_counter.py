@@ -34,16 +34,17 @@ def add(n):
 class CountingLib(object):
     """Proxy around a ``ctypes.CDLL`` that counts launches per call."""
 
-    def __init__(self, lib):
+    def __init__(self, lib, count=True):
         object.__setattr__(self, "_lib", lib)
         object.__setattr__(self, "_wrapped", {})
+        object.__setattr__(self, "_counts", bool(count))      # False: a host library (its calls launch no kernel)
 
     def __getattr__(self, name):
         w = self._wrapped.get(name)
         if w is not None:
             return w
         fn = getattr(self._lib, name)
-        k = KERNELS_PER_ENTRY.get(name, 1)
+        k = KERNELS_PER_ENTRY.get(name, 1) if self._counts else 0
         if not name.startswith("tsb_") or name in _tape.NOT_ACTIONS:
             return fn
 
